@@ -1,0 +1,133 @@
+/*
+ * b200idx -- C ABI of the B200-native search hot path (Flat / Int8Flat / IVFPQ search and
+ * multi-index batch search).  Plain pointers and sizes only; no C++ types, no exceptions.
+ * Every entry point returns an APP_ERROR-compatible int (0 = OK) and records a message that
+ * b200idx_last_error() returns.
+ *
+ * Each declaration names the interface of the reference (Ascend/IndexSDK) it stands in for.
+ * FR = feature_retrieval/src/ascendfaiss.
+ */
+#ifndef B200IDX_H
+#define B200IDX_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct b200idx_index b200idx_t;
+
+/* Status codes: FR/common/ErrorCode.h:50-66 (APP_ERR_OK, APP_ERR_INVALID_PARAM,
+ * APP_ERR_NOT_IMPLEMENT, APP_ERR_INNER_ERROR, APP_ERR_TIMEOUT). */
+enum {
+    B200IDX_OK = 0,
+    B200IDX_ERR_INVALID_PARAM = 2001,
+    B200IDX_ERR_NOT_IMPLEMENTED = 2008,
+    B200IDX_ERR_INNER = 2010,
+    B200IDX_ERR_TIMEOUT = 2011
+};
+
+/* Metric values mirror the device layer of the reference: FR/ascenddaemon/impl/Index.h:60-64. */
+enum { B200IDX_METRIC_INNER_PRODUCT = 0, B200IDX_METRIC_L2 = 1 };
+
+/* Storage / arithmetic type of a Flat index.
+ *   F32: fp32 rows; a bf16 tensor-core pass filters candidates, results are re-computed in fp32.
+ *   F16: fp16 rows, fp32 accumulation (the reference's own Flat arithmetic,
+ *        FR/ascend/impl/AscendIndexImpl.cpp:339-346). */
+enum { B200IDX_F32 = 0, B200IDX_F16 = 1 };
+
+/* ---- construction: AscendIndexFlat(int dims, MetricType, AscendIndexFlatConfig)
+ *      FR/ascend/AscendIndexFlat.h:56; AscendIndexInt8Flat(...) FR/ascend/AscendIndexInt8Flat.h:63-64;
+ *      AscendIndexIVFPQ(dims, metric, nlist, msubs, nbits, config) FR/ascend/AscendIndexIVFPQ.h:74-75.
+ *      One handle lives on one CUDA device (an entry of the reference's deviceList). ---- */
+int b200idx_create_flat(int d, int metric, int dtype, int device, b200idx_t** out);
+int b200idx_create_int8flat(int d, int metric, int device, b200idx_t** out);
+int b200idx_create_ivfpq(int d, int metric, int nlist, int M, int nbits, int by_residual, int device,
+                         b200idx_t** out);
+/* ~AscendIndex(): FR/ascend/AscendIndex.h:66 */
+int b200idx_destroy(b200idx_t* h);
+
+/* ---- add / add_with_ids: FR/ascend/AscendIndex.h:70-74 (float), :103-105 (fp16 bits),
+ *      FR/ascend/AscendIndexInt8.h:70-84 (int8).  x and ids are host pointers; ids may be NULL
+ *      (labels become ntotal + i, FR/ascend/impl/AscendIndexImpl.h:59-83). ---- */
+int b200idx_add(b200idx_t* h, int64_t n, const void* x, const int64_t* ids);
+int b200idx_add_f16(b200idx_t* h, int64_t n, const uint16_t* x, const int64_t* ids);
+/* Same with x resident on the index's device (no reference counterpart: the reference accepts
+ * host pointers only; used to build large synthetic bases without a host round trip). */
+int b200idx_add_device(b200idx_t* h, int64_t n, const void* x_dev, const int64_t* ids_host);
+
+/* ---- search: FR/ascend/AscendIndex.h:80-82 (float), :107 (fp16), FR/ascend/AscendIndexInt8.h:93-96.
+ *      Writes exactly n*k distances and labels; missing results are FLT_MAX / -1
+ *      (FR/ascend/impl/AscendIndexImpl.cpp:628-633). ---- */
+int b200idx_search(b200idx_t* h, int64_t n, const void* x, int k, float* distances, int64_t* labels);
+int b200idx_search_f16(b200idx_t* h, int64_t n, const uint16_t* x, int k, float* distances, int64_t* labels);
+/* Device-resident variant: x, distances, labels are device pointers on the index's device; the
+ * call returns after the index's stream has been synchronised. */
+int b200idx_search_device(b200idx_t* h, int64_t n, const void* x_dev, int k, float* distances_dev,
+                          int64_t* labels_dev);
+
+/* ---- multi-index batch search: faiss::ascend::Search(indexes, n, x, k, D, I, merged),
+ *      FR/ascend/AscendMultiIndexSearch.h:34-44, .cpp:230-324.  merged = 0: output layout
+ *      [index][n][k]; merged = 1: [n][k] by (distance, label)
+ *      (FR/ascend/utils/MergeResUtils.cpp:44-107).  Also serves base sets sharded over several
+ *      devices (FR/ascend/impl/AscendIndexImpl.cpp:375-403,587-642). ---- */
+int b200idx_search_multi(b200idx_t* const* hs, int nh, int64_t n, const void* x, int k, float* distances,
+                         int64_t* labels, int merged);
+
+/* Merge of nsrc sorted per-shard results resident on one device: Din/Iin [nsrc][n][k] ->
+ * D/I [n][k]; descending = 1 for inner-product scores.  Stands in for the host merge
+ * FR/ascend/impl/AscendIndexImpl.cpp:587-642 after a gather of per-rank results.
+ * stream: a cudaStream_t (NULL = default stream); asynchronous. */
+int b200idx_merge_topk_device(int nsrc, int64_t n, int k, int descending, const float* Din_dev,
+                              const int64_t* Iin_dev, float* D_dev, int64_t* I_dev, void* stream);
+
+/* ---- reset / remove_ids / bookkeeping: FR/ascend/AscendIndex.h:77,91;
+ *      getBaseSize / getBase / getIdxMap FR/ascend/AscendIndexFlat.h:69-75,
+ *      FR/ascend/AscendIndexInt8Flat.h:78-84. ---- */
+int b200idx_reset(b200idx_t* h);
+int b200idx_remove_ids(b200idx_t* h, int64_t n, const int64_t* ids, int64_t* n_removed);
+int64_t b200idx_ntotal(const b200idx_t* h);
+int b200idx_dim(const b200idx_t* h);
+int b200idx_device(const b200idx_t* h);
+/* rows [offset, offset+n): float (F32), fp16 bits (F16) or int8 */
+int b200idx_get_base(const b200idx_t* h, int64_t offset, int64_t n, void* out);
+int b200idx_get_ids(const b200idx_t* h, int64_t offset, int64_t n, int64_t* out);
+
+/* ---- IVFPQ: trained state comes in the way copyFrom(const faiss::IndexIVFPQ*) brings it
+ *      (FR/ascend/impl/AscendIndexIVFPQImpl.cpp:392-425): centroids [nlist][d], codebooks
+ *      [M][256][d/M] (layout FR/ascend/impl/AscendIndexIVFPQImpl.h:158-159). ---- */
+int b200idx_ivfpq_set_centroids(b200idx_t* h, const float* centroids);
+int b200idx_ivfpq_set_codebooks(b200idx_t* h, const float* codebooks);
+int b200idx_ivfpq_get_centroids(const b200idx_t* h, float* out);
+int b200idx_ivfpq_get_codebooks(const b200idx_t* h, float* out);
+/* pre-encoded vectors, e.g. the inverted lists of a CPU index (copyFrom) */
+int b200idx_ivfpq_add_codes(b200idx_t* h, int64_t n, const int32_t* list_no, const uint8_t* codes,
+                            const int64_t* ids);
+/* setNumProbes / getNumProbes: FR/ascend/AscendIndexIVF.h:93-96 */
+int b200idx_ivfpq_set_nprobe(b200idx_t* h, int nprobe);
+int b200idx_ivfpq_get_nprobe(const b200idx_t* h);
+/* getListLength / getListCodesAndIds: FR/ascend/AscendIndexIVF.h:105-108 */
+int64_t b200idx_ivfpq_list_length(const b200idx_t* h, int list);
+int b200idx_ivfpq_get_list(const b200idx_t* h, int list, uint8_t* codes, int64_t* ids);
+
+/* ---- counters (the reference has none; APP_LOG timings only) ---- */
+typedef struct {
+    uint64_t searches;
+    uint64_t queries;
+    uint64_t fallback_queries; /* queries re-run without a threshold after a candidate overflow */
+    uint64_t gemm_launches;
+    uint64_t kernel_launches;  /* kernels of this library launched by searches */
+    uint64_t scan_codes;       /* IVFPQ: PQ codes visited so far */
+} b200idx_stats_t;
+int b200idx_stats(b200idx_t* h, b200idx_stats_t* out, int reset);
+
+/* Message of the last failing call on this handle (h = NULL: last failing create). */
+const char* b200idx_last_error(const b200idx_t* h);
+const char* b200idx_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200IDX_H */

@@ -1,0 +1,61 @@
+// Distance GEMM with a fused selection epilogue (replaces the reference's distance operators
+// DistanceComputeFlatMin64 / DistanceFlatL2 / DistanceFlatIP / DistanceInt8* together with
+// the flag-polling AICPU TopkFlat: FR/ops/ascendc/op_kernel/distance_flat_l2.cpp:53-666,
+// FR/ops/cpukernel/impl/topk_flat_cpu_kernel.cpp:36-371).  The [nq x N] distance matrix is
+// never written: each 128 x 256 accumulator tile is consumed out of TMEM by one of two
+// epilogues,
+//   kModeBurstMin : per query row, the minimum key of every burst of 32 (or 8) base rows
+//   kModeAppend   : per query row, every (key, position) whose key <= tau[row]
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+constexpr int kTileQ = 128;   // query rows per accumulator tile (TMEM lanes)
+constexpr int kTileB = 256;   // base rows per accumulator tile (TMEM columns)
+constexpr int kChunkBytes = 128;  // K extent of one pipeline stage, in bytes (one 128-byte swizzle row)
+
+enum GemmKind : int { kKindF16 = 0, kKindBF16 = 1, kKindI8 = 2 };
+enum GemmMode : int { kModeBurstMin = 0, kModeAppend = 1 };
+
+struct GemmArgs {
+    const void* A;        // queries [nq, d] in the operand dtype (SIMT variant only)
+    const void* B;        // base    [N, d]  in the operand dtype (SIMT variant only)
+    int d;                // elements per row
+    int nq;
+    int64_t N;
+    int n_tiles_total;    // ceil(N / kTileB)
+    int n_tiles_sel;      // tiles visited by this pass; tile(i) = i * n_tiles_total / n_tiles_sel
+    int metric;           // kMetricIP / kMetricL2
+    const void* bnorm;    // float* (f16/bf16 kinds) or int32_t* (i8): squared norm per base row, L2 only
+    // kModeBurstMin
+    uint32_t* mins;       // [nq][mins_stride] ordered keys
+    int mins_stride;      // n_tiles_sel * (kTileB / burst)
+    // kModeAppend
+    const uint32_t* tau;  // [nq] inclusive threshold on the ordered key
+    uint64_t* cand;       // [nq][cap] packed (ordered key, position)
+    uint32_t* counts;     // [nq]
+    uint32_t cap;
+    int direct;           // 1: slot = position (cap >= N, no atomics); 0: slot = atomic counter
+    int* err;             // device error word
+};
+
+struct GemmLaunch {
+    int kind;     // GemmKind
+    int mode;     // GemmMode
+    int burst;    // 32 or 8 (kModeBurstMin)
+    int simt;     // 1: plain CUDA-core variant (cross-check), 0: tcgen05 pipeline
+    int num_sms;
+};
+
+// Operands for the tcgen05 variant: row-major [rows, d] tensors with 128-byte swizzled boxes.
+cudaError_t launch_dist_gemm(const GemmLaunch& L, const GemmArgs& a, const CUtensorMap* mapA, const CUtensorMap* mapB,
+                             cudaStream_t stream);
+
+// Encodes a 2-D row-major tensor map with a {128 bytes, box_rows} box and SWIZZLE_128B.
+// Returns 0 on success.
+int encode_operand_map(CUtensorMap* out, int kind, const void* base, int64_t rows, int d, int box_rows);
+
+}  // namespace b200

@@ -1,0 +1,101 @@
+// Per-device exact index (the counterpart of the reference's per-device IndexFlat /
+// IndexInt8Flat objects and their metric-specific search loops:
+// FR/ascenddaemon/impl/IndexFlat.cpp:82-125,551-562, FR/ascendhost/src/index/
+// IndexFlatL2Aicpu.cpp:157-305, FR/ascenddaemon/impl/IndexInt8Flat.cpp:523-692).
+// Storage is one contiguous row-major array per dtype, grown geometrically; there are no
+// 262144-row blocks and no fractal layouts.
+#pragma once
+#include <cuda.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "device_mem.h"
+
+namespace b200 {
+
+struct SearchStats {
+    uint64_t searches = 0;
+    uint64_t queries = 0;
+    uint64_t fallback_queries = 0;   // queries re-run without a threshold after a candidate overflow
+    uint64_t gemm_launches = 0;
+    uint64_t kernel_launches = 0;    // every kernel of this library launched by searches
+    uint64_t scan_codes = 0;         // IVFPQ: codes visited
+};
+
+class FlatIndex {
+public:
+    // dtype: kF32 (fp32 rows + bf16 filter copy, results refined in fp32), kF16 (fp16 rows,
+    // fp32 accumulation, results are the GEMM's), kI8 (int8 rows, exact int32).
+    FlatIndex(int d, int metric, int dtype, int device);
+    ~FlatIndex();
+
+    int d() const { return d_; }
+    int metric() const { return metric_; }
+    int dtype() const { return dtype_; }
+    int device() const { return device_; }
+    int64_t ntotal() const { return n_; }
+    cudaStream_t stream() const { return stream_; }
+    SearchStats& stats() { return stats_; }
+
+    // x: host or device pointer in the index's input dtype (float for kF32 and kF16 unless
+    // x_is_f16, int8 for kI8).  ids: host pointer or nullptr (labels = ntotal + i).
+    void add(int64_t n, const void* x, bool x_is_f16, const int64_t* ids, bool x_on_device);
+    void reset();
+    int64_t remove_ids(int64_t n, const int64_t* ids);
+    // Copies rows [offset, offset + n) to a host buffer: float for kF32, fp16 bits for kF16,
+    // int8 for kI8.
+    void get_base(int64_t offset, int64_t n, void* out_host) const;
+    void get_labels(int64_t offset, int64_t n, int64_t* out_host) const;
+
+    // Device-resident search.  xq: device pointer, rows of float (kF32, kF16 unless q_is_f16) or
+    // int8.  D/I: device pointers with row stride ldk >= k.  Work is enqueued on stream();
+    // the call synchronises that stream before returning (candidate-overflow check).
+    void search_device(int64_t nq, const void* xq, bool q_is_f16, int k, float* D, int64_t* I, int ldk);
+    // Host-pointer search: pinned staging, H2D, search_device, D2H.
+    void search_host(int64_t nq, const void* xq, bool q_is_f16, int k, float* D, int64_t* I);
+
+    // Raw access for composite indexes (IVFPQ coarse quantizer).
+    const float* rows_f32() const { return x32_.as<float>(); }
+
+private:
+    struct Plan {
+        bool sampled;
+        int burst;
+        int s_tiles;
+        uint32_t cap;
+    };
+    Plan make_plan(int k) const;
+    void run_page(int nq, const void* xq_raw, const void* xq_op, int k, float* D, int64_t* I, int ldk,
+                  const int32_t* qmap_dev, bool force_full);
+    void reserve(int64_t n);
+    size_t in_elem_bytes() const { return dtype_ == kI8 ? 1 : (dtype_ == kF16 ? 2 : 4); }
+    size_t op_elem_bytes() const { return dtype_ == kI8 ? 1 : 2; }
+    int gemm_kind() const;
+
+    int d_, metric_, dtype_, device_;
+    int num_sms_ = 0;
+    bool use_simt_ = false;
+    int64_t n_ = 0, cap_rows_ = 0;
+    int64_t next_auto_id_ = 0;
+    cudaStream_t stream_ = nullptr;
+
+    DeviceBuffer x32_;     // kF32: fp32 rows
+    DeviceBuffer xop_;     // GEMM operand rows: bf16 (kF32), fp16 (kF16), int8 (kI8)
+    DeviceBuffer norms_;   // float (kF32/kF16) or int32 (kI8), padded to a multiple of 256 rows
+    DeviceBuffer labels_;  // int64 per row
+    DeviceBuffer maxnorm_; // float: max squared base norm (kF32)
+    float max_norm_ = 0.f;
+    bool map_b_valid_ = false;
+    CUtensorMap map_b_;
+
+    // scratch
+    DeviceBuffer w_qop_, w_qraw_, w_qnorm_, w_eps_, w_mins_, w_tau_, w_cand_, w_counts_, w_sel_, w_over_, w_qmap_,
+        w_err_, w_stage_in_, w_stage_D_, w_stage_I_, w_fb_q_, w_fb_qop_;
+    PinnedBuffer h_over_, h_in_, h_D_, h_I_;
+    SearchStats stats_;
+};
+
+}  // namespace b200

@@ -1,0 +1,76 @@
+// Per-device IVFPQ index (counterpart of the reference's ascend::IndexIVFPQ three-stage search,
+// FR/ascenddaemon/impl/IndexIVFPQ.cpp:2104-2411, and of the host-side assignment / PQ encoding
+// in FR/ascend/impl/AscendIndexIVFPQImpl.cpp:603-805,879-921).
+//
+// Layout in HBM: inverted lists are one CSR structure -- list_offsets[nlist + 1], codes[ntotal][M]
+// (row-major, 16-byte aligned rows when M % 16 == 0), ids[ntotal], and, for residual encoding,
+// one float per vector (the list-dependent part of the distance, see ivfpq_index.cu).
+#pragma once
+#include <stdint.h>
+
+#include <memory>
+#include <vector>
+
+#include "flat_index.h"
+
+namespace b200 {
+
+class IvfpqIndex {
+public:
+    IvfpqIndex(int d, int nlist, int M, int nbits, bool by_residual, int device);
+    ~IvfpqIndex();
+
+    int d() const { return d_; }
+    int nlist() const { return nlist_; }
+    int M() const { return M_; }
+    bool by_residual() const { return by_residual_; }
+    int device() const { return device_; }
+    int64_t ntotal() const { return n_; }
+    int nprobe() const { return nprobe_; }
+    void set_nprobe(int p) { nprobe_ = p; }
+    bool is_trained() const { return has_centroids_ && has_codebooks_; }
+    SearchStats& stats() { return stats_; }
+    cudaStream_t stream() const { return coarse_->stream(); }
+
+    void set_centroids(const float* centroids_host);  // [nlist][d]
+    void set_codebooks(const float* codebooks_host);  // [M][256][d / M]
+    void get_centroids(float* out_host) const;
+    void get_codebooks(float* out_host) const;
+
+    // Assign + encode on the GPU, then merge into the lists.  x: host or device floats.
+    void add(int64_t n, const float* x, const int64_t* ids_host, bool x_on_device);
+    // Pre-encoded vectors (list ids, codes, ids on the host), e.g. from a CPU index.
+    void add_codes(int64_t n, const int32_t* list_no, const uint8_t* codes, const int64_t* ids);
+    void reset();
+    int64_t remove_ids(int64_t n, const int64_t* ids);
+    int64_t list_length(int list) const;
+    void get_list(int list, uint8_t* codes_host, int64_t* ids_host) const;
+
+    void search_device(int64_t nq, const float* xq, int k, float* D, int64_t* I);
+    void search_host(int64_t nq, const float* xq, int k, float* D, int64_t* I);
+
+private:
+    void merge_new(int64_t n, const int32_t* list_no_dev, const uint8_t* codes_dev, const float* t2_dev,
+                   const int64_t* ids_dev);
+    void compute_t2(int64_t n, const int32_t* list_no_dev, const uint8_t* codes_dev, float* t2_dev);
+
+    int d_, nlist_, M_, dsub_, device_;
+    bool by_residual_;
+    int nprobe_ = 1;
+    int64_t n_ = 0;
+    bool has_centroids_ = false, has_codebooks_ = false;
+    int num_sms_ = 0;
+
+    std::unique_ptr<FlatIndex> coarse_;   // nlist centroids, fp32, L2
+    DeviceBuffer codebooks_;              // [M][256][dsub] float
+    DeviceBuffer cbnorm_;                 // [M][256] float: canonical squared norm of each codeword
+    DeviceBuffer offsets_;                // int64 [nlist + 1]
+    std::vector<int64_t> offsets_host_;
+    DeviceBuffer codes_, ids_, t2_;
+    // scratch
+    DeviceBuffer w_lut_, w_cD_, w_cI_, w_pD_, w_pI_, w_q_, w_D_, w_I_, w_assign_D_, w_assign_I_, w_list_, w_codes_,
+        w_t2_, w_ids_, w_x_, w_tmp_;
+    SearchStats stats_;
+};
+
+}  // namespace b200

@@ -1,0 +1,517 @@
+#include "select.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kSelThreads = 256;
+
+// Inclusive scan of a 256-bin histogram held in shared memory; returns through `bucket`/`below`
+// the bin that contains rank r (1-based) and the number of elements in lower bins.
+__device__ __forceinline__ void find_bucket(uint32_t* hist, uint32_t* scan, uint32_t r, uint32_t* bucket,
+                                            uint32_t* below) {
+    const int t = threadIdx.x;
+    scan[t] = hist[t];
+    __syncthreads();
+    for (int off = 1; off < 256; off <<= 1) {
+        uint32_t v = t >= off ? scan[t - off] : 0u;
+        __syncthreads();
+        scan[t] += v;
+        __syncthreads();
+    }
+    const uint32_t incl = scan[t];
+    const uint32_t excl = incl - hist[t];
+    if (incl >= r && excl < r) {
+        *bucket = t;
+        *below = excl;
+    }
+    __syncthreads();
+}
+
+// k-th smallest (rank r, 1-based, r <= n) of n keys of KeyT read from global memory.
+template <typename KeyT>
+__device__ KeyT block_radix_kth(const KeyT* in, uint32_t n, uint32_t r, uint32_t* hist, uint32_t* scan,
+                                uint32_t* sh_bucket, uint32_t* sh_below) {
+    KeyT prefix = 0, mask = 0;
+    for (int shift = static_cast<int>(sizeof(KeyT)) * 8 - 8; shift >= 0; shift -= 8) {
+        hist[threadIdx.x] = 0;
+        __syncthreads();
+        for (uint32_t i = threadIdx.x; i < n; i += kSelThreads) {
+            const KeyT v = in[i];
+            if ((v & mask) == prefix) atomicAdd(&hist[static_cast<uint32_t>(v >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        find_bucket(hist, scan, r, sh_bucket, sh_below);
+        prefix |= static_cast<KeyT>(*sh_bucket) << shift;
+        mask |= static_cast<KeyT>(255) << shift;
+        r -= *sh_below;
+        __syncthreads();
+    }
+    return prefix;
+}
+
+__global__ void __launch_bounds__(kSelThreads)
+kth_threshold_kernel(const uint32_t* mins, int stride, int n, int k, const float* eps, uint32_t tau_all,
+                     uint32_t* tau) {
+    __shared__ uint32_t hist[256], scan[256], sh_bucket, sh_below;
+    const int q = blockIdx.x;
+    if (n < k) {
+        if (threadIdx.x == 0) tau[q] = tau_all;
+        return;
+    }
+    uint32_t kth = block_radix_kth<uint32_t>(mins + static_cast<int64_t>(q) * stride, n, k, hist, scan, &sh_bucket,
+                                             &sh_below);
+    if (threadIdx.x == 0) {
+        if (eps) {
+            float f = ord_to_float(kth);
+            f = f + 2.f * eps[q];
+            f = f + fabsf(f) * 9.5367431640625e-07f;  // one part in 2^20 against the rounding of the adds
+            kth = (f != f) ? tau_all : float_to_ord(f);
+            if (kth > tau_all) kth = tau_all;
+        }
+        tau[q] = kth;
+    }
+}
+
+__device__ __forceinline__ void bitonic_sort_u64(uint64_t* s, int P) {
+    for (int size = 2; size <= P; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int i = threadIdx.x; i < P / 2; i += blockDim.x) {
+                const int lo = 2 * i - (i & (stride - 1));
+                const int hi = lo + stride;
+                const bool up = (lo & size) == 0;
+                const uint64_t a = s[lo], b = s[hi];
+                if ((a > b) == up) {
+                    s[lo] = b;
+                    s[hi] = a;
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kSelThreads)
+select_topk_kernel(const uint64_t* cand, const uint32_t* counts, uint32_t n_fixed, uint32_t cap, int k, int P,
+                   uint64_t* out, uint8_t* overflow) {
+    extern __shared__ uint64_t sorted[];  // P entries
+    __shared__ uint32_t hist[256], scan[256], sh_bucket, sh_below, sh_fill;
+    const int q = blockIdx.x;
+    const uint64_t* row = cand + static_cast<int64_t>(q) * cap;
+    uint32_t n = counts ? counts[q] : n_fixed;
+    if (overflow && threadIdx.x == 0) overflow[q] = n > cap ? 1 : 0;
+    if (n > cap) n = cap;
+    for (int i = threadIdx.x; i < P; i += kSelThreads) sorted[i] = kCandInvalid;
+    if (threadIdx.x == 0) sh_fill = 0;
+    __syncthreads();
+    uint64_t kth = kCandInvalid;
+    if (n > static_cast<uint32_t>(k))
+        kth = block_radix_kth<uint64_t>(row, n, static_cast<uint32_t>(k), hist, scan, &sh_bucket, &sh_below);
+    for (uint32_t i = threadIdx.x; i < n; i += kSelThreads) {
+        const uint64_t v = row[i];
+        if (v <= kth && v != kCandInvalid) {
+            const uint32_t slot = atomicAdd(&sh_fill, 1u);
+            if (slot < static_cast<uint32_t>(P)) sorted[slot] = v;
+        }
+    }
+    __syncthreads();
+    bitonic_sort_u64(sorted, P);
+    uint64_t* orow = out + static_cast<int64_t>(q) * k;
+    for (int i = threadIdx.x; i < k; i += kSelThreads) orow[i] = sorted[i];
+}
+
+__global__ void __launch_bounds__(128)
+refine_f32_kernel(uint64_t* cand, const uint32_t* counts, uint32_t n_fixed, uint32_t cap, int d, int metric,
+                  const float* xq, const float* xb) {
+    const int q = blockIdx.y;
+    uint32_t n = counts ? counts[q] : n_fixed;
+    if (n > cap) n = cap;
+    uint64_t* row = cand + static_cast<int64_t>(q) * cap;
+    const float4* qv = reinterpret_cast<const float4*>(xq + static_cast<int64_t>(q) * d);
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const uint64_t c = row[i];
+        if (c == kCandInvalid) continue;
+        const uint32_t pos = static_cast<uint32_t>(c);
+        const float4* yv = reinterpret_cast<const float4*>(xb + static_cast<int64_t>(pos) * d);
+        float acc = 0.f;
+        if (metric == kMetricL2) {
+            for (int j = 0; j < d / 4; ++j) {
+                const float4 a = __ldg(qv + j), b = __ldg(yv + j);
+                float t;
+                t = a.x - b.x; acc = fmaf(t, t, acc);
+                t = a.y - b.y; acc = fmaf(t, t, acc);
+                t = a.z - b.z; acc = fmaf(t, t, acc);
+                t = a.w - b.w; acc = fmaf(t, t, acc);
+            }
+        } else {
+            for (int j = 0; j < d / 4; ++j) {
+                const float4 a = __ldg(qv + j), b = __ldg(yv + j);
+                acc = fmaf(a.x, b.x, acc);
+                acc = fmaf(a.y, b.y, acc);
+                acc = fmaf(a.z, b.z, acc);
+                acc = fmaf(a.w, b.w, acc);
+            }
+            acc = -acc;
+        }
+        row[i] = pack_cand(float_to_ord(acc), pos);
+    }
+}
+
+__global__ void emit_kernel(const EmitArgs e) {
+    const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= static_cast<int64_t>(e.nq) * e.k) return;
+    const int q = static_cast<int>(idx / e.k), j = static_cast<int>(idx % e.k);
+    const int orow = e.qmap ? e.qmap[q] : q;
+    const uint64_t c = e.sel[idx];
+    float dist;
+    int64_t label;
+    if (c == kCandInvalid) {
+        dist = 3.402823466e+38f;  // FLT_MAX padding, label -1
+        label = -1;
+    } else {
+        const uint32_t ok = static_cast<uint32_t>(c >> 32), pos = static_cast<uint32_t>(c);
+        label = e.labels ? e.labels[pos] : static_cast<int64_t>(pos);
+        if (e.mode == 2) {
+            int32_t kv = ord_to_int(ok);
+            if (e.metric == kMetricL2) dist = static_cast<float>(kv + static_cast<const int32_t*>(e.qnorm)[q]);
+            else dist = static_cast<float>(-kv);
+        } else {
+            float kv = ord_to_float(ok);
+            if (e.metric == kMetricL2) {
+                if (e.mode == 0) {
+                    kv += static_cast<const float*>(e.qnorm)[q];
+                    kv = kv < 0.f ? 0.f : kv;
+                }
+                dist = kv;
+            } else {
+                dist = -kv;
+            }
+        }
+    }
+    e.D[static_cast<int64_t>(orow) * e.ldk + j] = dist;
+    e.I[static_cast<int64_t>(orow) * e.ldk + j] = label;
+}
+
+// One warp per query; heads[] in shared memory.
+__global__ void __launch_bounds__(32)
+merge_topk_kernel(int nsrc, int64_t nq, int k, int descending, const float* Din, const int64_t* Iin, float* D,
+                  int64_t* I) {
+    extern __shared__ int heads[];
+    const int64_t q = blockIdx.x;
+    const int lane = threadIdx.x;
+    for (int s = lane; s < nsrc; s += 32) heads[s] = 0;
+    __syncwarp();
+    for (int j = 0; j < k; ++j) {
+        float bk = 0.f;
+        int64_t bl = -1;
+        int bs = -1;
+        for (int s = lane; s < nsrc; s += 32) {
+            const int h = heads[s];
+            if (h >= k) continue;
+            const int64_t off = (static_cast<int64_t>(s) * nq + q) * k + h;
+            const int64_t l = Iin[off];
+            if (l < 0) {
+                heads[s] = k;
+                continue;
+            }
+            const float key = descending ? -Din[off] : Din[off];
+            if (bs < 0 || key < bk || (key == bk && l < bl)) {
+                bk = key;
+                bl = l;
+                bs = s;
+            }
+        }
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ok = __shfl_xor_sync(0xffffffffu, bk, off);
+            const int64_t ol = __shfl_xor_sync(0xffffffffu, bl, off);
+            const int os = __shfl_xor_sync(0xffffffffu, bs, off);
+            if (os >= 0 && (bs < 0 || ok < bk || (ok == bk && ol < bl))) {
+                bk = ok;
+                bl = ol;
+                bs = os;
+            }
+        }
+        if (lane == 0) {
+            if (bs >= 0) {
+                D[q * k + j] = descending ? -bk : bk;
+                I[q * k + j] = bl;
+                heads[bs] += 1;
+            } else {
+                D[q * k + j] = 3.402823466e+38f;
+                I[q * k + j] = -1;
+            }
+        }
+        __syncwarp();
+    }
+}
+
+// ---- preparation kernels: one warp per row ----
+__device__ __forceinline__ float warp_sum(float v) {
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+__device__ __forceinline__ int warp_sum_i(int v) {
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+
+__global__ void prep_queries_f32_kernel(const float* xq, int nq, int d, int metric, float ymax,
+                                        __nv_bfloat16* qb, float* qnorm, float* eps) {
+    const int q = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (q >= nq) return;
+    float s = 0.f;
+    for (int i = lane; i < d; i += 32) {
+        const float v = xq[static_cast<int64_t>(q) * d + i];
+        s = fmaf(v, v, s);
+        qb[static_cast<int64_t>(q) * d + i] = __float2bfloat16_rn(v);
+    }
+    s = warp_sum(s);
+    if (lane == 0) {
+        qnorm[q] = s;
+        // Filter slack.  bf16 rounding of both operands perturbs every product by at most
+        // 2^-8 (1 + 2^-10) relatively, so |dot~ - dot| <= c |q||y| with the accumulation slack
+        // folded into c; the second term covers the fp32 rounding of norms and of the canonical
+        // distance itself.
+        const float qn = sqrtf(s) * 1.0001f;
+        const float c = 0.00390625f * 1.01f + static_cast<float>(d) * 4.76837158203125e-07f;
+        const float g = static_cast<float>(d + 4) * 2.384185791015625e-07f;
+        float e;
+        if (metric == kMetricL2) e = 2.f * c * qn * ymax + g * (qn + ymax) * (qn + ymax);
+        else e = c * qn * ymax + g * qn * ymax;
+        eps[q] = e;
+    }
+}
+
+__global__ void prep_queries_f16_kernel(const __half* xq, int nq, int d, float* qnorm) {
+    const int q = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (q >= nq) return;
+    float s = 0.f;
+    for (int i = lane; i < d; i += 32) {
+        const float v = __half2float(xq[static_cast<int64_t>(q) * d + i]);
+        s = fmaf(v, v, s);
+    }
+    s = warp_sum(s);
+    if (lane == 0) qnorm[q] = s;
+}
+
+__global__ void prep_queries_i8_kernel(const int8_t* xq, int nq, int d, int32_t* qnorm) {
+    const int q = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (q >= nq) return;
+    int s = 0;
+    for (int i = lane; i < d; i += 32) {
+        const int v = xq[static_cast<int64_t>(q) * d + i];
+        s += v * v;
+    }
+    s = warp_sum_i(s);
+    if (lane == 0) qnorm[q] = s;
+}
+
+__global__ void base_prep_f32_kernel(const float* x, int64_t n, int d, __nv_bfloat16* xb, float* norms,
+                                     float* max_norm_sq) {
+    const int64_t r = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (r >= n) return;
+    float s = 0.f;
+    for (int i = lane; i < d; i += 32) {
+        const float v = x[r * d + i];
+        s = fmaf(v, v, s);
+        xb[r * d + i] = __float2bfloat16_rn(v);
+    }
+    s = warp_sum(s);
+    if (lane == 0) {
+        norms[r] = s;
+        atomicMax(reinterpret_cast<unsigned int*>(max_norm_sq), __float_as_uint(s));
+    }
+}
+
+__global__ void base_prep_f16_kernel(const __half* x, int64_t n, int d, float* norms) {
+    const int64_t r = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (r >= n) return;
+    float s = 0.f;
+    for (int i = lane; i < d; i += 32) {
+        const float v = __half2float(x[r * d + i]);
+        s = fmaf(v, v, s);
+    }
+    s = warp_sum(s);
+    if (lane == 0) norms[r] = s;
+}
+
+__global__ void base_prep_i8_kernel(const int8_t* x, int64_t n, int d, int32_t* norms) {
+    const int64_t r = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (r >= n) return;
+    int s = 0;
+    for (int i = lane; i < d; i += 32) {
+        const int v = x[r * d + i];
+        s += v * v;
+    }
+    s = warp_sum_i(s);
+    if (lane == 0) norms[r] = s;
+}
+
+__global__ void f32_to_f16_kernel(const float* x, int64_t count, __half* out) {
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        out[i] = __float2half_rn(x[i]);
+}
+__global__ void f16_to_f32_kernel(const __half* x, int64_t count, float* out) {
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        out[i] = __half2float(x[i]);
+}
+
+__global__ void fill_u32_kernel(uint32_t* p, int64_t count, uint32_t value) {
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        p[i] = value;
+}
+__global__ void iota_i64_kernel(int64_t* p, int64_t count, int64_t start) {
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        p[i] = start + i;
+}
+__global__ void gather_rows_kernel(const uint32_t* src, const int32_t* idx, int n, int row_words, uint32_t* dst) {
+    const int r = blockIdx.x;
+    if (r >= n) return;
+    const uint32_t* s = src + static_cast<int64_t>(idx[r]) * row_words;
+    uint32_t* d = dst + static_cast<int64_t>(r) * row_words;
+    for (int i = threadIdx.x; i < row_words; i += blockDim.x) d[i] = s[i];
+}
+
+inline int next_pow2(int v) {
+    int p = 1;
+    while (p < v) p <<= 1;
+    return p;
+}
+
+}  // namespace
+
+cudaError_t launch_kth_threshold(const uint32_t* mins, int stride, int n, int nq, int k, const float* eps,
+                                 uint32_t tau_all, uint32_t* tau, cudaStream_t stream) {
+    if (nq <= 0) return cudaSuccess;
+    kth_threshold_kernel<<<nq, kSelThreads, 0, stream>>>(mins, stride, n, k, eps, tau_all, tau);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_select_topk(const uint64_t* cand, const uint32_t* counts, uint32_t n_fixed, uint32_t cap, int nq,
+                               int k, uint64_t* out, uint8_t* overflow, cudaStream_t stream) {
+    if (nq <= 0) return cudaSuccess;
+    int P = next_pow2(k < 32 ? 32 : k);
+    size_t smem = static_cast<size_t>(P) * sizeof(uint64_t);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(select_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+    }
+    select_topk_kernel<<<nq, kSelThreads, smem, stream>>>(cand, counts, n_fixed, cap, k, P, out, overflow);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_refine_f32(uint64_t* cand, const uint32_t* counts, uint32_t n_fixed, uint32_t cap, int nq, int d,
+                              int metric, const float* xq, const float* xb, cudaStream_t stream) {
+    if (nq <= 0) return cudaSuccess;
+    uint32_t per_row = counts ? cap : (n_fixed < cap ? n_fixed : cap);
+    int gx = static_cast<int>((per_row + 127) / 128);
+    if (gx > 64) gx = 64;
+    if (gx < 1) gx = 1;
+    for (int q0 = 0; q0 < nq; q0 += 65535) {
+        const int nqq = nq - q0 < 65535 ? nq - q0 : 65535;
+        refine_f32_kernel<<<dim3(gx, nqq), 128, 0, stream>>>(cand + static_cast<int64_t>(q0) * cap,
+                                                            counts ? counts + q0 : nullptr, n_fixed, cap, d, metric,
+                                                            xq + static_cast<int64_t>(q0) * d, xb);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_emit(const EmitArgs& e, cudaStream_t stream) {
+    const int64_t total = static_cast<int64_t>(e.nq) * e.k;
+    if (total <= 0) return cudaSuccess;
+    emit_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(e);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_merge_topk(int nsrc, int64_t nq, int k, int descending, const float* Din, const int64_t* Iin,
+                              float* D, int64_t* I, cudaStream_t stream) {
+    if (nq <= 0 || k <= 0) return cudaSuccess;
+    merge_topk_kernel<<<static_cast<unsigned>(nq), 32, static_cast<size_t>(nsrc) * sizeof(int), stream>>>(
+        nsrc, nq, k, descending, Din, Iin, D, I);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_prep_queries_f32(const float* xq, int nq, int d, int metric, float base_max_norm, void* q_bf16,
+                                    float* qnorm, float* eps, cudaStream_t stream) {
+    if (nq <= 0) return cudaSuccess;
+    prep_queries_f32_kernel<<<(nq + 7) / 8, 256, 0, stream>>>(xq, nq, d, metric, base_max_norm,
+                                                              static_cast<__nv_bfloat16*>(q_bf16), qnorm, eps);
+    return cudaGetLastError();
+}
+cudaError_t launch_prep_queries_f16(const void* xq, int nq, int d, float* qnorm, cudaStream_t stream) {
+    if (nq <= 0) return cudaSuccess;
+    prep_queries_f16_kernel<<<(nq + 7) / 8, 256, 0, stream>>>(static_cast<const __half*>(xq), nq, d, qnorm);
+    return cudaGetLastError();
+}
+cudaError_t launch_prep_queries_i8(const int8_t* xq, int nq, int d, int32_t* qnorm, cudaStream_t stream) {
+    if (nq <= 0) return cudaSuccess;
+    prep_queries_i8_kernel<<<(nq + 7) / 8, 256, 0, stream>>>(xq, nq, d, qnorm);
+    return cudaGetLastError();
+}
+cudaError_t launch_base_prep_f32(const float* x, int64_t n, int d, void* x_bf16, float* norms, float* max_norm_sq,
+                                 cudaStream_t stream) {
+    if (n <= 0) return cudaSuccess;
+    base_prep_f32_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(
+        x, n, d, static_cast<__nv_bfloat16*>(x_bf16), norms, max_norm_sq);
+    return cudaGetLastError();
+}
+cudaError_t launch_base_prep_f16(const void* x, int64_t n, int d, float* norms, cudaStream_t stream) {
+    if (n <= 0) return cudaSuccess;
+    base_prep_f16_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(static_cast<const __half*>(x), n, d,
+                                                                                 norms);
+    return cudaGetLastError();
+}
+cudaError_t launch_base_prep_i8(const int8_t* x, int64_t n, int d, int32_t* norms, cudaStream_t stream) {
+    if (n <= 0) return cudaSuccess;
+    base_prep_i8_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(x, n, d, norms);
+    return cudaGetLastError();
+}
+cudaError_t launch_f32_to_f16(const float* x, int64_t count, void* out, cudaStream_t stream) {
+    if (count <= 0) return cudaSuccess;
+    int grid = static_cast<int>((count + 255) / 256 < 65535 ? (count + 255) / 256 : 65535);
+    f32_to_f16_kernel<<<grid, 256, 0, stream>>>(x, count, static_cast<__half*>(out));
+    return cudaGetLastError();
+}
+cudaError_t launch_f16_to_f32(const void* x, int64_t count, float* out, cudaStream_t stream) {
+    if (count <= 0) return cudaSuccess;
+    int grid = static_cast<int>((count + 255) / 256 < 65535 ? (count + 255) / 256 : 65535);
+    f16_to_f32_kernel<<<grid, 256, 0, stream>>>(static_cast<const __half*>(x), count, static_cast<float*>(out));
+    return cudaGetLastError();
+}
+
+cudaError_t launch_fill_u32(uint32_t* p, int64_t count, uint32_t value, cudaStream_t stream) {
+    if (count <= 0) return cudaSuccess;
+    int grid = static_cast<int>((count + 255) / 256 < 4096 ? (count + 255) / 256 : 4096);
+    fill_u32_kernel<<<grid, 256, 0, stream>>>(p, count, value);
+    return cudaGetLastError();
+}
+cudaError_t launch_iota_i64(int64_t* p, int64_t count, int64_t start, cudaStream_t stream) {
+    if (count <= 0) return cudaSuccess;
+    int grid = static_cast<int>((count + 255) / 256 < 4096 ? (count + 255) / 256 : 4096);
+    iota_i64_kernel<<<grid, 256, 0, stream>>>(p, count, start);
+    return cudaGetLastError();
+}
+cudaError_t launch_gather_rows(const void* src, const int32_t* idx, int n, int row_bytes, void* dst,
+                               cudaStream_t stream) {
+    if (n <= 0) return cudaSuccess;
+    gather_rows_kernel<<<n, 128, 0, stream>>>(static_cast<const uint32_t*>(src), idx, n, row_bytes / 4,
+                                              static_cast<uint32_t*>(dst));
+    return cudaGetLastError();
+}
+
+}  // namespace b200

@@ -1,0 +1,373 @@
+/*
+ * CPU oracle for the vector-search hot path (Flat / Int8Flat / IVFPQ search and
+ * multi-index merge).  TEST INFRASTRUCTURE ONLY: the product library never links,
+ * loads or calls anything in this file; tests and the benchmark's CPU-baseline leg
+ * use it as the checker.
+ *
+ * PARITY UNPINNED: the reference (Ascend/IndexSDK) holds no golden vectors or
+ * known-answer files for this path.  Its device operators cannot run off Ascend
+ * hardware, its unit tests run on a mock runtime whose operators write zeros
+ * (feature_retrieval/opensource/AscendCLMock/acl/simu/AscendSimuSysOperator.cpp:430-447),
+ * and its CPU ground truth is the third-party library Faiss (v1.10.0 pinned by
+ * build/install_deps.sh:23-27, not vendored).  This file therefore restates the
+ * published semantics of Faiss' IndexFlatL2 / IndexFlatIP / IndexIVFPQ in its own
+ * code and anchors on the reference's call sites:
+ *   - Flat ground truth: examples/TestAscendIndexFlat.cpp:242-250 (faiss::IndexFlat),
+ *     self-hit property FR/test/ascend/TestAscendIndexFlat.cpp:117-123
+ *   - int8 dot product / squared distance in int32:
+ *     FR/ops/tbe/impl/distance_int8_cos_maxs.py:256-284 (accumulate part only; the
+ *     build follows the stricter raw-int32 contract, no fp16 rescale)
+ *   - IVFPQ: raw-vector or residual PQ encode, exhaustive nearest codeword, first
+ *     minimum wins: FR/ascend/impl/AscendIndexIVFPQImpl.cpp:879-910; one ADC table
+ *     per query [M][256]: FR/ascenddaemon/impl/IndexIVFPQ.cpp:1681-1704; table entry
+ *     semantics FR/ops/ascendc/op_kernel/ascendc_ivfpq_subspace_distance.cpp:222-258;
+ *     only non-empty probed lists are scanned: IndexIVFPQ.cpp:2166-2219
+ *   - result padding FLT_MAX / -1: FR/ascend/impl/AscendIndexImpl.cpp:628-633
+ *   - multi-index layout [index][query][k] and merge: FR/ascend/utils/MergeResUtils.cpp:44-107
+ *   (FR = feature_retrieval/src/ascendfaiss)
+ *
+ * Canonical arithmetic (the GPU path computes the same expressions in the same
+ * order, which is what makes fp32 and int8 results bit-comparable):
+ *   L2(q,y)  : acc = 0; for i in 0..d-1: t = q[i]-y[i]; acc = fmaf(t,t,acc)
+ *   IP(q,y)  : acc = 0; for i in 0..d-1: acc = fmaf(q[i],y[i],acc)
+ *   ADC      : acc = 0; for m in 0..M-1: acc = acc + LUT[m][code[m]]   (fp32 adds)
+ *   ordering : ascending (key, tie) with key = distance (L2) or -score (IP) and
+ *              tie = insertion position (Flat/Int8Flat) or label (IVFPQ, merges).
+ */
+#include <float.h>
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define ORC_METRIC_IP 0
+#define ORC_METRIC_L2 1
+
+typedef struct {
+    double key;
+    int64_t tie;
+} orc_item;
+
+static inline int item_less(const orc_item* a, const orc_item* b) {
+    return (a->key < b->key) || (a->key == b->key && a->tie < b->tie);
+}
+
+/* max-heap on (key, tie): root is the worst of the kept k */
+static void heap_sift_down(orc_item* h, int n, int i) {
+    for (;;) {
+        int l = 2 * i + 1, r = l + 1, m = i;
+        if (l < n && item_less(&h[m], &h[l])) m = l;
+        if (r < n && item_less(&h[m], &h[r])) m = r;
+        if (m == i) return;
+        orc_item t = h[i]; h[i] = h[m]; h[m] = t;
+        i = m;
+    }
+}
+
+static void heap_sift_up(orc_item* h, int i) {
+    while (i > 0) {
+        int p = (i - 1) / 2;
+        if (!item_less(&h[p], &h[i])) return;
+        orc_item t = h[i]; h[i] = h[p]; h[p] = t;
+        i = p;
+    }
+}
+
+static inline void heap_offer(orc_item* h, int* n, int k, double key, int64_t tie) {
+    orc_item it = {key, tie};
+    if (*n < k) {
+        h[*n] = it;
+        heap_sift_up(h, *n);
+        (*n)++;
+    } else if (item_less(&it, &h[0])) {
+        h[0] = it;
+        heap_sift_down(h, k, 0);
+    }
+}
+
+static int item_cmp(const void* a, const void* b) {
+    const orc_item* x = (const orc_item*)a;
+    const orc_item* y = (const orc_item*)b;
+    if (item_less(x, y)) return -1;
+    if (item_less(y, x)) return 1;
+    return 0;
+}
+
+/* write sorted heap content to the output row; pad with FLT_MAX / -1 */
+static void heap_emit(orc_item* h, int n, int k, int negate, float* D, int64_t* I) {
+    qsort(h, (size_t)n, sizeof(orc_item), item_cmp);
+    for (int j = 0; j < k; ++j) {
+        if (j < n) {
+            D[j] = (float)(negate ? -h[j].key : h[j].key);
+            I[j] = h[j].tie;
+        } else {
+            D[j] = FLT_MAX;
+            I[j] = -1;
+        }
+    }
+}
+
+static inline float l2_canon(const float* q, const float* y, int d) {
+    float acc = 0.f;
+    for (int i = 0; i < d; ++i) {
+        float t = q[i] - y[i];
+        acc = fmaf(t, t, acc);
+    }
+    return acc;
+}
+
+static inline float ip_canon(const float* q, const float* y, int d) {
+    float acc = 0.f;
+    for (int i = 0; i < d; ++i) acc = fmaf(q[i], y[i], acc);
+    return acc;
+}
+
+static inline double l2_f64(const float* q, const float* y, int d) {
+    double acc = 0.0;
+    for (int i = 0; i < d; ++i) {
+        double t = (double)q[i] - (double)y[i];
+        acc += t * t;
+    }
+    return acc;
+}
+
+static inline double ip_f64(const float* q, const float* y, int d) {
+    double acc = 0.0;
+    for (int i = 0; i < d; ++i) acc += (double)q[i] * (double)y[i];
+    return acc;
+}
+
+/*
+ * Exact Flat search.  precise = 0: canonical fp32 arithmetic (bit-comparable with the
+ * GPU fp32 mode); precise = 1: fp64 accumulation rounded to fp32 once (used to bound
+ * the error of every lower-precision mode).  labels: optional nb entries mapping
+ * position -> user id (NULL = identity); ties are broken by position.
+ */
+int orc_flat_search(int metric, int d, int64_t nb, const float* xb, const int64_t* labels,
+                    int64_t nq, const float* xq, int k, int precise, float* D, int64_t* I) {
+    if (d <= 0 || nb < 0 || nq < 0 || k <= 0) return -1;
+    int fail = 0;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int64_t q = 0; q < nq; ++q) {
+        orc_item* h = (orc_item*)malloc(sizeof(orc_item) * (size_t)k);
+        if (!h) { fail = 1; continue; }
+        int n = 0;
+        const float* qv = xq + q * d;
+        for (int64_t j = 0; j < nb; ++j) {
+            const float* yv = xb + j * d;
+            double key;
+            if (metric == ORC_METRIC_L2)
+                key = precise ? (double)(float)l2_f64(qv, yv, d) : (double)l2_canon(qv, yv, d);
+            else
+                key = -(precise ? (double)(float)ip_f64(qv, yv, d) : (double)ip_canon(qv, yv, d));
+            heap_offer(h, &n, k, key, j);
+        }
+        heap_emit(h, n, k, metric != ORC_METRIC_L2, D + q * k, I + q * k);
+        if (labels)
+            for (int j = 0; j < k; ++j)
+                if (I[q * k + j] >= 0) I[q * k + j] = labels[I[q * k + j]];
+        free(h);
+    }
+    return fail ? -2 : 0;
+}
+
+/* fp32 -> fp16 -> fp32 with round-to-nearest-even, the conversion the reference applies
+ * to base and queries on the host (FR/ascend/utils/fp16.cpp:73-93). */
+void orc_round_fp16(int64_t n, const float* x, float* out) {
+#pragma omp parallel for
+    for (int64_t i = 0; i < n; ++i) out[i] = (float)(_Float16)x[i];
+}
+
+void orc_round_bf16(int64_t n, const float* x, float* out) {
+#pragma omp parallel for
+    for (int64_t i = 0; i < n; ++i) {
+        uint32_t u;
+        memcpy(&u, &x[i], 4);
+        uint32_t r = u + 0x7FFFu + ((u >> 16) & 1u);
+        r &= 0xFFFF0000u;
+        if ((u & 0x7F800000u) == 0x7F800000u) r = u & 0xFFFF0000u; /* inf/nan: truncate */
+        memcpy(&out[i], &r, 4);
+    }
+}
+
+/*
+ * Exact int8 Flat search, int32 accumulation, no scaling.  IP: score = sum q*x, larger
+ * is better; L2: sum (q-x)^2, smaller is better.  Ties -> lower position.  Distances are
+ * returned as float (|value| <= 1024*2^14 < 2^24, exactly representable).
+ */
+int orc_int8_search(int metric, int d, int64_t nb, const int8_t* xb, const int64_t* labels,
+                    int64_t nq, const int8_t* xq, int k, float* D, int64_t* I) {
+    if (d <= 0 || nb < 0 || nq < 0 || k <= 0) return -1;
+    int fail = 0;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int64_t q = 0; q < nq; ++q) {
+        orc_item* h = (orc_item*)malloc(sizeof(orc_item) * (size_t)k);
+        if (!h) { fail = 1; continue; }
+        int n = 0;
+        const int8_t* qv = xq + q * d;
+        for (int64_t j = 0; j < nb; ++j) {
+            const int8_t* yv = xb + j * d;
+            int32_t acc = 0;
+            if (metric == ORC_METRIC_L2) {
+                for (int i = 0; i < d; ++i) {
+                    int32_t t = (int32_t)qv[i] - (int32_t)yv[i];
+                    acc += t * t;
+                }
+                heap_offer(h, &n, k, (double)acc, j);
+            } else {
+                for (int i = 0; i < d; ++i) acc += (int32_t)qv[i] * (int32_t)yv[i];
+                heap_offer(h, &n, k, -(double)acc, j);
+            }
+        }
+        heap_emit(h, n, k, metric != ORC_METRIC_L2, D + q * k, I + q * k);
+        if (labels)
+            for (int j = 0; j < k; ++j)
+                if (I[q * k + j] >= 0) I[q * k + j] = labels[I[q * k + j]];
+        free(h);
+    }
+    return fail ? -2 : 0;
+}
+
+/* ---- IVFPQ ---- */
+
+/* nearest centroid under canonical L2, ties -> lower list id */
+int orc_ivf_assign(int d, int nlist, const float* centroids, int64_t n, const float* x,
+                   int32_t* list_no) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) {
+        float best = INFINITY;
+        int32_t arg = 0;
+        for (int l = 0; l < nlist; ++l) {
+            float dd = l2_canon(x + i * d, centroids + (int64_t)l * d, d);
+            if (dd < best) { best = dd; arg = l; }
+        }
+        list_no[i] = arg;
+    }
+    return 0;
+}
+
+/*
+ * PQ encode: codebooks [M][ksub][dsub]; by_residual subtracts the assigned centroid
+ * first.  Exhaustive nearest codeword, first minimum wins.
+ */
+int orc_pq_encode(int d, int M, int ksub, const float* codebooks, int by_residual,
+                  const float* centroids, const int32_t* list_no, int64_t n, const float* x,
+                  uint8_t* codes) {
+    if (M <= 0 || d % M || ksub > 256) return -1;
+    int dsub = d / M;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) {
+        float r[4096];
+        const float* v = x + i * d;
+        if (by_residual) {
+            const float* c = centroids + (int64_t)list_no[i] * d;
+            for (int t = 0; t < d; ++t) r[t] = v[t] - c[t];
+            v = r;
+        }
+        for (int m = 0; m < M; ++m) {
+            float best = INFINITY;
+            int arg = 0;
+            for (int j = 0; j < ksub; ++j) {
+                float dd = l2_canon(v + m * dsub, codebooks + ((int64_t)m * ksub + j) * dsub, dsub);
+                if (dd < best) { best = dd; arg = j; }
+            }
+            codes[i * M + m] = (uint8_t)arg;
+        }
+    }
+    return 0;
+}
+
+/*
+ * IVFPQ search, L2 only (the reference forces L2: AscendIndexIVFPQImpl.cpp:701).
+ * Lists are CSR: list_offsets[nlist+1] into codes[ntotal][M] and ids[ntotal].
+ * Stage 1: nprobe nearest centroids by canonical L2, ties -> lower list id.
+ * Stage 2: by_residual = 0: one table per query, LUT[m][j] = L2(q_m, cb[m][j]);
+ *          by_residual = 1: one table per (query, list) on q - centroid[list].
+ * Stage 3: ADC sum in fp32, m ascending; top-k by (distance, label).
+ * coarse_out (optional, nq*nprobe) receives the probed list ids in rank order.
+ */
+int orc_ivfpq_search(int d, int nlist, int M, int ksub, const float* centroids,
+                     const float* codebooks, int by_residual, const int64_t* list_offsets,
+                     const uint8_t* codes, const int64_t* ids, int64_t nq, const float* xq,
+                     int nprobe, int k, float* D, int64_t* I, int32_t* coarse_out) {
+    if (M <= 0 || d % M || nprobe <= 0 || k <= 0 || ksub > 256 || d > 4096) return -1;
+    if (nprobe > nlist) nprobe = nlist;
+    int dsub = d / M;
+    int fail = 0;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int64_t q = 0; q < nq; ++q) {
+        const float* qv = xq + q * d;
+        orc_item* ch = (orc_item*)malloc(sizeof(orc_item) * (size_t)nprobe);
+        orc_item* h = (orc_item*)malloc(sizeof(orc_item) * (size_t)k);
+        float* lut = (float*)malloc(sizeof(float) * (size_t)M * ksub);
+        if (!ch || !h || !lut) { fail = 1; free(ch); free(h); free(lut); continue; }
+        int cn = 0;
+        for (int l = 0; l < nlist; ++l)
+            heap_offer(ch, &cn, nprobe, (double)l2_canon(qv, centroids + (int64_t)l * d, d), l);
+        qsort(ch, (size_t)cn, sizeof(orc_item), item_cmp);
+        if (coarse_out)
+            for (int p = 0; p < nprobe; ++p) coarse_out[q * nprobe + p] = p < cn ? (int32_t)ch[p].tie : -1;
+        int n = 0;
+        if (!by_residual) {
+            for (int m = 0; m < M; ++m)
+                for (int j = 0; j < ksub; ++j)
+                    lut[m * ksub + j] = l2_canon(qv + m * dsub, codebooks + ((int64_t)m * ksub + j) * dsub, dsub);
+        }
+        for (int p = 0; p < cn; ++p) {
+            int l = (int)ch[p].tie;
+            int64_t b = list_offsets[l], e = list_offsets[l + 1];
+            if (b == e) continue;
+            if (by_residual) {
+                float r[4096];
+                const float* c = centroids + (int64_t)l * d;
+                for (int t = 0; t < d; ++t) r[t] = qv[t] - c[t];
+                for (int m = 0; m < M; ++m)
+                    for (int j = 0; j < ksub; ++j)
+                        lut[m * ksub + j] = l2_canon(r + m * dsub, codebooks + ((int64_t)m * ksub + j) * dsub, dsub);
+            }
+            for (int64_t v = b; v < e; ++v) {
+                const uint8_t* c = codes + v * M;
+                float acc = 0.f;
+                for (int m = 0; m < M; ++m) acc = acc + lut[m * ksub + c[m]];
+                heap_offer(h, &n, k, (double)acc, ids[v]);
+            }
+        }
+        heap_emit(h, n, k, 0, D + q * k, I + q * k);
+        free(ch); free(h); free(lut);
+    }
+    return fail ? -2 : 0;
+}
+
+/*
+ * Merge nsrc sorted result sets [src][nq][k] into [nq][k] by (key, label); entries with
+ * label < 0 are padding.  descending = 1 for inner-product scores.
+ */
+int orc_merge_topk(int nsrc, int64_t nq, int k, int descending, const float* Din,
+                   const int64_t* Iin, float* D, int64_t* I) {
+#pragma omp parallel for schedule(static)
+    for (int64_t q = 0; q < nq; ++q) {
+        orc_item* h = (orc_item*)malloc(sizeof(orc_item) * (size_t)k);
+        int n = 0;
+        for (int s = 0; s < nsrc; ++s)
+            for (int j = 0; j < k; ++j) {
+                int64_t off = ((int64_t)s * nq + q) * k + j;
+                if (Iin[off] < 0) continue;
+                heap_offer(h, &n, k, descending ? -(double)Din[off] : (double)Din[off], Iin[off]);
+            }
+        heap_emit(h, n, k, descending, D + q * k, I + q * k);
+        free(h);
+    }
+    return 0;
+}
+
+int orc_num_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
