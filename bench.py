@@ -1,0 +1,535 @@
+#!/usr/bin/env python
+"""Benchmark of the search hot path on seeded synthetic data.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload ivfpq10m|flat1m|int8flat4m]
+                    [--impl ours|reference] [--by-residual 0|1]
+
+One "step" is one pass of the search path over one batch of queries.  The default workload is
+the IVFPQ configuration the headline metric is quoted on (10 M vectors, d=128, nlist=16384,
+M=16 x 8 bit, nprobe=64, k=10, 10 000 queries per step); `flat1m` and `int8flat4m` are the
+exact-search configurations.  Prints ONE JSON line (rank 0).
+
+  value : queries/s with queries and results resident in HBM (device-pointer C ABI call)
+  e2e   : queries/s through the host-pointer API, H2D of queries and D2H of results included
+  roofline : dominant kernel (IVFPQ: code scan, HBM-bound; Flat: distance GEMM, tensor-bound)
+             timed live with CUDA events on the index's own stream
+  cpu_baseline : the CPU oracle (a port of the reference's CPU semantics; Faiss itself is not
+             installed) on a bounded sample of the same queries, all host threads
+
+With --gpus N > 1 (launched by torchrun) the base is sharded by id modulo N, every rank
+searches all queries on its shard, and the per-rank top-k are all-gathered over NCCL and merged
+on device (strong scaling: total work is fixed).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+
+# DRAM bytes per launch of the dominant kernel taken from an ncu capture (see profiles/);
+# None until a capture exists for the workload.
+NCU_TRAFFIC_BYTES = {"ivfpq10m": None, "flat1m": None, "int8flat4m": None}
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            m = json.load(f)
+        return dict(hbm=float(m["hbm_gbs"]), tflops=float(m["bf16_tflops"]),
+                    tflops_sustained=float(m.get("bf16_tflops_sustained", m["bf16_tflops"])), source="measured")
+    return dict(hbm=FALLBACK_HBM_GBS, tflops=FALLBACK_BF16_TFLOPS, tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle sampling during the timed region (reads only)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, reasons, smax, power = [], set(), None, []
+        try:
+            for line in open(self.path):
+                f = [t.strip() for t in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    smax = float(f[2])
+                    power.append(float(f[3]))
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                   f[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+        finally:
+            try:
+                os.unlink(self.path)
+            except OSError:
+                pass
+        if sm:
+            busy = [c for c, p in zip(sm, power) if p >= 0.6 * max(power)] or sm
+            out.update(sm_mhz=float(np.median(busy)), sm_max_mhz=smax, reasons=sorted(reasons), samples=len(sm),
+                       power_w_max=max(power))
+        return out
+
+
+# --------------------------------------------------------------------------------------
+# workload construction (untimed; torch is plumbing for data generation and training)
+# --------------------------------------------------------------------------------------
+def torch_kmeans(x, k, niter, seed):
+    import torch
+    g = torch.Generator(device=x.device)
+    g.manual_seed(seed)
+    n = x.shape[0]
+    cent = x[torch.randperm(n, generator=g, device=x.device)[:k]].clone()
+    for _ in range(niter):
+        cn = (cent * cent).sum(1)
+        assign = torch.empty(n, dtype=torch.int64, device=x.device)
+        for s in range(0, n, 131072):
+            xs = x[s:s + 131072]
+            assign[s:s + 131072] = (cn[None, :] - 2.0 * (xs @ cent.T)).argmin(1)
+        counts = torch.bincount(assign, minlength=k)
+        sums = torch.zeros_like(cent).index_add_(0, assign, x)
+        nz = counts > 0
+        cent[nz] = sums[nz] / counts[nz, None].to(x.dtype)
+        ne = int((~nz).sum())
+        if ne:
+            cent[~nz] = x[torch.randint(0, n, (ne,), generator=g, device=x.device)]
+    return cent
+
+
+def assign_torch(x, cent):
+    import torch
+    cn = (cent * cent).sum(1)
+    out = torch.empty(x.shape[0], dtype=torch.int64, device=x.device)
+    for s in range(0, x.shape[0], 131072):
+        out[s:s + 131072] = (cn[None, :] - 2.0 * (x[s:s + 131072] @ cent.T)).argmin(1)
+    return out
+
+
+class Workload:
+    name = ""
+    k = 10
+    nq = 0
+    dtype = "f32"
+    descending = False
+
+
+class IvfpqWorkload(Workload):
+    """IVFPQ, d=128, N=10 M Gaussian mixture (16384 centres ~ N(0,1), sigma 0.1), nlist=16384,
+    M=16 x 8 bit trained by seeded k-means (25 iterations) on a 500 k sample, 10 000 queries from
+    the same mixture, nprobe=64, k=10."""
+    name = "ivfpq10m"
+
+    def __init__(self, b, dev, rank, world, by_residual, scale=1.0):
+        import torch
+        self.d, self.nlist, self.M, self.nprobe, self.k = 128, 16384, 16, 64, 10
+        self.N = int(10_000_000 * scale)
+        self.nq = 10_000
+        self.by_residual = bool(by_residual)
+        self.dtype = "f32"
+        nc = 16384
+        g = torch.Generator(device=dev)
+        g.manual_seed(4)
+        centers = torch.randn(nc, self.d, generator=g, device=dev)
+        chunk = 1_000_000
+
+        def gen(seed, n):
+            gg = torch.Generator(device=dev)
+            gg.manual_seed(seed)
+            which = torch.randint(0, nc, (n,), generator=gg, device=dev)
+            return centers[which] + 0.1 * torch.randn(n, self.d, generator=gg, device=dev)
+
+        t0 = time.time()
+        sample = gen(4000, min(chunk, self.N))[:500_000]
+        cent = torch_kmeans(sample, self.nlist, 25, seed=41)
+        train = sample
+        if self.by_residual:
+            train = sample - cent[assign_torch(sample, cent)]
+        dsub = self.d // self.M
+        cb = torch.stack([torch_kmeans(train[:, m * dsub:(m + 1) * dsub].contiguous(), 256, 25, seed=50 + m)
+                          for m in range(self.M)])
+        self.train_s = time.time() - t0
+        self.centroids = cent.cpu().numpy()
+        self.codebooks = cb.cpu().numpy()
+        ix = b.IndexIVFPQ(self.d, self.nlist, self.M, 8, by_residual=self.by_residual, device=dev.index)
+        ix.set_centroids(self.centroids)
+        ix.set_codebooks(self.codebooks)
+        t0 = time.time()
+        for c in range((self.N + chunk - 1) // chunk):
+            n = min(chunk, self.N - c * chunk)
+            x = gen(4000 + c, n)
+            ids = np.arange(c * chunk, c * chunk + n, dtype=np.int64)
+            if world > 1:
+                x = x[rank::world].contiguous()
+                ids = ids[rank::world].copy()
+            torch.cuda.synchronize(dev)
+            ix.add_device(x.data_ptr(), x.shape[0], ids)
+            del x
+        self.add_s = time.time() - t0
+        ix.nprobe = self.nprobe
+        self.index = ix
+        self.xq = gen(5, self.nq).cpu().pin_memory()
+        self.units_bytes_per_query = self.nprobe * (self.N / self.nlist) * self.M   # algorithmic scan bytes
+        self.desc = dict(workload="IVFPQ d=128 N=%d nlist=16384 M=16x8bit nprobe=64 k=10 nq=10000 "
+                                  "(Gaussian mixture, seeded k-means 25 it on 500k sample)" % self.N,
+                         by_residual=self.by_residual)
+
+    def roofline(self, stats, steps, peaks):
+        ms = stats["stage_ms"]["scan"] / max(1, stats["stage_launches"]["scan"])
+        alg = self.units_bytes_per_query * self.nq / max(1, self.world_size)
+        ach = alg / (ms * 1e-3) / 1e9 if ms > 0 else None
+        visited = stats["scan_codes_delta"] * self.M / max(1, stats["stage_launches"]["scan"])
+        return dict(bound="hbm", kernel="ivfpq_scan_kernel", achieved=ach, peak=peaks["hbm"], unit="GB/s",
+                    frac=(ach / peaks["hbm"]) if ach else None, peak_source=peaks["source"],
+                    traffic=NCU_TRAFFIC_BYTES.get(self.name), algorithmic_bytes_per_launch=alg,
+                    visited_code_bytes_per_launch=visited, ms_per_launch=ms)
+
+    def cpu_reference(self, oracle, nsample):
+        ix = self.index
+        offs = np.zeros(self.nlist + 1, np.int64)
+        lens = np.array([ix.list_length(l) for l in range(self.nlist)], np.int64)
+        np.cumsum(lens, out=offs[1:])
+        codes = np.empty((int(offs[-1]), self.M), np.uint8)
+        ids = np.empty(int(offs[-1]), np.int64)
+        for l in range(self.nlist):
+            if lens[l]:
+                c, i = ix.get_list(l)
+                codes[offs[l]:offs[l + 1]] = c
+                ids[offs[l]:offs[l + 1]] = i
+        xq = self.xq.numpy()
+        variant = 1 if self.by_residual else 0
+
+        def run(n):
+            t0 = time.perf_counter()
+            D, I = oracle.ivfpq_search(self.centroids, self.codebooks, variant, offs, codes, ids, xq[:n],
+                                       self.nprobe, self.k)
+            return time.perf_counter() - t0, D, I
+        return run
+
+
+class FlatWorkload(Workload):
+    """Flat L2 exact search, fp32: base 1 000 000 x 128 N(0,1), 1024 queries, k=100."""
+    name = "flat1m"
+
+    def __init__(self, b, dev, rank, world, scale=1.0):
+        import torch
+        self.d, self.k, self.nq = 128, 100, 1024
+        self.N = int(1_000_000 * scale)
+        self.dtype = "bf16 filter + f32 refine"
+        g = torch.Generator(device=dev)
+        g.manual_seed(0)
+        xb = torch.randn(self.N, self.d, generator=g, device=dev)
+        g.manual_seed(1)
+        xq = torch.randn(self.nq, self.d, generator=g, device=dev)
+        ids = np.arange(self.N, dtype=np.int64)
+        self.xb_host = None
+        if rank == 0:
+            self.xb_host = xb.cpu().numpy()
+        if world > 1:
+            lo, hi = self.N * rank // world, self.N * (rank + 1) // world   # contiguous slices
+            xb, ids = xb[lo:hi].contiguous(), ids[lo:hi].copy()
+        ix = b.IndexFlat(self.d, b.METRIC_L2, b.F32, device=dev.index)
+        torch.cuda.synchronize(dev)
+        ix.add_device(xb.data_ptr(), xb.shape[0], ids)
+        self.index = ix
+        self.xq = xq.cpu().pin_memory()
+        self.flops_per_query = 2.0 * self.N * self.d
+        self.desc = dict(workload="Flat L2 fp32 N=%d d=128 nq=1024 k=100 (i.i.d. N(0,1))" % self.N)
+
+    def roofline(self, stats, steps, peaks):
+        ms = stats["stage_ms"]["full_gemm"] / max(1, stats["stage_launches"]["full_gemm"])
+        alg = self.flops_per_query * self.nq / max(1, self.world_size)
+        ach = alg / (ms * 1e-3) / 1e12 if ms > 0 else None
+        return dict(bound="tensor", kernel="dist_gemm_tc_kernel (append pass)", achieved=ach, peak=peaks["tflops"],
+                    unit="TFLOP/s", frac=(ach / peaks["tflops"]) if ach else None, peak_source=peaks["source"],
+                    traffic=NCU_TRAFFIC_BYTES.get(self.name), algorithmic_flops_per_launch=alg, ms_per_launch=ms)
+
+    def cpu_reference(self, oracle, nsample):
+        xq = self.xq.numpy()
+
+        def run(n):
+            t0 = time.perf_counter()
+            D, I = oracle.flat_search(oracle.METRIC_L2, self.xb_host, xq[:n], self.k)
+            return time.perf_counter() - t0, D, I
+        return run
+
+
+class Int8Workload(Workload):
+    """Int8Flat inner product: base 4 000 000 x 256 int8 U[-128,127], 256 queries, k=100."""
+    name = "int8flat4m"
+    descending = True
+
+    def __init__(self, b, dev, rank, world, scale=1.0):
+        import torch
+        self.d, self.k, self.nq = 256, 100, 256
+        self.N = int(4_000_000 * scale)
+        self.dtype = "int8 -> int32"
+        g = torch.Generator(device=dev)
+        g.manual_seed(2)
+        xb = torch.randint(-128, 128, (self.N, self.d), generator=g, device=dev, dtype=torch.int8)
+        g.manual_seed(3)
+        xq = torch.randint(-128, 128, (self.nq, self.d), generator=g, device=dev, dtype=torch.int8)
+        ids = np.arange(self.N, dtype=np.int64)
+        self.xb_host = xb.cpu().numpy() if rank == 0 else None
+        if world > 1:
+            lo, hi = self.N * rank // world, self.N * (rank + 1) // world
+            xb, ids = xb[lo:hi].contiguous(), ids[lo:hi].copy()
+        ix = b.IndexInt8Flat(self.d, b.METRIC_INNER_PRODUCT, device=dev.index)
+        torch.cuda.synchronize(dev)
+        ix.add_device(xb.data_ptr(), xb.shape[0], ids)
+        self.index = ix
+        self.xq = xq.cpu().pin_memory()
+        self.desc = dict(workload="Int8Flat IP N=%d d=256 nq=256 k=100 (uniform int8)" % self.N)
+
+    def roofline(self, stats, steps, peaks):
+        ms = stats["stage_ms"]["full_gemm"] / max(1, stats["stage_launches"]["full_gemm"])
+        alg = float(self.N) * self.d / max(1, self.world_size)          # base bytes streamed once per batch
+        ach = alg / (ms * 1e-3) / 1e9 if ms > 0 else None
+        return dict(bound="hbm", kernel="dist_gemm_tc_kernel<i8> (append pass)", achieved=ach, peak=peaks["hbm"],
+                    unit="GB/s", frac=(ach / peaks["hbm"]) if ach else None, peak_source=peaks["source"],
+                    traffic=NCU_TRAFFIC_BYTES.get(self.name), algorithmic_bytes_per_launch=alg, ms_per_launch=ms)
+
+    def cpu_reference(self, oracle, nsample):
+        xq = self.xq.numpy()
+
+        def run(n):
+            t0 = time.perf_counter()
+            D, I = oracle.int8_search(oracle.METRIC_IP, self.xb_host, xq[:n], self.k)
+            return time.perf_counter() - t0, D, I
+        return run
+
+
+def make_workload(name, b, dev, rank, world, args):
+    if name == "ivfpq10m":
+        w = IvfpqWorkload(b, dev, rank, world, args.by_residual, args.scale)
+    elif name == "flat1m":
+        w = FlatWorkload(b, dev, rank, world, args.scale)
+    elif name == "int8flat4m":
+        w = Int8Workload(b, dev, rank, world, args.scale)
+    else:
+        raise SystemExit(f"unknown workload {name}")
+    w.world_size = world
+    return w
+
+
+def time_cpu(run, nq_total, target_s=12.0, first=16):
+    """Bounded CPU sample: a short probe sizes a run of about target_s seconds."""
+    n0 = min(first, nq_total)
+    t, _, _ = run(n0)
+    per = t / n0
+    n = int(max(n0, min(nq_total, target_s / max(per, 1e-9))))
+    t, D, I = run(n)
+    return n / t, n, t
+
+
+# --------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="ivfpq10m")
+    ap.add_argument("--by-residual", type=int, default=1)
+    ap.add_argument("--scale", type=float, default=1.0, help="shrinks the base (development only)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference" and rank != 0:
+        return   # the CPU arm runs on rank 0 alone
+
+    import torch
+    import torch.distributed as dist
+    import indexsdk_b200 as b
+    from indexsdk_b200.sharded import ShardedSearcher
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    b.load()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    ref_arm = args.impl == "reference"
+    if world > 1 and not ref_arm:
+        dist.init_process_group("nccl", device_id=dev)
+    eff_world = 1 if ref_arm else world
+
+    t_setup = time.time()
+    wl = make_workload(args.workload, b, dev, 0 if ref_arm else rank, eff_world, args)
+    setup_s = time.time() - t_setup
+    peaks = measured_peaks()
+    k, nq = wl.k, wl.nq
+
+    if ref_arm:
+        import oracle
+        run = wl.cpu_reference(oracle, None)
+        # each step: a bounded sample sized so that warmup + steps stay within a few minutes
+        budget = 150.0 / max(1, args.steps + args.warmup)
+        t, _, _ = run(min(8, nq))
+        n = int(max(8, min(nq, budget / max(t / min(8, nq), 1e-9))))
+        for _ in range(args.warmup):
+            run(n)
+        times = []
+        for _ in range(args.steps):
+            t, _, _ = run(n)
+            times.append(t)
+        ms = 1e3 * sum(times) / len(times)
+        val = n / (ms * 1e-3)
+        line = dict(metric="QPS", value=val, unit="queries/s", n_gpus=args.gpus, steps=args.steps,
+                    warmup=args.warmup, ms_per_step=ms, higher_is_better=True, scaling="strong", vs_baseline=None,
+                    dtype=wl.dtype, data="synthetic", impl="reference",
+                    config=dict(wl.desc, sample="%d of %d queries per step" % (n, nq)),
+                    cpu_baseline=dict(value=val, unit="queries/s", cores=oracle.num_threads(), kind="port",
+                                      sample="%d queries per step, all host threads (OpenMP), CPU oracle port; "
+                                             "Faiss is not installed" % n),
+                    e2e=dict(value=val, unit="queries/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+        print(json.dumps(line))
+        return
+
+    searcher = ShardedSearcher(wl.index, descending=wl.descending)
+    xq_host = wl.xq                                            # pinned CPU tensor
+    xq_dev = xq_host.to(dev)
+    outD = torch.empty((nq, k), dtype=torch.float32, pin_memory=True)
+    outI = torch.empty((nq, k), dtype=torch.int64, pin_memory=True)
+    xq_np, outD_np, outI_np = xq_host.numpy(), outD.numpy(), outI.numpy()
+    lib_stream = torch.cuda.ExternalStream(wl.index.stream_ptr, device=dev)
+
+    def step_device():
+        searcher.search_device(xq_dev, k)
+
+    def step_e2e():
+        if world == 1:
+            wl.index.search_into(xq_np, k, outD_np, outI_np)   # host pointers through the C ABI
+        else:
+            searcher.search(xq_host, k, outD, outI)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record(lib_stream)
+        for _ in range(steps):
+            fn()
+        torch.cuda.current_stream(dev).synchronize()
+        e1.record(lib_stream)
+        e1.synchronize()
+        torch.cuda.synchronize(dev)
+        wall = time.perf_counter() - t0
+        dev_ms = e0.elapsed_time(e1)
+        # the library stream is idle between the host-side stages of a step; wall clock covers
+        # the NCCL / copy work issued on torch's stream.  Take the larger of the two.
+        ms = max(dev_ms, wall * 1e3) if world > 1 else dev_ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / steps, wall * 1e3 / steps
+
+    for _ in range(args.warmup):
+        step_device()
+        step_e2e()
+    wl.index.stats(reset=True)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    wl.index.set_timing(True)
+    s0 = wl.index.stats()
+    ms_dev, wall_dev = timed(step_device, args.steps)
+    s1 = wl.index.stats()
+    wl.index.set_timing(False)
+    ms_e2e, wall_e2e = timed(step_e2e, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    s2 = wl.index.stats()
+
+    stats = dict(s1)
+    stats["scan_codes_delta"] = s1["scan_codes"] - s0["scan_codes"]
+    launches = s1["kernel_launches"] - s0["kernel_launches"] + (args.steps if world > 1 else 0)
+    roof = wl.roofline(stats, args.steps, peaks)
+
+    # parity spot check inside the bench (rank 0): the timed results against the oracle on a few queries
+    line = dict(metric="QPS", value=nq / (ms_dev * 1e-3), unit="queries/s", n_gpus=world, steps=args.steps,
+                warmup=args.warmup, ms_per_step=ms_dev, higher_is_better=True, scaling="strong", vs_baseline=None,
+                dtype=wl.dtype, data="synthetic",
+                config=dict(wl.desc, nq_per_step=nq, l2_flush="inputs larger than L2 (codes/base >> 126 MB)",
+                            parallelism=("single GPU" if world == 1 else "base sharded by id mod %d, NCCL all-gather "
+                                         "of per-rank top-k + merge kernel" % world),
+                            setup_s=round(setup_s, 1)),
+                e2e=dict(value=nq / (ms_e2e * 1e-3), unit="queries/s", ms_per_step=ms_e2e,
+                         h2d_bytes_per_step=int(xq_host.numel() * xq_host.element_size()),
+                         d2h_bytes_per_step=int(nq * k * 12)),
+                gpu_launches=int(launches),
+                roofline=roof,
+                stage_ms_per_step={n: v / args.steps for n, v in s1["stage_ms"].items() if v > 0},
+                fallback_queries=s2["fallback_queries"],
+                clocks=clocks)
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        import oracle
+        run = wl.cpu_reference(oracle, None)
+        qps, n, t = time_cpu(run, nq)
+        line["cpu_baseline"] = dict(value=qps, unit="queries/s", cores=oracle.num_threads(), kind="port",
+                                    sample="%d of %d queries, %.1f s, CPU oracle port with OpenMP on all host "
+                                           "threads (Faiss is not installed)" % (n, nq, t))
+        # parity of the timed GPU results against the same oracle run
+        _, Dr, Ir = run(min(n, 64))
+        m = Dr.shape[0]
+        same = float((outI_np[:m] == Ir).mean())
+        relerr = float(np.max(np.abs(outD_np[:m] - Dr) / np.maximum(np.abs(Dr), 1e-30)))
+        line["parity_check"] = dict(queries=m, id_agreement=same, max_rel_distance_error=relerr)
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

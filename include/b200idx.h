@@ -113,7 +113,20 @@ int64_t b200idx_ivfpq_list_length(const b200idx_t* h, int list);
 int b200idx_ivfpq_get_list(const b200idx_t* h, int list, uint8_t* codes, int64_t* ids);
 
 /* ---- counters (the reference has none; APP_LOG timings only) ---- */
+enum {
+    B200IDX_STAGE_SAMPLE = 0,    /* query prep + sample GEMM pass + threshold selection */
+    B200IDX_STAGE_FULL_GEMM = 1, /* full distance-GEMM pass with the append epilogue */
+    B200IDX_STAGE_REFINE = 2,    /* fp32 re-computation of candidates */
+    B200IDX_STAGE_SELECT = 3,    /* exact top-k of candidates + result emission */
+    B200IDX_STAGE_COARSE = 4,    /* IVFPQ: whole coarse-quantizer search (host-side span) */
+    B200IDX_STAGE_LUT = 5,       /* IVFPQ: lookup tables */
+    B200IDX_STAGE_SCAN = 6,      /* IVFPQ: code scan */
+    B200IDX_STAGE_MERGE = 7,     /* IVFPQ: merge of probe splits */
+    B200IDX_NUM_STAGES = 8
+};
 typedef struct {
+    double stage_ms[B200IDX_NUM_STAGES];        /* CUDA-event time per stage (timing enabled only) */
+    uint64_t stage_launches[B200IDX_NUM_STAGES];
     uint64_t searches;
     uint64_t queries;
     uint64_t fallback_queries; /* queries re-run without a threshold after a candidate overflow */
@@ -122,6 +135,11 @@ typedef struct {
     uint64_t scan_codes;       /* IVFPQ: PQ codes visited so far */
 } b200idx_stats_t;
 int b200idx_stats(b200idx_t* h, b200idx_stats_t* out, int reset);
+/* Per-stage CUDA-event timing on the index's stream (off by default; the reference only has
+ * verbose wall-clock prints, FR/ascend/impl/AscendIndexIVFPQImpl.cpp:114-118). */
+int b200idx_set_timing(b200idx_t* h, int enabled);
+/* The cudaStream_t all of this index's kernels are launched on. */
+void* b200idx_stream(const b200idx_t* h);
 
 /* Message of the last failing call on this handle (h = NULL: last failing create). */
 const char* b200idx_last_error(const b200idx_t* h);

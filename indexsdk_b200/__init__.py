@@ -30,9 +30,13 @@ class B200IdxError(RuntimeError):
         self.msg = msg
 
 
+STAGES = ("sample", "full_gemm", "refine", "select", "coarse", "lut", "scan", "merge")
+
+
 class Stats(C.Structure):
-    _fields_ = [(n, C.c_uint64) for n in
-                ("searches", "queries", "fallback_queries", "gemm_launches", "kernel_launches", "scan_codes")]
+    _fields_ = [("stage_ms", C.c_double * 8), ("stage_launches", C.c_uint64 * 8)] + [
+        (n, C.c_uint64) for n in
+        ("searches", "queries", "fallback_queries", "gemm_launches", "kernel_launches", "scan_codes")]
 
 
 def lib_path() -> str:
@@ -81,6 +85,8 @@ def load() -> C.CDLL:
         "b200idx_ivfpq_list_length": (i64, [vp, i32]),
         "b200idx_ivfpq_get_list": (i32, [vp, i32, vp, vp]),
         "b200idx_stats": (i32, [vp, C.POINTER(Stats), i32]),
+        "b200idx_set_timing": (i32, [vp, i32]),
+        "b200idx_stream": (vp, [vp]),
         "b200idx_last_error": (C.c_char_p, [vp]),
         "b200idx_version": (C.c_char_p, []),
     }
@@ -99,7 +105,8 @@ EXPORTED_SYMBOLS = [
     "b200idx_dim", "b200idx_device", "b200idx_get_base", "b200idx_get_ids", "b200idx_ivfpq_set_centroids",
     "b200idx_ivfpq_set_codebooks", "b200idx_ivfpq_get_centroids", "b200idx_ivfpq_get_codebooks",
     "b200idx_ivfpq_add_codes", "b200idx_ivfpq_set_nprobe", "b200idx_ivfpq_get_nprobe", "b200idx_ivfpq_list_length",
-    "b200idx_ivfpq_get_list", "b200idx_stats", "b200idx_last_error", "b200idx_version",
+    "b200idx_ivfpq_get_list", "b200idx_stats", "b200idx_set_timing", "b200idx_stream", "b200idx_last_error",
+    "b200idx_version",
 ]
 
 
@@ -190,7 +197,18 @@ class _Index:
     def stats(self, reset: bool = False) -> dict:
         s = Stats()
         _check(self._lib.b200idx_stats(self._h, C.byref(s), int(reset)), self._h)
-        return {n: int(getattr(s, n)) for n, _ in Stats._fields_}
+        out = {n: int(getattr(s, n)) for n, _ in Stats._fields_[2:]}
+        out["stage_ms"] = {n: float(s.stage_ms[i]) for i, n in enumerate(STAGES)}
+        out["stage_launches"] = {n: int(s.stage_launches[i]) for i, n in enumerate(STAGES)}
+        return out
+
+    def set_timing(self, enabled: bool):
+        _check(self._lib.b200idx_set_timing(self._h, int(enabled)), self._h)
+
+    @property
+    def stream_ptr(self) -> int:
+        """Address of the cudaStream_t this index launches on."""
+        return int(self._lib.b200idx_stream(self._h) or 0)
 
 
 class IndexFlat(_Index):

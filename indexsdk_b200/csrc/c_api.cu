@@ -407,6 +407,19 @@ int b200idx_ivfpq_get_list(const b200idx_t* h, int list, uint8_t* codes, int64_t
 int b200idx_stats(b200idx_t* h, b200idx_stats_t* out, int reset) {
     if (!h || !out) return B200IDX_ERR_INVALID_PARAM;
     SearchStats& s = h->kind == 2 ? h->ivfpq->stats() : h->flat->stats();
+    for (int i = 0; i < B200IDX_NUM_STAGES; ++i) {
+        out->stage_ms[i] = s.stage_ms[i];
+        out->stage_launches[i] = s.stage_launches[i];
+    }
+    if (h->kind == 2) {
+        // the coarse quantizer's own stages are reported in slots 0-3
+        SearchStats& c = h->ivfpq->coarse_stats();
+        for (int i = 0; i < 4; ++i) {
+            out->stage_ms[i] = c.stage_ms[i];
+            out->stage_launches[i] = c.stage_launches[i];
+        }
+        if (reset) c = SearchStats();
+    }
     out->searches = s.searches;
     out->queries = s.queries;
     out->fallback_queries = s.fallback_queries;
@@ -415,6 +428,18 @@ int b200idx_stats(b200idx_t* h, b200idx_stats_t* out, int reset) {
     out->scan_codes = s.scan_codes;
     if (reset) s = SearchStats();
     return B200IDX_OK;
+}
+
+int b200idx_set_timing(b200idx_t* h, int enabled) {
+    if (!h) return B200IDX_ERR_INVALID_PARAM;
+    if (h->kind == 2) h->ivfpq->set_timing(enabled != 0);
+    else h->flat->timer().enable(enabled != 0);
+    return B200IDX_OK;
+}
+
+void* b200idx_stream(const b200idx_t* h) {
+    if (!h) return nullptr;
+    return h->kind == 2 ? static_cast<void*>(h->ivfpq->stream()) : static_cast<void*>(h->flat->stream());
 }
 
 const char* b200idx_last_error(const b200idx_t* h) {

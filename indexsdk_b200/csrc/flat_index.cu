@@ -233,6 +233,7 @@ void FlatIndex::run_page(int nq, const void* xq_raw, const void* xq_op_in, int k
     const uint32_t tau_all = is_int ? kTauAllInt : kTauAllFloat;
 
     // 1. query preparation
+    timer_.begin(kStageSample, stream_);
     const void* xq_op = xq_op_in;
     float* eps = nullptr;
     void* qnorm = w_qnorm_.ensure(static_cast<size_t>(nq) * 4);
@@ -309,6 +310,8 @@ void FlatIndex::run_page(int nq, const void* xq_raw, const void* xq_op_in, int k
         stats_.kernel_launches += 1;
         a.direct = 1;
     }
+    timer_.end(stream_);
+    timer_.begin(kStageFullGemm, stream_);
     // 4. full pass: append every key <= tau
     a.n_tiles_sel = a.n_tiles_total;
     a.tau = tau;
@@ -320,15 +323,19 @@ void FlatIndex::run_page(int nq, const void* xq_raw, const void* xq_op_in, int k
     B200_CUDA_CHECK(launch_dist_gemm(L, a, &map_a, &map_b_, stream_));
     stats_.gemm_launches += 1;
     stats_.kernel_launches += 1;
+    timer_.end(stream_);
 
     const uint32_t* counts_arg = plan.sampled ? counts : nullptr;
     const uint32_t n_fixed = static_cast<uint32_t>(n_);
     // 5. fp32 refinement of the candidates
     if (dtype_ == kF32) {
+        timer_.begin(kStageRefine, stream_);
         B200_CUDA_CHECK(launch_refine_f32(cand, counts_arg, n_fixed, plan.cap, nq, d_, metric_,
                                           static_cast<const float*>(xq_raw), x32_.as<float>(), stream_));
         stats_.kernel_launches += 1;
+        timer_.end(stream_);
     }
+    timer_.begin(kStageSelect, stream_);
     // 6. exact top-k of the candidates, 7. results
     uint64_t* sel = static_cast<uint64_t*>(w_sel_.ensure(static_cast<size_t>(nq) * k * 8));
     uint8_t* over = static_cast<uint8_t*>(w_over_.ensure(static_cast<size_t>(nq)));
@@ -349,6 +356,7 @@ void FlatIndex::run_page(int nq, const void* xq_raw, const void* xq_op_in, int k
     e.qmap = qmap_dev;
     B200_CUDA_CHECK(launch_emit(e, stream_));
     stats_.kernel_launches += 2;
+    timer_.end(stream_);
 }
 
 void FlatIndex::search_device(int64_t nq, const void* xq, bool q_is_f16, int k, float* D, int64_t* I, int ldk) {
@@ -390,6 +398,7 @@ void FlatIndex::search_device(int64_t nq, const void* xq, bool q_is_f16, int k, 
         B200_CUDA_CHECK(cudaMemcpyAsync(h, w_over_.get(), static_cast<size_t>(nqp), cudaMemcpyDeviceToHost, stream_));
         B200_CUDA_CHECK(cudaMemcpyAsync(h + nqp, w_err_.get(), sizeof(int), cudaMemcpyDeviceToHost, stream_));
         B200_CUDA_CHECK(cudaStreamSynchronize(stream_));
+        timer_.collect(stats_);
         int err = 0;
         std::memcpy(&err, h + nqp, sizeof(int));
         if (err) {
@@ -416,6 +425,7 @@ void FlatIndex::search_device(int64_t nq, const void* xq, bool q_is_f16, int k, 
             stats_.kernel_launches += 1;
             run_page(m, fq, fq, k, D, I, ldk, qmap + o0, true);
             B200_CUDA_CHECK(cudaStreamSynchronize(stream_));
+            timer_.collect(stats_);
         }
     }
 }

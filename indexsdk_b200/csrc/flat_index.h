@@ -16,13 +16,75 @@
 
 namespace b200 {
 
+// Stages timed with CUDA events on the index's stream when timing is enabled.
+enum Stage : int {
+    kStageSample = 0,   // query prep + sample GEMM pass + threshold selection
+    kStageFullGemm = 1, // full GEMM pass with the append epilogue
+    kStageRefine = 2,   // fp32 re-computation of candidates
+    kStageSelect = 3,   // exact top-k of candidates + result emission
+    kStageCoarse = 4,   // IVFPQ: whole coarse-quantizer search
+    kStageLut = 5,      // IVFPQ: lookup tables
+    kStageScan = 6,     // IVFPQ: code scan
+    kStageMerge = 7,    // IVFPQ: merge of probe splits
+    kNumStages = 8
+};
+
 struct SearchStats {
+    double stage_ms[kNumStages] = {0, 0, 0, 0, 0, 0, 0, 0};
+    uint64_t stage_launches[kNumStages] = {0, 0, 0, 0, 0, 0, 0, 0};
     uint64_t searches = 0;
     uint64_t queries = 0;
     uint64_t fallback_queries = 0;   // queries re-run without a threshold after a candidate overflow
     uint64_t gemm_launches = 0;
     uint64_t kernel_launches = 0;    // every kernel of this library launched by searches
     uint64_t scan_codes = 0;         // IVFPQ: codes visited
+};
+
+// Records begin/end events per stage; elapsed times are folded into SearchStats after the
+// stream has been synchronised.  Disabled (no events recorded) unless enable(true) was called.
+class StageTimer {
+public:
+    ~StageTimer() {
+        for (auto& r : recs_) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+        for (auto& r : pool_) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+    }
+    void enable(bool on) { on_ = on; }
+    bool enabled() const { return on_; }
+    void begin(int stage, cudaStream_t st) {
+        if (!on_) return;
+        Rec r;
+        if (!pool_.empty()) { r = pool_.back(); pool_.pop_back(); }
+        else { cudaEventCreate(&r.a); cudaEventCreate(&r.b); }
+        r.stage = stage;
+        cudaEventRecord(r.a, st);
+        recs_.push_back(r);
+        open_ = static_cast<int>(recs_.size()) - 1;
+    }
+    void end(cudaStream_t st) {
+        if (!on_ || open_ < 0) return;
+        cudaEventRecord(recs_[open_].b, st);
+        open_ = -1;
+    }
+    // call only after the stream is idle
+    void collect(SearchStats& s) {
+        for (auto& r : recs_) {
+            float ms = 0.f;
+            if (cudaEventElapsedTime(&ms, r.a, r.b) == cudaSuccess) {
+                s.stage_ms[r.stage] += ms;
+                s.stage_launches[r.stage] += 1;
+            } else {
+                cudaGetLastError();
+            }
+            pool_.push_back(r);
+        }
+        recs_.clear();
+    }
+
+private:
+    struct Rec { cudaEvent_t a = nullptr, b = nullptr; int stage = 0; };
+    std::vector<Rec> recs_, pool_;
+    bool on_ = false;
+    int open_ = -1;
 };
 
 class FlatIndex {
@@ -39,6 +101,7 @@ public:
     int64_t ntotal() const { return n_; }
     cudaStream_t stream() const { return stream_; }
     SearchStats& stats() { return stats_; }
+    StageTimer& timer() { return timer_; }
 
     // x: host or device pointer in the index's input dtype (float for kF32 and kF16 unless
     // x_is_f16, int8 for kI8).  ids: host pointer or nullptr (labels = ntotal + i).
@@ -96,6 +159,7 @@ private:
         w_err_, w_stage_in_, w_stage_D_, w_stage_I_, w_fb_q_, w_fb_qop_;
     PinnedBuffer h_over_, h_in_, h_D_, h_I_;
     SearchStats stats_;
+    StageTimer timer_;
 };
 
 }  // namespace b200

@@ -620,11 +620,15 @@ void IvfpqIndex::search_device(int64_t nq, const float* xq, int k, float* D, int
         const float* xp = xq + q0 * d_;
         float* cD = static_cast<float*>(w_cD_.ensure(static_cast<size_t>(m) * nprobe * 4));
         int64_t* cI = static_cast<int64_t*>(w_cI_.ensure(static_cast<size_t>(m) * nprobe * 8));
+        timer_.begin(kStageCoarse, st);
         coarse_->search_device(m, xp, false, nprobe, cD, cI, nprobe);
+        timer_.end(st);
+        timer_.begin(kStageLut, st);
         float* lut = static_cast<float*>(w_lut_.ensure(static_cast<size_t>(m) * M_ * kKsub * 4));
         lut_kernel<<<blocks_for(m * M_ * kKsub, 256), 256, 0, st>>>(xp, m, d_, M_, dsub_, codebooks_.as<float>(),
                                                                    by_residual_ ? 1 : 0, lut);
         B200_CUDA_CHECK(cudaGetLastError());
+        timer_.end(st);
         int S = static_cast<int>((16LL * num_sms_ + m - 1) / m);
         S = std::max(1, std::min(S, (nprobe + kScanWarps - 1) / kScanWarps));
         ScanArgs a{};
@@ -645,19 +649,26 @@ void IvfpqIndex::search_device(int64_t nq, const float* xq, int k, float* D, int
         if (S == 1) {
             a.outD = D + q0 * k;
             a.outI = I + q0 * k;
+            timer_.begin(kStageScan, st);
             B200_CUDA_CHECK(launch_scan(a, st));
+            timer_.end(st);
             stats_.kernel_launches += 2;
         } else {
             a.outD = static_cast<float*>(w_pD_.ensure(static_cast<size_t>(S) * m * k * 4));
             a.outI = static_cast<int64_t*>(w_pI_.ensure(static_cast<size_t>(S) * m * k * 8));
+            timer_.begin(kStageScan, st);
             B200_CUDA_CHECK(launch_scan(a, st));
+            timer_.end(st);
+            timer_.begin(kStageMerge, st);
             B200_CUDA_CHECK(launch_merge_topk(S, m, k, 0, a.outD, a.outI, D + q0 * k, I + q0 * k, st));
+            timer_.end(st);
             stats_.kernel_launches += 3;
         }
     }
     unsigned long long scanned = 0;
     B200_CUDA_CHECK(cudaMemcpyAsync(&scanned, w_tmp_.get(), 8, cudaMemcpyDeviceToHost, st));
     B200_CUDA_CHECK(cudaStreamSynchronize(st));
+    timer_.collect(stats_);
     stats_.scan_codes = scanned;
     stats_.kernel_launches += coarse_->stats().kernel_launches;
     stats_.gemm_launches += coarse_->stats().gemm_launches;

@@ -30,6 +30,11 @@ public:
     void set_nprobe(int p) { nprobe_ = p; }
     bool is_trained() const { return has_centroids_ && has_codebooks_; }
     SearchStats& stats() { return stats_; }
+    SearchStats& coarse_stats() { return coarse_->stats(); }
+    void set_timing(bool on) {
+        timer_.enable(on);
+        coarse_->timer().enable(on);
+    }
     cudaStream_t stream() const { return coarse_->stream(); }
 
     void set_centroids(const float* centroids_host);  // [nlist][d]
@@ -71,6 +76,7 @@ private:
     DeviceBuffer w_lut_, w_cD_, w_cI_, w_pD_, w_pI_, w_q_, w_D_, w_I_, w_assign_D_, w_assign_I_, w_list_, w_codes_,
         w_t2_, w_ids_, w_x_, w_tmp_;
     SearchStats stats_;
+    StageTimer timer_;
 };
 
 }  // namespace b200

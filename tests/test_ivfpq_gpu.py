@@ -1,0 +1,151 @@
+"""GPU parity of IVFPQ (assignment, PQ encoding, three-stage search) against the CPU oracle.
+
+Raw-vector encoding (the reference's mode): codes, list contents, distances and ids bit-exact.
+Residual encoding (Faiss default): codes bit-exact; distances and ids bit-exact against the
+oracle's precomputed-table arithmetic (variant 2, what Faiss' use_precomputed_table computes,
+folded per vector) and within RESID_RTOL of the oracle's direct per-(query, list) tables -- the
+two differ by fp32 re-association only."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from indexsdk_b200 import datasets
+from helpers import assert_close_gap_aware, assert_exact
+
+pytestmark = pytest.mark.gpu
+# direct tables vs precomputed-table decomposition: error grows with |centroid| / |residual|
+RESID_RTOL = 5e-5
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _build(b200, xb, ids, cent, cb, resid, chunks=1):
+    nlist, M = cent.shape[0], cb.shape[0]
+    ix = b200.IndexIVFPQ(xb.shape[1], nlist, M, 8, by_residual=resid)
+    ix.set_centroids(cent)
+    ix.set_codebooks(cb)
+    for part, idp in zip(np.array_split(xb, chunks), np.array_split(ids, chunks)):
+        ix.add_with_ids(part, idp)
+    return ix
+
+
+def _oracle_lists(xb, ids, cent, cb, resid):
+    ln = oracle.ivf_assign(cent, xb)
+    codes = oracle.pq_encode(cb, xb, resid, cent, ln)
+    return ln, codes, oracle.build_lists(ln, codes, ids, cent.shape[0])
+
+
+@pytest.mark.parametrize("tag,resid", [("raw", False), ("res", True)])
+def test_golden_fixture(b200, tag, resid):
+    g = np.load(os.path.join(GOLD, "ivfpq_small.npz"))
+    xb = g["xb"]
+    ids = np.arange(xb.shape[0], dtype=np.int64)
+    ix = _build(b200, xb, ids, g[f"cent_{tag}"], g[f"cb_{tag}"], resid)
+    off, cs, idl = oracle.build_lists(g[f"list_no_{tag}"], g[f"codes_{tag}"], ids, 16)
+    for l in range(16):
+        codes, lid = ix.get_list(l)
+        np.testing.assert_array_equal(codes, cs[off[l]:off[l + 1]])
+        np.testing.assert_array_equal(lid, idl[off[l]:off[l + 1]])
+    ix.nprobe = 4
+    D, I = ix.search(g["xq"], 10)
+    if resid:
+        assert_close_gap_aware(D, I, g[f"D_{tag}"], g[f"I_{tag}"], rtol=RESID_RTOL, what="ivfpq residual")
+        D2, I2 = oracle.ivfpq_search(g[f"cent_{tag}"], g[f"cb_{tag}"], 2, off, cs, idl, g["xq"], 4, 10)
+        assert_exact(D, I, D2, I2)
+    else:
+        assert_exact(D, I, g[f"D_{tag}"], g[f"I_{tag}"])
+
+
+@pytest.mark.parametrize("resid", [False, True])
+@pytest.mark.parametrize("d,nlist,M,n,nq,nprobe,k,chunks", [
+    (128, 256, 16, 60000, 50, 16, 10, 3),
+    (128, 64, 16, 20000, 300, 64, 100, 1),
+    (96, 128, 48, 30000, 20, 32, 100, 2),
+    (64, 32, 8, 5000, 9, 8, 320, 1),
+    (128, 100, 32, 8000, 4, 100, 1, 1),
+    (64, 16, 4, 3000, 1, 1, 5, 1),
+])
+def test_search_vs_oracle(b200, resid, d, nlist, M, n, nq, nprobe, k, chunks):
+    xb, _ = datasets.mixture(n, d, max(nlist // 2, 4), seed=4)
+    xq, _ = datasets.mixture(nq, d, max(nlist // 2, 4), seed=5, centers_seed=4)
+    ids = (np.arange(n, dtype=np.int64) * 5 + 11)
+    cent, cb = datasets.train_ivfpq(xb[: min(n, 8000)], nlist, M, resid, niter=4)
+    ix = _build(b200, xb, ids, cent, cb, resid, chunks)
+    assert ix.ntotal == n
+    ln, codes, (off, cs, idl) = _oracle_lists(xb, ids, cent, cb, resid)
+    assert [ix.list_length(l) for l in range(nlist)] == np.diff(off).tolist()
+    for l in (0, nlist // 2, nlist - 1):
+        c, i = ix.get_list(l)
+        np.testing.assert_array_equal(c, cs[off[l]:off[l + 1]])
+        np.testing.assert_array_equal(i, idl[off[l]:off[l + 1]])
+    ix.nprobe = nprobe
+    D, I = ix.search(xq, k)
+    Dr, Ir = oracle.ivfpq_search(cent, cb, resid, off, cs, idl, xq, nprobe, k)
+    if resid:
+        assert_close_gap_aware(D, I, Dr, Ir, rtol=RESID_RTOL, what="ivfpq residual")
+        D2, I2 = oracle.ivfpq_search(cent, cb, 2, off, cs, idl, xq, nprobe, k)
+        assert_exact(D, I, D2, I2)
+    else:
+        assert_exact(D, I, Dr, Ir)
+
+
+def test_empty_lists_duplicates_and_short_results(b200):
+    d, nlist, M = 64, 32, 16
+    xb, _ = datasets.mixture(600, d, 4, seed=9)
+    xb = np.concatenate([xb, xb[:100]])          # duplicates -> identical codes -> distance ties
+    ids = np.arange(700, dtype=np.int64)[::-1].copy()
+    cent, cb = datasets.train_ivfpq(xb, nlist, M, False, niter=3)
+    cent[3] = 50.0                                # an empty, far list
+    ix = _build(b200, xb, ids, cent, cb, False)
+    ln, codes, (off, cs, idl) = _oracle_lists(xb, ids, cent, cb, False)
+    xq = xb[:40]
+    padded = False
+    for nprobe, k in ((nlist, 64), (1, 300), (2, 10)):
+        ix.nprobe = nprobe
+        D, I = ix.search(xq, k)
+        Dr, Ir = oracle.ivfpq_search(cent, cb, False, off, cs, idl, xq, nprobe, k)
+        assert_exact(D, I, Dr, Ir)
+        padded |= bool((Ir[:, -1] == -1).any())
+    assert padded                                 # nprobe=1, k=300 leaves padded tails
+
+
+def test_add_codes_reset_remove(b200):
+    d, nlist, M = 64, 16, 8
+    xb, _ = datasets.mixture(3000, d, 8, seed=21)
+    xq, _ = datasets.mixture(7, d, 8, seed=22, centers_seed=21)
+    ids = np.arange(3000, dtype=np.int64)
+    cent, cb = datasets.train_ivfpq(xb, nlist, M, True, niter=3)
+    ln, codes, (off, cs, idl) = _oracle_lists(xb, ids, cent, cb, True)
+    ix = b200.IndexIVFPQ(d, nlist, M, 8, by_residual=True)
+    ix.set_centroids(cent)
+    ix.set_codebooks(cb)
+    ix.add_codes(ln, codes, ids)                  # the copyFrom path: pre-encoded lists
+    ix.nprobe = 8
+    D, I = ix.search(xq, 10)
+    ix2 = _build(b200, xb, ids, cent, cb, True)
+    ix2.nprobe = 8
+    D2, I2 = ix2.search(xq, 10)
+    assert_exact(D, I, D2, I2)
+    # reset + re-add gives byte-identical lists (TestAscendIndexIVFPQ.cpp:118-146)
+    before = [ix2.get_list(l) for l in range(nlist)]
+    ix2.reset()
+    assert ix2.ntotal == 0
+    ix2.add_with_ids(xb, ids)
+    for l in range(nlist):
+        c, i = ix2.get_list(l)
+        np.testing.assert_array_equal(c, before[l][0])
+        np.testing.assert_array_equal(i, before[l][1])
+    assert ix.remove_ids(np.array([5, 6, 7, 99999])) == 3
+    keep = ~np.isin(ids, [5, 6, 7])
+    off2, cs2, idl2 = oracle.build_lists(ln[keep], codes[keep], ids[keep], nlist)
+    D, I = ix.search(xq, 10)
+    Dr, Ir = oracle.ivfpq_search(cent, cb, 2, off2, cs2, idl2, xq, 8, 10)
+    assert_exact(D, I, Dr, Ir)
+
+
+def test_untrained_index_is_rejected(b200):
+    ix = b200.IndexIVFPQ(64, 16, 8)
+    with pytest.raises(b200.B200IdxError) as e:
+        ix.add(datasets.gaussian(10, 64, seed=1))
+    assert e.value.code == 2001 and "not trained" in e.value.msg
