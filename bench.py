@@ -115,12 +115,37 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------
 # workload construction (untimed; torch is plumbing for data generation and training)
 # --------------------------------------------------------------------------------------
-def torch_kmeans(x, k, niter, seed):
+def farthest_first(x, k, seed):
+    """Deterministic k-means++-style seeding (farthest-first traversal): every new centre is the
+    point farthest from the centres chosen so far.  The reference exposes the same choice as
+    AscendIndexIVFConfig::useKmeansPP; with random seeding Lloyd iterations leave some mixture
+    components without a centroid and the inverted lists badly unbalanced."""
     import torch
     g = torch.Generator(device=x.device)
     g.manual_seed(seed)
     n = x.shape[0]
-    cent = x[torch.randperm(n, generator=g, device=x.device)[:k]].clone()
+    idx = int(torch.randint(0, n, (1,), generator=g, device=x.device))
+    cent = torch.empty((k, x.shape[1]), dtype=x.dtype, device=x.device)
+    xn = (x * x).sum(1)
+    mind = torch.full((n,), float("inf"), dtype=x.dtype, device=x.device)
+    sel = torch.tensor(idx, device=x.device)
+    for i in range(k):
+        c = x[sel]
+        cent[i] = c
+        mind = torch.minimum(mind, xn - 2.0 * (x @ c) + (c * c).sum())
+        sel = mind.argmax()
+    return cent
+
+
+def torch_kmeans(x, k, niter, seed, plusplus=False):
+    import torch
+    g = torch.Generator(device=x.device)
+    g.manual_seed(seed)
+    n = x.shape[0]
+    if plusplus:
+        cent = farthest_first(x, k, seed)
+    else:
+        cent = x[torch.randperm(n, generator=g, device=x.device)[:k]].clone()
     for _ in range(niter):
         cn = (cent * cent).sum(1)
         assign = torch.empty(n, dtype=torch.int64, device=x.device)
@@ -181,7 +206,7 @@ class IvfpqWorkload(Workload):
 
         t0 = time.time()
         sample = gen(4000, min(chunk, self.N))[:500_000]
-        cent = torch_kmeans(sample, self.nlist, 25, seed=41)
+        cent = torch_kmeans(sample, self.nlist, 25, seed=41, plusplus=True)
         train = sample
         if self.by_residual:
             train = sample - cent[assign_torch(sample, cent)]
@@ -210,9 +235,12 @@ class IvfpqWorkload(Workload):
         self.index = ix
         self.xq = gen(5, self.nq).cpu().pin_memory()
         self.units_bytes_per_query = self.nprobe * (self.N / self.nlist) * self.M   # algorithmic scan bytes
+        lens = np.array([ix.list_length(l) for l in range(self.nlist)], np.float64)
         self.desc = dict(workload="IVFPQ d=128 N=%d nlist=16384 M=16x8bit nprobe=64 k=10 nq=10000 "
-                                  "(Gaussian mixture, seeded k-means 25 it on 500k sample)" % self.N,
-                         by_residual=self.by_residual)
+                                  "(Gaussian mixture, seeded k-means++ init + 25 Lloyd it on 500k sample)" % self.N,
+                         by_residual=self.by_residual,
+                         list_len_mean=float(lens.mean()), list_len_max=float(lens.max()),
+                         list_len_size_biased_mean=float((lens * lens).sum() / max(lens.sum(), 1)))
 
     def roofline(self, stats, steps, peaks):
         ms = stats["stage_ms"]["scan"] / max(1, stats["stage_launches"]["scan"])
