@@ -68,6 +68,18 @@ int b200idx_search_f16(b200idx_t* h, int64_t n, const uint16_t* x, int k, float*
 int b200idx_search_device(b200idx_t* h, int64_t n, const void* x_dev, int k, float* distances_dev,
                           int64_t* labels_dev);
 
+/* Device-resident exact search that allocates nothing (no counterpart in the reference, whose
+ * operators always draw temporaries from a per-index pool).  For callers that may not allocate
+ * device memory while searching -- a process whose HBM is owned by its own pool, or a loop that
+ * cannot take the device-wide synchronisation of cudaMalloc / cudaFree.  Same kernels and same
+ * results as b200idx_search_device on a Flat or Int8Flat index, with every scratch buffer taken
+ * from one static 10 MiB device array: n * round_up(ntotal, 256) <= 2^20, k <= 1024,
+ * n * k <= 131072, n * d <= 524288; anything larger returns B200IDX_ERR_INVALID_PARAM.  Calls
+ * share that array: do not overlap two of them on one GPU.  The first call on a device resolves
+ * the array's address and should be made before any stream capture. */
+int b200idx_search_device_noalloc(b200idx_t* h, int64_t n, const void* x_dev, int k, float* distances_dev,
+                                  int64_t* labels_dev);
+
 /* ---- multi-index batch search: faiss::ascend::Search(indexes, n, x, k, D, I, merged),
  *      FR/ascend/AscendMultiIndexSearch.h:34-44, .cpp:230-324.  merged = 0: output layout
  *      [index][n][k]; merged = 1: [n][k] by (distance, label)

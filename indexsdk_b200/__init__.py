@@ -66,6 +66,7 @@ def load() -> C.CDLL:
         "b200idx_search": (i32, [vp, i64, vp, i32, vp, vp]),
         "b200idx_search_f16": (i32, [vp, i64, vp, i32, vp, vp]),
         "b200idx_search_device": (i32, [vp, i64, vp, i32, vp, vp]),
+        "b200idx_search_device_noalloc": (i32, [vp, i64, vp, i32, vp, vp]),
         "b200idx_search_multi": (i32, [pp, i32, i64, vp, i32, vp, vp, i32]),
         "b200idx_merge_topk_device": (i32, [i32, i64, i32, i32, vp, vp, vp, vp, vp]),
         "b200idx_reset": (i32, [vp]),
@@ -101,6 +102,7 @@ def load() -> C.CDLL:
 EXPORTED_SYMBOLS = [
     "b200idx_create_flat", "b200idx_create_int8flat", "b200idx_create_ivfpq", "b200idx_destroy", "b200idx_add",
     "b200idx_add_f16", "b200idx_add_device", "b200idx_search", "b200idx_search_f16", "b200idx_search_device",
+    "b200idx_search_device_noalloc",
     "b200idx_search_multi", "b200idx_merge_topk_device", "b200idx_reset", "b200idx_remove_ids", "b200idx_ntotal",
     "b200idx_dim", "b200idx_device", "b200idx_get_base", "b200idx_get_ids", "b200idx_ivfpq_set_centroids",
     "b200idx_ivfpq_set_codebooks", "b200idx_ivfpq_get_centroids", "b200idx_ivfpq_get_codebooks",
@@ -184,6 +186,12 @@ class _Index:
     def search_device(self, x_ptr: int, n: int, k: int, D_ptr: int, I_ptr: int):
         _check(self._lib.b200idx_search_device(self._h, n, C.c_void_p(x_ptr), k, C.c_void_p(D_ptr),
                                                C.c_void_p(I_ptr)), self._h)
+
+    def search_device_noalloc(self, x_ptr: int, n: int, k: int, D_ptr: int, I_ptr: int):
+        """Exact search with all scratch in the library's static device array (Flat / Int8Flat,
+        small requests only); for callers that may not allocate device memory while searching."""
+        _check(self._lib.b200idx_search_device_noalloc(self._h, n, C.c_void_p(x_ptr), k, C.c_void_p(D_ptr),
+                                                       C.c_void_p(I_ptr)), self._h)
 
     def reset(self):
         _check(self._lib.b200idx_reset(self._h), self._h)

@@ -15,7 +15,7 @@ CSRC = os.path.join(_HERE, "csrc")
 BUILD_DIR = os.path.join(_HERE, "_build")
 LIB_PATH = os.path.join(BUILD_DIR, "libb200idx.so")
 
-SOURCES = ["dist_gemm.cu", "select.cu", "flat_index.cu", "ivfpq_index.cu", "c_api.cu"]
+SOURCES = ["dist_gemm.cu", "select.cu", "flat_index.cu", "ivfpq_index.cu", "c_api.cu", "noalloc.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-O3", "--expt-relaxed-constexpr",

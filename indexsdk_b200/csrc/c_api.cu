@@ -10,6 +10,7 @@
 #include <thread>
 #include <vector>
 
+#include "c_api_internal.h"
 #include "flat_index.h"
 #include "ivfpq_index.h"
 #include "select.cuh"
@@ -100,6 +101,11 @@ bool descending_of(const b200idx_index* h) {
 }
 
 }  // namespace
+
+namespace b200_capi {
+int guarded(const b200idx_t* h, const std::function<void()>& f) { return ::guarded(h, f); }
+b200::FlatIndex* flat_of(b200idx_t* h) { return (h && h->kind != 2) ? h->flat.get() : nullptr; }
+}  // namespace b200_capi
 
 extern "C" {
 

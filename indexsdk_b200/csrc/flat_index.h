@@ -123,6 +123,24 @@ public:
     // Raw access for composite indexes (IVFPQ coarse quantizer).
     const float* rows_f32() const { return x32_.as<float>(); }
 
+    // Read-only view of the stored arrays (device pointers) for entry points that bring their
+    // own scratch memory.
+    struct RawView {
+        const void* operand;     // bf16 (kF32), fp16 (kF16) or int8 (kI8) rows
+        const float* rows_f32;   // kF32 only
+        const void* norms;       // float or int32 squared norms
+        const int64_t* labels;
+        int64_t n;
+        float max_norm;
+        int num_sms;
+        bool use_simt;
+    };
+    RawView raw_view() const {
+        return RawView{xop_.get(), x32_.as<float>(), norms_.get(), labels_.as<int64_t>(), n_, max_norm_, num_sms_,
+                       use_simt_};
+    }
+    int gemm_kind_public() const { return gemm_kind(); }
+
 private:
     struct Plan {
         bool sampled;
