@@ -1,14 +1,15 @@
 // tcgen05 / TMEM / TMA distance GEMM with fused selection epilogues, plus a plain CUDA-core
 // variant that shares the epilogue code and serves as an on-device cross-check.
 //
-// Pipeline of the tcgen05 variant (one persistent CTA per SM, 192 threads):
+// Pipeline of the tcgen05 variant (one persistent CTA per SM, 320 threads):
 //   warp 0 (one lane)  : TMA producer.  Per K chunk of 128 bytes: query box 128 x 128 B and base
 //                        box 256 x 128 B into a 4-stage ring of 48 KB stages (SWIZZLE_128B).
 //   warp 1 (one lane)  : issues tcgen05.mma 128 x 256 x (32 bytes of K) from shared-memory
 //                        descriptors into one of two 256-column TMEM accumulators; commits free
 //                        the stage (per chunk) and publish the accumulator (per tile).
-//   warps 2-5          : epilogue.  Thread = query row = TMEM lane; reads 32 columns at a time
-//                        with tcgen05.ld and applies the norm-add and the selection predicate.
+//   warps 2-9          : epilogue, two warps per scheduler.  Thread = (query row = TMEM lane, one
+//                        half of the tile's columns); reads 32 columns at a time with tcgen05.ld
+//                        (double-buffered) and applies the norm-add and the selection predicate.
 // Work items are (query block, base tile) pairs, query block fastest, so the CTAs running at
 // the same time read the same base tiles and HBM sees each base tile about once per pass.
 #include "dist_gemm.cuh"
@@ -29,7 +30,9 @@ constexpr int kStageABytes = kTileQ * kChunkBytes;               // 16 KB
 constexpr int kStageBBytes = kTileB * kChunkBytes;               // 32 KB
 constexpr int kStageBytes = kStageABytes + kStageBBytes;         // 48 KB
 constexpr int kGemmSmemBytes = kStages * kStageBytes + 1024;     // + slack for 1024-byte alignment
-constexpr int kGemmThreads = 192;
+constexpr int kEpiWarps = 8;                                    // two per scheduler; pairs split the tile's columns
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kGemmThreads = 64 + kEpiThreads;                   // producer warp + MMA warp + epilogue warps
 constexpr uint32_t kTmemCols = 512;
 
 template <typename AccT>
@@ -42,6 +45,16 @@ struct KeyOps<float> {
     static __device__ __forceinline__ uint32_t ord(float k) { return float_to_ord(k); }
     static __device__ __forceinline__ float tau(uint32_t o) { return ord_to_float(o); }
     static __device__ __forceinline__ float worst() { return __int_as_float(0x7f800000); }
+    // smallest value strictly above t (t itself when t = +inf): key <= t  <=>  key - above(t) < 0
+    static __device__ __forceinline__ float above(float t) {
+        return t == __int_as_float(0x7f800000) ? t : ord_to_float(float_to_ord(t) + 1u);
+    }
+    // sign word of (l2 ? bn - 2 acc : -acc) - tup
+    static __device__ __forceinline__ uint32_t sign_l2(float acc, float bn, float tup) {
+        return __float_as_uint(fmaf(-2.f, acc, bn) - tup);
+    }
+    static __device__ __forceinline__ uint32_t sign_ip(float acc, float ntup) { return __float_as_uint(ntup - acc); }
+    static __device__ __forceinline__ float neg(float v) { return -v; }
 };
 template <>
 struct KeyOps<int32_t> {
@@ -51,64 +64,166 @@ struct KeyOps<int32_t> {
     static __device__ __forceinline__ uint32_t ord(int32_t k) { return int_to_ord(k); }
     static __device__ __forceinline__ int32_t tau(uint32_t o) { return ord_to_int(o); }
     static __device__ __forceinline__ int32_t worst() { return 0x7fffffff; }
+    static __device__ __forceinline__ int32_t above(int32_t t) { return t == 0x7fffffff ? t : t + 1; }
+    static __device__ __forceinline__ uint32_t sign_l2(int32_t acc, int32_t bn, int32_t tup) {
+        return static_cast<uint32_t>(bn - 2 * acc - tup);
+    }
+    static __device__ __forceinline__ uint32_t sign_ip(int32_t acc, int32_t ntup) {
+        return static_cast<uint32_t>(ntup - acc);
+    }
+    static __device__ __forceinline__ int32_t neg(int32_t v) { return -v; }
 };
 
-// Consumes 32 consecutive accumulator columns of one query row.
-//   r       : raw 32-bit accumulators (float or int32 bit patterns)
-//   q       : query row (caller guarantees q < nq)
-//   col0    : base position of r[0]; nvalid: how many of the 32 columns are real base rows
-//   bslot   : first burst slot of this chunk inside the row's mins[] segment (kModeBurstMin)
+constexpr int kStageSlots = 8;   // per-row candidate staging slots per tile (shared memory)
+
+// Shared-memory side of the epilogue: the tile's base norms (double-buffered with the TMEM
+// accumulators) and a per-row staging area for candidates found in the current tile.
+struct EpiShared {
+    uint32_t norm[2][kTileB];
+    uint64_t stage[kStageSlots][2 * kTileQ];   // one column of slots per epilogue thread
+};
+
+// Per-thread (= per query row) epilogue state for one tile.
+//   append mode : candidates of the tile are staged in shared memory (thread-private slots, no
+//                 atomics) and flushed with ONE global atomicAdd per row per tile, so the
+//                 latency of the L2 atomic is paid once per tile instead of once per candidate.
+//   direct mode : every key is written to cand[q][position] (no threshold, no atomics).
 template <typename AccT, int MODE, int BURST>
-__device__ __forceinline__ void epilogue_chunk(const GemmArgs& a, const uint32_t (&r)[32], int q, int64_t col0,
-                                               int nvalid, int bslot, AccT tau) {
+struct RowEpilogue {
     using K = KeyOps<AccT>;
-    using Norm = typename K::Norm;
-    const bool l2 = a.metric == kMetricL2;
-    Norm bn[32];
-    if (l2) {
-        const uint4* p = reinterpret_cast<const uint4*>(static_cast<const Norm*>(a.bnorm) + col0);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            uint4 v = __ldg(p + j);
-            bn[4 * j + 0] = K::from_bits(v.x);
-            bn[4 * j + 1] = K::from_bits(v.y);
-            bn[4 * j + 2] = K::from_bits(v.z);
-            bn[4 * j + 3] = K::from_bits(v.w);
-        }
-    } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) bn[j] = Norm(0);
-    }
-    if (MODE == kModeBurstMin) {
-        constexpr int NB = 32 / BURST;
-        uint32_t out[NB];
-#pragma unroll
-        for (int b = 0; b < NB; ++b) {
-            AccT m = K::worst();
-#pragma unroll
-            for (int j = 0; j < BURST; ++j) {
-                const int c = b * BURST + j;
-                AccT key = K::key(K::from_bits(r[c]), bn[c], l2);
-                if (c < nvalid) m = key < m ? key : m;
-            }
-            out[b] = K::ord(m);
-        }
-        uint32_t* dst = a.mins + static_cast<int64_t>(q) * a.mins_stride + bslot;
-#pragma unroll
-        for (int b = 0; b < NB; ++b) dst[b] = out[b];
-    } else {
-        uint64_t* crow = a.cand + static_cast<int64_t>(q) * a.cap;
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-            AccT key = K::key(K::from_bits(r[c]), bn[c], l2);
-            if (key <= tau && c < nvalid) {
-                const uint32_t pos = static_cast<uint32_t>(col0 + c);
-                uint32_t slot = a.direct ? pos : atomicAdd(a.counts + q, 1u);
-                if (slot < a.cap) crow[slot] = pack_cand(K::ord(key), pos);
-            }
+    const GemmArgs& a;
+    EpiShared& sh;
+    int q;        // query row, valid when row_ok
+    int tid;      // row inside the tile, 0..127
+    bool row_ok;
+    bool l2;
+    AccT tau, tau_up;
+    uint32_t cnt;
+
+    // tid_: index of this thread's private staging column
+    __device__ __forceinline__ RowEpilogue(const GemmArgs& a_, EpiShared& sh_, int tid_)
+        : a(a_), sh(sh_), q(0), tid(tid_), row_ok(false), l2(a_.metric == kMetricL2), tau(AccT(0)),
+          tau_up(AccT(0)), cnt(0) {}
+
+    __device__ __forceinline__ void begin_tile(int q_, bool ok) {
+        q = q_;
+        row_ok = ok;
+        cnt = 0;
+        if (MODE == kModeAppend && ok) {
+            tau = K::tau(__ldg(a.tau + q));
+            tau_up = K::above(tau);
         }
     }
-}
+
+    __device__ __forceinline__ void slow_append(uint64_t e) {
+        const uint32_t slot = atomicAdd(a.counts + q, 1u);
+        if (slot < a.cap) a.cand[static_cast<int64_t>(q) * a.cap + slot] = e;
+    }
+
+    // Value of r[c] for a run-time c without indexing registers dynamically (select tree).
+    static __device__ __forceinline__ uint32_t pick(const uint32_t (&r)[32], uint32_t c) {
+        uint32_t v16[16], v8[8], v4[4], v2[2];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v16[i] = (c & 16u) ? r[16 + i] : r[i];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v8[i] = (c & 8u) ? v16[8 + i] : v16[i];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v4[i] = (c & 4u) ? v8[4 + i] : v8[i];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) v2[i] = (c & 2u) ? v4[2 + i] : v4[i];
+        return (c & 1u) ? v2[1] : v2[0];
+    }
+
+    // r: 32 accumulator columns; nb: the matching 32 norms in shared memory; col0: base position
+    // of r[0]; nvalid: real base rows among the 32; bslot: first burst slot (burst-min mode).
+    // The hot path is straight-line code: the threshold test of the 32 columns is folded into a
+    // bit mask, and only a non-zero mask (rare) enters the compact candidate loop.
+    __device__ __forceinline__ void chunk(const uint32_t (&r)[32], const uint32_t* nb, int64_t col0, int nvalid,
+                                          int bslot) {
+        if (!row_ok) return;
+        uint32_t bnb[32];
+        if (l2) {
+            const uint4* p = reinterpret_cast<const uint4*>(nb);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint4 v = p[j];
+                bnb[4 * j + 0] = v.x;
+                bnb[4 * j + 1] = v.y;
+                bnb[4 * j + 2] = v.z;
+                bnb[4 * j + 3] = v.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) bnb[j] = 0u;   // +0.0f / 0
+        }
+        const uint32_t valid = nvalid >= 32 ? 0xFFFFFFFFu : ((1u << nvalid) - 1u);
+        if (MODE == kModeBurstMin) {
+            constexpr int NB = 32 / BURST;
+            uint32_t* dst = a.mins + static_cast<int64_t>(q) * a.mins_stride + bslot;
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                AccT m[4] = {K::worst(), K::worst(), K::worst(), K::worst()};   // independent chains
+#pragma unroll
+                for (int j = 0; j < BURST; ++j) {
+                    const int c = b * BURST + j;
+                    const AccT key = K::key(K::from_bits(r[c]), K::from_bits(bnb[c]), l2);
+                    if ((valid >> c) & 1u) m[j & 3] = key < m[j & 3] ? key : m[j & 3];
+                }
+                const AccT ma = m[0] < m[1] ? m[0] : m[1], mb = m[2] < m[3] ? m[2] : m[3];
+                dst[b] = K::ord(ma < mb ? ma : mb);
+            }
+        } else if (a.direct) {
+            uint64_t* crow = a.cand + static_cast<int64_t>(q) * a.cap + col0;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                const AccT key = K::key(K::from_bits(r[c]), K::from_bits(bnb[c]), l2);
+                // NaN keys are left at the buffer's "invalid" fill
+                if (((valid >> c) & 1u) && key <= tau) crow[c] = pack_cand(K::ord(key), static_cast<uint32_t>(col0 + c));
+            }
+        } else {
+            // bit (31 - c) of mask = "column c passes": the sign of key - above(tau), shifted in
+            // with one funnel shift per column (two independent chains for the scheduler).
+            uint32_t m0 = 0, m1 = 0;
+            if (l2) {
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    m0 = __funnelshift_l(K::sign_l2(K::from_bits(r[c]), K::from_bits(bnb[c]), tau_up), m0, 1);
+                    m1 = __funnelshift_l(K::sign_l2(K::from_bits(r[16 + c]), K::from_bits(bnb[16 + c]), tau_up), m1, 1);
+                }
+            } else {
+                const AccT ntup = K::neg(tau_up);
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    m0 = __funnelshift_l(K::sign_ip(K::from_bits(r[c]), ntup), m0, 1);
+                    m1 = __funnelshift_l(K::sign_ip(K::from_bits(r[16 + c]), ntup), m1, 1);
+                }
+            }
+            uint32_t mask = (m0 << 16) | (m1 & 0xFFFFu);
+            mask &= nvalid >= 32 ? 0xFFFFFFFFu : ~(0xFFFFFFFFu >> nvalid);
+            while (mask) {
+                const uint32_t c = __clz(mask);
+                mask &= ~(0x80000000u >> c);
+                const AccT key = K::key(K::from_bits(pick(r, c)), K::from_bits(pick(bnb, c)), l2);
+                if (!(key <= tau)) continue;   // NaN
+                const uint64_t e = pack_cand(K::ord(key), static_cast<uint32_t>(col0 + c));
+                if (cnt < kStageSlots) sh.stage[cnt][tid] = e;
+                else slow_append(e);
+                ++cnt;
+            }
+        }
+    }
+
+    __device__ __forceinline__ void end_tile() {
+        if (MODE != kModeAppend || !row_ok || a.direct) return;
+        const uint32_t n_st = cnt < kStageSlots ? cnt : kStageSlots;
+        if (n_st) {
+            const uint32_t slot0 = atomicAdd(a.counts + q, n_st);
+            uint64_t* crow = a.cand + static_cast<int64_t>(q) * a.cap;
+            for (uint32_t i = 0; i < n_st; ++i)
+                if (slot0 + i < a.cap) crow[slot0 + i] = sh.stage[i][tid];
+        }
+    }
+};
 
 __device__ __forceinline__ int tile_of(const GemmArgs& a, int sel) {
     return static_cast<int>(static_cast<int64_t>(sel) * a.n_tiles_total / a.n_tiles_sel);
@@ -134,6 +249,7 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     __shared__ uint64_t bar_acc_empty[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
+    __shared__ __align__(16) EpiShared epi_sh;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -146,7 +262,7 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(&bar_acc_full[b], 1);
-            ptx::mbar_init(&bar_acc_empty[b], 4);
+            ptx::mbar_init(&bar_acc_empty[b], kEpiWarps);
         }
         abort_flag = 0;
         ptx::mbar_fence_init();
@@ -170,34 +286,47 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
+            long long pw = 0;
+            const long long k0 = a.prof ? clock64() : 0;
             for (int64_t item = blockIdx.x; item < total && ok; item += gridDim.x) {
                 const int qb = static_cast<int>(item % n_qb);
                 const int tile = tile_of(a, static_cast<int>(item / n_qb));
                 for (int kc = 0; kc < nkc; ++kc, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1u;
+                    const long long w0 = a.prof ? clock64() : 0;
                     if (!ptx::mbar_wait_bounded(&bar_empty[s], ph ^ 1u, &abort_flag)) { ok = false; break; }
+                    if (a.prof) pw += clock64() - w0;
                     ptx::mbar_expect_tx(&bar_full[s], kStageBytes);
                     uint8_t* sa = smem + s * kStageBytes;
                     ptx::tma_load_2d(sa, &mapA, &bar_full[s], kc * kChunkElems, qb * kTileQ);
                     ptx::tma_load_2d(sa + kStageABytes, &mapB, &bar_full[s], kc * kChunkElems, tile * kTileB);
                 }
             }
+            if (a.prof) {
+                atomicAdd(a.prof + 0, static_cast<unsigned long long>(pw));
+                atomicAdd(a.prof + 7, static_cast<unsigned long long>(clock64() - k0));
+            }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             uint32_t it = 0, t = 0;
             bool ok = true;
+            long long mw0 = 0, mw1 = 0;
             for (int64_t item = blockIdx.x; item < total && ok; item += gridDim.x, ++t) {
                 const uint32_t ab = t & 1u;
                 const uint32_t aph = (t >> 1) & 1u;
+                long long w0 = a.prof ? clock64() : 0;
                 if (!ptx::mbar_wait_bounded(&bar_acc_empty[ab], aph ^ 1u, &abort_flag)) { ok = false; break; }
+                if (a.prof) mw0 += clock64() - w0;
                 ptx::tc_fence_after();
                 const uint32_t tacc = tmem_base + ab * kTileB;
                 for (int kc = 0; kc < nkc; ++kc, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1u;
+                    w0 = a.prof ? clock64() : 0;
                     if (!ptx::mbar_wait_bounded(&bar_full[s], ph, &abort_flag)) { ok = false; break; }
+                    if (a.prof) mw1 += clock64() - w0;
                     ptx::tc_fence_after();
                     const uint32_t sa = ptx::smem_u32(smem + s * kStageBytes);
                     const uint32_t sb = sa + kStageABytes;
@@ -213,12 +342,24 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 }
                 if (ok) ptx::umma_commit(&bar_acc_full[ab]);
             }
+            if (a.prof) {
+                atomicAdd(a.prof + 1, static_cast<unsigned long long>(mw0));
+                atomicAdd(a.prof + 2, static_cast<unsigned long long>(mw1));
+            }
         }
     } else {
-        const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+        const int quarter = warp & 3;          // TMEM lane quarter this warp may read
+        const int half = (warp - 2) >> 2;      // which 128 columns of the tile this warp drains
         const int row_in_tile = quarter * 32 + lane;
+        const int et = threadIdx.x - 64;       // epilogue thread index, 0..255
+        constexpr int kCols = kTileB / 2;      // columns per epilogue thread
+        RowEpilogue<AccT, MODE, BURST> epi(a, epi_sh, et);
+        const bool l2 = a.metric == kMetricL2;
+        const uint32_t* gnorm = static_cast<const uint32_t*>(a.bnorm);
         uint32_t t = 0;
         bool ok = true;
+        long long ew = 0, ec = 0, ef = 0, elw = 0, ebar = 0, ecc = 0;
+        const bool profiler = a.prof && warp == 2 && lane == 0;
         for (int64_t item = blockIdx.x; item < total && ok; item += gridDim.x, ++t) {
             const int qb = static_cast<int>(item % n_qb);
             const int sel = static_cast<int>(item / n_qb);
@@ -226,29 +367,77 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             const uint32_t ab = t & 1u;
             const uint32_t aph = (t >> 1) & 1u;
             const int q = qb * kTileQ + row_in_tile;
-            const bool row_ok = q < a.nq;
-            AccT tau = AccT(0);
-            if (MODE == kModeAppend && row_ok) tau = KeyOps<AccT>::tau(__ldg(a.tau + q));
-            if (!ptx::mbar_wait_bounded(&bar_acc_full[ab], aph, &abort_flag)) { ok = false; break; }
-            ptx::tc_fence_after();
-            const uint32_t tacc = tmem_base + ab * kTileB + (static_cast<uint32_t>(quarter * 32) << 16);
             const int64_t tile_col0 = static_cast<int64_t>(tile) * kTileB;
+            const long long e0 = profiler ? clock64() : 0;
+            // The tile's norms travel global -> registers while the MMA is still running.
+            uint32_t n0 = 0;
+            if (l2) n0 = __ldg(gnorm + tile_col0 + et);
+            epi.begin_tile(q, q < a.nq);
+            if (!ptx::mbar_wait_bounded(&bar_acc_full[ab], aph, &abort_flag)) {
+                // leave without stranding a sibling warp at the named barrier below
+                asm volatile("bar.arrive 1, 256;" ::: "memory");
+                ok = false;
+                break;
+            }
+            const long long e1 = profiler ? clock64() : 0;
+            ptx::tc_fence_after();
+            epi_sh.norm[ab][et] = n0;
+            const long long b0 = profiler ? clock64() : 0;
+            asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight epilogue warps
+            if (profiler) ebar += clock64() - b0;
+            const uint32_t tacc =
+                tmem_base + ab * kTileB + half * kCols + (static_cast<uint32_t>(quarter * 32) << 16);
+            const int64_t half_col0 = tile_col0 + half * kCols;
+            const uint32_t* hnorm = &epi_sh.norm[ab][half * kCols];
+            const int hslot = sel * (kTileB / BURST) + half * (kCols / BURST);
+            uint32_t ra[32], rb[32];
+            ptx::tmem_ld_32x32(tacc, ra);
 #pragma unroll 1
-            for (int c = 0; c < kTileB / 32; ++c) {
-                uint32_t r[32];
-                ptx::tmem_ld_32x32(tacc + c * 32, r);
-                ptx::tmem_ld_wait();
-                const int64_t col0 = tile_col0 + c * 32;
-                int64_t rem = a.N - col0;
-                const int nvalid = rem >= 32 ? 32 : (rem > 0 ? static_cast<int>(rem) : 0);
-                if (row_ok && (nvalid > 0 || MODE == kModeBurstMin)) {
-                    const int bslot = sel * (kTileB / BURST) + c * (32 / BURST);
-                    epilogue_chunk<AccT, MODE, BURST>(a, r, q, col0, nvalid, bslot, tau);
+            for (int c = 0; c < kCols / 32; c += 2) {
+                const long long w0 = profiler ? clock64() : 0;
+                ptx::tmem_ld_wait(ra);
+                if (profiler) elw += clock64() - w0;
+                ptx::tmem_ld_32x32(tacc + (c + 1) * 32, rb);
+                {
+                    const long long c0 = profiler ? clock64() : 0;
+                    const int64_t col0 = half_col0 + c * 32;
+                    const int64_t rem = a.N - col0;
+                    epi.chunk(ra, hnorm + c * 32, col0, rem >= 32 ? 32 : (rem > 0 ? static_cast<int>(rem) : 0),
+                              hslot + c * (32 / BURST));
+                    if (profiler) ecc += clock64() - c0;
+                }
+                const long long w1 = profiler ? clock64() : 0;
+                ptx::tmem_ld_wait(rb);
+                if (profiler) elw += clock64() - w1;
+                if (c + 2 < kCols / 32) ptx::tmem_ld_32x32(tacc + (c + 2) * 32, ra);
+                {
+                    const int64_t col0 = half_col0 + (c + 1) * 32;
+                    const int64_t rem = a.N - col0;
+                    epi.chunk(rb, hnorm + (c + 1) * 32, col0, rem >= 32 ? 32 : (rem > 0 ? static_cast<int>(rem) : 0),
+                              hslot + (c + 1) * (32 / BURST));
                 }
             }
+            // accumulator drained: hand the TMEM buffer back before the global flush
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&bar_acc_empty[ab]);
+            const long long e2 = profiler ? clock64() : 0;
+            epi.end_tile();
+            if (profiler) {
+                const long long e3 = clock64();
+                ew += e1 - e0;
+                ec += e2 - e1;
+                ef += e3 - e2;
+            }
+        }
+        if (profiler) {
+            atomicAdd(a.prof + 3, static_cast<unsigned long long>(ew));
+            atomicAdd(a.prof + 4, static_cast<unsigned long long>(ec));
+            atomicAdd(a.prof + 5, static_cast<unsigned long long>(ef));
+            atomicAdd(a.prof + 6, static_cast<unsigned long long>(t));
+            atomicAdd(a.prof + 8, static_cast<unsigned long long>(elw));
+            atomicAdd(a.prof + 9, static_cast<unsigned long long>(ebar));
+            atomicAdd(a.prof + 10, static_cast<unsigned long long>(ecc));
         }
     }
 
@@ -284,8 +473,12 @@ template <int KIND, int MODE, int BURST>
 __global__ void __launch_bounds__(kTileQ)
 dist_gemm_simt_kernel(const GemmArgs a) {
     using AccT = typename std::conditional<KIND == kKindI8, int32_t, float>::type;
+    __shared__ __align__(16) EpiShared epi_sh;
     const int n_qb = (a.nq + kTileQ - 1) / kTileQ;
     const int64_t total = static_cast<int64_t>(n_qb) * a.n_tiles_sel;
+    const bool l2 = a.metric == kMetricL2;
+    const uint32_t* gnorm = static_cast<const uint32_t*>(a.bnorm);
+    RowEpilogue<AccT, MODE, BURST> epi(a, epi_sh, threadIdx.x);
     for (int64_t item = blockIdx.x; item < total; item += gridDim.x) {
         const int qb = static_cast<int>(item % n_qb);
         const int sel = static_cast<int>(item / n_qb);
@@ -293,10 +486,14 @@ dist_gemm_simt_kernel(const GemmArgs a) {
         const int q = qb * kTileQ + threadIdx.x;
         const bool row_ok = q < a.nq;
         const int qc = row_ok ? q : a.nq - 1;
-        AccT tau = AccT(0);
-        if (MODE == kModeAppend && row_ok) tau = KeyOps<AccT>::tau(__ldg(a.tau + q));
+        const int64_t tile_col0 = static_cast<int64_t>(tile) * kTileB;
+        __syncthreads();
+        epi_sh.norm[0][threadIdx.x] = l2 ? __ldg(gnorm + tile_col0 + threadIdx.x) : 0u;
+        epi_sh.norm[0][kTileQ + threadIdx.x] = l2 ? __ldg(gnorm + tile_col0 + kTileQ + threadIdx.x) : 0u;
+        __syncthreads();
+        epi.begin_tile(q, row_ok);
         for (int c = 0; c < kTileB / 32; ++c) {
-            const int64_t col0 = static_cast<int64_t>(tile) * kTileB + c * 32;
+            const int64_t col0 = tile_col0 + c * 32;
             int64_t rem = a.N - col0;
             const int nvalid = rem >= 32 ? 32 : (rem > 0 ? static_cast<int>(rem) : 0);
             uint32_t r[32];
@@ -309,11 +506,10 @@ dist_gemm_simt_kernel(const GemmArgs a) {
                 if (KIND == kKindI8) r[j] = static_cast<uint32_t>(acc);
                 else r[j] = __float_as_uint(acc);
             }
-            if (row_ok && (nvalid > 0 || MODE == kModeBurstMin)) {
-                const int bslot = sel * (kTileB / BURST) + c * (32 / BURST);
-                epilogue_chunk<AccT, MODE, BURST>(a, r, q, col0, nvalid, bslot, tau);
-            }
+            const int bslot = sel * (kTileB / BURST) + c * (32 / BURST);
+            epi.chunk(r, &epi_sh.norm[0][c * 32], col0, nvalid, bslot);
         }
+        epi.end_tile();
     }
 }
 

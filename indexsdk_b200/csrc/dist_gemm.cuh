@@ -40,6 +40,10 @@ struct GemmArgs {
     uint32_t cap;
     int direct;           // 1: slot = position (cap >= N, no atomics); 0: slot = atomic counter
     int* err;             // device error word
+    // optional phase profile (nullptr = off): 8 counters of SM cycles summed over CTAs
+    //   0 producer wait-empty   1 mma wait-acc-empty   2 mma wait-full   3 epilogue wait-acc-full
+    //   4 epilogue chunks       5 epilogue flush       6 items           7 total kernel cycles (per CTA, summed)
+    unsigned long long* prof;
 };
 
 struct GemmLaunch {

@@ -1,6 +1,7 @@
 #include "flat_index.h"
 
 #include <algorithm>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <unordered_set>
@@ -44,6 +45,11 @@ FlatIndex::FlatIndex(int d, int metric, int dtype, int device)
     B200_CUDA_CHECK(cudaDeviceGetAttribute(&num_sms_, cudaDevAttrMultiProcessorCount, device_));
     B200_CUDA_CHECK(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
     use_simt_ = env_flag("B200IDX_GEMM", "simt");
+    prof_ = env_flag("B200IDX_PROF", "1");   // development aid: per-role cycle counters of the GEMM kernel
+    if (prof_) {
+        w_prof_.ensure(32 * 8);
+        B200_CUDA_CHECK(cudaMemset(w_prof_.get(), 0, 32 * 8));
+    }
     w_err_.ensure(sizeof(int));
     B200_CUDA_CHECK(cudaMemset(w_err_.get(), 0, sizeof(int)));
     maxnorm_.ensure(sizeof(float));
@@ -280,6 +286,7 @@ void FlatIndex::run_page(int nq, const void* xq_raw, const void* xq_op_in, int k
     a.metric = metric_;
     a.bnorm = norms_.get();
     a.err = w_err_.as<int>();
+    a.prof = nullptr;
     GemmLaunch L{};
     L.kind = kind;
     L.simt = use_simt_ ? 1 : 0;
@@ -298,6 +305,7 @@ void FlatIndex::run_page(int nq, const void* xq_raw, const void* xq_op_in, int k
         a.mins_stride = stride;
         L.mode = kModeBurstMin;
         L.burst = plan.burst;
+        a.prof = prof_ ? w_prof_.as<unsigned long long>() : nullptr;
         B200_CUDA_CHECK(launch_dist_gemm(L, a, &map_a, &map_b_, stream_));
         B200_CUDA_CHECK(launch_kth_threshold(mins, stride, stride, nq, k, eps, tau_all, tau, stream_));
         B200_CUDA_CHECK(cudaMemsetAsync(counts, 0, static_cast<size_t>(nq) * 4, stream_));
@@ -320,6 +328,7 @@ void FlatIndex::run_page(int nq, const void* xq_raw, const void* xq_op_in, int k
     a.cap = plan.cap;
     L.mode = kModeAppend;
     L.burst = 32;
+    a.prof = prof_ ? w_prof_.as<unsigned long long>() + 16 : nullptr;
     B200_CUDA_CHECK(launch_dist_gemm(L, a, &map_a, &map_b_, stream_));
     stats_.gemm_launches += 1;
     stats_.kernel_launches += 1;
@@ -399,6 +408,19 @@ void FlatIndex::search_device(int64_t nq, const void* xq, bool q_is_f16, int k, 
         B200_CUDA_CHECK(cudaMemcpyAsync(h + nqp, w_err_.get(), sizeof(int), cudaMemcpyDeviceToHost, stream_));
         B200_CUDA_CHECK(cudaStreamSynchronize(stream_));
         timer_.collect(stats_);
+        if (prof_) {
+            unsigned long long pc[32];
+            cudaMemcpy(pc, w_prof_.get(), sizeof(pc), cudaMemcpyDeviceToHost);
+            cudaMemset(w_prof_.get(), 0, sizeof(pc));
+            for (int p = 0; p < 2; ++p) {
+                const unsigned long long* c = pc + 16 * p;
+                const double items = c[6] ? static_cast<double>(c[6]) : 1.0;
+                fprintf(stderr, "[b200idx prof] %s pass: items %.0f per-item cycles: prod_wait_empty %.0f mma_wait_acc_empty %.0f "
+                                "mma_wait_full %.0f | epi: wait_acc_full %.0f span %.0f (barrier %.0f, tmem_wait %.0f, first-of-2 chunk calls %.0f) flush %.0f | CTA total %.0f\n",
+                        p ? "append" : "sample", items, c[0] / items, c[1] / items, c[2] / items, c[3] / items,
+                        c[4] / items, c[9] / items, c[8] / items, c[10] / items, c[5] / items, c[7] / items);
+            }
+        }
         int err = 0;
         std::memcpy(&err, h + nqp, sizeof(int));
         if (err) {

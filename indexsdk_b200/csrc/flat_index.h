@@ -174,7 +174,8 @@ private:
 
     // scratch
     DeviceBuffer w_qop_, w_qraw_, w_qnorm_, w_eps_, w_mins_, w_tau_, w_cand_, w_counts_, w_sel_, w_over_, w_qmap_,
-        w_err_, w_stage_in_, w_stage_D_, w_stage_I_, w_fb_q_, w_fb_qop_;
+        w_err_, w_stage_in_, w_stage_D_, w_stage_I_, w_fb_q_, w_fb_qop_, w_prof_;
+    bool prof_ = false;
     PinnedBuffer h_over_, h_in_, h_D_, h_I_;
     SearchStats stats_;
     StageTimer timer_;

@@ -147,6 +147,7 @@ extern "C" int b200idx_search_device_noalloc(b200idx_t* h, int64_t n, const void
         a.cap = cap;
         a.direct = 1;
         a.err = err;
+        a.prof = nullptr;
         GemmLaunch L{};
         L.kind = kind;
         L.mode = kModeAppend;
