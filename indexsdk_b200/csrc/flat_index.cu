@@ -207,7 +207,16 @@ FlatIndex::Plan FlatIndex::make_plan(int k) const {
     const int64_t n_tiles = (n_ + kTileB - 1) / kTileB;
     const int64_t need = std::max<int64_t>(4LL * k, 1024);
     p.sampled = false;
+    if (n_tiles <= 256 && n_tiles >= 8 && need <= n_tiles * (kTileB / 8)) {
+        // Small base (e.g. an IVF coarse quantizer): the "sample" is the whole base with bursts
+        // of 8.  A second cheap GEMM pass buys a threshold that admits ~k candidates instead of
+        // ~k / fraction, which is what the refinement and selection kernels pay for.
+        p.sampled = true;
+        p.burst = 8;
+        p.s_tiles = static_cast<int>(n_tiles);
+    }
     for (int burst : {32, 8}) {
+        if (p.sampled) break;
         const int bpt = kTileB / burst;
         const int64_t s = std::max<int64_t>((n_tiles + 15) / 16, (need + bpt - 1) / bpt);
         if (s * 2 <= n_tiles) {
@@ -221,7 +230,7 @@ FlatIndex::Plan FlatIndex::make_plan(int k) const {
     if (p.sampled) {
         const double inv_f = static_cast<double>(n_tiles) / p.s_tiles;
         uint64_t want = static_cast<uint64_t>(4.0 * k * inv_f);
-        p.cap = pow2_ceil(std::max<uint64_t>(2048, want));
+        p.cap = pow2_ceil(std::max<uint64_t>(p.s_tiles == n_tiles ? 512 : 2048, want));
         if (p.cap >= static_cast<uint64_t>(n_pad)) p.sampled = false;
     }
     if (!p.sampled) {

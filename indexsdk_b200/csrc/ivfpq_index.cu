@@ -7,22 +7,37 @@
 // Stage 2  lookup tables, one [M][256] fp32 table per query (replaces
 //          AscendcIvfpqSubspaceDistance, FR/ops/ascendc/op_kernel/
 //          ascendc_ivfpq_subspace_distance.cpp:46-617).
-//            raw encoding      : LUT[m][j] = |q_m - cb[m][j]|^2
-//            residual encoding : LUT[m][j] = -2 q_m . cb[m][j]; the list-dependent remainder
+//            raw encoding      : T[m][j] = |q_m - cb[m][j]|^2
+//            residual encoding : T[m][j] = -2 q_m . cb[m][j]; the list-dependent remainder
 //              |cb|^2 + 2 c_list . cb is summed over a vector's codes once, at add time, into one
-//              float per vector (t2), and |q - c_list|^2 is the coarse distance.  The distance
-//              |q - c - r|^2 = |q - c|^2 + (|r|^2 + 2 c.r) - 2 q.r is the same decomposition Faiss
-//              uses for its precomputed tables, with the per-list table folded per vector.
+//              float per vector (t2), and |q - c_list|^2 is the coarse distance:
+//              |q - c - r|^2 = |q - c|^2 + (|r|^2 + 2 c.r) - 2 q.r.
 // Stage 3  code scan (replaces AscendcIvfpqSearchDistanceL2 + TopkIvfpqL3, FR/ops/ascendc/
 //          op_kernel/ascendc_ivfpq_search_distance_topk.h:95-810, FR/ops/cpukernel/impl/
-//          topk_ivfpq_l3_cpu_kernel.cpp:36-254): one CTA per (query, probe split); the query's
-//          table sits in shared memory; each warp streams the codes of its probed lists with
-//          128-bit coalesced loads (one vector per lane), sums M table entries in fp32 in
-//          ascending m, and keeps a sorted top-k distributed over the warp's registers; the four
-//          warp lists are merged by a shared-memory bitonic sort.
+//          topk_ivfpq_l3_cpu_kernel.cpp:36-254) as filter + exact refinement:
+//            3a  ivfpq_fast_scan_kernel: CTA per (query, probe split), the query's table in shared
+//                memory laid out [code][32] (sub-quantizer in the bank index, two replicas) so
+//                that lane l, which handles sub-quantizer (s + l) mod 16 at step s, always hits
+//                bank l -- no bank conflicts.  Codes are stored rotated by (position mod 16), so
+//                byte s of a lane's 128-bit load is exactly the sub-quantizer it needs at step s.
+//                The fp32 sum therefore runs in a rotated order; it is used as a FILTER: each warp
+//                keeps the k' = 32 * KPT best (approximate distance, position) in registers.
+//            3b  ivfpq_refine_kernel: the k' survivors per query are re-computed in the oracle's
+//                canonical arithmetic (raw: table entries summed in ascending m; residual: the
+//                direct form sum_m |(q - c)_m - cb[m][code_m]|^2), ordered by (distance, label),
+//                and the result is VERIFIED: it is accepted only if the exact k-th distance lies
+//                below (worst kept approximate distance - error bound); otherwise the query is
+//                flagged.
+//            3c  ivfpq_exact_scan_kernel: flagged queries (heavy ties, more duplicates than k')
+//                are re-scanned in canonical arithmetic -- for residual encoding with one table
+//                per (query, list) built in shared memory from q - c_list.
+//          Results are therefore bit-identical to the CPU oracle for both encodings.
 #include "ivfpq_index.h"
 
 #include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
 #include <cub/cub.cuh>
 #include <unordered_set>
 
@@ -34,6 +49,19 @@ namespace {
 constexpr int kKsub = 256;
 constexpr int kScanThreads = 128;
 constexpr int kScanWarps = kScanThreads / 32;
+constexpr float kInf = 3.402823466e+38f;   // FLT_MAX used as padding distance
+constexpr uint32_t kNoPos = 0xFFFFFFFFu;
+constexpr int64_t kNoLabel = 0x7fffffffffffffffll;
+
+// Position of entry (m, code) inside one query's table.  M % 16 == 0: [m / 16][code][m % 16]
+// (the scan's layout minus the replication); otherwise [m][code].
+__host__ __device__ __forceinline__ int lut_index(int M, int m, int code) {
+    return (M & 15) == 0 ? ((m >> 4) * (kKsub * 16) + code * 16 + (m & 15)) : (m * kKsub + code);
+}
+// Byte offset of sub-quantizer m inside the stored code of the vector at `pos`.
+__device__ __forceinline__ int code_byte(bool rotated, int m, int64_t pos) {
+    return rotated ? ((m & ~15) | ((m - static_cast<int>(pos & 15)) & 15)) : m;
+}
 
 __global__ void cb_norm_kernel(const float* cb, int M, int dsub, float* out) {
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -44,7 +72,63 @@ __global__ void cb_norm_kernel(const float* cb, int M, int dsub, float* out) {
     out[idx] = acc;
 }
 
-// lut[q][m][j]; one thread per entry.
+// Table entries in lut_index() order, M % 16 == 0.  A CTA owns one 64-code slice of one group of
+// 16 sub-quantizers: it stages that slice of the codebook (16 x 64 x dsub floats) in shared memory
+// once and then produces the slice's entries for kLutQueries queries, so the codebook crosses L2
+// once per kLutQueries queries instead of once per query.  Thread (code, quarter) computes the four
+// adjacent entries m = 16 g + 4 quarter .. + 3 of its code and stores them as one float4; a warp
+// writes 512 contiguous bytes.
+constexpr int kLutQueries = 32;
+constexpr int kLutCodes = 64;
+__global__ void __launch_bounds__(256)
+lut_group_kernel(const float* xq, int64_t nq, int d, int M, int dsub, const float* cb, int by_residual,
+                 float* lut) {
+    extern __shared__ float lut_sm[];            // [16][kLutCodes][dsub] codebook slice, then [kLutQueries][16*dsub] queries
+    const int groups = M >> 4;
+    const int g = blockIdx.y / (kKsub / kLutCodes);
+    const int code0 = (blockIdx.y % (kKsub / kLutCodes)) * kLutCodes;
+    const int64_t q0 = static_cast<int64_t>(blockIdx.x) * kLutQueries;
+    float* cbs = lut_sm;
+    float* qs = lut_sm + 16 * kLutCodes * dsub;
+    for (int i = threadIdx.x; i < 16 * kLutCodes * dsub; i += 256) {
+        const int mm = i / (kLutCodes * dsub), rest = i % (kLutCodes * dsub);
+        cbs[i] = cb[(static_cast<int64_t>(g * 16 + mm) * kKsub + code0) * dsub + rest];
+    }
+    const int qn = static_cast<int>(min(static_cast<int64_t>(kLutQueries), nq - q0));
+    for (int i = threadIdx.x; i < qn * 16 * dsub; i += 256) {
+        const int qi = i / (16 * dsub), rest = i % (16 * dsub);
+        qs[i] = xq[(q0 + qi) * d + g * 16 * dsub + rest];
+    }
+    __syncthreads();
+    const int code = threadIdx.x & (kLutCodes - 1);
+    const int quarter = threadIdx.x / kLutCodes;        // 0..3
+    for (int qi = 0; qi < qn; ++qi) {
+        float out[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int mm = quarter * 4 + u;
+            const float* qv = qs + qi * 16 * dsub + mm * dsub;
+            const float* c = cbs + (mm * kLutCodes + code) * dsub;
+            float acc = 0.f;
+            if (by_residual) {
+                for (int t = 0; t < dsub; ++t) acc = fmaf(qv[t], c[t], acc);
+                acc = -2.f * acc;
+            } else {
+                for (int t = 0; t < dsub; ++t) {
+                    const float df = qv[t] - c[t];
+                    acc = fmaf(df, df, acc);
+                }
+            }
+            out[u] = acc;
+        }
+        float4* dst = reinterpret_cast<float4*>(lut + (q0 + qi) * M * kKsub + g * (kKsub * 16) + (code0 + code) * 16 +
+                                                quarter * 4);
+        *dst = make_float4(out[0], out[1], out[2], out[3]);
+    }
+    (void)groups;
+}
+
+// Any M: one thread per entry, [m][code] layout.
 __global__ void lut_kernel(const float* xq, int64_t nq, int d, int M, int dsub, const float* cb, int by_residual,
                            float* lut) {
     const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -64,7 +148,7 @@ __global__ void lut_kernel(const float* xq, int64_t nq, int d, int M, int dsub, 
             acc = fmaf(df, df, acc);
         }
     }
-    lut[idx] = acc;
+    lut[q * M * kKsub + m * kKsub + j] = acc;
 }
 
 // PQ encode: one warp per (vector, sub-quantizer); exhaustive nearest codeword under the
@@ -104,7 +188,7 @@ __global__ void encode_kernel(const float* x, int64_t n, int d, int M, int dsub,
     if (lane == 0) codes[v * M + m] = static_cast<uint8_t>(arg);
 }
 
-// t2[v] = sum_m ( |cb[m][code]|^2 + 2 c_list,m . cb[m][code] ), fp32, m ascending.
+// t2[v] = sum_m ( |cb[m][code]|^2 + 2 c_list,m . cb[m][code] ), fp32, m ascending (canonical codes).
 __global__ void t2_kernel(int64_t n, int d, int M, int dsub, const float* cb, const float* cbnorm,
                           const float* centroids, const int32_t* list_no, const uint8_t* codes, float* t2) {
     const int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -140,9 +224,21 @@ __global__ void iota_i32_kernel(int32_t* p, int64_t n) {
     const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i < n) p[i] = static_cast<int32_t>(i);
 }
+// Copies one code from position `src` (stored with rotation src_rot) to position `dst`
+// (stored with rotation dst & 15 when rotated).
+__device__ __forceinline__ void copy_code(const uint8_t* from, uint8_t* to, int M, bool rotated, int64_t src,
+                                          int src_rot, int64_t dst) {
+    if (!rotated) {
+        for (int b = 0; b < M; ++b) to[dst * M + b] = from[src * M + b];
+        return;
+    }
+    const int delta = (static_cast<int>(dst & 15) - src_rot) & 15;
+    for (int g = 0; g < M; g += 16)
+        for (int s = 0; s < 16; ++s) to[dst * M + g + s] = from[src * M + g + ((s + delta) & 15)];
+}
 __global__ void scatter_old_kernel(int64_t n_old, int nlist, const int64_t* old_off, const int64_t* new_off, int M,
-                                   const uint8_t* codes, const int64_t* ids, const float* t2, uint8_t* ncodes,
-                                   int64_t* nids, float* nt2) {
+                                   int rotated, const uint8_t* codes, const int64_t* ids, const float* t2,
+                                   uint8_t* ncodes, int64_t* nids, float* nt2) {
     const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= n_old) return;
     int lo = 0, hi = nlist;  // largest l with old_off[l] <= i
@@ -152,57 +248,40 @@ __global__ void scatter_old_kernel(int64_t n_old, int nlist, const int64_t* old_
         else hi = mid;
     }
     const int64_t dst = new_off[lo] + (i - old_off[lo]);
-    for (int b = 0; b < M; ++b) ncodes[dst * M + b] = codes[i * M + b];
+    copy_code(codes, ncodes, M, rotated != 0, i, static_cast<int>(i & 15), dst);
     nids[dst] = ids[i];
     if (t2) nt2[dst] = t2[i];
 }
 __global__ void scatter_new_kernel(int64_t n_new, const int32_t* sorted_list, const int32_t* sorted_src,
                                    const int64_t* old_off, const int64_t* new_off, const int64_t* new_first, int M,
-                                   const uint8_t* codes, const int64_t* ids, const float* t2, uint8_t* ncodes,
-                                   int64_t* nids, float* nt2) {
+                                   int rotated, const uint8_t* codes, const int64_t* ids, const float* t2,
+                                   uint8_t* ncodes, int64_t* nids, float* nt2) {
     const int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (j >= n_new) return;
     const int l = sorted_list[j];
     const int64_t src = sorted_src[j];
     const int64_t dst = new_off[l] + (old_off[l + 1] - old_off[l]) + (j - new_first[l]);
-    for (int b = 0; b < M; ++b) ncodes[dst * M + b] = codes[src * M + b];
+    copy_code(codes, ncodes, M, rotated != 0, src, 0, dst);
     nids[dst] = ids[src];
     if (t2) nt2[dst] = t2[src];
 }
 
-// ---- scan ----
-struct ScanArgs {
-    const float* lut;        // [nq][M][256]
-    const int64_t* cI;       // [nq][nprobe] probed list ids (-1 = none)
-    const float* cD;         // [nq][nprobe] coarse distances
-    int nprobe;
-    const int64_t* offsets;  // [nlist + 1]
-    const uint8_t* codes;
-    const int64_t* ids;
-    const float* t2;
-    int by_residual;
-    int k;
-    int S;                   // probe splits per query
-    int M;
-    int64_t nq;
-    float* outD;             // [S][nq][k]
-    int64_t* outI;
-    unsigned long long* scanned;  // statistics: codes visited
-};
-
-__device__ __forceinline__ bool pair_less(float d1, int64_t l1, float d2, int64_t l2) {
+// ---- top-k kept in a warp's registers ----
+template <typename L>
+__device__ __forceinline__ bool pair_less(float d1, L l1, float d2, L l2) {
     return d1 < d2 || (d1 == d2 && l1 < l2);
 }
 
-// Sorted top-(32*KPT) list spread over a warp: rank r lives in lane r / KPT, slot r % KPT.
-template <int KPT>
-__device__ __forceinline__ void warp_insert(float (&dk)[KPT], int64_t (&lb)[KPT], float vd, int64_t vl, int lane) {
+// Sorted list of 32*KPT (distance, payload) pairs spread over a warp: rank r lives in lane
+// r / KPT, slot r % KPT.  Inserting shifts the tail by one with a single shuffle per register.
+template <int KPT, typename L>
+__device__ __forceinline__ void warp_insert(float (&dk)[KPT], L (&lb)[KPT], float vd, L vl, int lane) {
     const float pd = __shfl_up_sync(0xffffffffu, dk[KPT - 1], 1);
-    const int64_t pl = __shfl_up_sync(0xffffffffu, lb[KPT - 1], 1);
+    const L pl = __shfl_up_sync(0xffffffffu, lb[KPT - 1], 1);
     bool ls[KPT];
 #pragma unroll
-    for (int s = 0; s < KPT; ++s) ls[s] = pair_less(dk[s], lb[s], vd, vl);
-    const bool prev_less = lane == 0 ? true : pair_less(pd, pl, vd, vl);
+    for (int s = 0; s < KPT; ++s) ls[s] = pair_less<L>(dk[s], lb[s], vd, vl);
+    const bool prev_less = lane == 0 ? true : pair_less<L>(pd, pl, vd, vl);
 #pragma unroll
     for (int s = KPT - 1; s >= 0; --s) {
         if (!ls[s]) {
@@ -218,110 +297,18 @@ __device__ __forceinline__ void warp_insert(float (&dk)[KPT], int64_t (&lb)[KPT]
     }
 }
 
-__device__ __forceinline__ float lut_sum_word(const float* lut, int m0, uint32_t w, float acc) {
-    acc = acc + lut[(m0 + 0) * kKsub + (w & 255u)];
-    acc = acc + lut[(m0 + 1) * kKsub + ((w >> 8) & 255u)];
-    acc = acc + lut[(m0 + 2) * kKsub + ((w >> 16) & 255u)];
-    acc = acc + lut[(m0 + 3) * kKsub + (w >> 24)];
-    return acc;
-}
-
-// MT: 16-byte words per code (M = 16 * MT), or 0 for any M (byte loads).
-template <int MT, int KPT>
-__global__ void __launch_bounds__(kScanThreads)
-ivfpq_scan_kernel(const ScanArgs a) {
-    extern __shared__ __align__(16) uint8_t scan_smem[];
-    float* lut = reinterpret_cast<float*>(scan_smem);
-    const int64_t q = blockIdx.x;
-    const int split = blockIdx.y;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int M = MT > 0 ? MT * 16 : a.M;
-
-    {
-        const float4* src = reinterpret_cast<const float4*>(a.lut + q * M * kKsub);
-        float4* dst = reinterpret_cast<float4*>(lut);
-        for (int i = threadIdx.x; i < M * kKsub / 4; i += kScanThreads) dst[i] = __ldg(src + i);
-    }
-    __syncthreads();
-
-    float dk[KPT];
-    int64_t lb[KPT];
-#pragma unroll
-    for (int s = 0; s < KPT; ++s) {
-        dk[s] = __int_as_float(0x7f800000);
-        lb[s] = 0x7fffffffffffffffll;
-    }
-    float th_d = __int_as_float(0x7f800000);
-    int64_t th_l = 0x7fffffffffffffffll;
-    unsigned long long visited = 0;
-
-    for (int p = split + a.S * warp; p < a.nprobe; p += a.S * kScanWarps) {
-        const int64_t list = a.cI[q * a.nprobe + p];
-        if (list < 0) continue;
-        const int64_t begin = a.offsets[list], end = a.offsets[list + 1];
-        const float base = a.by_residual ? a.cD[q * a.nprobe + p] : 0.f;
-        visited += static_cast<unsigned long long>(end - begin);
-        for (int64_t v0 = begin; v0 < end; v0 += 32) {
-            const int64_t v = v0 + lane;
-            const bool valid = v < end;
-            float acc = base;
-            if (valid) {
-                if (a.by_residual) acc = acc + a.t2[v];
-                if (MT > 0) {
-                    const uint4* cp = reinterpret_cast<const uint4*>(a.codes + v * M);
-#pragma unroll
-                    for (int w = 0; w < MT; ++w) {
-                        const uint4 c = __ldg(cp + w);
-                        acc = lut_sum_word(lut, w * 16 + 0, c.x, acc);
-                        acc = lut_sum_word(lut, w * 16 + 4, c.y, acc);
-                        acc = lut_sum_word(lut, w * 16 + 8, c.z, acc);
-                        acc = lut_sum_word(lut, w * 16 + 12, c.w, acc);
-                    }
-                } else {
-                    const uint8_t* cp = a.codes + v * M;
-                    for (int m = 0; m < M; ++m) acc = acc + lut[m * kKsub + cp[m]];
-                }
-            }
-            bool pass = valid && acc <= th_d;
-            int64_t label = 0;
-            if (pass) {
-                label = a.ids[v];
-                pass = pair_less(acc, label, th_d, th_l);
-            }
-            unsigned bal = __ballot_sync(0xffffffffu, pass);
-            while (bal) {
-                const int src = __ffs(bal) - 1;
-                bal &= bal - 1;
-                const float vd = __shfl_sync(0xffffffffu, acc, src);
-                const int64_t vl = __shfl_sync(0xffffffffu, label, src);
-                warp_insert<KPT>(dk, lb, vd, vl, lane);
-                th_d = __shfl_sync(0xffffffffu, dk[KPT - 1], 31);
-                th_l = __shfl_sync(0xffffffffu, lb[KPT - 1], 31);
-            }
-        }
-    }
-    if (a.scanned && lane == 0 && visited) atomicAdd(a.scanned, visited);
-
-    // merge the warp lists
-    __syncthreads();  // everyone is done with the table
-    constexpr int E = kScanThreads * KPT;
-    int64_t* sl = reinterpret_cast<int64_t*>(scan_smem);
-    float* sd = reinterpret_cast<float*>(scan_smem + static_cast<size_t>(E) * 8);
-#pragma unroll
-    for (int s = 0; s < KPT; ++s) {
-        sd[threadIdx.x * KPT + s] = dk[s];
-        sl[threadIdx.x * KPT + s] = lb[s];
-    }
-    __syncthreads();
+// Bitonic sort of E (power of two) pairs held in shared memory, ascending by (distance, payload).
+template <typename L>
+__device__ __forceinline__ void block_sort_pairs(float* sd, L* sl, int E) {
     for (int size = 2; size <= E; size <<= 1) {
         for (int stride = size >> 1; stride > 0; stride >>= 1) {
-            for (int i = threadIdx.x; i < E / 2; i += kScanThreads) {
+            for (int i = threadIdx.x; i < E / 2; i += blockDim.x) {
                 const int lo = 2 * i - (i & (stride - 1));
                 const int hi = lo + stride;
                 const bool up = (lo & size) == 0;
                 const float d1 = sd[lo], d2 = sd[hi];
-                const int64_t l1 = sl[lo], l2 = sl[hi];
-                if (pair_less(d2, l2, d1, l1) == up) {
+                const L l1 = sl[lo], l2 = sl[hi];
+                if (pair_less<L>(d2, l2, d1, l1) == up) {
                     sd[lo] = d2; sd[hi] = d1;
                     sl[lo] = l2; sl[hi] = l1;
                 }
@@ -329,64 +316,496 @@ ivfpq_scan_kernel(const ScanArgs a) {
             __syncthreads();
         }
     }
-    float* oD = a.outD + (static_cast<int64_t>(split) * a.nq + q) * a.k;
-    int64_t* oI = a.outI + (static_cast<int64_t>(split) * a.nq + q) * a.k;
-    for (int i = threadIdx.x; i < a.k; i += kScanThreads) {
-        const bool real = i < E && sl[i] != 0x7fffffffffffffffll;
-        oD[i] = real ? sd[i] : 3.402823466e+38f;
-        oI[i] = real ? sl[i] : -1;
+}
+
+struct ScanArgs {
+    const float* lut;        // [nq][M * 256] in lut_index() order
+    const int64_t* cI;       // [nq][nprobe] probed list ids (-1 = none)
+    const float* cD;         // [nq][nprobe] coarse distances
+    int nprobe;
+    const int64_t* offsets;  // [nlist + 1]
+    const uint8_t* codes;
+    const int64_t* ids;
+    const float* t2;
+    int by_residual;
+    int rotated;
+    int k;
+    int S;                   // probe splits per query (fast scan)
+    int M, d, dsub, nlist;
+    int64_t nq;
+    const float* xq;         // [nq][d]
+    const float* centroids;  // [nlist][d]
+    const float* codebooks;  // [M][256][dsub]
+    // fast scan output
+    float* fd;               // [nq][S][kprime] approximate distances
+    uint32_t* fp;            // [nq][S][kprime] positions (kNoPos = empty)
+    float* fth;              // [nq][S] worst kept approximate distance when the split's list is full, else +inf
+    int kprime;
+    float err_rel;           // filter error bound: eps = err_rel * approx + err_abs[q-dependent part]
+    float err_abs_c0, err_abs_c1;   // eps_abs = err_abs_c0 * (coarse_max + c1_const) + ... see refine kernel
+    float t2_bound;          // bound on |t2|
+    float cb_bound;          // sqrt(sum_m max_j |cb|^2)
+    // results
+    float* outD;             // [nq][k]
+    int64_t* outI;
+    uint8_t* flag;           // [nq] 1 = not verified, re-scan exactly
+    const int32_t* qlist;    // exact scan: indices of the queries to process
+    unsigned long long* scanned;
+};
+
+// ---------------------------------------------------------------------------------------
+// 3a. fast scan (filter)
+// ---------------------------------------------------------------------------------------
+// Adds the 16 table entries of 16-byte code group G (and the following groups) to acc.
+// offb[s]: shared-space byte address of this lane's column in the row of code 0, group 0.
+template <int G, int MT>
+struct GroupSum {
+    static __device__ __forceinline__ void run(const uint4 (&cc)[MT], const uint32_t (&offb)[16], float& acc) {
+        const uint32_t w[4] = {cc[G].x, cc[G].y, cc[G].z, cc[G].w};
+#pragma unroll
+        for (int s = 0; s < 16; ++s) {
+            // byte s of the code -> row address code * 128 bytes, + this lane's column
+            const uint32_t byte = __byte_perm(w[s >> 2], 0u, 0x4440u + (s & 3));
+            const uint32_t addr = byte * 128u + offb[s];
+            float val;
+            asm("ld.shared.f32 %0, [%1+%2];" : "=f"(val) : "r"(addr), "n"(G * kKsub * 32 * 4));
+            acc = acc + val;
+        }
+        GroupSum<G + 1, MT>::run(cc, offb, acc);
     }
+};
+template <int MT>
+struct GroupSum<MT, MT> {
+    static __device__ __forceinline__ void run(const uint4 (&)[MT], const uint32_t (&)[16], float&) {}
+};
+
+template <int MT, int KPT>
+__global__ void __launch_bounds__(kScanThreads)
+ivfpq_fast_scan_kernel(const ScanArgs a) {
+    extern __shared__ __align__(16) uint8_t scan_smem[];
+    float* lut = reinterpret_cast<float*>(scan_smem);   // [MT][256][32]
+    const int64_t q = blockIdx.x;
+    const int split = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int M = MT * 16;
+
+    {   // table: global [g][code][16] -> shared [g][code][32] with the 16 entries replicated
+        const float4* src = reinterpret_cast<const float4*>(a.lut + q * M * kKsub);
+        for (int i = threadIdx.x; i < MT * kKsub * 4; i += kScanThreads) {
+            const float4 v = __ldg(src + i);
+            const int row = i >> 2, part = i & 3;          // row = g * 256 + code
+            float4* dst = reinterpret_cast<float4*>(lut + row * 32 + part * 4);
+            dst[0] = v;
+            dst[4] = v;                                     // + 16 floats
+        }
+    }
+    __syncthreads();
+
+    float dk[KPT];
+    uint32_t pk[KPT];
+#pragma unroll
+    for (int s = 0; s < KPT; ++s) {
+        dk[s] = __int_as_float(0x7f800000);
+        pk[s] = kNoPos;
+    }
+    float th_d = __int_as_float(0x7f800000);
+    uint32_t th_p = kNoPos;
+    unsigned long long visited = 0;
+
+    // Lane l reads sub-quantizer (s + l) mod 16 at step s.  offb[s]: shared-space byte address of
+    // that lane's column inside the [code][32] row of code 0 (group 0).
+    const uint32_t lut_base = static_cast<uint32_t>(__cvta_generic_to_shared(lut));
+    uint32_t offb[16];
+#pragma unroll
+    for (int s = 0; s < 16; ++s) offb[s] = lut_base + 4u * (((s + lane) & 15) + (lane & 16));
+
+    // The warp's probes are visited in batches of 32: lane i fetches the metadata of the batch's
+    // i-th probe (list bounds, coarse distance), so the dependent chain probe -> offsets is paid
+    // once per batch, and the code loads are software-pipelined across list boundaries.
+    // Positions fit 32 bits (an index holds fewer than 2^31 vectors).
+    const int stride = a.S * kScanWarps;
+    const uint4* codes4 = reinterpret_cast<const uint4*>(a.codes);
+    for (int p0 = split + a.S * warp; p0 < a.nprobe; p0 += 32 * stride) {
+        uint32_t my_begin = 0, my_end = 0;
+        float my_base = 0.f;
+        {
+            const int p = p0 + lane * stride;
+            if (p < a.nprobe) {
+                const int64_t list = a.cI[q * a.nprobe + p];
+                if (list >= 0) {
+                    my_begin = static_cast<uint32_t>(a.offsets[list]);
+                    my_end = static_cast<uint32_t>(a.offsets[list + 1]);
+                    if (a.by_residual) my_base = a.cD[q * a.nprobe + p];
+                }
+            }
+        }
+        visited += my_end - my_begin;   // per lane; all lanes add their share at the end
+        int li = -1;
+        uint32_t begin = 0, end = 0, v0 = 0;
+        float base = 0.f;
+        constexpr int U = 2;                 // 32-vector sub-chunks per loop iteration
+        auto advance = [&]() -> bool {      // moves (li, v0) to the next chunk; false when the batch is done
+            v0 += 32 * U;
+            while (li < 0 || v0 >= end) {
+                ++li;
+                if (li >= 32) return false;
+                begin = __shfl_sync(0xffffffffu, my_begin, li);
+                end = __shfl_sync(0xffffffffu, my_end, li);
+                base = __shfl_sync(0xffffffffu, my_base, li);
+                v0 = begin & ~31u;
+                if (begin == end) v0 = end;   // empty or absent list
+            }
+            return true;
+        };
+        uint4 cn[U][MT];
+        float tn[U];
+        auto fetch = [&](uint32_t vv0, uint32_t b, uint32_t e) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const uint32_t v = vv0 + 32 * u + lane;
+                tn[u] = 0.f;
+                if (v >= b && v < e) {
+                    const uint4* cp = codes4 + static_cast<size_t>(v) * MT;
+#pragma unroll
+                    for (int g = 0; g < MT; ++g) cn[u][g] = __ldg(cp + g);
+                    if (a.by_residual) tn[u] = __ldg(a.t2 + v);
+                }
+            }
+        };
+        bool have = advance();
+        if (have) fetch(v0, begin, end);
+        while (have) {
+            const uint32_t cv0 = v0, cbegin = begin, cend = end;
+            float acc[U];
+            uint4 cc[U][MT];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                acc[u] = base + tn[u];
+#pragma unroll
+                for (int g = 0; g < MT; ++g) cc[u][g] = cn[u][g];
+            }
+            // next chunk's loads are in flight while this one is processed
+            have = advance();
+            if (have) fetch(v0, begin, end);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const uint32_t v = cv0 + 32 * u + lane;     // v & 15 == lane & 15: the stored rotation
+                const bool valid = v >= cbegin && v < cend;
+                if (valid) GroupSum<0, MT>::run(cc[u], offb, acc[u]);
+                const bool pass = valid && pair_less<uint32_t>(acc[u], v, th_d, th_p);
+                unsigned bal = __ballot_sync(0xffffffffu, pass);
+                while (bal) {
+                    const int src = __ffs(bal) - 1;
+                    bal &= bal - 1;
+                    const float vd = __shfl_sync(0xffffffffu, acc[u], src);
+                    const uint32_t vp = __shfl_sync(0xffffffffu, v, src);
+                    warp_insert<KPT, uint32_t>(dk, pk, vd, vp, lane);
+                    th_d = __shfl_sync(0xffffffffu, dk[KPT - 1], 31);
+                    th_p = __shfl_sync(0xffffffffu, pk[KPT - 1], 31);
+                }
+            }
+        }
+    }
+    if (a.scanned && visited) atomicAdd(a.scanned, visited);
+
+    // merge the four warp lists, keep the kprime best of the CTA
+    __syncthreads();
+    constexpr int E = kScanThreads * KPT;
+    constexpr int KP = 32 * KPT;
+    uint32_t* sp = reinterpret_cast<uint32_t*>(scan_smem);
+    float* sd = reinterpret_cast<float*>(scan_smem + static_cast<size_t>(E) * 4);
+#pragma unroll
+    for (int s = 0; s < KPT; ++s) {
+        sd[threadIdx.x * KPT + s] = dk[s];
+        sp[threadIdx.x * KPT + s] = pk[s];
+    }
+    __syncthreads();
+    block_sort_pairs<uint32_t>(sd, sp, E);
+    float* od = a.fd + (q * a.S + split) * KP;
+    uint32_t* op = a.fp + (q * a.S + split) * KP;
+    for (int i = threadIdx.x; i < KP; i += kScanThreads) {
+        od[i] = sd[i];
+        op[i] = sp[i];
+    }
+    if (threadIdx.x == 0) {
+        // Everything this CTA dropped has an approximate distance >= the worst kept one; if the
+        // kept list is not full nothing was dropped.
+        a.fth[q * a.S + split] = sp[KP - 1] != kNoPos ? sd[KP - 1] : __int_as_float(0x7f800000);
+    }
+}
+
+// Canonical distance of the vector at `pos` (probed through list `list`).
+__device__ __forceinline__ float exact_distance(const ScanArgs& a, int64_t q, int64_t pos, int64_t list) {
+    const uint8_t* code = a.codes + pos * a.M;
+    float acc = 0.f;
+    if (!a.by_residual) {
+        const float* lut = a.lut + q * a.M * kKsub;
+        for (int m = 0; m < a.M; ++m)
+            acc = acc + lut[lut_index(a.M, m, code[code_byte(a.rotated != 0, m, pos)])];
+    } else {
+        const float* qv = a.xq + q * a.d;
+        const float* cen = a.centroids + list * a.d;
+        for (int m = 0; m < a.M; ++m) {
+            const float* cw = a.codebooks +
+                              (static_cast<int64_t>(m) * kKsub + code[code_byte(a.rotated != 0, m, pos)]) * a.dsub;
+            float e = 0.f;
+            for (int t = 0; t < a.dsub; ++t) {
+                const float r = qv[m * a.dsub + t] - cen[m * a.dsub + t];
+                const float df = r - cw[t];
+                e = fmaf(df, df, e);
+            }
+            acc = acc + e;
+        }
+    }
+    return acc;
+}
+
+// ---------------------------------------------------------------------------------------
+// 3b. exact re-computation of the survivors, ordering by (distance, label), verification
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kScanThreads)
+ivfpq_refine_kernel(const ScanArgs a, int P) {
+    extern __shared__ __align__(16) uint8_t ref_smem[];
+    int64_t* sl = reinterpret_cast<int64_t*>(ref_smem);                       // P labels
+    float* sd = reinterpret_cast<float*>(ref_smem + static_cast<size_t>(P) * 8);   // P distances
+    __shared__ float s_qn2;
+    const int64_t q = blockIdx.x;
+    const int n_c = a.S * a.kprime;
+    for (int i = threadIdx.x; i < P; i += kScanThreads) {
+        float dist = __int_as_float(0x7f800000);
+        int64_t label = kNoLabel;
+        if (i < n_c) {
+            const uint32_t pos = a.fp[q * n_c + i];
+            if (pos != kNoPos) {
+                int64_t list = 0;
+                if (a.by_residual) {          // owning list of the position
+                    int lo = 0, hi = a.nlist;
+                    while (hi - lo > 1) {
+                        const int mid = (lo + hi) >> 1;
+                        if (a.offsets[mid] <= static_cast<int64_t>(pos)) lo = mid;
+                        else hi = mid;
+                    }
+                    list = lo;
+                }
+                dist = exact_distance(a, q, pos, list);
+                label = a.ids[pos];
+            }
+        }
+        sd[i] = dist;
+        sl[i] = label;
+    }
+    if (threadIdx.x < 32) {   // |q|^2 for the residual error bound
+        float s = 0.f;
+        if (a.by_residual)
+            for (int t = threadIdx.x; t < a.d; t += 32) s = fmaf(a.xq[q * a.d + t], a.xq[q * a.d + t], s);
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (threadIdx.x == 0) s_qn2 = s;
+    }
+    __syncthreads();
+    block_sort_pairs<int64_t>(sd, sl, P);
+    for (int i = threadIdx.x; i < a.k; i += kScanThreads) {
+        const bool real = i < P && sl[i] != kNoLabel;
+        a.outD[q * a.k + i] = real ? sd[i] : kInf;
+        a.outI[q * a.k + i] = real ? sl[i] : -1;
+    }
+    if (threadIdx.x == 0) {
+        // Anything a split dropped has approximate distance >= that split's threshold, hence an
+        // exact distance >= threshold - eps.  The refined top-k stands if its k-th distance is
+        // strictly below that for every split.
+        float a_min = __int_as_float(0x7f800000);
+        for (int s = 0; s < a.S; ++s) a_min = fminf(a_min, a.fth[q * a.S + s]);
+        uint8_t bad = 0;
+        if (a_min != __int_as_float(0x7f800000)) {
+            float eps = a.err_rel * fabsf(a_min);
+            if (a.by_residual) {
+                const float coarse_max = a.cD[q * a.nprobe + a.nprobe - 1];
+                const float bound = fabsf(coarse_max) + a.t2_bound + 2.f * sqrtf(s_qn2) * a.cb_bound + fabsf(a_min);
+                eps = a.err_rel * bound;
+            }
+            const int kk = a.k <= P ? a.k : P;
+            const bool have_k = sl[kk - 1] != kNoLabel;
+            // fewer than k survivors although something was dropped, or the k-th is too close
+            if (!have_k || !(sd[kk - 1] < a_min - eps)) bad = 1;
+        }
+        a.flag[q] = bad;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// 3c. exact scan (canonical arithmetic), one CTA per listed query.  Residual encoding builds
+//     one table per (query, list) in shared memory from q - c_list.
+// ---------------------------------------------------------------------------------------
+template <int KPT>
+__global__ void __launch_bounds__(kScanThreads)
+ivfpq_exact_scan_kernel(const ScanArgs a) {
+    extern __shared__ __align__(16) uint8_t ex_smem[];
+    float* lut = reinterpret_cast<float*>(ex_smem);                  // [M][256] canonical layout
+    float* resid = lut + a.M * kKsub;                                // [d]
+    const int64_t q = a.qlist ? a.qlist[blockIdx.x] : blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int M = a.M;
+    const bool rotated = a.rotated != 0;
+
+    if (!a.by_residual) {
+        const float* src = a.lut + q * M * kKsub;
+        for (int i = threadIdx.x; i < M * kKsub; i += kScanThreads)
+            lut[i] = src[lut_index(M, i / kKsub, i % kKsub)];
+    }
+    float dk[KPT];
+    int64_t lb[KPT];
+#pragma unroll
+    for (int s = 0; s < KPT; ++s) {
+        dk[s] = __int_as_float(0x7f800000);
+        lb[s] = kNoLabel;
+    }
+    float th_d = __int_as_float(0x7f800000);
+    int64_t th_l = kNoLabel;
+
+    for (int p = 0; p < a.nprobe; ++p) {
+        const int64_t list = a.cI[q * a.nprobe + p];
+        if (list < 0) continue;
+        const int64_t begin = a.offsets[list], end = a.offsets[list + 1];
+        if (begin == end) continue;
+        __syncthreads();   // previous list fully scanned before the table changes
+        if (a.by_residual) {
+            for (int t = threadIdx.x; t < a.d; t += kScanThreads)
+                resid[t] = a.xq[q * a.d + t] - a.centroids[list * a.d + t];
+            __syncthreads();
+            for (int i = threadIdx.x; i < M * kKsub; i += kScanThreads) {
+                const int m = i / kKsub;
+                const float* cw = a.codebooks + static_cast<int64_t>(i) * a.dsub;
+                float e = 0.f;
+                for (int t = 0; t < a.dsub; ++t) {
+                    const float df = resid[m * a.dsub + t] - cw[t];
+                    e = fmaf(df, df, e);
+                }
+                lut[i] = e;
+            }
+        }
+        __syncthreads();
+        for (int64_t v0 = begin + warp * 32; v0 < end; v0 += kScanThreads) {
+            const int64_t v = v0 + lane;
+            const bool valid = v < end;
+            float acc = 0.f;
+            if (valid) {
+                const uint8_t* cp = a.codes + v * M;
+                for (int m = 0; m < M; ++m) acc = acc + lut[m * kKsub + cp[code_byte(rotated, m, v)]];
+            }
+            bool pass = valid && acc <= th_d;
+            int64_t label = 0;
+            if (pass) {
+                label = a.ids[v];
+                pass = pair_less<int64_t>(acc, label, th_d, th_l);
+            }
+            unsigned bal = __ballot_sync(0xffffffffu, pass);
+            while (bal) {
+                const int src = __ffs(bal) - 1;
+                bal &= bal - 1;
+                const float vd = __shfl_sync(0xffffffffu, acc, src);
+                const int64_t vl = __shfl_sync(0xffffffffu, label, src);
+                warp_insert<KPT, int64_t>(dk, lb, vd, vl, lane);
+                th_d = __shfl_sync(0xffffffffu, dk[KPT - 1], 31);
+                th_l = __shfl_sync(0xffffffffu, lb[KPT - 1], 31);
+            }
+        }
+    }
+    __syncthreads();
+    constexpr int E = kScanThreads * KPT;
+    int64_t* sl = reinterpret_cast<int64_t*>(ex_smem);
+    float* sd = reinterpret_cast<float*>(ex_smem + static_cast<size_t>(E) * 8);
+#pragma unroll
+    for (int s = 0; s < KPT; ++s) {
+        sd[threadIdx.x * KPT + s] = dk[s];
+        sl[threadIdx.x * KPT + s] = lb[s];
+    }
+    __syncthreads();
+    block_sort_pairs<int64_t>(sd, sl, E);
+    for (int i = threadIdx.x; i < a.k; i += kScanThreads) {
+        const bool real = i < E && sl[i] != kNoLabel;
+        a.outD[q * a.k + i] = real ? sd[i] : kInf;
+        a.outI[q * a.k + i] = real ? sl[i] : -1;
+    }
+}
+
+template <typename Kern>
+cudaError_t set_smem(Kern kern, size_t smem) {
+    if (smem > 48 * 1024)
+        return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    return cudaSuccess;
 }
 
 template <int MT>
-cudaError_t launch_scan_mt(const ScanArgs& a, int kpt, size_t smem, dim3 grid, cudaStream_t st) {
-#define B200_SCAN_CASE(KP)                                                                                      \
-    case KP: {                                                                                                   \
-        auto kern = ivfpq_scan_kernel<MT, KP>;                                                                   \
-        if (smem > 48 * 1024) {                                                                                  \
-            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
-            if (e != cudaSuccess) return e;                                                                      \
-        }                                                                                                        \
-        kern<<<grid, kScanThreads, smem, st>>>(a);                                                               \
-        return cudaGetLastError();                                                                               \
+cudaError_t launch_fast_mt(const ScanArgs& a, int kpt, cudaStream_t st) {
+    const size_t smem = std::max(static_cast<size_t>(MT) * kKsub * 32 * 4, static_cast<size_t>(kScanThreads) * kpt * 8);
+    dim3 grid(static_cast<unsigned>(a.nq), static_cast<unsigned>(a.S));
+#define B200_FAST_CASE(KP)                                           \
+    case KP: {                                                       \
+        auto kern = ivfpq_fast_scan_kernel<MT, KP>;                  \
+        cudaError_t e = set_smem(kern, smem);                        \
+        if (e != cudaSuccess) return e;                              \
+        kern<<<grid, kScanThreads, smem, st>>>(a);                   \
+        return cudaGetLastError();                                   \
     }
     switch (kpt) {
-        B200_SCAN_CASE(1)
-        B200_SCAN_CASE(2)
-        B200_SCAN_CASE(4)
-        B200_SCAN_CASE(8)
-        B200_SCAN_CASE(16)
-        B200_SCAN_CASE(32)
+        B200_FAST_CASE(1)
+        B200_FAST_CASE(2)
+        B200_FAST_CASE(4)
+        B200_FAST_CASE(8)
+        B200_FAST_CASE(16)
+        B200_FAST_CASE(32)
         default: return cudaErrorInvalidValue;
     }
-#undef B200_SCAN_CASE
+#undef B200_FAST_CASE
 }
 
-cudaError_t launch_scan(const ScanArgs& a, cudaStream_t st) {
+cudaError_t launch_fast(const ScanArgs& a, int kpt, cudaStream_t st) {
+    switch (a.M / 16) {
+        case 1: return launch_fast_mt<1>(a, kpt, st);
+        case 2: return launch_fast_mt<2>(a, kpt, st);
+        case 3: return launch_fast_mt<3>(a, kpt, st);
+        case 4: return launch_fast_mt<4>(a, kpt, st);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t launch_exact(const ScanArgs& a, int nq_launch, cudaStream_t st) {
     int kpt = 1;
     while (kpt * 32 < a.k) kpt <<= 1;
     if (kpt > 32) return cudaErrorInvalidValue;
-    const size_t lut_bytes = static_cast<size_t>(a.M) * kKsub * 4;
-    const size_t sort_bytes = static_cast<size_t>(kScanThreads) * kpt * 12;
-    const size_t smem = std::max(lut_bytes, sort_bytes);
-    dim3 grid(static_cast<unsigned>(a.nq), static_cast<unsigned>(a.S));
-    if (a.M % 16 == 0 && a.M <= 64) {
-        switch (a.M / 16) {
-            case 1: return launch_scan_mt<1>(a, kpt, smem, grid, st);
-            case 2: return launch_scan_mt<2>(a, kpt, smem, grid, st);
-            case 3: return launch_scan_mt<3>(a, kpt, smem, grid, st);
-            case 4: return launch_scan_mt<4>(a, kpt, smem, grid, st);
-        }
+    const size_t smem = std::max(static_cast<size_t>(a.M) * kKsub * 4 + static_cast<size_t>(a.d) * 4,
+                                 static_cast<size_t>(kScanThreads) * kpt * 12);
+#define B200_EXACT_CASE(KP)                                          \
+    case KP: {                                                       \
+        auto kern = ivfpq_exact_scan_kernel<KP>;                     \
+        cudaError_t e = set_smem(kern, smem);                        \
+        if (e != cudaSuccess) return e;                              \
+        kern<<<nq_launch, kScanThreads, smem, st>>>(a);              \
+        return cudaGetLastError();                                   \
     }
-    return launch_scan_mt<0>(a, kpt, smem, grid, st);
+    switch (kpt) {
+        B200_EXACT_CASE(1)
+        B200_EXACT_CASE(2)
+        B200_EXACT_CASE(4)
+        B200_EXACT_CASE(8)
+        B200_EXACT_CASE(16)
+        B200_EXACT_CASE(32)
+        default: return cudaErrorInvalidValue;
+    }
+#undef B200_EXACT_CASE
 }
 
 inline unsigned blocks_for(int64_t n, int threads) { return static_cast<unsigned>((n + threads - 1) / threads); }
+inline int pow2_ceil_int(int v) {
+    int p = 1;
+    while (p < v) p <<= 1;
+    return p;
+}
 
 }  // namespace
 
 IvfpqIndex::IvfpqIndex(int d, int nlist, int M, int nbits, bool by_residual, int device)
-    : d_(d), nlist_(nlist), M_(M), dsub_(d / M), device_(device), by_residual_(by_residual) {
+    : d_(d), nlist_(nlist), M_(M), dsub_(d / M), device_(device), by_residual_(by_residual),
+      rotated_(M % 16 == 0 && M <= 64) {
     if (nbits != 8) throw std::invalid_argument("IVFPQ supports nbits = 8 only");
     if (M <= 0 || d % M != 0) throw std::invalid_argument("d must be a multiple of M");
     DeviceGuard g(device_);
@@ -397,6 +816,8 @@ IvfpqIndex::IvfpqIndex(int d, int nlist, int M, int nbits, bool by_residual, int
     offsets_host_.assign(static_cast<size_t>(nlist_ + 1), 0);
     w_tmp_.ensure(sizeof(unsigned long long));
     B200_CUDA_CHECK(cudaMemset(w_tmp_.get(), 0, sizeof(unsigned long long)));
+    const char* e = std::getenv("B200IDX_IVFPQ_EXACT");
+    force_exact_ = e && std::strcmp(e, "1") == 0;
 }
 
 IvfpqIndex::~IvfpqIndex() {
@@ -421,6 +842,18 @@ void IvfpqIndex::set_codebooks(const float* cb) {
                                                                      cbnorm_.as<float>());
     B200_CUDA_CHECK(cudaGetLastError());
     B200_CUDA_CHECK(cudaStreamSynchronize(stream()));
+    double acc = 0.0;
+    for (int m = 0; m < M_; ++m) {
+        double mx = 0.0;
+        for (int j = 0; j < kKsub; ++j) {
+            double s = 0.0;
+            const float* c = cb + (static_cast<size_t>(m) * kKsub + j) * dsub_;
+            for (int t = 0; t < dsub_; ++t) s += static_cast<double>(c[t]) * c[t];
+            mx = std::max(mx, s);
+        }
+        acc += mx;
+    }
+    cb_norm_bound_ = static_cast<float>(std::sqrt(acc) * 1.0001);
     has_codebooks_ = true;
 }
 
@@ -499,7 +932,8 @@ void IvfpqIndex::add_codes(int64_t n, const int32_t* list_no, const uint8_t* cod
 }
 
 // Stable merge of a batch into the CSR lists: existing entries keep their order, new entries
-// follow in arrival order (the order the reference's per-list append produces).
+// follow in arrival order (the order the reference's per-list append produces).  Codes are
+// re-rotated for their new positions on the way.
 void IvfpqIndex::merge_new(int64_t n, const int32_t* ln, const uint8_t* cd, const float* t2, const int64_t* idd) {
     cudaStream_t st = stream();
     const int64_t n_new_total = n_ + n;
@@ -536,10 +970,11 @@ void IvfpqIndex::merge_new(int64_t n, const int32_t* ln, const uint8_t* cd, cons
     float* nt = by_residual_ ? static_cast<float*>(nt2.ensure(static_cast<size_t>(n_new_total) * 4)) : nullptr;
     if (n_ > 0)
         scatter_old_kernel<<<blocks_for(n_, 256), 256, 0, st>>>(n_, nlist_, offsets_.as<int64_t>(), noff, M_,
-                                                                codes_.as<uint8_t>(), ids_.as<int64_t>(),
+                                                                rotated_ ? 1 : 0, codes_.as<uint8_t>(),
+                                                                ids_.as<int64_t>(),
                                                                 by_residual_ ? t2_.as<float>() : nullptr, nc, ni, nt);
-    scatter_new_kernel<<<blocks_for(n, 256), 256, 0, st>>>(n, kout, vout, offsets_.as<int64_t>(), noff, nfirst, M_, cd,
-                                                           idd, t2, nc, ni, nt);
+    scatter_new_kernel<<<blocks_for(n, 256), 256, 0, st>>>(n, kout, vout, offsets_.as<int64_t>(), noff, nfirst, M_,
+                                                           rotated_ ? 1 : 0, cd, idd, t2, nc, ni, nt);
     B200_CUDA_CHECK(cudaGetLastError());
     B200_CUDA_CHECK(cudaMemcpyAsync(offsets_host_.data(), noff, static_cast<size_t>(nlist_ + 1) * 8,
                                     cudaMemcpyDeviceToHost, st));
@@ -559,6 +994,20 @@ void IvfpqIndex::reset() {
     offsets_host_.assign(static_cast<size_t>(nlist_ + 1), 0);
 }
 
+// codes: n stored codes starting at CSR position first_pos -> canonical byte order, in place.
+void IvfpqIndex::unrotate_host(uint8_t* codes, int64_t first_pos, int64_t n) const {
+    if (!rotated_) return;
+    uint8_t tmp[16];
+    for (int64_t i = 0; i < n; ++i) {
+        const int rot = static_cast<int>((first_pos + i) & 15);
+        for (int g = 0; g < M_; g += 16) {
+            uint8_t* c = codes + i * M_ + g;
+            for (int m = 0; m < 16; ++m) tmp[m] = c[(m - rot) & 15];
+            std::memcpy(c, tmp, 16);
+        }
+    }
+}
+
 int64_t IvfpqIndex::remove_ids(int64_t n, const int64_t* ids) {
     if (n <= 0 || n_ == 0) return 0;
     DeviceGuard g(device_);
@@ -566,6 +1015,7 @@ int64_t IvfpqIndex::remove_ids(int64_t n, const int64_t* ids) {
     std::vector<uint8_t> hcodes(static_cast<size_t>(n_) * M_);
     B200_CUDA_CHECK(cudaMemcpy(hid.data(), ids_.get(), hid.size() * 8, cudaMemcpyDeviceToHost));
     B200_CUDA_CHECK(cudaMemcpy(hcodes.data(), codes_.get(), hcodes.size(), cudaMemcpyDeviceToHost));
+    unrotate_host(hcodes.data(), 0, n_);
     std::unordered_set<int64_t> rm(ids, ids + n);
     std::vector<int32_t> ln;
     std::vector<int64_t> kid;
@@ -600,20 +1050,28 @@ void IvfpqIndex::get_list(int list, uint8_t* codes, int64_t* ids) const {
     if (len == 0) return;
     DeviceGuard g(device_);
     const int64_t b = offsets_host_[static_cast<size_t>(list)];
-    if (codes)
+    if (codes) {
         B200_CUDA_CHECK(cudaMemcpy(codes, codes_.as<uint8_t>() + b * M_, static_cast<size_t>(len) * M_,
                                    cudaMemcpyDeviceToHost));
+        unrotate_host(codes, b, len);
+    }
     if (ids) B200_CUDA_CHECK(cudaMemcpy(ids, ids_.as<int64_t>() + b, static_cast<size_t>(len) * 8, cudaMemcpyDeviceToHost));
 }
 
 void IvfpqIndex::search_device(int64_t nq, const float* xq, int k, float* D, int64_t* I) {
     if (nq <= 0) return;
     if (!is_trained()) throw std::invalid_argument("IVFPQ index is not trained (centroids / codebooks missing)");
+    if (k > 1024) throw std::invalid_argument("IVFPQ search supports k <= 1024");
     DeviceGuard g(device_);
     cudaStream_t st = stream();
     stats_.searches += 1;
     stats_.queries += static_cast<uint64_t>(nq);
     const int nprobe = std::max(1, std::min(nprobe_, nlist_));
+    // filter width: k' = 32 * KPT >= k + 16
+    int kpt = 1;
+    while (kpt * 32 < k + 16) kpt <<= 1;
+    const bool fast = rotated_ && !force_exact_ && kpt <= 32;
+    const int kprime = 32 * kpt;
     const int64_t page = 16384;
     for (int64_t q0 = 0; q0 < nq; q0 += page) {
         const int64_t m = std::min(page, nq - q0);
@@ -625,12 +1083,19 @@ void IvfpqIndex::search_device(int64_t nq, const float* xq, int k, float* D, int
         timer_.end(st);
         timer_.begin(kStageLut, st);
         float* lut = static_cast<float*>(w_lut_.ensure(static_cast<size_t>(m) * M_ * kKsub * 4));
-        lut_kernel<<<blocks_for(m * M_ * kKsub, 256), 256, 0, st>>>(xp, m, d_, M_, dsub_, codebooks_.as<float>(),
-                                                                   by_residual_ ? 1 : 0, lut);
+        if ((M_ & 15) == 0) {
+            const size_t lsm = (static_cast<size_t>(16) * kLutCodes * dsub_ + static_cast<size_t>(kLutQueries) * 16 * dsub_) * 4;
+            B200_CUDA_CHECK(set_smem(lut_group_kernel, lsm));
+            dim3 lgrid(blocks_for(m, kLutQueries), static_cast<unsigned>((M_ / 16) * (kKsub / kLutCodes)));
+            lut_group_kernel<<<lgrid, 256, lsm, st>>>(xp, m, d_, M_, dsub_, codebooks_.as<float>(),
+                                                      by_residual_ ? 1 : 0, lut);
+        } else {
+            lut_kernel<<<blocks_for(m * M_ * kKsub, 256), 256, 0, st>>>(xp, m, d_, M_, dsub_, codebooks_.as<float>(),
+                                                                       by_residual_ ? 1 : 0, lut);
+        }
         B200_CUDA_CHECK(cudaGetLastError());
         timer_.end(st);
-        int S = static_cast<int>((16LL * num_sms_ + m - 1) / m);
-        S = std::max(1, std::min(S, (nprobe + kScanWarps - 1) / kScanWarps));
+
         ScanArgs a{};
         a.lut = lut;
         a.cI = cI;
@@ -641,28 +1106,73 @@ void IvfpqIndex::search_device(int64_t nq, const float* xq, int k, float* D, int
         a.ids = ids_.as<int64_t>();
         a.t2 = t2_.as<float>();
         a.by_residual = by_residual_ ? 1 : 0;
+        a.rotated = rotated_ ? 1 : 0;
         a.k = k;
-        a.S = S;
         a.M = M_;
+        a.d = d_;
+        a.dsub = dsub_;
+        a.nlist = nlist_;
         a.nq = m;
+        a.xq = xp;
+        a.centroids = coarse_->rows_f32();
+        a.codebooks = codebooks_.as<float>();
+        a.outD = D + q0 * k;
+        a.outI = I + q0 * k;
         a.scanned = w_tmp_.as<unsigned long long>();
-        if (S == 1) {
-            a.outD = D + q0 * k;
-            a.outI = I + q0 * k;
+        a.qlist = nullptr;
+
+        if (!fast) {
             timer_.begin(kStageScan, st);
-            B200_CUDA_CHECK(launch_scan(a, st));
+            B200_CUDA_CHECK(launch_exact(a, static_cast<int>(m), st));
             timer_.end(st);
             stats_.kernel_launches += 2;
-        } else {
-            a.outD = static_cast<float*>(w_pD_.ensure(static_cast<size_t>(S) * m * k * 4));
-            a.outI = static_cast<int64_t*>(w_pI_.ensure(static_cast<size_t>(S) * m * k * 8));
-            timer_.begin(kStageScan, st);
-            B200_CUDA_CHECK(launch_scan(a, st));
-            timer_.end(st);
-            timer_.begin(kStageMerge, st);
-            B200_CUDA_CHECK(launch_merge_topk(S, m, k, 0, a.outD, a.outI, D + q0 * k, I + q0 * k, st));
-            timer_.end(st);
-            stats_.kernel_launches += 3;
+            continue;
+        }
+        // probe splits: enough CTAs to fill the machine, bounded so that the refine kernel's
+        // candidate set (S * k') stays within shared memory
+        int S = static_cast<int>((16LL * num_sms_ + m - 1) / m);
+        S = std::max(1, std::min(S, (nprobe + kScanWarps - 1) / kScanWarps));
+        S = std::max(1, std::min(S, 4096 / kprime));
+        a.S = S;
+        a.kprime = kprime;
+        a.fd = static_cast<float*>(w_fd_.ensure(static_cast<size_t>(m) * S * kprime * 4));
+        a.fp = static_cast<uint32_t*>(w_fp_.ensure(static_cast<size_t>(m) * S * kprime * 4));
+        a.fth = static_cast<float*>(w_fth_.ensure(static_cast<size_t>(m) * S * 4));
+        a.flag = static_cast<uint8_t*>(w_flag_.ensure(static_cast<size_t>(m)));
+        // error bound of the filter arithmetic relative to the canonical value:
+        //   raw      : re-ordering a sum of M non-negative fp32 terms -> (2M + 8) ulp of the sum
+        //   residual : every rounding acts on a partial sum bounded by
+        //              B = |coarse| + |t2|max + 2 |q| cbnorm + |result|, about 2M + 2 dsub + 16 of them
+        const float ulp = 5.9604645e-08f;
+        a.err_rel = by_residual_ ? (2.f * M_ + 2.f * dsub_ + 16.f) * ulp : (2.f * M_ + 8.f) * ulp;
+        a.cb_bound = cb_norm_bound_;
+        const float cmax = coarse_->raw_view().max_norm;
+        a.t2_bound = cb_norm_bound_ * cb_norm_bound_ + 2.f * cmax * cb_norm_bound_;
+        timer_.begin(kStageScan, st);
+        B200_CUDA_CHECK(launch_fast(a, kpt, st));
+        timer_.end(st);
+        timer_.begin(kStageMerge, st);
+        const int P = pow2_ceil_int(std::max(S * kprime, 32));
+        const size_t rsmem = static_cast<size_t>(P) * 12;
+        B200_CUDA_CHECK(set_smem(ivfpq_refine_kernel, rsmem));
+        ivfpq_refine_kernel<<<static_cast<unsigned>(m), kScanThreads, rsmem, st>>>(a, P);
+        B200_CUDA_CHECK(cudaGetLastError());
+        timer_.end(st);
+        stats_.kernel_launches += 3;
+        uint8_t* hf = static_cast<uint8_t*>(h_flag_.ensure(static_cast<size_t>(m)));
+        B200_CUDA_CHECK(cudaMemcpyAsync(hf, a.flag, static_cast<size_t>(m), cudaMemcpyDeviceToHost, st));
+        B200_CUDA_CHECK(cudaStreamSynchronize(st));
+        std::vector<int32_t> bad;
+        for (int64_t i = 0; i < m; ++i)
+            if (hf[i]) bad.push_back(static_cast<int32_t>(i));
+        if (!bad.empty()) {
+            stats_.fallback_queries += bad.size();
+            int32_t* ql = static_cast<int32_t*>(w_qlist_.ensure(bad.size() * 4));
+            B200_CUDA_CHECK(cudaMemcpyAsync(ql, bad.data(), bad.size() * 4, cudaMemcpyHostToDevice, st));
+            a.qlist = ql;
+            B200_CUDA_CHECK(launch_exact(a, static_cast<int>(bad.size()), st));
+            B200_CUDA_CHECK(cudaStreamSynchronize(st));
+            stats_.kernel_launches += 1;
         }
     }
     unsigned long long scanned = 0;

@@ -2,9 +2,12 @@
 // FR/ascenddaemon/impl/IndexIVFPQ.cpp:2104-2411, and of the host-side assignment / PQ encoding
 // in FR/ascend/impl/AscendIndexIVFPQImpl.cpp:603-805,879-921).
 //
-// Layout in HBM: inverted lists are one CSR structure -- list_offsets[nlist + 1], codes[ntotal][M]
-// (row-major, 16-byte aligned rows when M % 16 == 0), ids[ntotal], and, for residual encoding,
-// one float per vector (the list-dependent part of the distance, see ivfpq_index.cu).
+// Layout in HBM: inverted lists are one CSR structure -- list_offsets[nlist + 1], codes[ntotal][M],
+// ids[ntotal], and, for residual encoding, one float per vector (the list-dependent part of the
+// distance, see ivfpq_index.cu).  When M is a multiple of 16 the 16 code bytes of each 16-byte
+// group are stored rotated by (position mod 16): stored[s] = code[(s + position) & 15].  The scan
+// kernel walks the sub-quantizers of a vector in that rotated order, which makes its shared-memory
+// table reads bank-conflict free; everything that leaves the index (get_list) is un-rotated.
 #pragma once
 #include <stdint.h>
 
@@ -58,13 +61,17 @@ private:
     void merge_new(int64_t n, const int32_t* list_no_dev, const uint8_t* codes_dev, const float* t2_dev,
                    const int64_t* ids_dev);
     void compute_t2(int64_t n, const int32_t* list_no_dev, const uint8_t* codes_dev, float* t2_dev);
+    void unrotate_host(uint8_t* codes, int64_t first_pos, int64_t n) const;
 
     int d_, nlist_, M_, dsub_, device_;
     bool by_residual_;
+    bool rotated_;                        // M % 16 == 0: rotated code storage + conflict-free scan
     int nprobe_ = 1;
     int64_t n_ = 0;
     bool has_centroids_ = false, has_codebooks_ = false;
     int num_sms_ = 0;
+    float cb_norm_bound_ = 0.f;           // sqrt(sum_m max_j |cb[m][j]|^2), for the filter's error bound
+    bool force_exact_ = false;            // B200IDX_IVFPQ_EXACT=1: always use the exact scan kernels
 
     std::unique_ptr<FlatIndex> coarse_;   // nlist centroids, fp32, L2
     DeviceBuffer codebooks_;              // [M][256][dsub] float
@@ -73,8 +80,9 @@ private:
     std::vector<int64_t> offsets_host_;
     DeviceBuffer codes_, ids_, t2_;
     // scratch
-    DeviceBuffer w_lut_, w_cD_, w_cI_, w_pD_, w_pI_, w_q_, w_D_, w_I_, w_assign_D_, w_assign_I_, w_list_, w_codes_,
-        w_t2_, w_ids_, w_x_, w_tmp_;
+    DeviceBuffer w_lut_, w_cD_, w_cI_, w_fd_, w_fp_, w_fth_, w_flag_, w_qlist_, w_q_, w_D_, w_I_, w_assign_D_,
+        w_assign_I_, w_list_, w_codes_, w_t2_, w_ids_, w_x_, w_tmp_;
+    PinnedBuffer h_flag_;
     SearchStats stats_;
     StageTimer timer_;
 };

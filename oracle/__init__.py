@@ -130,8 +130,8 @@ def build_lists(list_no, codes, ids, nlist):
 
 def ivfpq_search(centroids, codebooks, by_residual, list_offsets, codes, ids, xq, nprobe, k,
                  return_coarse=False):
-    """by_residual: False/0 raw vectors, True/1 residual with direct per-(query, list) tables,
-    2 residual through the precomputed-table decomposition (see oracle.c)."""
+    """by_residual: False raw vectors (one table per query), True residual encoding (one table
+    per (query, list) on q - centroid)."""
     centroids, codebooks, xq = _f32(centroids), _f32(codebooks), _f32(xq)
     nlist, d = centroids.shape
     M, ksub, _ = codebooks.shape

@@ -287,12 +287,6 @@ int orc_pq_encode(int d, int M, int ksub, const float* codebooks, int by_residua
  * Stage 1: nprobe nearest centroids by canonical L2, ties -> lower list id.
  * Stage 2: by_residual = 0: one table per query, LUT[m][j] = L2(q_m, cb[m][j]);
  *          by_residual = 1: one table per (query, list) on q - centroid[list] (direct form);
- *          by_residual = 2: the same distance through the precomputed-table decomposition
- *            |q-c-r|^2 = |q-c|^2 + (|r|^2 + 2 c.r) - 2 q.r   (Faiss' use_precomputed_table),
- *            with the list-dependent middle term summed per vector: t2 = sum_m fmaf(2,
- *            IP(c_m, cb[m][code_m]), IP(cb, cb)); acc = coarse + t2; acc += -2 IP(q_m, cb) for
- *            m ascending.  This is the arithmetic of the GPU's residual mode, bit for bit; it
- *            differs from the direct form by fp32 re-association only.
  * Stage 3: ADC sum in fp32, m ascending; top-k by (distance, label).
  * coarse_out (optional, nq*nprobe) receives the probed list ids in rank order.
  */
@@ -322,32 +316,11 @@ int orc_ivfpq_search(int d, int nlist, int M, int ksub, const float* centroids,
             for (int m = 0; m < M; ++m)
                 for (int j = 0; j < ksub; ++j)
                     lut[m * ksub + j] = l2_canon(qv + m * dsub, codebooks + ((int64_t)m * ksub + j) * dsub, dsub);
-        } else if (by_residual == 2) {
-            for (int m = 0; m < M; ++m)
-                for (int j = 0; j < ksub; ++j)
-                    lut[m * ksub + j] =
-                        -2.f * ip_canon(qv + m * dsub, codebooks + ((int64_t)m * ksub + j) * dsub, dsub);
         }
         for (int p = 0; p < cn; ++p) {
             int l = (int)ch[p].tie;
             int64_t b = list_offsets[l], e = list_offsets[l + 1];
             if (b == e) continue;
-            if (by_residual == 2) {
-                const float* cen = centroids + (int64_t)l * d;
-                const float coarse = (float)ch[p].key;
-                for (int64_t v = b; v < e; ++v) {
-                    const uint8_t* c = codes + v * M;
-                    float t2 = 0.f;
-                    for (int m = 0; m < M; ++m) {
-                        const float* cw = codebooks + ((int64_t)m * ksub + c[m]) * dsub;
-                        t2 = t2 + fmaf(2.f, ip_canon(cen + m * dsub, cw, dsub), ip_canon(cw, cw, dsub));
-                    }
-                    float acc = coarse + t2;
-                    for (int m = 0; m < M; ++m) acc = acc + lut[m * ksub + c[m]];
-                    heap_offer(h, &n, k, (double)acc, ids[v]);
-                }
-                continue;
-            }
             if (by_residual) {
                 float r[4096];
                 const float* c = centroids + (int64_t)l * d;

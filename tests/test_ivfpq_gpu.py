@@ -1,10 +1,9 @@
 """GPU parity of IVFPQ (assignment, PQ encoding, three-stage search) against the CPU oracle.
 
-Raw-vector encoding (the reference's mode): codes, list contents, distances and ids bit-exact.
-Residual encoding (Faiss default): codes bit-exact; distances and ids bit-exact against the
-oracle's precomputed-table arithmetic (variant 2, what Faiss' use_precomputed_table computes,
-folded per vector) and within RESID_RTOL of the oracle's direct per-(query, list) tables -- the
-two differ by fp32 re-association only."""
+Both encodings -- raw vectors (the reference's mode) and residuals (Faiss default, one table per
+(query, list) in the oracle) -- must give codes, list contents, distances and ids that are
+bit-identical to the oracle: the GPU's scan is a filter whose survivors are re-computed in the
+oracle's canonical arithmetic and verified, with an exact re-scan for queries that fail the check."""
 import os
 
 import numpy as np
@@ -12,11 +11,9 @@ import pytest
 
 import oracle
 from indexsdk_b200 import datasets
-from helpers import assert_close_gap_aware, assert_exact
+from helpers import assert_exact
 
 pytestmark = pytest.mark.gpu
-# direct tables vs precomputed-table decomposition: error grows with |centroid| / |residual|
-RESID_RTOL = 5e-5
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
 
 
@@ -49,12 +46,7 @@ def test_golden_fixture(b200, tag, resid):
         np.testing.assert_array_equal(lid, idl[off[l]:off[l + 1]])
     ix.nprobe = 4
     D, I = ix.search(g["xq"], 10)
-    if resid:
-        assert_close_gap_aware(D, I, g[f"D_{tag}"], g[f"I_{tag}"], rtol=RESID_RTOL, what="ivfpq residual")
-        D2, I2 = oracle.ivfpq_search(g[f"cent_{tag}"], g[f"cb_{tag}"], 2, off, cs, idl, g["xq"], 4, 10)
-        assert_exact(D, I, D2, I2)
-    else:
-        assert_exact(D, I, g[f"D_{tag}"], g[f"I_{tag}"])
+    assert_exact(D, I, g[f"D_{tag}"], g[f"I_{tag}"])
 
 
 @pytest.mark.parametrize("resid", [False, True])
@@ -82,12 +74,7 @@ def test_search_vs_oracle(b200, resid, d, nlist, M, n, nq, nprobe, k, chunks):
     ix.nprobe = nprobe
     D, I = ix.search(xq, k)
     Dr, Ir = oracle.ivfpq_search(cent, cb, resid, off, cs, idl, xq, nprobe, k)
-    if resid:
-        assert_close_gap_aware(D, I, Dr, Ir, rtol=RESID_RTOL, what="ivfpq residual")
-        D2, I2 = oracle.ivfpq_search(cent, cb, 2, off, cs, idl, xq, nprobe, k)
-        assert_exact(D, I, D2, I2)
-    else:
-        assert_exact(D, I, Dr, Ir)
+    assert_exact(D, I, Dr, Ir)
 
 
 def test_empty_lists_duplicates_and_short_results(b200):
@@ -108,6 +95,43 @@ def test_empty_lists_duplicates_and_short_results(b200):
         assert_exact(D, I, Dr, Ir)
         padded |= bool((Ir[:, -1] == -1).any())
     assert padded                                 # nprobe=1, k=300 leaves padded tails
+
+
+@pytest.mark.parametrize("resid", [False, True])
+def test_more_duplicates_than_the_filter_keeps(b200, resid):
+    """200 copies of each vector: the filter keeps k' = 32 candidates per query, the top ties are
+    wider than that, verification must fail and the exact re-scan must return the lowest labels."""
+    d, nlist, M = 64, 8, 16
+    base, _ = datasets.mixture(40, d, 4, seed=3)
+    xb = np.repeat(base, 200, axis=0)
+    ids = np.random.default_rng(0).permutation(xb.shape[0]).astype(np.int64)
+    cent, cb = datasets.train_ivfpq(base, nlist, M, resid, niter=3)
+    ix = _build(b200, xb, ids, cent, cb, resid, chunks=2)
+    ln, codes, (off, cs, idl) = _oracle_lists(xb, ids, cent, cb, resid)
+    ix.nprobe = nlist
+    xq = base[:12]
+    D, I = ix.search(xq, 10)
+    Dr, Ir = oracle.ivfpq_search(cent, cb, resid, off, cs, idl, xq, nlist, 10)
+    assert_exact(D, I, Dr, Ir)
+    assert ix.stats()["fallback_queries"] == 12
+
+
+def test_exact_scan_kernels_alone(b200, monkeypatch):
+    """B200IDX_IVFPQ_EXACT=1 routes every query through the canonical-arithmetic scan kernels
+    (per-(query, list) tables in shared memory for residual encoding)."""
+    monkeypatch.setenv("B200IDX_IVFPQ_EXACT", "1")
+    d, nlist, M = 64, 32, 16
+    xb, _ = datasets.mixture(6000, d, 16, seed=4)
+    xq, _ = datasets.mixture(9, d, 16, seed=5, centers_seed=4)
+    ids = np.arange(6000, dtype=np.int64)
+    for resid in (False, True):
+        cent, cb = datasets.train_ivfpq(xb, nlist, M, resid, niter=3)
+        ix = _build(b200, xb, ids, cent, cb, resid)
+        ln, codes, (off, cs, idl) = _oracle_lists(xb, ids, cent, cb, resid)
+        ix.nprobe = 8
+        D, I = ix.search(xq, 20)
+        Dr, Ir = oracle.ivfpq_search(cent, cb, resid, off, cs, idl, xq, 8, 20)
+        assert_exact(D, I, Dr, Ir)
 
 
 def test_add_codes_reset_remove(b200):
@@ -140,7 +164,7 @@ def test_add_codes_reset_remove(b200):
     keep = ~np.isin(ids, [5, 6, 7])
     off2, cs2, idl2 = oracle.build_lists(ln[keep], codes[keep], ids[keep], nlist)
     D, I = ix.search(xq, 10)
-    Dr, Ir = oracle.ivfpq_search(cent, cb, 2, off2, cs2, idl2, xq, 8, 10)
+    Dr, Ir = oracle.ivfpq_search(cent, cb, True, off2, cs2, idl2, xq, 8, 10)
     assert_exact(D, I, Dr, Ir)
 
 
