@@ -504,7 +504,6 @@ def main():
     for _ in range(args.warmup):
         step_device()
         step_e2e()
-    wl.index.stats(reset=True)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -517,8 +516,11 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
     s2 = wl.index.stats()
 
+    # counters are cumulative: everything below is the difference over the device-resident region
     stats = dict(s1)
     stats["scan_codes_delta"] = s1["scan_codes"] - s0["scan_codes"]
+    stats["stage_ms"] = {n: s1["stage_ms"][n] - s0["stage_ms"][n] for n in s1["stage_ms"]}
+    stats["stage_launches"] = {n: s1["stage_launches"][n] - s0["stage_launches"][n] for n in s1["stage_launches"]}
     launches = s1["kernel_launches"] - s0["kernel_launches"] + (args.steps if world > 1 else 0)
     roof = wl.roofline(stats, args.steps, peaks)
 
@@ -535,8 +537,8 @@ def main():
                          d2h_bytes_per_step=int(nq * k * 12)),
                 gpu_launches=int(launches),
                 roofline=roof,
-                stage_ms_per_step={n: v / args.steps for n, v in s1["stage_ms"].items() if v > 0},
-                fallback_queries=s2["fallback_queries"],
+                stage_ms_per_step={n: v / args.steps for n, v in stats["stage_ms"].items() if v > 0},
+                fallback_queries_per_step=(s1["fallback_queries"] - s0["fallback_queries"]) / args.steps,
                 clocks=clocks)
 
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -83,16 +83,20 @@ constexpr int kLutCodes = 64;
 __global__ void __launch_bounds__(256)
 lut_group_kernel(const float* xq, int64_t nq, int d, int M, int dsub, const float* cb, int by_residual,
                  float* lut) {
-    extern __shared__ float lut_sm[];            // [16][kLutCodes][dsub] codebook slice, then [kLutQueries][16*dsub] queries
+    // [16][kLutCodes][dsub + 1] codebook slice (rows padded by one word: a warp's 32 codewords then
+    // start in 32 different banks), then [kLutQueries][16 * dsub] queries
+    extern __shared__ float lut_sm[];
     const int groups = M >> 4;
     const int g = blockIdx.y / (kKsub / kLutCodes);
     const int code0 = (blockIdx.y % (kKsub / kLutCodes)) * kLutCodes;
     const int64_t q0 = static_cast<int64_t>(blockIdx.x) * kLutQueries;
+    const int ds1 = dsub + 1;
     float* cbs = lut_sm;
-    float* qs = lut_sm + 16 * kLutCodes * dsub;
+    float* qs = lut_sm + 16 * kLutCodes * ds1;
     for (int i = threadIdx.x; i < 16 * kLutCodes * dsub; i += 256) {
         const int mm = i / (kLutCodes * dsub), rest = i % (kLutCodes * dsub);
-        cbs[i] = cb[(static_cast<int64_t>(g * 16 + mm) * kKsub + code0) * dsub + rest];
+        cbs[(mm * kLutCodes + rest / dsub) * ds1 + rest % dsub] =
+            cb[(static_cast<int64_t>(g * 16 + mm) * kKsub + code0) * dsub + rest];
     }
     const int qn = static_cast<int>(min(static_cast<int64_t>(kLutQueries), nq - q0));
     for (int i = threadIdx.x; i < qn * 16 * dsub; i += 256) {
@@ -108,7 +112,7 @@ lut_group_kernel(const float* xq, int64_t nq, int d, int M, int dsub, const floa
         for (int u = 0; u < 4; ++u) {
             const int mm = quarter * 4 + u;
             const float* qv = qs + qi * 16 * dsub + mm * dsub;
-            const float* c = cbs + (mm * kLutCodes + code) * dsub;
+            const float* c = cbs + (mm * kLutCodes + code) * ds1;
             float acc = 0.f;
             if (by_residual) {
                 for (int t = 0; t < dsub; ++t) acc = fmaf(qv[t], c[t], acc);
@@ -1084,7 +1088,7 @@ void IvfpqIndex::search_device(int64_t nq, const float* xq, int k, float* D, int
         timer_.begin(kStageLut, st);
         float* lut = static_cast<float*>(w_lut_.ensure(static_cast<size_t>(m) * M_ * kKsub * 4));
         if ((M_ & 15) == 0) {
-            const size_t lsm = (static_cast<size_t>(16) * kLutCodes * dsub_ + static_cast<size_t>(kLutQueries) * 16 * dsub_) * 4;
+            const size_t lsm = (static_cast<size_t>(16) * kLutCodes * (dsub_ + 1) + static_cast<size_t>(kLutQueries) * 16 * dsub_) * 4;
             B200_CUDA_CHECK(set_smem(lut_group_kernel, lsm));
             dim3 lgrid(blocks_for(m, kLutQueries), static_cast<unsigned>((M_ / 16) * (kKsub / kLutCodes)));
             lut_group_kernel<<<lgrid, 256, lsm, st>>>(xp, m, d_, M_, dsub_, codebooks_.as<float>(),

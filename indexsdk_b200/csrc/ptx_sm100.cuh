@@ -1,4 +1,4 @@
-// Thin inline-PTX layer for sm_100a: mbarrier, TMA (cp.async.bulk.tensor, no multicast),
+// Thin inline-PTX layer for sm_100a: mbarrier, TMA (cp.async.bulk.tensor into this CTA only),
 // tcgen05 (TMEM alloc, UMMA issue/commit, TMEM loads).  Every wait in this file is bounded:
 // a wait that runs out returns false and the caller records an error word and leaves.
 #pragma once

@@ -9,6 +9,7 @@ namespace b200 {
 namespace {
 
 constexpr int kSelThreads = 256;
+constexpr int kSmallSet = 512;   // candidate sets up to this size are ranked by counting
 
 // Inclusive scan of a 256-bin histogram held in shared memory; returns through `bucket`/`below`
 // the bin that contains rank r (1-based) and the number of elements in lower bins.
@@ -105,6 +106,24 @@ select_topk_kernel(const uint64_t* cand, const uint32_t* counts, uint32_t n_fixe
     uint32_t n = counts ? counts[q] : n_fixed;
     if (overflow && threadIdx.x == 0) overflow[q] = n > cap ? 1 : 0;
     if (n > cap) n = cap;
+    uint64_t* orow_fast = out + static_cast<int64_t>(q) * k;
+    if (n <= static_cast<uint32_t>(kSmallSet)) {
+        // Small candidate set (the common case after a tight threshold): stage it in shared
+        // memory and place every element by its rank, counted against all others.  Candidates
+        // are distinct (positions are unique), so ranks are a permutation.
+        __shared__ uint64_t small[kSmallSet];
+        for (uint32_t i = threadIdx.x; i < n; i += kSelThreads) small[i] = row[i];
+        for (int i = threadIdx.x; i < k; i += kSelThreads) orow_fast[i] = kCandInvalid;
+        __syncthreads();
+        for (uint32_t i = threadIdx.x; i < n; i += kSelThreads) {
+            const uint64_t v = small[i];
+            if (v == kCandInvalid) continue;
+            uint32_t rank = 0;
+            for (uint32_t j = 0; j < n; ++j) rank += small[j] < v ? 1u : 0u;
+            if (rank < static_cast<uint32_t>(k)) orow_fast[rank] = v;
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < P; i += kSelThreads) sorted[i] = kCandInvalid;
     if (threadIdx.x == 0) sh_fill = 0;
     __syncthreads();
