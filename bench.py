@@ -41,7 +41,11 @@ FALLBACK_BF16_TFLOPS = 1590.0
 
 # DRAM bytes per launch of the dominant kernel taken from an ncu capture (see profiles/);
 # None until a capture exists for the workload.
-NCU_TRAFFIC_BYTES = {"ivfpq10m": None, "flat1m": None, "int8flat4m": None}
+NCU_TRAFFIC_BYTES = {
+    "ivfpq10m": 1.764e9,     # profiles/ivfpq_fast_scan_kernel_ivfpq10m.md (full-size launch)
+    "flat1m": 2.69e8,        # profiles/dist_gemm_tc_kernel_flat_quarter.md, 67.3 MB at N = 250 k, x4
+    "int8flat4m": None,
+}
 
 
 def measured_peaks():
@@ -247,7 +251,7 @@ class IvfpqWorkload(Workload):
         alg = self.units_bytes_per_query * self.nq / max(1, self.world_size)
         ach = alg / (ms * 1e-3) / 1e9 if ms > 0 else None
         visited = stats["scan_codes_delta"] * self.M / max(1, stats["stage_launches"]["scan"])
-        return dict(bound="hbm", kernel="ivfpq_scan_kernel", achieved=ach, peak=peaks["hbm"], unit="GB/s",
+        return dict(bound="hbm", kernel="ivfpq_fast_scan_kernel", achieved=ach, peak=peaks["hbm"], unit="GB/s",
                     frac=(ach / peaks["hbm"]) if ach else None, peak_source=peaks["source"],
                     traffic=NCU_TRAFFIC_BYTES.get(self.name), algorithmic_bytes_per_launch=alg,
                     visited_code_bytes_per_launch=visited, ms_per_launch=ms)
