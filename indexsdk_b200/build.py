@@ -14,6 +14,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 BUILD_DIR = os.path.join(_HERE, "_build")
 LIB_PATH = os.path.join(BUILD_DIR, "libb200idx.so")
+SHIM_LIB_PATH = os.path.join(BUILD_DIR, "libb200idx_ascend.so")
 
 SOURCES = ["dist_gemm.cu", "select.cu", "flat_index.cu", "ivfpq_index.cu", "c_api.cu", "noalloc.cu"]
 NVCC_FLAGS = [
@@ -32,7 +33,8 @@ def _nvcc() -> str:
 
 def _digest() -> str:
     h = hashlib.sha256()
-    for root in (CSRC, os.path.join(_HERE, "..", "include")):
+    inc = os.path.join(_HERE, "..", "include")
+    for root in (CSRC, os.path.join(CSRC, "shim"), inc, os.path.join(inc, "b200")):
         for name in sorted(os.listdir(root)):
             p = os.path.join(root, name)
             if os.path.isfile(p):
@@ -69,6 +71,14 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if r.returncode:
         sys.stderr.write(r.stdout + r.stderr)
         raise RuntimeError("link failed")
+    # header-compatible faiss::ascend classes over the C ABI (host C++ only)
+    shim = os.path.join(CSRC, "shim", "ascend_api.cpp")
+    cmd = ["/usr/bin/g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-I", os.path.join(_HERE, "..", "include"),
+           shim, "-o", SHIM_LIB_PATH, "-L", BUILD_DIR, "-lb200idx", "-Wl,-rpath,$ORIGIN", "-lpthread"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError("building the faiss::ascend shim failed")
     with open(stamp, "w") as f:
         f.write(digest)
     return LIB_PATH
