@@ -142,6 +142,59 @@ static inline double ip_f64(const float* q, const float* y, int d) {
 }
 
 /*
+ * Blocked forms of the canonical kernels: ORC_B independent accumulator chains side by side
+ * (one per query, centroid or codeword of a block, operands transposed to [i][ORC_B]) so that
+ * the compiler can use one vector FMA per step.  Each chain performs exactly the operations of
+ * l2_canon / ip_canon in the same order, so results are bit-identical to the scalar forms.
+ */
+#define ORC_B 8
+static inline void l2_canon_qblock(const float* qT, const float* y, int d, float* acc) {
+    for (int b = 0; b < ORC_B; ++b) acc[b] = 0.f;
+    for (int i = 0; i < d; ++i) {
+        const float yi = y[i];
+#pragma omp simd
+        for (int b = 0; b < ORC_B; ++b) {
+            float t = qT[i * ORC_B + b] - yi;
+            acc[b] = fmaf(t, t, acc[b]);
+        }
+    }
+}
+static inline void ip_canon_qblock(const float* qT, const float* y, int d, float* acc) {
+    for (int b = 0; b < ORC_B; ++b) acc[b] = 0.f;
+    for (int i = 0; i < d; ++i) {
+        const float yi = y[i];
+#pragma omp simd
+        for (int b = 0; b < ORC_B; ++b) acc[b] = fmaf(qT[i * ORC_B + b], yi, acc[b]);
+    }
+}
+/* one query against a block of ORC_B rows stored transposed yT[i][ORC_B] */
+static inline void l2_canon_yblock(const float* q, const float* yT, int d, float* acc) {
+    for (int b = 0; b < ORC_B; ++b) acc[b] = 0.f;
+    for (int i = 0; i < d; ++i) {
+        const float qi = q[i];
+#pragma omp simd
+        for (int b = 0; b < ORC_B; ++b) {
+            float t = qi - yT[i * ORC_B + b];
+            acc[b] = fmaf(t, t, acc[b]);
+        }
+    }
+}
+/* rows [n][d] -> blocks [ceil(n/ORC_B)][d][ORC_B]; rows past n repeat the last row */
+static float* transpose_blocks(const float* x, int64_t n, int d) {
+    int64_t nb = (n + ORC_B - 1) / ORC_B;
+    float* t = (float*)malloc(sizeof(float) * (size_t)nb * d * ORC_B);
+    if (!t) return NULL;
+    for (int64_t blk = 0; blk < nb; ++blk)
+        for (int i = 0; i < d; ++i)
+            for (int b = 0; b < ORC_B; ++b) {
+                int64_t r = blk * ORC_B + b;
+                if (r >= n) r = n - 1;
+                t[(blk * d + i) * ORC_B + b] = x[r * d + i];
+            }
+    return t;
+}
+
+/*
  * Exact Flat search.  precise = 0: canonical fp32 arithmetic (bit-comparable with the
  * GPU fp32 mode); precise = 1: fp64 accumulation rounded to fp32 once (used to bound
  * the error of every lower-precision mode).  labels: optional nb entries mapping
@@ -151,6 +204,37 @@ int orc_flat_search(int metric, int d, int64_t nb, const float* xb, const int64_
                     int64_t nq, const float* xq, int k, int precise, float* D, int64_t* I) {
     if (d <= 0 || nb < 0 || nq < 0 || k <= 0) return -1;
     int fail = 0;
+    if (!precise && nq > 0) {
+        /* blocks of ORC_B queries share every pass over the base */
+        float* qT = transpose_blocks(xq, nq, d);
+        if (!qT) return -2;
+        const int64_t nblk = (nq + ORC_B - 1) / ORC_B;
+#pragma omp parallel for schedule(dynamic, 1)
+        for (int64_t blk = 0; blk < nblk; ++blk) {
+            orc_item* h = (orc_item*)malloc(sizeof(orc_item) * (size_t)k * ORC_B);
+            if (!h) { fail = 1; continue; }
+            int n[ORC_B] = {0};
+            const float* qb = qT + blk * d * ORC_B;
+            const int live = (int)((nq - blk * ORC_B) < ORC_B ? (nq - blk * ORC_B) : ORC_B);
+            float acc[ORC_B];
+            for (int64_t j = 0; j < nb; ++j) {
+                if (metric == ORC_METRIC_L2) l2_canon_qblock(qb, xb + j * d, d, acc);
+                else ip_canon_qblock(qb, xb + j * d, d, acc);
+                for (int b = 0; b < live; ++b)
+                    heap_offer(h + (size_t)b * k, &n[b], k, metric == ORC_METRIC_L2 ? (double)acc[b] : -(double)acc[b], j);
+            }
+            for (int b = 0; b < live; ++b) {
+                const int64_t q = blk * ORC_B + b;
+                heap_emit(h + (size_t)b * k, n[b], k, metric != ORC_METRIC_L2, D + q * k, I + q * k);
+                if (labels)
+                    for (int j = 0; j < k; ++j)
+                        if (I[q * k + j] >= 0) I[q * k + j] = labels[I[q * k + j]];
+            }
+            free(h);
+        }
+        free(qT);
+        return fail ? -2 : 0;
+    }
 #pragma omp parallel for schedule(dynamic, 1)
     for (int64_t q = 0; q < nq; ++q) {
         orc_item* h = (orc_item*)malloc(sizeof(orc_item) * (size_t)k);
@@ -298,6 +382,11 @@ int orc_ivfpq_search(int d, int nlist, int M, int ksub, const float* centroids,
     if (nprobe > nlist) nprobe = nlist;
     int dsub = d / M;
     int fail = 0;
+    /* transposed copies: centroids in blocks of ORC_B rows, each sub-codebook in blocks of
+       ORC_B codewords, so the canonical per-row sums run ORC_B at a time */
+    float* cT = transpose_blocks(centroids, nlist, d);
+    float* cbT = transpose_blocks(codebooks, (int64_t)M * ksub, dsub);
+    if (!cT || !cbT || ksub % ORC_B) { free(cT); free(cbT); return ksub % ORC_B ? -1 : -2; }
 #pragma omp parallel for schedule(dynamic, 1)
     for (int64_t q = 0; q < nq; ++q) {
         const float* qv = xq + q * d;
@@ -306,16 +395,20 @@ int orc_ivfpq_search(int d, int nlist, int M, int ksub, const float* centroids,
         float* lut = (float*)malloc(sizeof(float) * (size_t)M * ksub);
         if (!ch || !h || !lut) { fail = 1; free(ch); free(h); free(lut); continue; }
         int cn = 0;
-        for (int l = 0; l < nlist; ++l)
-            heap_offer(ch, &cn, nprobe, (double)l2_canon(qv, centroids + (int64_t)l * d, d), l);
+        for (int l0 = 0; l0 < nlist; l0 += ORC_B) {
+            float acc[ORC_B];
+            l2_canon_yblock(qv, cT + (int64_t)(l0 / ORC_B) * d * ORC_B, d, acc);
+            for (int b = 0; b < ORC_B && l0 + b < nlist; ++b) heap_offer(ch, &cn, nprobe, (double)acc[b], l0 + b);
+        }
         qsort(ch, (size_t)cn, sizeof(orc_item), item_cmp);
         if (coarse_out)
             for (int p = 0; p < nprobe; ++p) coarse_out[q * nprobe + p] = p < cn ? (int32_t)ch[p].tie : -1;
         int n = 0;
         if (!by_residual) {
             for (int m = 0; m < M; ++m)
-                for (int j = 0; j < ksub; ++j)
-                    lut[m * ksub + j] = l2_canon(qv + m * dsub, codebooks + ((int64_t)m * ksub + j) * dsub, dsub);
+                for (int j = 0; j < ksub; j += ORC_B)
+                    l2_canon_yblock(qv + m * dsub, cbT + (int64_t)((m * ksub + j) / ORC_B) * dsub * ORC_B, dsub,
+                                    lut + m * ksub + j);
         }
         for (int p = 0; p < cn; ++p) {
             int l = (int)ch[p].tie;
@@ -326,8 +419,9 @@ int orc_ivfpq_search(int d, int nlist, int M, int ksub, const float* centroids,
                 const float* c = centroids + (int64_t)l * d;
                 for (int t = 0; t < d; ++t) r[t] = qv[t] - c[t];
                 for (int m = 0; m < M; ++m)
-                    for (int j = 0; j < ksub; ++j)
-                        lut[m * ksub + j] = l2_canon(r + m * dsub, codebooks + ((int64_t)m * ksub + j) * dsub, dsub);
+                    for (int j = 0; j < ksub; j += ORC_B)
+                        l2_canon_yblock(r + m * dsub, cbT + (int64_t)((m * ksub + j) / ORC_B) * dsub * ORC_B, dsub,
+                                        lut + m * ksub + j);
             }
             for (int64_t v = b; v < e; ++v) {
                 const uint8_t* c = codes + v * M;
@@ -339,6 +433,7 @@ int orc_ivfpq_search(int d, int nlist, int M, int ksub, const float* centroids,
         heap_emit(h, n, k, 0, D + q * k, I + q * k);
         free(ch); free(h); free(lut);
     }
+    free(cT); free(cbT);
     return fail ? -2 : 0;
 }
 
