@@ -207,13 +207,21 @@ FlatIndex::Plan FlatIndex::make_plan(int k) const {
     const int64_t n_tiles = (n_ + kTileB - 1) / kTileB;
     const int64_t need = std::max<int64_t>(4LL * k, 1024);
     p.sampled = false;
-    if (n_tiles <= 256 && n_tiles >= 8 && need <= n_tiles * (kTileB / 8)) {
-        // Small base (e.g. an IVF coarse quantizer): the "sample" is the whole base with bursts
-        // of 8.  A second cheap GEMM pass buys a threshold that admits ~k candidates instead of
-        // ~k / fraction, which is what the refinement and selection kernels pay for.
-        p.sampled = true;
-        p.burst = 8;
-        p.s_tiles = static_cast<int>(n_tiles);
+    if (n_tiles <= 256 && n_tiles >= 8) {
+        // Small base (e.g. an IVF coarse quantizer): the "sample" is the whole base, so the k-th
+        // smallest burst minimum is a certain upper bound of the k-th smallest key and admits
+        // little more than k candidates as long as bursts are plentiful against k (with k / bursts
+        // = 1/8 and bursts of 32 about 1.07 k keys pass).  A second cheap GEMM pass is what the
+        // refinement and selection kernels then do not pay for.
+        const int64_t b32 = n_tiles * (kTileB / 32), b8 = n_tiles * (kTileB / 8);
+        if (8LL * k <= b32) {
+            p.sampled = true;
+            p.burst = 32;
+        } else if (4LL * k <= b8) {
+            p.sampled = true;
+            p.burst = 8;
+        }
+        if (p.sampled) p.s_tiles = static_cast<int>(n_tiles);
     }
     for (int burst : {32, 8}) {
         if (p.sampled) break;

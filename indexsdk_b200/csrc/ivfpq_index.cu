@@ -4,9 +4,10 @@
 //          the same tcgen05 distance GEMM, filter + fp32 refinement, so probe lists and their
 //          distances are the canonical fp32 values (replaces DistanceFlatL2MinsAtFP32 +
 //          TopkFlatFp32, FR/ascenddaemon/impl/IndexIVFPQ.cpp:2104-2164).
-// Stage 2  lookup tables, one [M][256] fp32 table per query (replaces
-//          AscendcIvfpqSubspaceDistance, FR/ops/ascendc/op_kernel/
-//          ascendc_ivfpq_subspace_distance.cpp:46-617).
+// Stage 2  lookup tables (replaces AscendcIvfpqSubspaceDistance, FR/ops/ascendc/op_kernel/
+//          ascendc_ivfpq_subspace_distance.cpp:46-617): never materialised in HBM -- every scan CTA
+//          builds its query's [M][256] fp32 table straight into shared memory from a regrouped
+//          copy of the codebooks (L2-resident), which costs about 1 % of the scan's instructions.
 //            raw encoding      : T[m][j] = |q_m - cb[m][j]|^2
 //            residual encoding : T[m][j] = -2 q_m . cb[m][j]; the list-dependent remainder
 //              |cb|^2 + 2 c_list . cb is summed over a vector's codes once, at add time, into one
@@ -23,14 +24,14 @@
 //                The fp32 sum therefore runs in a rotated order; it is used as a FILTER: each warp
 //                keeps the k' = 32 * KPT best (approximate distance, position) in registers.
 //            3b  ivfpq_refine_kernel: the k' survivors per query are re-computed in the oracle's
-//                canonical arithmetic (raw: table entries summed in ascending m; residual: the
+//                canonical arithmetic (raw: sum_m |q_m - cb[m][code_m]|^2 in ascending m; residual: the
 //                direct form sum_m |(q - c)_m - cb[m][code_m]|^2), ordered by (distance, label),
 //                and the result is VERIFIED: it is accepted only if the exact k-th distance lies
 //                below (worst kept approximate distance - error bound); otherwise the query is
 //                flagged.
 //            3c  ivfpq_exact_scan_kernel: flagged queries (heavy ties, more duplicates than k')
-//                are re-scanned in canonical arithmetic -- for residual encoding with one table
-//                per (query, list) built in shared memory from q - c_list.
+//                are re-scanned in canonical arithmetic with a canonical table built in shared
+//                memory -- one per query (raw) or one per (query, list) from q - c_list (residual).
 //          Results are therefore bit-identical to the CPU oracle for both encodings.
 #include "ivfpq_index.h"
 
@@ -53,11 +54,6 @@ constexpr float kInf = 3.402823466e+38f;   // FLT_MAX used as padding distance
 constexpr uint32_t kNoPos = 0xFFFFFFFFu;
 constexpr int64_t kNoLabel = 0x7fffffffffffffffll;
 
-// Position of entry (m, code) inside one query's table.  M % 16 == 0: [m / 16][code][m % 16]
-// (the scan's layout minus the replication); otherwise [m][code].
-__host__ __device__ __forceinline__ int lut_index(int M, int m, int code) {
-    return (M & 15) == 0 ? ((m >> 4) * (kKsub * 16) + code * 16 + (m & 15)) : (m * kKsub + code);
-}
 // Byte offset of sub-quantizer m inside the stored code of the vector at `pos`.
 __device__ __forceinline__ int code_byte(bool rotated, int m, int64_t pos) {
     return rotated ? ((m & ~15) | ((m - static_cast<int>(pos & 15)) & 15)) : m;
@@ -70,89 +66,6 @@ __global__ void cb_norm_kernel(const float* cb, int M, int dsub, float* out) {
     float acc = 0.f;
     for (int t = 0; t < dsub; ++t) acc = fmaf(c[t], c[t], acc);
     out[idx] = acc;
-}
-
-// Table entries in lut_index() order, M % 16 == 0.  A CTA owns one 64-code slice of one group of
-// 16 sub-quantizers: it stages that slice of the codebook (16 x 64 x dsub floats) in shared memory
-// once and then produces the slice's entries for kLutQueries queries, so the codebook crosses L2
-// once per kLutQueries queries instead of once per query.  Thread (code, quarter) computes the four
-// adjacent entries m = 16 g + 4 quarter .. + 3 of its code and stores them as one float4; a warp
-// writes 512 contiguous bytes.
-constexpr int kLutQueries = 32;
-constexpr int kLutCodes = 64;
-__global__ void __launch_bounds__(256)
-lut_group_kernel(const float* xq, int64_t nq, int d, int M, int dsub, const float* cb, int by_residual,
-                 float* lut) {
-    // [16][kLutCodes][dsub + 1] codebook slice (rows padded by one word: a warp's 32 codewords then
-    // start in 32 different banks), then [kLutQueries][16 * dsub] queries
-    extern __shared__ float lut_sm[];
-    const int groups = M >> 4;
-    const int g = blockIdx.y / (kKsub / kLutCodes);
-    const int code0 = (blockIdx.y % (kKsub / kLutCodes)) * kLutCodes;
-    const int64_t q0 = static_cast<int64_t>(blockIdx.x) * kLutQueries;
-    const int ds1 = dsub + 1;
-    float* cbs = lut_sm;
-    float* qs = lut_sm + 16 * kLutCodes * ds1;
-    for (int i = threadIdx.x; i < 16 * kLutCodes * dsub; i += 256) {
-        const int mm = i / (kLutCodes * dsub), rest = i % (kLutCodes * dsub);
-        cbs[(mm * kLutCodes + rest / dsub) * ds1 + rest % dsub] =
-            cb[(static_cast<int64_t>(g * 16 + mm) * kKsub + code0) * dsub + rest];
-    }
-    const int qn = static_cast<int>(min(static_cast<int64_t>(kLutQueries), nq - q0));
-    for (int i = threadIdx.x; i < qn * 16 * dsub; i += 256) {
-        const int qi = i / (16 * dsub), rest = i % (16 * dsub);
-        qs[i] = xq[(q0 + qi) * d + g * 16 * dsub + rest];
-    }
-    __syncthreads();
-    const int code = threadIdx.x & (kLutCodes - 1);
-    const int quarter = threadIdx.x / kLutCodes;        // 0..3
-    for (int qi = 0; qi < qn; ++qi) {
-        float out[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int mm = quarter * 4 + u;
-            const float* qv = qs + qi * 16 * dsub + mm * dsub;
-            const float* c = cbs + (mm * kLutCodes + code) * ds1;
-            float acc = 0.f;
-            if (by_residual) {
-                for (int t = 0; t < dsub; ++t) acc = fmaf(qv[t], c[t], acc);
-                acc = -2.f * acc;
-            } else {
-                for (int t = 0; t < dsub; ++t) {
-                    const float df = qv[t] - c[t];
-                    acc = fmaf(df, df, acc);
-                }
-            }
-            out[u] = acc;
-        }
-        float4* dst = reinterpret_cast<float4*>(lut + (q0 + qi) * M * kKsub + g * (kKsub * 16) + (code0 + code) * 16 +
-                                                quarter * 4);
-        *dst = make_float4(out[0], out[1], out[2], out[3]);
-    }
-    (void)groups;
-}
-
-// Any M: one thread per entry, [m][code] layout.
-__global__ void lut_kernel(const float* xq, int64_t nq, int d, int M, int dsub, const float* cb, int by_residual,
-                           float* lut) {
-    const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (idx >= nq * M * kKsub) return;
-    const int j = static_cast<int>(idx % kKsub);
-    const int m = static_cast<int>((idx / kKsub) % M);
-    const int64_t q = idx / (static_cast<int64_t>(kKsub) * M);
-    const float* qv = xq + q * d + m * dsub;
-    const float* c = cb + (static_cast<int64_t>(m) * kKsub + j) * dsub;
-    float acc = 0.f;
-    if (by_residual) {
-        for (int t = 0; t < dsub; ++t) acc = fmaf(qv[t], c[t], acc);
-        acc = -2.f * acc;
-    } else {
-        for (int t = 0; t < dsub; ++t) {
-            const float df = qv[t] - c[t];
-            acc = fmaf(df, df, acc);
-        }
-    }
-    lut[q * M * kKsub + m * kKsub + j] = acc;
 }
 
 // PQ encode: one warp per (vector, sub-quantizer); exhaustive nearest codeword under the
@@ -323,7 +236,7 @@ __device__ __forceinline__ void block_sort_pairs(float* sd, L* sl, int E) {
 }
 
 struct ScanArgs {
-    const float* lut;        // [nq][M * 256] in lut_index() order
+    const float* cbT;        // codebooks regrouped [M / 16][256][16][dsub] (fast scan only)
     const int64_t* cI;       // [nq][nprobe] probed list ids (-1 = none)
     const float* cD;         // [nq][nprobe] coarse distances
     int nprobe;
@@ -383,8 +296,65 @@ struct GroupSum<MT, MT> {
     static __device__ __forceinline__ void run(const uint4 (&)[MT], const uint32_t (&)[16], float&) {}
 };
 
+// Filter table of query q in shared memory, [g][code][32]: entry (m, code) sits in column m % 16 of
+// row (m / 16, code) and again 16 columns on.
+//   raw encoding      : |q_m - cb[m][code]|^2        residual encoding : -2 q_m . cb[m][code]
+// Lane l owns sub-quantizer l % 16; the two half-warps take adjacent codes, so a warp reads 32 * dsub
+// contiguous floats of the regrouped codebook per step and its two stores touch 32 distinct banks.
+// DS = dsub at compile time (query slice in registers), DS = 0: any dsub.
+template <int DS>
+__device__ __forceinline__ void build_scan_table(const ScanArgs& a, int64_t q, int groups, float* lut) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int mm = lane & 15, half = lane >> 4;
+    const int dsub = DS > 0 ? DS : a.dsub;
+    for (int g = 0; g < groups; ++g) {
+        const float* qrow = a.xq + q * a.d + (g * 16 + mm) * dsub;
+        float qr[DS > 0 ? DS : 1];
+        if (DS > 0) {
+#pragma unroll
+            for (int t = 0; t < DS; ++t) qr[t] = __ldg(qrow + t);
+        }
+#pragma unroll 4
+        for (int c = 2 * warp + half; c < kKsub; c += 2 * kScanWarps) {
+            const float* cw = a.cbT + (static_cast<size_t>(g * kKsub + c) * 16 + mm) * dsub;
+            float acc = 0.f;
+            if (DS > 0 && DS % 4 == 0) {
+#pragma unroll
+                for (int t4 = 0; t4 < DS / 4; ++t4) {
+                    const float4 cv = __ldg(reinterpret_cast<const float4*>(cw) + t4);
+                    const float c4[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        if (a.by_residual) {
+                            acc = fmaf(qr[t4 * 4 + u], c4[u], acc);
+                        } else {
+                            const float df = qr[t4 * 4 + u] - c4[u];
+                            acc = fmaf(df, df, acc);
+                        }
+                    }
+                }
+            } else {
+                for (int t = 0; t < dsub; ++t) {
+                    const float qt = __ldg(qrow + t);
+                    const float ct = __ldg(cw + t);
+                    if (a.by_residual) {
+                        acc = fmaf(qt, ct, acc);
+                    } else {
+                        const float df = qt - ct;
+                        acc = fmaf(df, df, acc);
+                    }
+                }
+            }
+            if (a.by_residual) acc = -2.f * acc;
+            float* row = lut + (g * kKsub + c) * 32;
+            row[mm + 16 * half] = acc;
+            row[mm + 16 * (half ^ 1)] = acc;
+        }
+    }
+}
+
 template <int MT, int KPT>
-__global__ void __launch_bounds__(kScanThreads)
+__global__ void __launch_bounds__(kScanThreads, (MT == 1 && KPT <= 2) ? 6 : 1)
 ivfpq_fast_scan_kernel(const ScanArgs a) {
     extern __shared__ __align__(16) uint8_t scan_smem[];
     float* lut = reinterpret_cast<float*>(scan_smem);   // [MT][256][32]
@@ -393,15 +363,14 @@ ivfpq_fast_scan_kernel(const ScanArgs a) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int M = MT * 16;
 
-    {   // table: global [g][code][16] -> shared [g][code][32] with the 16 entries replicated
-        const float4* src = reinterpret_cast<const float4*>(a.lut + q * M * kKsub);
-        for (int i = threadIdx.x; i < MT * kKsub * 4; i += kScanThreads) {
-            const float4 v = __ldg(src + i);
-            const int row = i >> 2, part = i & 3;          // row = g * 256 + code
-            float4* dst = reinterpret_cast<float4*>(lut + row * 32 + part * 4);
-            dst[0] = v;
-            dst[4] = v;                                     // + 16 floats
-        }
+    // Smallest "worst kept distance" of any warp of this CTA whose list is full (float bits, >= 0):
+    // nothing above it can reach the CTA's k' best, so every warp also filters with it.
+    int& s_gth = *reinterpret_cast<int*>(scan_smem + static_cast<size_t>(MT) * kKsub * 32 * 4);
+    if (threadIdx.x == 0) s_gth = 0x7f800000;
+    switch (a.dsub) {
+        case 4: build_scan_table<4>(a, q, MT, lut); break;
+        case 8: build_scan_table<8>(a, q, MT, lut); break;
+        default: build_scan_table<0>(a, q, MT, lut); break;
     }
     __syncthreads();
 
@@ -447,7 +416,7 @@ ivfpq_fast_scan_kernel(const ScanArgs a) {
         int li = -1;
         uint32_t begin = 0, end = 0, v0 = 0;
         float base = 0.f;
-        constexpr int U = 2;                 // 32-vector sub-chunks per loop iteration
+        constexpr int U = 2;                 // 32-vector sub-chunks per chunk
         auto advance = [&]() -> bool {      // moves (li, v0) to the next chunk; false when the batch is done
             v0 += 32 * U;
             while (li < 0 || v0 >= end) {
@@ -461,53 +430,75 @@ ivfpq_fast_scan_kernel(const ScanArgs a) {
             }
             return true;
         };
-        uint4 cn[U][MT];
-        float tn[U];
-        auto fetch = [&](uint32_t vv0, uint32_t b, uint32_t e) {
+        // One chunk in flight: codes, the per-vector term and where it came from.  Lanes outside
+        // the list read a clamped (valid) address and carry NaN, which fails every comparison, so
+        // the lookups and the threshold test run without any per-lane validity branch.
+        struct Chunk {
+            uint4 c[U][MT];
+            float t[U];      // per-vector term (loaded; consumed only when the chunk is processed)
+            float bias[U];   // the list's term, or NaN for a lane outside the list
+            uint32_t v0;
+        };
+        auto fetch = [&](Chunk& ch) {
+            ch.v0 = v0;
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const uint32_t v = vv0 + 32 * u + lane;
-                tn[u] = 0.f;
-                if (v >= b && v < e) {
-                    const uint4* cp = codes4 + static_cast<size_t>(v) * MT;
+                const uint32_t v = v0 + 32 * u + lane;
+                const bool valid = (v - begin) < (end - begin);
+                const uint32_t vc = min(max(v, begin), end - 1);
+                const uint4* cp = codes4 + static_cast<size_t>(vc) * MT;
 #pragma unroll
-                    for (int g = 0; g < MT; ++g) cn[u][g] = __ldg(cp + g);
-                    if (a.by_residual) tn[u] = __ldg(a.t2 + v);
-                }
+                for (int g = 0; g < MT; ++g) ch.c[u][g] = __ldg(cp + g);
+                ch.t[u] = a.by_residual ? __ldg(a.t2 + vc) : 0.f;
+                ch.bias[u] = valid ? base : __int_as_float(0x7fc00000);
             }
         };
-        bool have = advance();
-        if (have) fetch(v0, begin, end);
-        while (have) {
-            const uint32_t cv0 = v0, cbegin = begin, cend = end;
+        auto process = [&](const Chunk& ch) {
+            // the CTA-wide bound is read before the lookups and used after them
+            const float lim = fminf(th_d, __int_as_float(*reinterpret_cast<volatile int*>(&s_gth)));
             float acc[U];
-            uint4 cc[U][MT];
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                acc[u] = base + tn[u];
+            for (int u = 0; u < U; ++u) acc[u] = ch.bias[u] + ch.t[u];
 #pragma unroll
-                for (int g = 0; g < MT; ++g) cc[u][g] = cn[u][g];
-            }
-            // next chunk's loads are in flight while this one is processed
-            have = advance();
-            if (have) fetch(v0, begin, end);
+            for (int u = 0; u < U; ++u) GroupSum<0, MT>::run(ch.c[u], offb, acc[u]);
+            bool maybe = false;
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const uint32_t v = cv0 + 32 * u + lane;     // v & 15 == lane & 15: the stored rotation
-                const bool valid = v >= cbegin && v < cend;
-                if (valid) GroupSum<0, MT>::run(cc[u], offb, acc[u]);
-                const bool pass = valid && pair_less<uint32_t>(acc[u], v, th_d, th_p);
-                unsigned bal = __ballot_sync(0xffffffffu, pass);
-                while (bal) {
-                    const int src = __ffs(bal) - 1;
-                    bal &= bal - 1;
-                    const float vd = __shfl_sync(0xffffffffu, acc[u], src);
-                    const uint32_t vp = __shfl_sync(0xffffffffu, v, src);
-                    warp_insert<KPT, uint32_t>(dk, pk, vd, vp, lane);
-                    th_d = __shfl_sync(0xffffffffu, dk[KPT - 1], 31);
-                    th_p = __shfl_sync(0xffffffffu, pk[KPT - 1], 31);
+            for (int u = 0; u < U; ++u) maybe |= acc[u] <= lim;
+            if (__any_sync(0xffffffffu, maybe)) {
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const uint32_t v = ch.v0 + 32 * u + lane;   // v & 15 == lane & 15: the stored rotation
+                    const bool pass = acc[u] <= lim && pair_less<uint32_t>(acc[u], v, th_d, th_p);
+                    unsigned bal = __ballot_sync(0xffffffffu, pass);
+                    while (bal) {
+                        const int src = __ffs(bal) - 1;
+                        bal &= bal - 1;
+                        const float vd = __shfl_sync(0xffffffffu, acc[u], src);
+                        const uint32_t vp = __shfl_sync(0xffffffffu, v, src);
+                        if (pair_less<uint32_t>(vd, vp, th_d, th_p)) {
+                            warp_insert<KPT, uint32_t>(dk, pk, vd, vp, lane);
+                            th_d = __shfl_sync(0xffffffffu, dk[KPT - 1], 31);
+                            th_p = __shfl_sync(0xffffffffu, pk[KPT - 1], 31);
+                        }
+                    }
                 }
+                // a full list bounds what the whole CTA still needs: publish its worst distance
+                // (clamped at 0 so that the integer minimum orders like the float)
+                if (lane == 0 && th_d < lim) atomicMin(&s_gth, __float_as_int(fmaxf(th_d, 0.f)));
             }
+        };
+        Chunk ca, cb;
+        bool have = advance();
+        if (have) fetch(ca);
+        while (have) {
+            // the next chunk's loads are in flight while this one is processed
+            have = advance();
+            if (have) fetch(cb);
+            process(ca);
+            if (!have) break;
+            have = advance();
+            if (have) fetch(ca);
+            process(cb);
         }
     }
     if (a.scanned && visited) atomicAdd(a.scanned, visited);
@@ -543,9 +534,17 @@ __device__ __forceinline__ float exact_distance(const ScanArgs& a, int64_t q, in
     const uint8_t* code = a.codes + pos * a.M;
     float acc = 0.f;
     if (!a.by_residual) {
-        const float* lut = a.lut + q * a.M * kKsub;
-        for (int m = 0; m < a.M; ++m)
-            acc = acc + lut[lut_index(a.M, m, code[code_byte(a.rotated != 0, m, pos)])];
+        const float* qv = a.xq + q * a.d;
+        for (int m = 0; m < a.M; ++m) {
+            const float* cw = a.codebooks +
+                              (static_cast<int64_t>(m) * kKsub + code[code_byte(a.rotated != 0, m, pos)]) * a.dsub;
+            float e = 0.f;
+            for (int t = 0; t < a.dsub; ++t) {
+                const float df = qv[m * a.dsub + t] - cw[t];
+                e = fmaf(df, df, e);
+            }
+            acc = acc + e;
+        }
     } else {
         const float* qv = a.xq + q * a.d;
         const float* cen = a.centroids + list * a.d;
@@ -650,10 +649,23 @@ ivfpq_exact_scan_kernel(const ScanArgs a) {
     const int M = a.M;
     const bool rotated = a.rotated != 0;
 
+    // Canonical table of `resid` (the query, or the query minus a list's centroid): [m][code].
+    auto build_table = [&]() {
+        for (int i = threadIdx.x; i < M * kKsub; i += kScanThreads) {
+            const int m = i / kKsub;
+            const float* cw = a.codebooks + static_cast<int64_t>(i) * a.dsub;
+            float e = 0.f;
+            for (int t = 0; t < a.dsub; ++t) {
+                const float df = resid[m * a.dsub + t] - cw[t];
+                e = fmaf(df, df, e);
+            }
+            lut[i] = e;
+        }
+    };
     if (!a.by_residual) {
-        const float* src = a.lut + q * M * kKsub;
-        for (int i = threadIdx.x; i < M * kKsub; i += kScanThreads)
-            lut[i] = src[lut_index(M, i / kKsub, i % kKsub)];
+        for (int t = threadIdx.x; t < a.d; t += kScanThreads) resid[t] = a.xq[q * a.d + t];
+        __syncthreads();
+        build_table();
     }
     float dk[KPT];
     int64_t lb[KPT];
@@ -675,16 +687,7 @@ ivfpq_exact_scan_kernel(const ScanArgs a) {
             for (int t = threadIdx.x; t < a.d; t += kScanThreads)
                 resid[t] = a.xq[q * a.d + t] - a.centroids[list * a.d + t];
             __syncthreads();
-            for (int i = threadIdx.x; i < M * kKsub; i += kScanThreads) {
-                const int m = i / kKsub;
-                const float* cw = a.codebooks + static_cast<int64_t>(i) * a.dsub;
-                float e = 0.f;
-                for (int t = 0; t < a.dsub; ++t) {
-                    const float df = resid[m * a.dsub + t] - cw[t];
-                    e = fmaf(df, df, e);
-                }
-                lut[i] = e;
-            }
+            build_table();
         }
         __syncthreads();
         for (int64_t v0 = begin + warp * 32; v0 < end; v0 += kScanThreads) {
@@ -740,7 +743,8 @@ cudaError_t set_smem(Kern kern, size_t smem) {
 
 template <int MT>
 cudaError_t launch_fast_mt(const ScanArgs& a, int kpt, cudaStream_t st) {
-    const size_t smem = std::max(static_cast<size_t>(MT) * kKsub * 32 * 4, static_cast<size_t>(kScanThreads) * kpt * 8);
+    // table + the CTA-wide bound; reused for the final merge
+    const size_t smem = std::max(static_cast<size_t>(MT) * kKsub * 32 * 4 + 16, static_cast<size_t>(kScanThreads) * kpt * 8);
     dim3 grid(static_cast<unsigned>(a.nq), static_cast<unsigned>(a.S));
 #define B200_FAST_CASE(KP)                                           \
     case KP: {                                                       \
@@ -858,6 +862,17 @@ void IvfpqIndex::set_codebooks(const float* cb) {
         acc += mx;
     }
     cb_norm_bound_ = static_cast<float>(std::sqrt(acc) * 1.0001);
+    if (rotated_) {
+        // [M / 16][256][16][dsub]: the 16 codewords (one per sub-quantizer of a group) that share a
+        // code value lie together, the order in which the scan kernel builds its table
+        std::vector<float> t(static_cast<size_t>(M_) * kKsub * dsub_);
+        for (int m = 0; m < M_; ++m)
+            for (int j = 0; j < kKsub; ++j)
+                std::memcpy(&t[((static_cast<size_t>(m >> 4) * kKsub + j) * 16 + (m & 15)) * dsub_],
+                            cb + (static_cast<size_t>(m) * kKsub + j) * dsub_, static_cast<size_t>(dsub_) * 4);
+        codebooks_t_.ensure(bytes);
+        B200_CUDA_CHECK(cudaMemcpy(codebooks_t_.get(), t.data(), bytes, cudaMemcpyHostToDevice));
+    }
     has_codebooks_ = true;
 }
 
@@ -1085,23 +1100,8 @@ void IvfpqIndex::search_device(int64_t nq, const float* xq, int k, float* D, int
         timer_.begin(kStageCoarse, st);
         coarse_->search_device(m, xp, false, nprobe, cD, cI, nprobe);
         timer_.end(st);
-        timer_.begin(kStageLut, st);
-        float* lut = static_cast<float*>(w_lut_.ensure(static_cast<size_t>(m) * M_ * kKsub * 4));
-        if ((M_ & 15) == 0) {
-            const size_t lsm = (static_cast<size_t>(16) * kLutCodes * (dsub_ + 1) + static_cast<size_t>(kLutQueries) * 16 * dsub_) * 4;
-            B200_CUDA_CHECK(set_smem(lut_group_kernel, lsm));
-            dim3 lgrid(blocks_for(m, kLutQueries), static_cast<unsigned>((M_ / 16) * (kKsub / kLutCodes)));
-            lut_group_kernel<<<lgrid, 256, lsm, st>>>(xp, m, d_, M_, dsub_, codebooks_.as<float>(),
-                                                      by_residual_ ? 1 : 0, lut);
-        } else {
-            lut_kernel<<<blocks_for(m * M_ * kKsub, 256), 256, 0, st>>>(xp, m, d_, M_, dsub_, codebooks_.as<float>(),
-                                                                       by_residual_ ? 1 : 0, lut);
-        }
-        B200_CUDA_CHECK(cudaGetLastError());
-        timer_.end(st);
-
         ScanArgs a{};
-        a.lut = lut;
+        a.cbT = codebooks_t_.as<float>();
         a.cI = cI;
         a.cD = cD;
         a.nprobe = nprobe;

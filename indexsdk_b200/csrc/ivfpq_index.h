@@ -75,12 +75,13 @@ private:
 
     std::unique_ptr<FlatIndex> coarse_;   // nlist centroids, fp32, L2
     DeviceBuffer codebooks_;              // [M][256][dsub] float
+    DeviceBuffer codebooks_t_;            // the same regrouped [M / 16][256][16][dsub] (M % 16 == 0)
     DeviceBuffer cbnorm_;                 // [M][256] float: canonical squared norm of each codeword
     DeviceBuffer offsets_;                // int64 [nlist + 1]
     std::vector<int64_t> offsets_host_;
     DeviceBuffer codes_, ids_, t2_;
     // scratch
-    DeviceBuffer w_lut_, w_cD_, w_cI_, w_fd_, w_fp_, w_fth_, w_flag_, w_qlist_, w_q_, w_D_, w_I_, w_assign_D_,
+    DeviceBuffer w_cD_, w_cI_, w_fd_, w_fp_, w_fth_, w_flag_, w_qlist_, w_q_, w_D_, w_I_, w_assign_D_,
         w_assign_I_, w_list_, w_codes_, w_t2_, w_ids_, w_x_, w_tmp_;
     PinnedBuffer h_flag_;
     SearchStats stats_;

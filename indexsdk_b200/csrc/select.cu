@@ -158,6 +158,7 @@ refine_f32_kernel(uint64_t* cand, const uint32_t* counts, uint32_t n_fixed, uint
         const float4* yv = reinterpret_cast<const float4*>(xb + static_cast<int64_t>(pos) * d);
         float acc = 0.f;
         if (metric == kMetricL2) {
+#pragma unroll 8
             for (int j = 0; j < d / 4; ++j) {
                 const float4 a = __ldg(qv + j), b = __ldg(yv + j);
                 float t;
@@ -167,6 +168,7 @@ refine_f32_kernel(uint64_t* cand, const uint32_t* counts, uint32_t n_fixed, uint
                 t = a.w - b.w; acc = fmaf(t, t, acc);
             }
         } else {
+#pragma unroll 8
             for (int j = 0; j < d / 4; ++j) {
                 const float4 a = __ldg(qv + j), b = __ldg(yv + j);
                 acc = fmaf(a.x, b.x, acc);
