@@ -73,7 +73,7 @@ int b200idx_search_device(b200idx_t* h, int64_t n, const void* x_dev, int k, flo
  * device memory while searching -- a process whose HBM is owned by its own pool, or a loop that
  * cannot take the device-wide synchronisation of cudaMalloc / cudaFree.  Same kernels and same
  * results as b200idx_search_device on a Flat or Int8Flat index, with every scratch buffer taken
- * from one static 10 MiB device array: n * round_up(ntotal, 256) <= 2^20, k <= 1024,
+ * from one static device array of 10 MiB + 96 KiB: n * round_up(ntotal, 256) <= 2^20, k <= 1024,
  * n * k <= 131072, n * d <= 524288; anything larger returns B200IDX_ERR_INVALID_PARAM.  Calls
  * share that array: do not overlap two of them on one GPU.  The first call on a device resolves
  * the array's address and should be made before any stream capture. */

@@ -88,7 +88,11 @@ struct EpiShared {
 //                 atomics) and flushed with ONE global atomicAdd per row per tile, so the
 //                 latency of the L2 atomic is paid once per tile instead of once per candidate.
 //   direct mode : every key is written to cand[q][position] (no threshold, no atomics).
-template <typename AccT, int MODE, int BURST>
+//   FOLD        : the operands carry 16 extra K columns (see GemmArgs::fold), so the accumulator
+//                 already holds  D = q.y - |y|^2/2 + tau/2  (L2; inner product: q.y + tau).  No
+//                 norms are read and "key <= tau" is the sign of D: 32 columns are tested with a
+//                 16-instruction AND tree, and the burst minimum of the key is a maximum of D.
+template <typename AccT, int MODE, int BURST, bool FOLD>
 struct RowEpilogue {
     using K = KeyOps<AccT>;
     const GemmArgs& a;
@@ -109,9 +113,75 @@ struct RowEpilogue {
         q = q_;
         row_ok = ok;
         cnt = 0;
-        if (MODE == kModeAppend && ok) {
+        if (MODE == kModeAppend && ok && (!FOLD || a.direct)) {
             tau = K::tau(__ldg(a.tau + q));
             tau_up = K::above(tau);
+        }
+    }
+
+    // Folded operands: r holds D for 32 columns.
+    __device__ __forceinline__ void chunk_fold(const uint32_t (&r)[32], int64_t col0, int nvalid, int bslot) {
+        if (!row_ok) return;
+        if (MODE == kModeBurstMin) {
+            constexpr int NB = 32 / BURST;
+            uint32_t* dst = a.mins + static_cast<int64_t>(q) * a.mins_stride + bslot;
+            const float ninf = __int_as_float(0xff800000);
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                float v[BURST];
+#pragma unroll
+                for (int j = 0; j < BURST; ++j) {
+                    const int c = b * BURST + j;
+                    v[j] = __uint_as_float(r[c]);
+                    if (nvalid < 32 && c >= nvalid) v[j] = ninf;   // rows past the end of the base
+                }
+#pragma unroll
+                for (int w = BURST / 2; w > 0; w >>= 1)
+#pragma unroll
+                    for (int j = 0; j < w; ++j) v[j] = fmaxf(v[j], v[j + w]);   // NaN never wins
+                const float key = l2 ? -2.f * v[0] : -v[0];
+                dst[b] = float_to_ord(key);
+            }
+        } else if (a.direct) {
+            uint64_t* crow = a.cand + static_cast<int64_t>(q) * a.cap + col0;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                const float dv = __uint_as_float(r[c]);
+                const float key = l2 ? -2.f * dv : -dv;
+                // NaN keys are left at the buffer's "invalid" fill
+                if (c < nvalid && key <= tau) crow[c] = pack_cand(float_to_ord(key), static_cast<uint32_t>(col0 + c));
+            }
+        } else {
+            uint32_t t[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) t[i] = r[2 * i] & r[2 * i + 1];
+#pragma unroll
+            for (int w = 8; w > 0; w >>= 1)
+#pragma unroll
+                for (int i = 0; i < w; ++i) t[i] &= t[i + w];
+            if (static_cast<int32_t>(t[0]) < 0) return;   // every D negative: no key <= tau here
+            uint32_t m0 = 0, m1 = 0;                      // bit (31 - c): D of column c has its sign set
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                m0 = __funnelshift_l(r[c], m0, 1);
+                m1 = __funnelshift_l(r[16 + c], m1, 1);
+            }
+            uint32_t mask = ~((m0 << 16) | (m1 & 0xFFFFu));
+            mask &= nvalid >= 32 ? 0xFFFFFFFFu : ~(0xFFFFFFFFu >> nvalid);
+            if (!mask) return;
+            const float tq = ord_to_float(__ldg(a.tau + q));
+            while (mask) {
+                const uint32_t c = __clz(mask);
+                mask &= ~(0x80000000u >> c);
+                const float dv = __uint_as_float(pick(r, c));
+                if (!(dv >= 0.f)) continue;   // NaN
+                // approximate key (the fp32 refinement recomputes it): D = (tau' - key) / 2 or tau' - key
+                const float key = l2 ? fmaf(-2.f, dv, tq) : tq - dv;
+                const uint64_t e = pack_cand(float_to_ord(key), static_cast<uint32_t>(col0 + c));
+                if (cnt < kStageSlots) sh.stage[cnt][tid] = e;
+                else slow_append(e);
+                ++cnt;
+            }
         }
     }
 
@@ -140,6 +210,10 @@ struct RowEpilogue {
     // bit mask, and only a non-zero mask (rare) enters the compact candidate loop.
     __device__ __forceinline__ void chunk(const uint32_t (&r)[32], const uint32_t* nb, int64_t col0, int nvalid,
                                           int bslot) {
+        if (FOLD) {
+            chunk_fold(r, col0, nvalid, bslot);
+            return;
+        }
         if (!row_ok) return;
         uint32_t bnb[32];
         if (l2) {
@@ -203,7 +277,7 @@ struct RowEpilogue {
             while (mask) {
                 const uint32_t c = __clz(mask);
                 mask &= ~(0x80000000u >> c);
-                const AccT key = K::key(K::from_bits(pick(r, c)), K::from_bits(pick(bnb, c)), l2);
+                const AccT key = K::key(K::from_bits(pick(r, c)), K::from_bits(l2 ? nb[c] : 0u), l2);
                 if (!(key <= tau)) continue;   // NaN
                 const uint64_t e = pack_cand(K::ord(key), static_cast<uint32_t>(col0 + c));
                 if (cnt < kStageSlots) sh.stage[cnt][tid] = e;
@@ -239,6 +313,7 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     using AccT = typename std::conditional<KIND == kKindI8, int32_t, float>::type;
     constexpr int kElemBytes = KIND == kKindI8 ? 1 : 2;
     constexpr int kChunkElems = kChunkBytes / kElemBytes;
+    constexpr bool FOLD = KIND == kKindBF16;
     constexpr uint32_t kIdesc = KIND == kKindI8 ? ptx::umma_idesc(2, 1, kTileQ, kTileB)
                                                 : ptx::umma_idesc(1, KIND == kKindBF16 ? 1 : 0, kTileQ, kTileB);
 
@@ -330,8 +405,12 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                     ptx::tc_fence_after();
                     const uint32_t sa = ptx::smem_u32(smem + s * kStageBytes);
                     const uint32_t sb = sa + kStageABytes;
+                    // the last chunk may hold fewer than four 32-byte K steps (the rest is zero fill)
+                    const int rem_bytes = a.d * kElemBytes - kc * kChunkBytes;
+                    const int nks = rem_bytes >= kChunkBytes ? kChunkBytes / 32 : (rem_bytes + 31) / 32;
 #pragma unroll
                     for (int ks = 0; ks < kChunkBytes / 32; ++ks) {
+                        if (ks >= nks) break;
                         const uint64_t da = ptx::umma_desc_k_sw128(sa + ks * 32);
                         const uint64_t db = ptx::umma_desc_k_sw128(sb + ks * 32);
                         const uint32_t accum = (kc > 0 || ks > 0) ? 1u : 0u;
@@ -353,8 +432,8 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         const int row_in_tile = quarter * 32 + lane;
         const int et = threadIdx.x - 64;       // epilogue thread index, 0..255
         constexpr int kCols = kTileB / 2;      // columns per epilogue thread
-        RowEpilogue<AccT, MODE, BURST> epi(a, epi_sh, et);
-        const bool l2 = a.metric == kMetricL2;
+        RowEpilogue<AccT, MODE, BURST, FOLD> epi(a, epi_sh, et);
+        const bool l2 = a.metric == kMetricL2 && !FOLD;   // FOLD: no norms to fetch
         const uint32_t* gnorm = static_cast<const uint32_t*>(a.bnorm);
         uint32_t t = 0;
         bool ok = true;
@@ -375,15 +454,17 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             epi.begin_tile(q, q < a.nq);
             if (!ptx::mbar_wait_bounded(&bar_acc_full[ab], aph, &abort_flag)) {
                 // leave without stranding a sibling warp at the named barrier below
-                asm volatile("bar.arrive 1, 256;" ::: "memory");
+                if (!FOLD) asm volatile("bar.arrive 1, 256;" ::: "memory");
                 ok = false;
                 break;
             }
             const long long e1 = profiler ? clock64() : 0;
             ptx::tc_fence_after();
-            epi_sh.norm[ab][et] = n0;
             const long long b0 = profiler ? clock64() : 0;
-            asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight epilogue warps
+            if (!FOLD) {
+                epi_sh.norm[ab][et] = n0;
+                asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight epilogue warps
+            }
             if (profiler) ebar += clock64() - b0;
             const uint32_t tacc =
                 tmem_base + ab * kTileB + half * kCols + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -478,7 +559,7 @@ dist_gemm_simt_kernel(const GemmArgs a) {
     const int64_t total = static_cast<int64_t>(n_qb) * a.n_tiles_sel;
     const bool l2 = a.metric == kMetricL2;
     const uint32_t* gnorm = static_cast<const uint32_t*>(a.bnorm);
-    RowEpilogue<AccT, MODE, BURST> epi(a, epi_sh, threadIdx.x);
+    RowEpilogue<AccT, MODE, BURST, KIND == kKindBF16> epi(a, epi_sh, threadIdx.x);
     for (int64_t item = blockIdx.x; item < total; item += gridDim.x) {
         const int qb = static_cast<int>(item % n_qb);
         const int sel = static_cast<int>(item / n_qb);

@@ -18,12 +18,22 @@ constexpr int kTileB = 256;   // base rows per accumulator tile (TMEM columns)
 constexpr int kChunkBytes = 128;  // K extent of one pipeline stage, in bytes (one 128-byte swizzle row)
 
 enum GemmKind : int { kKindF16 = 0, kKindBF16 = 1, kKindI8 = 2 };
+
+// bf16 operands are "folded": every row carries kFoldCols extra K columns so that the tensor core
+// itself adds the base norm and the query's threshold to the dot product,
+//   base row  y : [ y (d) | h0 h1 h2 | 1 1 1 | 0 .. ]   h0 + h1 + h2 = -|y|^2 / 2   (0 for inner product)
+//   query row q : [ q (d) | 1  1  1  | t0 t1 t2 | 0 .. ]  t0 + t1 + t2 = tau / 2     (tau for inner product;
+//                                                          0 while no threshold is known)
+// each value split into three bf16 terms (24 significant bits).  The accumulator then holds
+// D = q.y - |y|^2/2 + tau/2 = (tau - key) / 2 with key = |y|^2 - 2 q.y, so the epilogue reads no
+// norms: "key <= tau" is "D >= 0", and min(key) over a burst is -2 max(D).
+constexpr int kFoldCols = 16;
 enum GemmMode : int { kModeBurstMin = 0, kModeAppend = 1 };
 
 struct GemmArgs {
     const void* A;        // queries [nq, d] in the operand dtype (SIMT variant only)
     const void* B;        // base    [N, d]  in the operand dtype (SIMT variant only)
-    int d;                // elements per row
+    int d;                // elements per operand row = K extent (bf16 kind: includes the 16 folded columns)
     int nq;
     int64_t N;
     int n_tiles_total;    // ceil(N / kTileB)

@@ -72,7 +72,7 @@ void FlatIndex::reserve(int64_t n) {
     if (n <= cap_rows_) return;
     int64_t want = std::max<int64_t>(n, cap_rows_ + cap_rows_ / 2);
     want = round_up(want, kTileB);
-    const size_t row_op = static_cast<size_t>(d_) * op_elem_bytes();
+    const size_t row_op = static_cast<size_t>(op_cols()) * op_elem_bytes();
     if (dtype_ == kF32)
         x32_.grow_keep(static_cast<size_t>(want) * d_ * 4, static_cast<size_t>(n_) * d_ * 4, stream_);
     xop_.grow_keep(static_cast<size_t>(want) * row_op, static_cast<size_t>(n_) * row_op, stream_);
@@ -96,7 +96,7 @@ void FlatIndex::add(int64_t n, const void* x, bool x_is_f16, const int64_t* ids,
             float* dst = x32_.as<float>() + row0 * d_;
             B200_CUDA_CHECK(cudaMemcpyAsync(dst, static_cast<const float*>(x) + off * d_,
                                             static_cast<size_t>(m) * d_ * 4, kind, stream_));
-            B200_CUDA_CHECK(launch_base_prep_f32(dst, m, d_, xop_.as<uint16_t>() + row0 * d_,
+            B200_CUDA_CHECK(launch_base_prep_f32(dst, m, d_, metric_, xop_.as<uint16_t>() + row0 * op_cols(),
                                                  norms_.as<float>() + row0, maxnorm_.as<float>(), stream_));
         } else if (dtype_ == kF16) {
             uint16_t* dst = xop_.as<uint16_t>() + row0 * d_;
@@ -155,7 +155,7 @@ int64_t FlatIndex::remove_ids(int64_t n, const int64_t* ids) {
         if (rm.count(lab[static_cast<size_t>(i)])) pos.push_back(i);
     // Swap-with-last compaction, highest position first, as the reference's removeIds does
     // (FR/ascenddaemon/impl/Index.cpp:86-140).
-    const size_t row_op = static_cast<size_t>(d_) * op_elem_bytes();
+    const size_t row_op = static_cast<size_t>(op_cols()) * op_elem_bytes();
     const size_t norm_b = 4;
     int64_t last = n_ - 1;
     for (auto it = pos.rbegin(); it != pos.rend(); ++it, --last) {
@@ -261,8 +261,8 @@ void FlatIndex::run_page(int nq, const void* xq_raw, const void* xq_op_in, int k
     float* eps = nullptr;
     void* qnorm = w_qnorm_.ensure(static_cast<size_t>(nq) * 4);
     if (dtype_ == kF32) {
-        void* qop = force_full ? w_fb_qop_.ensure(static_cast<size_t>(nq) * d_ * 2)
-                               : w_qop_.ensure(static_cast<size_t>(nq) * d_ * 2);
+        void* qop = force_full ? w_fb_qop_.ensure(static_cast<size_t>(nq) * op_cols() * 2)
+                               : w_qop_.ensure(static_cast<size_t>(nq) * op_cols() * 2);
         eps = static_cast<float*>(w_eps_.ensure(static_cast<size_t>(nq) * 4));
         B200_CUDA_CHECK(launch_prep_queries_f32(static_cast<const float*>(xq_raw), nq, d_, metric_, max_norm_, qop,
                                                 static_cast<float*>(qnorm), eps, stream_));
@@ -279,11 +279,11 @@ void FlatIndex::run_page(int nq, const void* xq_raw, const void* xq_op_in, int k
     CUtensorMap map_a;
     if (!use_simt_) {
         if (!map_b_valid_) {
-            if (encode_operand_map(&map_b_, kind, xop_.get(), n_, d_, kTileB) != 0)
+            if (encode_operand_map(&map_b_, kind, xop_.get(), n_, op_cols(), kTileB) != 0)
                 throw std::runtime_error("cuTensorMapEncodeTiled failed for the base operand");
             map_b_valid_ = true;
         }
-        if (encode_operand_map(&map_a, kind, xq_op, nq, d_, kTileQ) != 0)
+        if (encode_operand_map(&map_a, kind, xq_op, nq, op_cols(), kTileQ) != 0)
             throw std::runtime_error("cuTensorMapEncodeTiled failed for the query operand");
     }
 
@@ -296,7 +296,7 @@ void FlatIndex::run_page(int nq, const void* xq_raw, const void* xq_op_in, int k
     GemmArgs a{};
     a.A = xq_op;
     a.B = xop_.get();
-    a.d = d_;
+    a.d = op_cols();
     a.nq = nq;
     a.N = n_;
     a.n_tiles_total = static_cast<int>((n_ + kTileB - 1) / kTileB);
@@ -325,6 +325,12 @@ void FlatIndex::run_page(int nq, const void* xq_raw, const void* xq_op_in, int k
         a.prof = prof_ ? w_prof_.as<unsigned long long>() : nullptr;
         B200_CUDA_CHECK(launch_dist_gemm(L, a, &map_a, &map_b_, stream_));
         B200_CUDA_CHECK(launch_kth_threshold(mins, stride, stride, nq, k, eps, tau_all, tau, stream_));
+        if (dtype_ == kF32) {
+            // the full pass tests "key <= tau" inside the GEMM: the threshold joins the query operand
+            B200_CUDA_CHECK(launch_fold_tau(tau, static_cast<const float*>(qnorm), max_norm_, nq, d_, metric_,
+                                            const_cast<void*>(xq_op), stream_));
+            stats_.kernel_launches += 1;
+        }
         B200_CUDA_CHECK(cudaMemsetAsync(counts, 0, static_cast<size_t>(nq) * 4, stream_));
         stats_.gemm_launches += 1;
         stats_.kernel_launches += 2;
@@ -433,7 +439,7 @@ void FlatIndex::search_device(int64_t nq, const void* xq, bool q_is_f16, int k, 
                 const unsigned long long* c = pc + 16 * p;
                 const double items = c[6] ? static_cast<double>(c[6]) : 1.0;
                 fprintf(stderr, "[b200idx prof] %s pass: items %.0f per-item cycles: prod_wait_empty %.0f mma_wait_acc_empty %.0f "
-                                "mma_wait_full %.0f | epi: wait_acc_full %.0f span %.0f (barrier %.0f, tmem_wait %.0f, first-of-2 chunk calls %.0f) flush %.0f | CTA total %.0f\n",
+                                "mma_wait_full %.0f | epi: wait_acc_full %.0f span %.0f (barrier %.0f, tmem_wait %.0f, chunk calls %.0f) flush %.0f | CTA total %.0f\n",
                         p ? "append" : "sample", items, c[0] / items, c[1] / items, c[2] / items, c[3] / items,
                         c[4] / items, c[9] / items, c[8] / items, c[10] / items, c[5] / items, c[7] / items);
             }

@@ -5,6 +5,7 @@
 // Storage is one contiguous row-major array per dtype, grown geometrically; there are no
 // 262144-row blocks and no fractal layouts.
 #pragma once
+#include "dist_gemm.cuh"
 #include <cuda.h>
 #include <stdint.h>
 
@@ -154,6 +155,10 @@ private:
     void reserve(int64_t n);
     size_t in_elem_bytes() const { return dtype_ == kI8 ? 1 : (dtype_ == kF16 ? 2 : 4); }
     size_t op_elem_bytes() const { return dtype_ == kI8 ? 1 : 2; }
+  public:
+    // elements per GEMM operand row: fp32 indexes carry the folded norm / threshold columns
+    int op_cols() const { return dtype_ == kF32 ? d_ + kFoldCols : d_; }
+  private:
     int gemm_kind() const;
 
     int d_, metric_, dtype_, device_;

@@ -35,9 +35,9 @@ constexpr int kMaxKNoAlloc = 1024;
 constexpr int kMaxQueries = 1024;
 constexpr size_t kCandBytes = kMaxCandidates * 8;                 // 8 MiB of (key, position) pairs
 constexpr size_t kSelBudget = size_t(1) << 20;                    // n * k <= 128 Ki selected pairs (1 MiB)
-constexpr size_t kQopBytes = size_t(1) << 20;                     // n * d * 2 <= 1 MiB operand copy
+constexpr size_t kQopBytes = (size_t(1) << 20) + (size_t(32) << 10);   // n * d * 2 <= 1 MiB operand copy + 16 folded columns per row
 constexpr size_t kSmallBytes = size_t(64) << 10;                  // norms, slack, thresholds, flags
-constexpr size_t kArenaBytes = kCandBytes + kSelBudget + kQopBytes + kSmallBytes;  // 10 MiB + 64 KiB
+constexpr size_t kArenaBytes = kCandBytes + kSelBudget + kQopBytes + kSmallBytes;  // 10 MiB + 96 KiB
 
 // Host code must not use this name as an address: it is a host-side stand-in.  The device
 // address comes from cudaGetSymbolAddress below.
@@ -127,14 +127,14 @@ extern "C" int b200idx_search_device_noalloc(b200idx_t* h, int64_t n, const void
         const int kind = ix->gemm_kind_public();
         CUtensorMap map_a, map_b;
         if (!v.use_simt) {
-            if (encode_operand_map(&map_b, kind, v.operand, v.n, d, kTileB) != 0 ||
-                encode_operand_map(&map_a, kind, xq_op, nq, d, kTileQ) != 0)
+            if (encode_operand_map(&map_b, kind, v.operand, v.n, ix->op_cols(), kTileB) != 0 ||
+                encode_operand_map(&map_a, kind, xq_op, nq, ix->op_cols(), kTileQ) != 0)
                 throw std::runtime_error("cuTensorMapEncodeTiled failed");
         }
         GemmArgs a{};
         a.A = xq_op;
         a.B = v.operand;
-        a.d = d;
+        a.d = ix->op_cols();
         a.nq = nq;
         a.N = v.n;
         a.n_tiles_total = static_cast<int>(n_pad / kTileB);

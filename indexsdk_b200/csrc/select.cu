@@ -4,6 +4,7 @@
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "dist_gemm.cuh"
 
 namespace b200 {
 namespace {
@@ -143,42 +144,82 @@ select_topk_kernel(const uint64_t* cand, const uint32_t* counts, uint32_t n_fixe
     for (int i = threadIdx.x; i < k; i += kSelThreads) orow[i] = sorted[i];
 }
 
+// Canonical fp32 distances of the candidates (sequential fmaf over the dimensions, the arithmetic
+// of the CPU oracle).  The chain of one candidate cannot be split over lanes, so a lane owns a
+// candidate -- but the rows are fetched co-operatively: a warp reads the rows of its 32 candidates
+// kRefChunk floats at a time, each row as one contiguous piece spread over consecutive lanes
+// (a few cache lines per load instruction instead of 32), parks them in shared memory and every
+// lane then walks its own row there.  Rows are padded by 4 floats: 8 consecutive lanes reading one
+// float4 each fall into 8 different 16-byte bank groups.
+constexpr int kRefChunk = 64;
+constexpr int kRefPitch = kRefChunk + 4;
 __global__ void __launch_bounds__(128)
 refine_f32_kernel(uint64_t* cand, const uint32_t* counts, uint32_t n_fixed, uint32_t cap, int d, int metric,
                   const float* xq, const float* xb) {
+    extern __shared__ __align__(16) float ref_sm[];
+    float* qs = ref_sm;                                              // [d]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* rows = ref_sm + d + warp * (32 * kRefPitch);              // [32][kRefPitch] per warp
     const int q = blockIdx.y;
     uint32_t n = counts ? counts[q] : n_fixed;
     if (n > cap) n = cap;
+    if (blockIdx.x * 128u >= n) return;
+    for (int i = threadIdx.x; i < d / 4; i += 128)
+        reinterpret_cast<float4*>(qs)[i] = __ldg(reinterpret_cast<const float4*>(xq + static_cast<int64_t>(q) * d) + i);
+    __syncthreads();
     uint64_t* row = cand + static_cast<int64_t>(q) * cap;
-    const float4* qv = reinterpret_cast<const float4*>(xq + static_cast<int64_t>(q) * d);
-    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-        const uint64_t c = row[i];
-        if (c == kCandInvalid) continue;
-        const uint32_t pos = static_cast<uint32_t>(c);
-        const float4* yv = reinterpret_cast<const float4*>(xb + static_cast<int64_t>(pos) * d);
+    for (uint32_t i0 = (blockIdx.x * 4 + warp) * 32; i0 < n; i0 += gridDim.x * 128) {
+        const uint32_t i = i0 + lane;
+        const uint64_t c = i < n ? row[i] : kCandInvalid;
+        const bool live = c != kCandInvalid;
+        const uint32_t pos = live ? static_cast<uint32_t>(c) : 0u;
         float acc = 0.f;
-        if (metric == kMetricL2) {
+        for (int ch0 = 0; ch0 < d; ch0 += kRefChunk) {
+            const int w = d - ch0 < kRefChunk ? d - ch0 : kRefChunk;
+            const int lpr = w >> 2;                                  // float4 pieces per row
+            if (lpr == kRefChunk / 4) {
 #pragma unroll 8
-            for (int j = 0; j < d / 4; ++j) {
-                const float4 a = __ldg(qv + j), b = __ldg(yv + j);
-                float t;
-                t = a.x - b.x; acc = fmaf(t, t, acc);
-                t = a.y - b.y; acc = fmaf(t, t, acc);
-                t = a.z - b.z; acc = fmaf(t, t, acc);
-                t = a.w - b.w; acc = fmaf(t, t, acc);
+                for (int it = 0; it < 16; ++it) {                    // two of the 32 rows per load instruction
+                    const int r = it * 2 + (lane >> 4), j = lane & 15;
+                    const uint32_t pr = __shfl_sync(0xffffffffu, pos, r);
+                    const float4 v = __ldg(reinterpret_cast<const float4*>(xb + static_cast<int64_t>(pr) * d + ch0) + j);
+                    *reinterpret_cast<float4*>(rows + r * kRefPitch + 4 * j) = v;
+                }
+            } else {
+                for (int idx = lane; idx < 32 * lpr; idx += 32) {
+                    const int r = idx / lpr, j = idx - r * lpr;
+                    const uint32_t pr = __shfl_sync(0xffffffffu, pos, r);
+                    const float4 v = __ldg(reinterpret_cast<const float4*>(xb + static_cast<int64_t>(pr) * d + ch0) + j);
+                    *reinterpret_cast<float4*>(rows + r * kRefPitch + 4 * j) = v;
+                }
             }
-        } else {
-#pragma unroll 8
-            for (int j = 0; j < d / 4; ++j) {
-                const float4 a = __ldg(qv + j), b = __ldg(yv + j);
-                acc = fmaf(a.x, b.x, acc);
-                acc = fmaf(a.y, b.y, acc);
-                acc = fmaf(a.z, b.z, acc);
-                acc = fmaf(a.w, b.w, acc);
+            __syncwarp();
+            const float4* mine = reinterpret_cast<const float4*>(rows + lane * kRefPitch);
+            const float4* qv = reinterpret_cast<const float4*>(qs + ch0);
+            if (metric == kMetricL2) {
+#pragma unroll 4
+                for (int j = 0; j < lpr; ++j) {
+                    const float4 a = qv[j], b = mine[j];
+                    float t;
+                    t = a.x - b.x; acc = fmaf(t, t, acc);
+                    t = a.y - b.y; acc = fmaf(t, t, acc);
+                    t = a.z - b.z; acc = fmaf(t, t, acc);
+                    t = a.w - b.w; acc = fmaf(t, t, acc);
+                }
+            } else {
+#pragma unroll 4
+                for (int j = 0; j < lpr; ++j) {
+                    const float4 a = qv[j], b = mine[j];
+                    acc = fmaf(a.x, b.x, acc);
+                    acc = fmaf(a.y, b.y, acc);
+                    acc = fmaf(a.z, b.z, acc);
+                    acc = fmaf(a.w, b.w, acc);
+                }
             }
-            acc = -acc;
+            __syncwarp();
         }
-        row[i] = pack_cand(float_to_ord(acc), pos);
+        if (metric != kMetricL2) acc = -acc;
+        if (live) row[i] = pack_cand(float_to_ord(acc), pos);
     }
 }
 
@@ -280,17 +321,34 @@ __device__ __forceinline__ int warp_sum_i(int v) {
     return v;
 }
 
+// Three bf16 terms whose sum reproduces v to 24 significant bits (an infinite v stays in the
+// first term).
+__device__ __forceinline__ void split3_bf16(float v, __nv_bfloat16* out) {
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    float r = isfinite(v) ? v - __bfloat162float(h) : 0.f;
+    const __nv_bfloat16 m = __float2bfloat16_rn(r);
+    r -= __bfloat162float(m);
+    out[0] = h;
+    out[1] = m;
+    out[2] = __float2bfloat16_rn(r);
+}
+
+// Query operand rows of d + kFoldCols bf16: the query, three ones (they pick up the base row's
+// folded norm), three zeros (the threshold terms, written by fold_tau_kernel once the threshold is
+// known) and zero padding.
 __global__ void prep_queries_f32_kernel(const float* xq, int nq, int d, int metric, float ymax,
                                         __nv_bfloat16* qb, float* qnorm, float* eps) {
     const int q = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (q >= nq) return;
+    const int dp = d + kFoldCols;
     float s = 0.f;
     for (int i = lane; i < d; i += 32) {
         const float v = xq[static_cast<int64_t>(q) * d + i];
         s = fmaf(v, v, s);
-        qb[static_cast<int64_t>(q) * d + i] = __float2bfloat16_rn(v);
+        qb[static_cast<int64_t>(q) * dp + i] = __float2bfloat16_rn(v);
     }
+    if (lane < kFoldCols) qb[static_cast<int64_t>(q) * dp + d + lane] = __float2bfloat16_rn(lane < 3 ? 1.f : 0.f);
     s = warp_sum(s);
     if (lane == 0) {
         qnorm[q] = s;
@@ -306,6 +364,22 @@ __global__ void prep_queries_f32_kernel(const float* xq, int nq, int d, int metr
         else e = c * qn * ymax + g * qn * ymax;
         eps[q] = e;
     }
+}
+
+// Writes the threshold terms of the folded query rows: c = tau / 2 (L2) or tau (inner product).
+// tau is first raised by a margin for the fp32 accumulation inside the tensor core: d + 16
+// additions of terms whose partial sums stay below M = |q||y|max + |y|max^2 / 2 + |tau| perturb a
+// key by less than 2^-14.8 M in either pass, and 2^-12 M covers the sample pass, the full pass and
+// the threshold's own term together, so no key <= tau is missed.
+__global__ void fold_tau_kernel(const uint32_t* tau, const float* qnorm, float ymax, int nq, int d, int metric,
+                                __nv_bfloat16* qb) {
+    const int q = blockIdx.x * blockDim.x + threadIdx.x;
+    if (q >= nq) return;
+    const float t = ord_to_float(tau[q]);
+    const float m = sqrtf(qnorm[q]) * ymax + 0.5f * ymax * ymax + fabsf(t);
+    float c = t + 0.000244140625f * m;
+    if (metric == kMetricL2) c *= 0.5f;
+    split3_bf16(c, qb + static_cast<int64_t>(q) * (d + kFoldCols) + d + 3);
 }
 
 __global__ void prep_queries_f16_kernel(const __half* xq, int nq, int d, float* qnorm) {
@@ -334,19 +408,24 @@ __global__ void prep_queries_i8_kernel(const int8_t* xq, int nq, int d, int32_t*
     if (lane == 0) qnorm[q] = s;
 }
 
-__global__ void base_prep_f32_kernel(const float* x, int64_t n, int d, __nv_bfloat16* xb, float* norms,
+// Base operand rows of d + kFoldCols bf16: the vector, -|y|^2 / 2 in three terms (zeros for inner
+// product), three ones (they pick up the query's threshold terms) and zero padding.
+__global__ void base_prep_f32_kernel(const float* x, int64_t n, int d, int metric, __nv_bfloat16* xb, float* norms,
                                      float* max_norm_sq) {
     const int64_t r = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (r >= n) return;
+    const int dp = d + kFoldCols;
     float s = 0.f;
     for (int i = lane; i < d; i += 32) {
         const float v = x[r * d + i];
         s = fmaf(v, v, s);
-        xb[r * d + i] = __float2bfloat16_rn(v);
+        xb[r * dp + i] = __float2bfloat16_rn(v);
     }
     s = warp_sum(s);
+    if (lane >= 3 && lane < kFoldCols) xb[r * dp + d + lane] = __float2bfloat16_rn(lane < 6 ? 1.f : 0.f);
     if (lane == 0) {
+        split3_bf16(metric == kMetricL2 ? -0.5f * s : 0.f, xb + r * dp + d);
         norms[r] = s;
         atomicMax(reinterpret_cast<unsigned int*>(max_norm_sq), __float_as_uint(s));
     }
@@ -443,9 +522,15 @@ cudaError_t launch_refine_f32(uint64_t* cand, const uint32_t* counts, uint32_t n
     int gx = static_cast<int>((per_row + 127) / 128);
     if (gx > 64) gx = 64;
     if (gx < 1) gx = 1;
+    const size_t smem = (static_cast<size_t>(d) + 4 * 32 * kRefPitch) * sizeof(float);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(refine_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+    }
     for (int q0 = 0; q0 < nq; q0 += 65535) {
         const int nqq = nq - q0 < 65535 ? nq - q0 : 65535;
-        refine_f32_kernel<<<dim3(gx, nqq), 128, 0, stream>>>(cand + static_cast<int64_t>(q0) * cap,
+        refine_f32_kernel<<<dim3(gx, nqq), 128, smem, stream>>>(cand + static_cast<int64_t>(q0) * cap,
                                                             counts ? counts + q0 : nullptr, n_fixed, cap, d, metric,
                                                             xq + static_cast<int64_t>(q0) * d, xb);
     }
@@ -484,11 +569,18 @@ cudaError_t launch_prep_queries_i8(const int8_t* xq, int nq, int d, int32_t* qno
     prep_queries_i8_kernel<<<(nq + 7) / 8, 256, 0, stream>>>(xq, nq, d, qnorm);
     return cudaGetLastError();
 }
-cudaError_t launch_base_prep_f32(const float* x, int64_t n, int d, void* x_bf16, float* norms, float* max_norm_sq,
-                                 cudaStream_t stream) {
+cudaError_t launch_base_prep_f32(const float* x, int64_t n, int d, int metric, void* x_bf16, float* norms,
+                                 float* max_norm_sq, cudaStream_t stream) {
     if (n <= 0) return cudaSuccess;
     base_prep_f32_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(
-        x, n, d, static_cast<__nv_bfloat16*>(x_bf16), norms, max_norm_sq);
+        x, n, d, metric, static_cast<__nv_bfloat16*>(x_bf16), norms, max_norm_sq);
+    return cudaGetLastError();
+}
+cudaError_t launch_fold_tau(const uint32_t* tau, const float* qnorm, float base_max_norm, int nq, int d, int metric,
+                            void* q_bf16, cudaStream_t stream) {
+    if (nq <= 0) return cudaSuccess;
+    fold_tau_kernel<<<(nq + 255) / 256, 256, 0, stream>>>(tau, qnorm, base_max_norm, nq, d, metric,
+                                                          static_cast<__nv_bfloat16*>(q_bf16));
     return cudaGetLastError();
 }
 cudaError_t launch_base_prep_f16(const void* x, int64_t n, int d, float* norms, cudaStream_t stream) {

@@ -54,8 +54,12 @@ cudaError_t launch_prep_queries_f16(const void* xq_f16, int nq, int d, float* qn
 cudaError_t launch_prep_queries_i8(const int8_t* xq, int nq, int d, int32_t* qnorm, cudaStream_t stream);
 
 // Base preparation at add time.
-cudaError_t launch_base_prep_f32(const float* x, int64_t n, int d, void* x_bf16, float* norms, float* max_norm_sq,
-                                 cudaStream_t stream);
+// fp32 index: operand rows are d + kFoldCols bf16 wide (see dist_gemm.cuh)
+cudaError_t launch_base_prep_f32(const float* x, int64_t n, int d, int metric, void* x_bf16, float* norms,
+                                 float* max_norm_sq, cudaStream_t stream);
+// threshold terms of the folded query rows, from the ordered-key thresholds tau[nq]
+cudaError_t launch_fold_tau(const uint32_t* tau, const float* qnorm, float base_max_norm, int nq, int d, int metric,
+                            void* q_bf16, cudaStream_t stream);
 cudaError_t launch_base_prep_f16(const void* x_f16, int64_t n, int d, float* norms, cudaStream_t stream);
 cudaError_t launch_base_prep_i8(const int8_t* x, int64_t n, int d, int32_t* norms, cudaStream_t stream);
 cudaError_t launch_f32_to_f16(const float* x, int64_t count, void* out, cudaStream_t stream);
