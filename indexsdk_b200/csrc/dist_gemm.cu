@@ -25,11 +25,12 @@
 namespace b200 {
 namespace {
 
-constexpr int kStages = 4;
+constexpr int kMaxStages = 8;
 constexpr int kStageABytes = kTileQ * kChunkBytes;               // 16 KB
 constexpr int kStageBBytes = kTileB * kChunkBytes;               // 32 KB
 constexpr int kStageBytes = kStageABytes + kStageBBytes;         // 48 KB
-constexpr int kGemmSmemBytes = kStages * kStageBytes + 1024;     // + slack for 1024-byte alignment
+constexpr int kGemmSmemBudget = 224 * 1024;                      // dynamic shared memory incl. 1 KB alignment slack
+constexpr int kResidentMaxChunks = 4;                            // query tile kept in shared memory up to 64 KB
 constexpr int kEpiWarps = 8;                                    // two per scheduler; pairs split the tile's columns
 constexpr int kEpiThreads = kEpiWarps * 32;
 constexpr int kGemmThreads = 64 + kEpiThreads;                   // producer warp + MMA warp + epilogue warps
@@ -74,57 +75,112 @@ struct KeyOps<int32_t> {
     static __device__ __forceinline__ int32_t neg(int32_t v) { return -v; }
 };
 
-constexpr int kStageSlots = 8;   // per-row candidate staging slots per tile (shared memory)
+constexpr uint32_t kCandBlock = 8;   // candidate slots a thread reserves with one atomic
 
-// Shared-memory side of the epilogue: the tile's base norms (double-buffered with the TMEM
-// accumulators) and a per-row staging area for candidates found in the current tile.
+// Shared-memory side of the epilogue: the tile's base norms, double-buffered with the TMEM
+// accumulators (kinds whose operands are not folded).
 struct EpiShared {
     uint32_t norm[2][kTileB];
-    uint64_t stage[kStageSlots][2 * kTileQ];   // one column of slots per epilogue thread
 };
 
-// Per-thread (= per query row) epilogue state for one tile.
-//   append mode : candidates of the tile are staged in shared memory (thread-private slots, no
-//                 atomics) and flushed with ONE global atomicAdd per row per tile, so the
-//                 latency of the L2 atomic is paid once per tile instead of once per candidate.
+// Per-thread (= query row x part of the tile's columns) epilogue state.
+//   append mode : a thread reserves kCandBlock consecutive slots of its row's candidate list with
+//                 ONE atomicAdd and fills them over as many tiles as it takes -- a CTA walks
+//                 consecutive base tiles of the same query block, so the row stays the same.
+//                 When the row changes (or the kernel ends) the unused slots of the open block are
+//                 written as "invalid"; the consumers skip those.  counts[row] is therefore the
+//                 number of RESERVED slots, an upper bound of the candidates.
 //   direct mode : every key is written to cand[q][position] (no threshold, no atomics).
-//   FOLD        : the operands carry 16 extra K columns (see GemmArgs::fold), so the accumulator
+//   FOLD        : the operands carry 16 extra K columns (GemmArgs / kFoldCols), so the accumulator
 //                 already holds  D = q.y - |y|^2/2 + tau/2  (L2; inner product: q.y + tau).  No
 //                 norms are read and "key <= tau" is the sign of D: 32 columns are tested with a
 //                 16-instruction AND tree, and the burst minimum of the key is a maximum of D.
-template <typename AccT, int MODE, int BURST, bool FOLD>
+// NCH: 32-column chunks a thread handles per tile.
+template <typename AccT, int MODE, int BURST, bool FOLD, int NCH>
 struct RowEpilogue {
     using K = KeyOps<AccT>;
     const GemmArgs& a;
-    EpiShared& sh;
     int q;        // query row, valid when row_ok
-    int tid;      // row inside the tile, 0..127
     bool row_ok;
     bool l2;
     AccT tau, tau_up;
-    uint32_t cnt;
+    float tq;                 // FOLD append: the row's threshold, for the approximate key
+    int blk_q;                // row of the open candidate block (-1: none)
+    uint32_t blk_next, blk_left;
+    uint32_t pre_base;        // a second block reserved ahead of need (its atomic is issued at the end of a
+    bool pre_ok;              // tile and not read before the open block runs out, so nobody waits for it)
+    uint32_t res[NCH * (32 / BURST)];   // burst-min results of this thread's part of the tile
 
-    // tid_: index of this thread's private staging column
-    __device__ __forceinline__ RowEpilogue(const GemmArgs& a_, EpiShared& sh_, int tid_)
-        : a(a_), sh(sh_), q(0), tid(tid_), row_ok(false), l2(a_.metric == kMetricL2), tau(AccT(0)),
-          tau_up(AccT(0)), cnt(0) {}
+    __device__ __forceinline__ explicit RowEpilogue(const GemmArgs& a_)
+        : a(a_), q(0), row_ok(false), l2(a_.metric == kMetricL2), tau(AccT(0)), tau_up(AccT(0)), tq(0.f),
+          blk_q(-1), blk_next(0), blk_left(0), pre_base(0), pre_ok(false) {}
+
+    // Fills what is left of the open block with the "invalid" marker.
+    __device__ __forceinline__ void close_block() {
+        if (blk_q >= 0) {
+            uint64_t* crow = a.cand + static_cast<int64_t>(blk_q) * a.cap;
+            for (uint32_t i = 0; i < blk_left; ++i)
+                if (blk_next + i < a.cap) crow[blk_next + i] = kCandInvalid;
+            if (pre_ok)
+                for (uint32_t i = 0; i < kCandBlock; ++i)
+                    if (pre_base + i < a.cap) crow[pre_base + i] = kCandInvalid;
+        }
+        blk_q = -1;
+        blk_left = 0;
+        pre_ok = false;
+    }
 
     __device__ __forceinline__ void begin_tile(int q_, bool ok) {
+        if (MODE == kModeAppend && !a.direct && (q_ != blk_q || !ok)) close_block();
         q = q_;
         row_ok = ok;
-        cnt = 0;
-        if (MODE == kModeAppend && ok && (!FOLD || a.direct)) {
-            tau = K::tau(__ldg(a.tau + q));
-            tau_up = K::above(tau);
+        if (MODE == kModeAppend && ok) {
+            const uint32_t to = __ldg(a.tau + q);
+            if (FOLD && !a.direct) {
+                tq = ord_to_float(to);
+            } else {
+                tau = K::tau(to);
+                tau_up = K::above(tau);
+            }
         }
     }
 
+    __device__ __forceinline__ void append(uint64_t e) {
+        if (blk_left == 0) {
+            if (pre_ok) {
+                blk_next = pre_base;
+                pre_ok = false;
+            } else {
+                blk_next = atomicAdd(a.counts + q, kCandBlock);   // first block of a run, or a burst of candidates
+            }
+            blk_left = kCandBlock;
+            blk_q = q;
+        }
+        if (blk_next < a.cap) a.cand[static_cast<int64_t>(q) * a.cap + blk_next] = e;
+        ++blk_next;
+        --blk_left;
+    }
+
+    // Value of r[c] for a run-time c without indexing registers dynamically (select tree).
+    static __device__ __forceinline__ uint32_t pick(const uint32_t (&r)[32], uint32_t c) {
+        uint32_t v16[16], v8[8], v4[4], v2[2];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v16[i] = (c & 16u) ? r[16 + i] : r[i];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v8[i] = (c & 8u) ? v16[8 + i] : v16[i];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v4[i] = (c & 4u) ? v8[4 + i] : v8[i];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) v2[i] = (c & 2u) ? v4[2 + i] : v4[i];
+        return (c & 1u) ? v2[1] : v2[0];
+    }
+
     // Folded operands: r holds D for 32 columns.
-    __device__ __forceinline__ void chunk_fold(const uint32_t (&r)[32], int64_t col0, int nvalid, int bslot) {
+    // ci: index of the chunk inside this thread's part of the tile (a constant after unrolling)
+    __device__ __forceinline__ void chunk_fold(const uint32_t (&r)[32], int64_t col0, int nvalid, int ci) {
         if (!row_ok) return;
         if (MODE == kModeBurstMin) {
             constexpr int NB = 32 / BURST;
-            uint32_t* dst = a.mins + static_cast<int64_t>(q) * a.mins_stride + bslot;
             const float ninf = __int_as_float(0xff800000);
 #pragma unroll
             for (int b = 0; b < NB; ++b) {
@@ -140,7 +196,7 @@ struct RowEpilogue {
 #pragma unroll
                     for (int j = 0; j < w; ++j) v[j] = fmaxf(v[j], v[j + w]);   // NaN never wins
                 const float key = l2 ? -2.f * v[0] : -v[0];
-                dst[b] = float_to_ord(key);
+                res[ci * NB + b] = float_to_ord(key);
             }
         } else if (a.direct) {
             uint64_t* crow = a.cand + static_cast<int64_t>(q) * a.cap + col0;
@@ -168,8 +224,6 @@ struct RowEpilogue {
             }
             uint32_t mask = ~((m0 << 16) | (m1 & 0xFFFFu));
             mask &= nvalid >= 32 ? 0xFFFFFFFFu : ~(0xFFFFFFFFu >> nvalid);
-            if (!mask) return;
-            const float tq = ord_to_float(__ldg(a.tau + q));
             while (mask) {
                 const uint32_t c = __clz(mask);
                 mask &= ~(0x80000000u >> c);
@@ -177,41 +231,20 @@ struct RowEpilogue {
                 if (!(dv >= 0.f)) continue;   // NaN
                 // approximate key (the fp32 refinement recomputes it): D = (tau' - key) / 2 or tau' - key
                 const float key = l2 ? fmaf(-2.f, dv, tq) : tq - dv;
-                const uint64_t e = pack_cand(float_to_ord(key), static_cast<uint32_t>(col0 + c));
-                if (cnt < kStageSlots) sh.stage[cnt][tid] = e;
-                else slow_append(e);
-                ++cnt;
+                append(pack_cand(float_to_ord(key), static_cast<uint32_t>(col0 + c)));
             }
         }
     }
 
-    __device__ __forceinline__ void slow_append(uint64_t e) {
-        const uint32_t slot = atomicAdd(a.counts + q, 1u);
-        if (slot < a.cap) a.cand[static_cast<int64_t>(q) * a.cap + slot] = e;
-    }
-
-    // Value of r[c] for a run-time c without indexing registers dynamically (select tree).
-    static __device__ __forceinline__ uint32_t pick(const uint32_t (&r)[32], uint32_t c) {
-        uint32_t v16[16], v8[8], v4[4], v2[2];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) v16[i] = (c & 16u) ? r[16 + i] : r[i];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v8[i] = (c & 8u) ? v16[8 + i] : v16[i];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) v4[i] = (c & 4u) ? v8[4 + i] : v8[i];
-#pragma unroll
-        for (int i = 0; i < 2; ++i) v2[i] = (c & 2u) ? v4[2 + i] : v4[i];
-        return (c & 1u) ? v2[1] : v2[0];
-    }
-
     // r: 32 accumulator columns; nb: the matching 32 norms in shared memory; col0: base position
-    // of r[0]; nvalid: real base rows among the 32; bslot: first burst slot (burst-min mode).
-    // The hot path is straight-line code: the threshold test of the 32 columns is folded into a
-    // bit mask, and only a non-zero mask (rare) enters the compact candidate loop.
+    // of r[0]; nvalid: real base rows among the 32; bslot: first burst slot (burst-min mode);
+    // ci: see chunk_fold.  The hot path is straight-line code: the threshold test of the 32
+    // columns is folded into a bit mask, and only a non-zero mask (rare) enters the compact
+    // candidate loop.
     __device__ __forceinline__ void chunk(const uint32_t (&r)[32], const uint32_t* nb, int64_t col0, int nvalid,
-                                          int bslot) {
+                                          int bslot, int ci) {
         if (FOLD) {
-            chunk_fold(r, col0, nvalid, bslot);
+            chunk_fold(r, col0, nvalid, ci);
             return;
         }
         if (!row_ok) return;
@@ -279,33 +312,76 @@ struct RowEpilogue {
                 mask &= ~(0x80000000u >> c);
                 const AccT key = K::key(K::from_bits(pick(r, c)), K::from_bits(l2 ? nb[c] : 0u), l2);
                 if (!(key <= tau)) continue;   // NaN
-                const uint64_t e = pack_cand(K::ord(key), static_cast<uint32_t>(col0 + c));
-                if (cnt < kStageSlots) sh.stage[cnt][tid] = e;
-                else slow_append(e);
-                ++cnt;
+                append(pack_cand(K::ord(key), static_cast<uint32_t>(col0 + c)));
             }
         }
     }
 
-    __device__ __forceinline__ void end_tile() {
-        if (MODE != kModeAppend || !row_ok || a.direct) return;
-        const uint32_t n_st = cnt < kStageSlots ? cnt : kStageSlots;
-        if (n_st) {
-            const uint32_t slot0 = atomicAdd(a.counts + q, n_st);
-            uint64_t* crow = a.cand + static_cast<int64_t>(q) * a.cap;
-            for (uint32_t i = 0; i < n_st; ++i)
-                if (slot0 + i < a.cap) crow[slot0 + i] = sh.stage[i][tid];
+    // hslot: first burst slot of this thread's part of the tile (burst-min mode)
+    __device__ __forceinline__ void end_tile(int hslot) {
+        if (MODE == kModeAppend && !a.direct && row_ok && blk_q == q && !pre_ok && blk_left <= kCandBlock / 2) {
+            pre_base = atomicAdd(a.counts + q, kCandBlock);
+            pre_ok = true;
         }
+        if (MODE == kModeBurstMin && FOLD && row_ok) {
+            // one 16-byte store per four results instead of four scattered words
+            uint4* dst = reinterpret_cast<uint4*>(a.mins + static_cast<int64_t>(q) * a.mins_stride + hslot);
+#pragma unroll
+            for (int i = 0; i < static_cast<int>(sizeof(res) / 16); ++i)
+                dst[i] = make_uint4(res[4 * i], res[4 * i + 1], res[4 * i + 2], res[4 * i + 3]);
+        }
+    }
+
+    __device__ __forceinline__ void finish() {
+        if (MODE == kModeAppend && !a.direct) close_block();
     }
 };
 
 __device__ __forceinline__ int tile_of(const GemmArgs& a, int sel) {
+    if (a.n_tiles_sel == a.n_tiles_total) return sel;   // full pass: no 64-bit division on the hot path
     return static_cast<int>(static_cast<int64_t>(sel) * a.n_tiles_total / a.n_tiles_sel);
 }
+
+// Work of one CTA: a contiguous range of the (query block, base tile) items in query-block-major
+// order.  Consecutive items of a CTA share the query block, which is what lets the query tile stay
+// in shared memory and a thread keep one candidate block open across tiles; CTAs of different
+// query blocks walk the base tiles in step, so a base tile is read from HBM about once.
+struct ItemRange {
+    int64_t count;       // items of this CTA
+    int qb0, sel0;       // first item
+    int n_sel;
+    __device__ __forceinline__ ItemRange(const GemmArgs& a, int n_qb) {
+        const int64_t total = static_cast<int64_t>(n_qb) * a.n_tiles_sel;
+        const int64_t lo = total * blockIdx.x / gridDim.x;
+        const int64_t hi = total * (blockIdx.x + 1) / gridDim.x;
+        count = hi - lo;
+        n_sel = a.n_tiles_sel;
+        qb0 = static_cast<int>(lo / n_sel);
+        sel0 = static_cast<int>(lo % n_sel);
+    }
+};
+// Walks a range without divisions (the roles that run one thread deep cannot afford them).
+struct ItemCursor {
+    int qb, sel;
+    int n_sel;
+    __device__ __forceinline__ explicit ItemCursor(const ItemRange& r) : qb(r.qb0), sel(r.sel0), n_sel(r.n_sel) {}
+    __device__ __forceinline__ void next() {
+        if (++sel == n_sel) {
+            sel = 0;
+            ++qb;
+        }
+    }
+    __device__ __forceinline__ bool last_of_qb() const { return sel + 1 == n_sel; }
+};
 
 // ---------------------------------------------------------------------------------------
 // tcgen05 variant
 // ---------------------------------------------------------------------------------------
+// Shared memory is the scarce resource of this kernel: a 128 x 256 x 16 UMMA reads 12 KB of
+// operands, and with K of a few hundred every operand byte that TMA writes is read about once, so
+// TMA writes and UMMA reads together are bounded by the 128 B/clk of the shared-memory pipe.  When
+// the query tile is small enough (a.a_resident) it is therefore loaded once per query block and
+// only base chunks (32 KB) travel through the stage ring.
 template <int KIND, int MODE, int BURST>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
@@ -318,10 +394,12 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                                                 : ptx::umma_idesc(1, KIND == kKindBF16 ? 1 : 0, kTileQ, kTileB);
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t bar_full[kStages];
-    __shared__ uint64_t bar_empty[kStages];
+    __shared__ uint64_t bar_full[kMaxStages];
+    __shared__ uint64_t bar_empty[kMaxStages];
     __shared__ uint64_t bar_acc_full[2];
     __shared__ uint64_t bar_acc_empty[2];
+    __shared__ uint64_t bar_a_full;      // resident query tile landed
+    __shared__ uint64_t bar_a_free;      // every UMMA that read the resident query tile has completed
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
     __shared__ __align__(16) EpiShared epi_sh;
@@ -329,9 +407,14 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int nkc = (a.d + kChunkElems - 1) / kChunkElems;
+    const bool resident = a.a_resident != 0;
+    const int nst = a.n_stages;
+    const uint32_t stage_bytes = resident ? kStageBBytes : kStageBytes;
+    uint8_t* ring = smem + (resident ? nkc * kStageABytes : 0);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < nst; ++s) {
             ptx::mbar_init(&bar_full[s], 1);
             ptx::mbar_init(&bar_empty[s], 1);
         }
@@ -339,6 +422,8 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             ptx::mbar_init(&bar_acc_full[b], 1);
             ptx::mbar_init(&bar_acc_empty[b], kEpiWarps);
         }
+        ptx::mbar_init(&bar_a_full, 1);
+        ptx::mbar_init(&bar_a_free, 1);
         abort_flag = 0;
         ptx::mbar_fence_init();
         ptx::prefetch_tensormap(&mapA);
@@ -354,28 +439,42 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     const uint32_t tmem_base = tmem_base_slot;
 
     const int n_qb = (a.nq + kTileQ - 1) / kTileQ;
-    const int64_t total = static_cast<int64_t>(n_qb) * a.n_tiles_sel;
-    const int nkc = (a.d + kChunkElems - 1) / kChunkElems;
+    const ItemRange range(a, n_qb);
 
     if (warp == 0) {
         if (lane == 0) {
-            uint32_t it = 0;
+            int s = 0;
+            uint32_t ph = 0;
+            int cur_qb = -1;
+            uint32_t a_loads = 0;
             bool ok = true;
             long long pw = 0;
             const long long k0 = a.prof ? clock64() : 0;
-            for (int64_t item = blockIdx.x; item < total && ok; item += gridDim.x) {
-                const int qb = static_cast<int>(item % n_qb);
-                const int tile = tile_of(a, static_cast<int>(item / n_qb));
-                for (int kc = 0; kc < nkc; ++kc, ++it) {
-                    const int s = it % kStages;
-                    const uint32_t ph = (it / kStages) & 1u;
+            ItemCursor cur(range);
+            for (int64_t i = 0; i < range.count && ok; ++i, cur.next()) {
+                const int qb = cur.qb;
+                const int tile = tile_of(a, cur.sel);
+                if (resident && qb != cur_qb) {
+                    // the previous query block's UMMAs must be done with the tile before it is overwritten
+                    if (a_loads && !ptx::mbar_wait_bounded(&bar_a_free, (a_loads - 1u) & 1u, &abort_flag)) { ok = false; break; }
+                    ptx::mbar_expect_tx(&bar_a_full, static_cast<uint32_t>(nkc) * kStageABytes);
+                    for (int kc = 0; kc < nkc; ++kc)
+                        ptx::tma_load_2d(smem + kc * kStageABytes, &mapA, &bar_a_full, kc * kChunkElems, qb * kTileQ);
+                    ++a_loads;
+                    cur_qb = qb;
+                }
+                for (int kc = 0; kc < nkc; ++kc) {
                     const long long w0 = a.prof ? clock64() : 0;
                     if (!ptx::mbar_wait_bounded(&bar_empty[s], ph ^ 1u, &abort_flag)) { ok = false; break; }
                     if (a.prof) pw += clock64() - w0;
-                    ptx::mbar_expect_tx(&bar_full[s], kStageBytes);
-                    uint8_t* sa = smem + s * kStageBytes;
-                    ptx::tma_load_2d(sa, &mapA, &bar_full[s], kc * kChunkElems, qb * kTileQ);
-                    ptx::tma_load_2d(sa + kStageABytes, &mapB, &bar_full[s], kc * kChunkElems, tile * kTileB);
+                    ptx::mbar_expect_tx(&bar_full[s], stage_bytes);
+                    uint8_t* st = ring + static_cast<size_t>(s) * stage_bytes;
+                    if (!resident) {
+                        ptx::tma_load_2d(st, &mapA, &bar_full[s], kc * kChunkElems, qb * kTileQ);
+                        st += kStageABytes;
+                    }
+                    ptx::tma_load_2d(st, &mapB, &bar_full[s], kc * kChunkElems, tile * kTileB);
+                    if (++s == nst) { s = 0; ph ^= 1u; }
                 }
             }
             if (a.prof) {
@@ -385,10 +484,28 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            uint32_t it = 0, t = 0;
+            int s = 0;
+            uint32_t ph = 0, t = 0;
+            int cur_qb = -1;
+            uint32_t a_seen = 0;
             bool ok = true;
             long long mw0 = 0, mw1 = 0;
-            for (int64_t item = blockIdx.x; item < total && ok; item += gridDim.x, ++t) {
+            // Descriptors differ only in their 14-bit address field: build the constant part once
+            // and add byte offsets / 16 (the single issuing thread is on the critical path).
+            const uint64_t desc_hi = ptx::umma_desc_k_sw128(0);
+            const uint32_t a_res_lo = (ptx::smem_u32(smem) & 0x3FFFFu) >> 4;
+            const uint32_t ring_lo = (ptx::smem_u32(ring) & 0x3FFFFu) >> 4;
+            const uint32_t stage_lo = stage_bytes >> 4;
+            const int tail_bytes = a.d * kElemBytes - (nkc - 1) * kChunkBytes;   // bytes of K in the last chunk
+            const int tail_nks = tail_bytes >= kChunkBytes ? kChunkBytes / 32 : (tail_bytes + 31) / 32;
+            ItemCursor cur(range);
+            for (int64_t i = 0; i < range.count && ok; ++i, ++t, cur.next()) {
+                const int qb = cur.qb;
+                if (resident && qb != cur_qb) {
+                    if (!ptx::mbar_wait_bounded(&bar_a_full, a_seen & 1u, &abort_flag)) { ok = false; break; }
+                    ++a_seen;
+                    cur_qb = qb;
+                }
                 const uint32_t ab = t & 1u;
                 const uint32_t aph = (t >> 1) & 1u;
                 long long w0 = a.prof ? clock64() : 0;
@@ -396,30 +513,33 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 if (a.prof) mw0 += clock64() - w0;
                 ptx::tc_fence_after();
                 const uint32_t tacc = tmem_base + ab * kTileB;
-                for (int kc = 0; kc < nkc; ++kc, ++it) {
-                    const int s = it % kStages;
-                    const uint32_t ph = (it / kStages) & 1u;
+                for (int kc = 0; kc < nkc; ++kc) {
                     w0 = a.prof ? clock64() : 0;
                     if (!ptx::mbar_wait_bounded(&bar_full[s], ph, &abort_flag)) { ok = false; break; }
                     if (a.prof) mw1 += clock64() - w0;
                     ptx::tc_fence_after();
-                    const uint32_t sa = ptx::smem_u32(smem + s * kStageBytes);
-                    const uint32_t sb = sa + kStageABytes;
+                    const uint32_t st_lo = ring_lo + static_cast<uint32_t>(s) * stage_lo;
+                    const uint32_t sa_lo = resident ? a_res_lo + static_cast<uint32_t>(kc) * (kStageABytes >> 4) : st_lo;
+                    const uint32_t sb_lo = resident ? st_lo : st_lo + (kStageABytes >> 4);
                     // the last chunk may hold fewer than four 32-byte K steps (the rest is zero fill)
-                    const int rem_bytes = a.d * kElemBytes - kc * kChunkBytes;
-                    const int nks = rem_bytes >= kChunkBytes ? kChunkBytes / 32 : (rem_bytes + 31) / 32;
+                    const int nks = kc + 1 == nkc ? tail_nks : kChunkBytes / 32;
 #pragma unroll
                     for (int ks = 0; ks < kChunkBytes / 32; ++ks) {
                         if (ks >= nks) break;
-                        const uint64_t da = ptx::umma_desc_k_sw128(sa + ks * 32);
-                        const uint64_t db = ptx::umma_desc_k_sw128(sb + ks * 32);
+                        const uint64_t da = desc_hi | static_cast<uint64_t>(sa_lo + ks * 2);
+                        const uint64_t db = desc_hi | static_cast<uint64_t>(sb_lo + ks * 2);
                         const uint32_t accum = (kc > 0 || ks > 0) ? 1u : 0u;
                         if (KIND == kKindI8) ptx::umma_i8(tacc, da, db, kIdesc, accum);
                         else ptx::umma_f16(tacc, da, db, kIdesc, accum);
                     }
                     ptx::umma_commit(&bar_empty[s]);
+                    if (++s == nst) { s = 0; ph ^= 1u; }
                 }
-                if (ok) ptx::umma_commit(&bar_acc_full[ab]);
+                if (!ok) break;
+                ptx::umma_commit(&bar_acc_full[ab]);
+                // last item of this CTA for the query block: the resident tile may be replaced once
+                // everything issued so far has completed
+                if (resident && (i + 1 == range.count || cur.last_of_qb())) ptx::umma_commit(&bar_a_free);
             }
             if (a.prof) {
                 atomicAdd(a.prof + 1, static_cast<unsigned long long>(mw0));
@@ -432,16 +552,17 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         const int row_in_tile = quarter * 32 + lane;
         const int et = threadIdx.x - 64;       // epilogue thread index, 0..255
         constexpr int kCols = kTileB / 2;      // columns per epilogue thread
-        RowEpilogue<AccT, MODE, BURST, FOLD> epi(a, epi_sh, et);
+        RowEpilogue<AccT, MODE, BURST, FOLD, kCols / 32> epi(a);
         const bool l2 = a.metric == kMetricL2 && !FOLD;   // FOLD: no norms to fetch
         const uint32_t* gnorm = static_cast<const uint32_t*>(a.bnorm);
         uint32_t t = 0;
         bool ok = true;
         long long ew = 0, ec = 0, ef = 0, elw = 0, ebar = 0, ecc = 0;
         const bool profiler = a.prof && warp == 2 && lane == 0;
-        for (int64_t item = blockIdx.x; item < total && ok; item += gridDim.x, ++t) {
-            const int qb = static_cast<int>(item % n_qb);
-            const int sel = static_cast<int>(item / n_qb);
+        ItemCursor cur(range);
+        for (int64_t i = 0; i < range.count && ok; ++i, ++t, cur.next()) {
+            const int qb = cur.qb;
+            const int sel = cur.sel;
             const int tile = tile_of(a, sel);
             const uint32_t ab = t & 1u;
             const uint32_t aph = (t >> 1) & 1u;
@@ -473,8 +594,8 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             const int hslot = sel * (kTileB / BURST) + half * (kCols / BURST);
             uint32_t ra[32], rb[32];
             ptx::tmem_ld_32x32(tacc, ra);
-#pragma unroll 1
-            for (int c = 0; c < kCols / 32; c += 2) {
+            // two chunks per step, the TMEM load of the next chunk in flight behind the current one
+            auto step = [&](int c) {
                 const long long w0 = profiler ? clock64() : 0;
                 ptx::tmem_ld_wait(ra);
                 if (profiler) elw += clock64() - w0;
@@ -484,7 +605,7 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                     const int64_t col0 = half_col0 + c * 32;
                     const int64_t rem = a.N - col0;
                     epi.chunk(ra, hnorm + c * 32, col0, rem >= 32 ? 32 : (rem > 0 ? static_cast<int>(rem) : 0),
-                              hslot + c * (32 / BURST));
+                              hslot + c * (32 / BURST), c);
                     if (profiler) ecc += clock64() - c0;
                 }
                 const long long w1 = profiler ? clock64() : 0;
@@ -495,15 +616,22 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                     const int64_t col0 = half_col0 + (c + 1) * 32;
                     const int64_t rem = a.N - col0;
                     epi.chunk(rb, hnorm + (c + 1) * 32, col0, rem >= 32 ? 32 : (rem > 0 ? static_cast<int>(rem) : 0),
-                              hslot + (c + 1) * (32 / BURST));
+                              hslot + (c + 1) * (32 / BURST), c + 1);
                 }
+            };
+            if (FOLD) {   // small body: unrolled, so the chunk index is a constant
+#pragma unroll
+                for (int c = 0; c < kCols / 32; c += 2) step(c);
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < kCols / 32; c += 2) step(c);
             }
-            // accumulator drained: hand the TMEM buffer back before the global flush
+            // accumulator drained: hand the TMEM buffer back before the global stores
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&bar_acc_empty[ab]);
             const long long e2 = profiler ? clock64() : 0;
-            epi.end_tile();
+            epi.end_tile(hslot);
             if (profiler) {
                 const long long e3 = clock64();
                 ew += e1 - e0;
@@ -511,6 +639,7 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 ef += e3 - e2;
             }
         }
+        epi.finish();
         if (profiler) {
             atomicAdd(a.prof + 3, static_cast<unsigned long long>(ew));
             atomicAdd(a.prof + 4, static_cast<unsigned long long>(ec));
@@ -556,13 +685,14 @@ dist_gemm_simt_kernel(const GemmArgs a) {
     using AccT = typename std::conditional<KIND == kKindI8, int32_t, float>::type;
     __shared__ __align__(16) EpiShared epi_sh;
     const int n_qb = (a.nq + kTileQ - 1) / kTileQ;
-    const int64_t total = static_cast<int64_t>(n_qb) * a.n_tiles_sel;
+    const ItemRange range(a, n_qb);
     const bool l2 = a.metric == kMetricL2;
     const uint32_t* gnorm = static_cast<const uint32_t*>(a.bnorm);
-    RowEpilogue<AccT, MODE, BURST, KIND == kKindBF16> epi(a, epi_sh, threadIdx.x);
-    for (int64_t item = blockIdx.x; item < total; item += gridDim.x) {
-        const int qb = static_cast<int>(item % n_qb);
-        const int sel = static_cast<int>(item / n_qb);
+    RowEpilogue<AccT, MODE, BURST, KIND == kKindBF16, kTileB / 32> epi(a);
+    ItemCursor cur(range);
+    for (int64_t i = 0; i < range.count; ++i, cur.next()) {
+        const int qb = cur.qb;
+        const int sel = cur.sel;
         const int tile = tile_of(a, sel);
         const int q = qb * kTileQ + threadIdx.x;
         const bool row_ok = q < a.nq;
@@ -588,14 +718,15 @@ dist_gemm_simt_kernel(const GemmArgs a) {
                 else r[j] = __float_as_uint(acc);
             }
             const int bslot = sel * (kTileB / BURST) + c * (32 / BURST);
-            epi.chunk(r, &epi_sh.norm[0][c * 32], col0, nvalid, bslot);
+            epi.chunk(r, &epi_sh.norm[0][c * 32], col0, nvalid, bslot, c);
         }
-        epi.end_tile();
+        epi.end_tile(sel * (kTileB / BURST));
     }
+    epi.finish();
 }
 
 template <int KIND, int MODE, int BURST>
-cudaError_t launch_one(const GemmLaunch& L, const GemmArgs& a, const CUtensorMap* mapA, const CUtensorMap* mapB,
+cudaError_t launch_one(const GemmLaunch& L, GemmArgs a, const CUtensorMap* mapA, const CUtensorMap* mapB,
                        cudaStream_t stream) {
     const int n_qb = (a.nq + kTileQ - 1) / kTileQ;
     const int64_t total = static_cast<int64_t>(n_qb) * a.n_tiles_sel;
@@ -605,12 +736,22 @@ cudaError_t launch_one(const GemmLaunch& L, const GemmArgs& a, const CUtensorMap
         dist_gemm_simt_kernel<KIND, MODE, BURST><<<grid, kTileQ, 0, stream>>>(a);
         return cudaGetLastError();
     }
+    // shared-memory plan: resident query tile (if it is small) + as many ring stages as fit
+    const int elem = KIND == kKindI8 ? 1 : 2;
+    const int nkc = (a.d * elem + kChunkBytes - 1) / kChunkBytes;
+    a.a_resident = nkc <= kResidentMaxChunks ? 1 : 0;
+    const int a_bytes = a.a_resident ? nkc * kStageABytes : 0;
+    const int stage_bytes = a.a_resident ? kStageBBytes : kStageBytes;
+    int nst = (kGemmSmemBudget - 1024 - a_bytes) / stage_bytes;
+    if (nst > kMaxStages) nst = kMaxStages;
+    a.n_stages = nst;
+    const int smem = a_bytes + nst * stage_bytes + 1024;
     auto kern = dist_gemm_tc_kernel<KIND, MODE, BURST>;
     // per-device attribute; cheap enough to set on every launch
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBudget);
     if (e != cudaSuccess) return e;
     const int grid = static_cast<int>(total < L.num_sms ? total : L.num_sms);
-    kern<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(*mapA, *mapB, a);
+    kern<<<grid, kGemmThreads, smem, stream>>>(*mapA, *mapB, a);
     return cudaGetLastError();
 }
 

@@ -45,8 +45,8 @@ struct GemmArgs {
     int mins_stride;      // n_tiles_sel * (kTileB / burst)
     // kModeAppend
     const uint32_t* tau;  // [nq] inclusive threshold on the ordered key
-    uint64_t* cand;       // [nq][cap] packed (ordered key, position)
-    uint32_t* counts;     // [nq]
+    uint64_t* cand;       // [nq][cap] packed (ordered key, position); reserved but unused slots hold "invalid"
+    uint32_t* counts;     // [nq] slots reserved (blocks of 8 per thread and query block run): >= candidates
     uint32_t cap;
     int direct;           // 1: slot = position (cap >= N, no atomics); 0: slot = atomic counter
     int* err;             // device error word
@@ -54,6 +54,9 @@ struct GemmArgs {
     //   0 producer wait-empty   1 mma wait-acc-empty   2 mma wait-full   3 epilogue wait-acc-full
     //   4 epilogue chunks       5 epilogue flush       6 items           7 total kernel cycles (per CTA, summed)
     unsigned long long* prof;
+    // filled in by launch_dist_gemm (tcgen05 variant): shared-memory plan
+    int a_resident;       // 1: the query tile stays in shared memory for a whole query block
+    int n_stages;         // ring stages (base chunks, or query + base chunks when not resident)
 };
 
 struct GemmLaunch {

@@ -202,7 +202,7 @@ void FlatIndex::get_labels(int64_t offset, int64_t n, int64_t* out) const {
 // element at or below it), so appending every key <= that bound in the full pass cannot lose a
 // true top-k member.  The expected number of appended candidates is about k / (sample
 // fraction); cap is four times that.
-FlatIndex::Plan FlatIndex::make_plan(int k) const {
+FlatIndex::Plan FlatIndex::make_plan(int k, int64_t nq) const {
     Plan p{};
     const int64_t n_tiles = (n_ + kTileB - 1) / kTileB;
     const int64_t need = std::max<int64_t>(4LL * k, 1024);
@@ -238,6 +238,12 @@ FlatIndex::Plan FlatIndex::make_plan(int k) const {
     if (p.sampled) {
         const double inv_f = static_cast<double>(n_tiles) / p.s_tiles;
         uint64_t want = static_cast<uint64_t>(4.0 * k * inv_f);
+        // The append epilogue reserves slots in blocks of 8 per (thread, run of tiles of one query
+        // block); a row is shared by two threads in each of the CTAs that walk its query block, and
+        // every one of them may leave a block partly unused.
+        const int64_t n_qb = (std::max<int64_t>(nq, 1) + kTileQ - 1) / kTileQ;
+        const uint64_t owners = 2 * static_cast<uint64_t>((num_sms_ + n_qb - 1) / n_qb + 1);
+        want += owners * 16;   // an open block and one reserved ahead
         p.cap = pow2_ceil(std::max<uint64_t>(p.s_tiles == n_tiles ? 512 : 2048, want));
         if (p.cap >= static_cast<uint64_t>(n_pad)) p.sampled = false;
     }
@@ -287,7 +293,7 @@ void FlatIndex::run_page(int nq, const void* xq_raw, const void* xq_op_in, int k
             throw std::runtime_error("cuTensorMapEncodeTiled failed for the query operand");
     }
 
-    Plan plan = make_plan(k);
+    Plan plan = make_plan(k, nq);
     if (force_full) {
         plan.sampled = false;
         plan.cap = static_cast<uint32_t>(round_up(n_, kTileB));
@@ -417,7 +423,7 @@ void FlatIndex::search_device(int64_t nq, const void* xq, bool q_is_f16, int k, 
     }
     const size_t in_row = static_cast<size_t>(d_) * in_elem_bytes();
 
-    const Plan plan = make_plan(k);
+    const Plan plan = make_plan(k, nq);
     int64_t page = static_cast<int64_t>(kCandBudgetBytes / (static_cast<size_t>(plan.cap) * 8));
     if (page >= kTileQ) page = page / kTileQ * kTileQ;
     if (page < 1) page = 1;

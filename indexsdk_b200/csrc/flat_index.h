@@ -149,7 +149,7 @@ private:
         int s_tiles;
         uint32_t cap;
     };
-    Plan make_plan(int k) const;
+    Plan make_plan(int k, int64_t nq) const;
     void run_page(int nq, const void* xq_raw, const void* xq_op, int k, float* D, int64_t* I, int ldk,
                   const int32_t* qmap_dev, bool force_full);
     void reserve(int64_t n);

@@ -519,7 +519,11 @@ cudaError_t launch_refine_f32(uint64_t* cand, const uint32_t* counts, uint32_t n
                               int metric, const float* xq, const float* xb, cudaStream_t stream) {
     if (nq <= 0) return cudaSuccess;
     uint32_t per_row = counts ? cap : (n_fixed < cap ? n_fixed : cap);
+    // Blocks stride over a row's candidates, so a few thousand blocks in total keep the machine
+    // busy; one block per 128 candidate SLOTS would mostly launch blocks that find nothing to do.
     int gx = static_cast<int>((per_row + 127) / 128);
+    const int want = (2048 + nq - 1) / nq;
+    if (gx > want) gx = want;
     if (gx > 64) gx = 64;
     if (gx < 1) gx = 1;
     const size_t smem = (static_cast<size_t>(d) + 4 * 32 * kRefPitch) * sizeof(float);
