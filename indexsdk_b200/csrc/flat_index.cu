@@ -368,6 +368,12 @@ void FlatIndex::run_page(int nq, const void* xq_raw, const void* xq_op_in, int k
     // 5. fp32 refinement of the candidates
     if (dtype_ == kF32) {
         timer_.begin(kStageRefine, stream_);
+        // worth a pass only when the threshold came from a subset of the tiles (about 1 / fraction
+        // times more candidates than k)
+        if (plan.sampled && static_cast<int64_t>(plan.s_tiles) * 2 <= (n_ + kTileB - 1) / kTileB) {
+            B200_CUDA_CHECK(launch_prune_candidates(cand, counts, plan.cap, nq, k, eps, stream_));
+            stats_.kernel_launches += 1;
+        }
         B200_CUDA_CHECK(launch_refine_f32(cand, counts_arg, n_fixed, plan.cap, nq, d_, metric_,
                                           static_cast<const float*>(xq_raw), x32_.as<float>(), stream_));
         stats_.kernel_launches += 1;

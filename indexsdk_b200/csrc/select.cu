@@ -16,17 +16,19 @@ constexpr int kSmallSet = 512;   // candidate sets up to this size are ranked by
 // the bin that contains rank r (1-based) and the number of elements in lower bins.
 __device__ __forceinline__ void find_bucket(uint32_t* hist, uint32_t* scan, uint32_t r, uint32_t* bucket,
                                             uint32_t* below) {
-    const int t = threadIdx.x;
-    scan[t] = hist[t];
-    __syncthreads();
-    for (int off = 1; off < 256; off <<= 1) {
-        uint32_t v = t >= off ? scan[t - off] : 0u;
-        __syncthreads();
-        scan[t] += v;
-        __syncthreads();
+    // 256 threads, one bin each: shuffle scan inside the warp, the eight warp totals through `scan`
+    const int t = threadIdx.x, lane = t & 31, w = t >> 5;
+    const uint32_t v = hist[t];
+    uint32_t incl = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t u = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += u;
     }
-    const uint32_t incl = scan[t];
-    const uint32_t excl = incl - hist[t];
+    if (lane == 31) scan[w] = incl;
+    __syncthreads();
+    for (int i = 0; i < w; ++i) incl += scan[i];
+    const uint32_t excl = incl - v;
     if (incl >= r && excl < r) {
         *bucket = t;
         *below = excl;
@@ -76,6 +78,63 @@ kth_threshold_kernel(const uint32_t* mins, int stride, int n, int k, const float
             if (kth > tau_all) kth = tau_all;
         }
         tau[q] = kth;
+    }
+}
+
+// Drops candidates that cannot reach the exact top-k before the (costly) exact refinement.  The
+// keys in the list are approximate, |approx - exact| <= eps for every candidate.  With A_k the k-th
+// smallest approximate key, k candidates have exact keys <= A_k + eps, so the exact k-th key is
+// <= A_k + eps and every member of the exact top-k has an approximate key <= A_k + 2 eps; all
+// others are overwritten with the "invalid" marker.  A constant offset common to a row's keys
+// cancels out of this argument.
+constexpr int kPruneKeys = 4096;    // keys staged in shared memory for the rank search
+constexpr int kPruneKeep = 2048;    // survivors staged for the in-place compaction
+__global__ void __launch_bounds__(kSelThreads)
+prune_candidates_kernel(uint64_t* cand, uint32_t* counts, uint32_t cap, int k, const float* eps) {
+    __shared__ uint32_t hist[256], scan[256], sh_bucket, sh_below, sh_fill;
+    __shared__ uint32_t keys[kPruneKeys];
+    __shared__ uint64_t keep[kPruneKeep];
+    const int q = blockIdx.x;
+    uint64_t* row = cand + static_cast<int64_t>(q) * cap;
+    const uint32_t n = counts[q];
+    if (n > cap) return;   // overflowed row: left as it is for the selection kernel to flag
+    if (n <= static_cast<uint32_t>(k)) return;
+    uint32_t kth_ord;
+    if (n <= static_cast<uint32_t>(kPruneKeys)) {
+        for (uint32_t i = threadIdx.x; i < n; i += kSelThreads) keys[i] = static_cast<uint32_t>(row[i] >> 32);
+        __syncthreads();
+        kth_ord = block_radix_kth<uint32_t>(keys, n, static_cast<uint32_t>(k), hist, scan, &sh_bucket, &sh_below);
+    } else {
+        kth_ord = static_cast<uint32_t>(
+            block_radix_kth<uint64_t>(row, n, static_cast<uint32_t>(k), hist, scan, &sh_bucket, &sh_below) >> 32);
+    }
+    if (kth_ord == 0xFFFFFFFFu) return;   // fewer than k real candidates
+    float lim = ord_to_float(kth_ord);
+    lim = lim + 2.f * eps[q];
+    lim = lim + fabsf(lim) * 9.5367431640625e-07f + eps[q] * 0.125f;   // slack for the adds and the accumulation
+    if (lim != lim) return;
+    const uint32_t lim_ord = float_to_ord(lim);
+    if (threadIdx.x == 0) sh_fill = 0;
+    __syncthreads();
+    // survivors go to shared memory first: the row is compacted in place
+    for (uint32_t i = threadIdx.x; i < n; i += kSelThreads) {
+        const uint64_t v = row[i];
+        if (v != kCandInvalid && static_cast<uint32_t>(v >> 32) <= lim_ord) {
+            const uint32_t slot = atomicAdd(&sh_fill, 1u);
+            if (slot < static_cast<uint32_t>(kPruneKeep)) keep[slot] = v;
+        }
+    }
+    __syncthreads();
+    const uint32_t m = sh_fill;
+    if (m <= static_cast<uint32_t>(kPruneKeep)) {
+        for (uint32_t i = threadIdx.x; i < m; i += kSelThreads) row[i] = keep[i];
+        if (threadIdx.x == 0) counts[q] = m;
+    } else {
+        // too many to stage: invalidate the losers where they are
+        for (uint32_t i = threadIdx.x; i < n; i += kSelThreads) {
+            const uint64_t v = row[i];
+            if (v != kCandInvalid && static_cast<uint32_t>(v >> 32) > lim_ord) row[i] = kCandInvalid;
+        }
     }
 }
 
@@ -512,6 +571,13 @@ cudaError_t launch_select_topk(const uint64_t* cand, const uint32_t* counts, uin
         if (e != cudaSuccess) return e;
     }
     select_topk_kernel<<<nq, kSelThreads, smem, stream>>>(cand, counts, n_fixed, cap, k, P, out, overflow);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_prune_candidates(uint64_t* cand, uint32_t* counts, uint32_t cap, int nq, int k,
+                                    const float* eps, cudaStream_t stream) {
+    if (nq <= 0) return cudaSuccess;
+    prune_candidates_kernel<<<nq, kSelThreads, 0, stream>>>(cand, counts, cap, k, eps);
     return cudaGetLastError();
 }
 

@@ -24,6 +24,11 @@ cudaError_t launch_select_topk(const uint64_t* cand, const uint32_t* counts, uin
 // fp32 refinement: replaces the key of every candidate by the canonical fp32 distance
 // (sequential fmaf over the dimension) computed from the fp32 rows; L2 -> distance,
 // IP -> negated dot product.
+// fp32 index, thresholded path: removes candidates whose approximate key exceeds the k-th smallest
+// approximate key of the row by more than 2 eps[row] (they cannot be in the exact top-k); the row
+// is compacted and counts[row] updated
+cudaError_t launch_prune_candidates(uint64_t* cand, uint32_t* counts, uint32_t cap, int nq, int k,
+                                    const float* eps, cudaStream_t stream);
 cudaError_t launch_refine_f32(uint64_t* cand, const uint32_t* counts, uint32_t n_fixed, uint32_t cap, int nq, int d,
                               int metric, const float* xq, const float* xb, cudaStream_t stream);
 
