@@ -268,6 +268,7 @@ struct ScanArgs {
     uint8_t* flag;           // [nq] 1 = not verified, re-scan exactly
     const int32_t* qlist;    // exact scan: indices of the queries to process
     unsigned long long* scanned;
+    unsigned int* work;      // persistent scan: next query to hand out (zeroed before the launch)
 };
 
 // ---------------------------------------------------------------------------------------
@@ -302,9 +303,12 @@ struct GroupSum<MT, MT> {
 // Lane l owns sub-quantizer l % 16; the two half-warps take adjacent codes, so a warp reads 32 * dsub
 // contiguous floats of the regrouped codebook per step and its two stores touch 32 distinct banks.
 // DS = dsub at compile time (query slice in registers), DS = 0: any dsub.
+// pitch: floats per table row (32, or 64 when two queries share a row); warp / nwarps: the
+// building warps.
 template <int DS>
-__device__ __forceinline__ void build_scan_table(const ScanArgs& a, int64_t q, int groups, float* lut) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+__device__ __forceinline__ void build_scan_table(const ScanArgs& a, int64_t q, int groups, float* lut, int pitch,
+                                                 int warp, int nwarps) {
+    const int lane = threadIdx.x & 31;
     const int mm = lane & 15, half = lane >> 4;
     const int dsub = DS > 0 ? DS : a.dsub;
     for (int g = 0; g < groups; ++g) {
@@ -315,7 +319,7 @@ __device__ __forceinline__ void build_scan_table(const ScanArgs& a, int64_t q, i
             for (int t = 0; t < DS; ++t) qr[t] = __ldg(qrow + t);
         }
 #pragma unroll 4
-        for (int c = 2 * warp + half; c < kKsub; c += 2 * kScanWarps) {
+        for (int c = 2 * warp + half; c < kKsub; c += 2 * nwarps) {
             const float* cw = a.cbT + (static_cast<size_t>(g * kKsub + c) * 16 + mm) * dsub;
             float acc = 0.f;
             if (DS > 0 && DS % 4 == 0) {
@@ -346,12 +350,180 @@ __device__ __forceinline__ void build_scan_table(const ScanArgs& a, int64_t q, i
                 }
             }
             if (a.by_residual) acc = -2.f * acc;
-            float* row = lut + (g * kKsub + c) * 32;
+            float* row = lut + (g * kKsub + c) * pitch;
             row[mm + 16 * half] = acc;
             row[mm + 16 * (half ^ 1)] = acc;
         }
     }
 }
+
+// Where a warp gets its probes (inverted lists) from.
+//   StaticFeed : probes p_first, p_first + stride, ... in batches of 32 -- lane i fetches the
+//                metadata of the batch's i-th probe (list bounds, coarse distance), so the dependent
+//                chain probe -> offsets is paid once per batch.
+//   SharedFeed : the probes' metadata sits in shared memory and the warps working on the query take
+//                them one at a time from a shared counter, so none of them idles while another
+//                still has lists to scan.
+struct StaticFeed {
+    const ScanArgs& a;
+    int64_t q;
+    int next_p0, stride, lane;
+    int li;
+    uint32_t my_begin, my_end;
+    float my_base;
+    unsigned long long& visited;
+    __device__ __forceinline__ StaticFeed(const ScanArgs& a_, int64_t q_, int p_first, int p_stride, int lane_,
+                                          unsigned long long& visited_)
+        : a(a_), q(q_), next_p0(p_first), stride(p_stride), lane(lane_), li(32), my_begin(0), my_end(0),
+          my_base(0.f), visited(visited_) {}
+    __device__ __forceinline__ bool next(uint32_t& begin, uint32_t& end, float& base) {
+        if (li >= 32) {
+            if (next_p0 >= a.nprobe) return false;
+            my_begin = my_end = 0;
+            my_base = 0.f;
+            const int p = next_p0 + lane * stride;
+            if (p < a.nprobe) {
+                const int64_t list = a.cI[q * a.nprobe + p];
+                if (list >= 0) {
+                    my_begin = static_cast<uint32_t>(a.offsets[list]);
+                    my_end = static_cast<uint32_t>(a.offsets[list + 1]);
+                    if (a.by_residual) my_base = a.cD[q * a.nprobe + p];
+                }
+            }
+            visited += my_end - my_begin;   // per lane; all lanes add their share at the end
+            next_p0 += 32 * stride;
+            li = 0;
+        }
+        begin = __shfl_sync(0xffffffffu, my_begin, li);
+        end = __shfl_sync(0xffffffffu, my_end, li);
+        base = __shfl_sync(0xffffffffu, my_base, li);
+        ++li;
+        return true;
+    }
+};
+
+struct SharedFeed {
+    const uint32_t* s_begin;   // [nprobe]
+    const uint32_t* s_end;
+    const float* s_base;
+    int* s_next;               // next probe to hand out
+    int nprobe, lane;
+    __device__ __forceinline__ bool next(uint32_t& begin, uint32_t& end, float& base) {
+        int p = 0;
+        if (lane == 0) p = atomicAdd(s_next, 1);
+        p = __shfl_sync(0xffffffffu, p, 0);
+        if (p >= nprobe) return false;
+        begin = s_begin[p];
+        end = s_end[p];
+        base = s_base[p];
+        return true;
+    }
+};
+
+// The filter loop of one warp over the probes its feed hands out.  `sum` adds the table entries of
+// one vector's codes to an accumulator; `gth` is the bound shared by the warps that work on the
+// same query (float bits, >= 0).  dk / pk: the warp's sorted k' best so far.  The code loads are
+// software-pipelined across list boundaries.  Positions fit 32 bits (an index holds fewer than
+// 2^31 vectors).
+template <int MT, int KPT, typename Sum, typename Feed>
+__device__ __forceinline__ void scan_warp_probes(const ScanArgs& a, Feed& feed, int lane, const Sum& sum, int* gth,
+                                                 float (&dk)[KPT], uint32_t (&pk)[KPT]) {
+    float th_d = __shfl_sync(0xffffffffu, dk[KPT - 1], 31);
+    uint32_t th_p = __shfl_sync(0xffffffffu, pk[KPT - 1], 31);
+    const uint4* codes4 = reinterpret_cast<const uint4*>(a.codes);
+    uint32_t begin = 0, end = 0, v0 = 0;
+    float base = 0.f;
+    constexpr int U = 2;                 // 32-vector sub-chunks per chunk
+    auto advance = [&]() -> bool {      // moves to the next chunk; false when the feed has run dry
+        v0 += 32 * U;
+        while (v0 >= end) {
+            if (!feed.next(begin, end, base)) return false;
+            v0 = begin & ~31u;
+            if (begin == end) v0 = end;   // empty or absent list
+        }
+        return true;
+    };
+    // One chunk in flight: codes, the per-vector term and where it came from.  Lanes outside
+    // the list read a clamped (valid) address and carry NaN, which fails every comparison, so
+    // the lookups and the threshold test run without any per-lane validity branch.
+    struct Chunk {
+        uint4 c[U][MT];
+        float t[U];      // per-vector term (loaded; consumed only when the chunk is processed)
+        float bias[U];   // the list's term, or NaN for a lane outside the list
+        uint32_t v0;
+    };
+    auto fetch = [&](Chunk& ch) {
+        ch.v0 = v0;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t v = v0 + 32 * u + lane;
+            const bool valid = (v - begin) < (end - begin);
+            const uint32_t vc = min(max(v, begin), end - 1);
+            const uint4* cp = codes4 + static_cast<size_t>(vc) * MT;
+#pragma unroll
+            for (int g = 0; g < MT; ++g) ch.c[u][g] = __ldg(cp + g);
+            ch.t[u] = a.by_residual ? __ldg(a.t2 + vc) : 0.f;
+            ch.bias[u] = valid ? base : __int_as_float(0x7fc00000);
+        }
+    };
+    auto process = [&](const Chunk& ch) {
+        // the CTA-wide bound is read before the lookups and used after them
+        const float lim = fminf(th_d, __int_as_float(*reinterpret_cast<volatile int*>(gth)));
+        float acc[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) acc[u] = ch.bias[u] + ch.t[u];
+#pragma unroll
+        for (int u = 0; u < U; ++u) sum(ch.c[u], acc[u]);
+        bool maybe = false;
+#pragma unroll
+        for (int u = 0; u < U; ++u) maybe |= acc[u] <= lim;
+        if (__any_sync(0xffffffffu, maybe)) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const uint32_t v = ch.v0 + 32 * u + lane;   // v & 15 == lane & 15: the stored rotation
+                const bool pass = acc[u] <= lim && pair_less<uint32_t>(acc[u], v, th_d, th_p);
+                unsigned bal = __ballot_sync(0xffffffffu, pass);
+                while (bal) {
+                    const int src = __ffs(bal) - 1;
+                    bal &= bal - 1;
+                    const float vd = __shfl_sync(0xffffffffu, acc[u], src);
+                    const uint32_t vp = __shfl_sync(0xffffffffu, v, src);
+                    if (pair_less<uint32_t>(vd, vp, th_d, th_p)) {
+                        warp_insert<KPT, uint32_t>(dk, pk, vd, vp, lane);
+                        th_d = __shfl_sync(0xffffffffu, dk[KPT - 1], 31);
+                        th_p = __shfl_sync(0xffffffffu, pk[KPT - 1], 31);
+                    }
+                }
+            }
+            // a full list bounds what the whole CTA still needs: publish its worst distance
+            // (clamped at 0 so that the integer minimum orders like the float)
+            if (lane == 0 && th_d < lim) atomicMin(gth, __float_as_int(fmaxf(th_d, 0.f)));
+        }
+    };
+    Chunk ca, cb;
+    bool have = advance();
+    if (have) fetch(ca);
+    while (have) {
+        // the next chunk's loads are in flight while this one is processed
+        have = advance();
+        if (have) fetch(cb);
+        process(ca);
+        if (!have) break;
+        have = advance();
+        if (have) fetch(ca);
+        process(cb);
+    }
+}
+
+// Table lookups of the [g][code][32] layout (128-byte rows): three integer instructions and a load
+// per entry.
+template <int MT>
+struct RowSum128 {
+    uint32_t offb[16];   // shared-space byte address of this lane's column in the row of code 0, group 0
+    __device__ __forceinline__ void operator()(const uint4 (&c)[MT], float& acc) const {
+        GroupSum<0, MT>::run(c, offb, acc);
+    }
+};
 
 template <int MT, int KPT>
 __global__ void __launch_bounds__(kScanThreads, (MT == 1 && KPT <= 2) ? 6 : 1)
@@ -368,9 +540,9 @@ ivfpq_fast_scan_kernel(const ScanArgs a) {
     int& s_gth = *reinterpret_cast<int*>(scan_smem + static_cast<size_t>(MT) * kKsub * 32 * 4);
     if (threadIdx.x == 0) s_gth = 0x7f800000;
     switch (a.dsub) {
-        case 4: build_scan_table<4>(a, q, MT, lut); break;
-        case 8: build_scan_table<8>(a, q, MT, lut); break;
-        default: build_scan_table<0>(a, q, MT, lut); break;
+        case 4: build_scan_table<4>(a, q, MT, lut, 32, warp, kScanWarps); break;
+        case 8: build_scan_table<8>(a, q, MT, lut, 32, warp, kScanWarps); break;
+        default: build_scan_table<0>(a, q, MT, lut, 32, warp, kScanWarps); break;
     }
     __syncthreads();
 
@@ -381,126 +553,15 @@ ivfpq_fast_scan_kernel(const ScanArgs a) {
         dk[s] = __int_as_float(0x7f800000);
         pk[s] = kNoPos;
     }
-    float th_d = __int_as_float(0x7f800000);
-    uint32_t th_p = kNoPos;
     unsigned long long visited = 0;
 
-    // Lane l reads sub-quantizer (s + l) mod 16 at step s.  offb[s]: shared-space byte address of
-    // that lane's column inside the [code][32] row of code 0 (group 0).
+    // Lane l reads sub-quantizer (s + l) mod 16 at step s: its column inside a [code][32] row.
     const uint32_t lut_base = static_cast<uint32_t>(__cvta_generic_to_shared(lut));
-    uint32_t offb[16];
+    RowSum128<MT> sum;
 #pragma unroll
-    for (int s = 0; s < 16; ++s) offb[s] = lut_base + 4u * (((s + lane) & 15) + (lane & 16));
-
-    // The warp's probes are visited in batches of 32: lane i fetches the metadata of the batch's
-    // i-th probe (list bounds, coarse distance), so the dependent chain probe -> offsets is paid
-    // once per batch, and the code loads are software-pipelined across list boundaries.
-    // Positions fit 32 bits (an index holds fewer than 2^31 vectors).
-    const int stride = a.S * kScanWarps;
-    const uint4* codes4 = reinterpret_cast<const uint4*>(a.codes);
-    for (int p0 = split + a.S * warp; p0 < a.nprobe; p0 += 32 * stride) {
-        uint32_t my_begin = 0, my_end = 0;
-        float my_base = 0.f;
-        {
-            const int p = p0 + lane * stride;
-            if (p < a.nprobe) {
-                const int64_t list = a.cI[q * a.nprobe + p];
-                if (list >= 0) {
-                    my_begin = static_cast<uint32_t>(a.offsets[list]);
-                    my_end = static_cast<uint32_t>(a.offsets[list + 1]);
-                    if (a.by_residual) my_base = a.cD[q * a.nprobe + p];
-                }
-            }
-        }
-        visited += my_end - my_begin;   // per lane; all lanes add their share at the end
-        int li = -1;
-        uint32_t begin = 0, end = 0, v0 = 0;
-        float base = 0.f;
-        constexpr int U = 2;                 // 32-vector sub-chunks per chunk
-        auto advance = [&]() -> bool {      // moves (li, v0) to the next chunk; false when the batch is done
-            v0 += 32 * U;
-            while (li < 0 || v0 >= end) {
-                ++li;
-                if (li >= 32) return false;
-                begin = __shfl_sync(0xffffffffu, my_begin, li);
-                end = __shfl_sync(0xffffffffu, my_end, li);
-                base = __shfl_sync(0xffffffffu, my_base, li);
-                v0 = begin & ~31u;
-                if (begin == end) v0 = end;   // empty or absent list
-            }
-            return true;
-        };
-        // One chunk in flight: codes, the per-vector term and where it came from.  Lanes outside
-        // the list read a clamped (valid) address and carry NaN, which fails every comparison, so
-        // the lookups and the threshold test run without any per-lane validity branch.
-        struct Chunk {
-            uint4 c[U][MT];
-            float t[U];      // per-vector term (loaded; consumed only when the chunk is processed)
-            float bias[U];   // the list's term, or NaN for a lane outside the list
-            uint32_t v0;
-        };
-        auto fetch = [&](Chunk& ch) {
-            ch.v0 = v0;
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const uint32_t v = v0 + 32 * u + lane;
-                const bool valid = (v - begin) < (end - begin);
-                const uint32_t vc = min(max(v, begin), end - 1);
-                const uint4* cp = codes4 + static_cast<size_t>(vc) * MT;
-#pragma unroll
-                for (int g = 0; g < MT; ++g) ch.c[u][g] = __ldg(cp + g);
-                ch.t[u] = a.by_residual ? __ldg(a.t2 + vc) : 0.f;
-                ch.bias[u] = valid ? base : __int_as_float(0x7fc00000);
-            }
-        };
-        auto process = [&](const Chunk& ch) {
-            // the CTA-wide bound is read before the lookups and used after them
-            const float lim = fminf(th_d, __int_as_float(*reinterpret_cast<volatile int*>(&s_gth)));
-            float acc[U];
-#pragma unroll
-            for (int u = 0; u < U; ++u) acc[u] = ch.bias[u] + ch.t[u];
-#pragma unroll
-            for (int u = 0; u < U; ++u) GroupSum<0, MT>::run(ch.c[u], offb, acc[u]);
-            bool maybe = false;
-#pragma unroll
-            for (int u = 0; u < U; ++u) maybe |= acc[u] <= lim;
-            if (__any_sync(0xffffffffu, maybe)) {
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    const uint32_t v = ch.v0 + 32 * u + lane;   // v & 15 == lane & 15: the stored rotation
-                    const bool pass = acc[u] <= lim && pair_less<uint32_t>(acc[u], v, th_d, th_p);
-                    unsigned bal = __ballot_sync(0xffffffffu, pass);
-                    while (bal) {
-                        const int src = __ffs(bal) - 1;
-                        bal &= bal - 1;
-                        const float vd = __shfl_sync(0xffffffffu, acc[u], src);
-                        const uint32_t vp = __shfl_sync(0xffffffffu, v, src);
-                        if (pair_less<uint32_t>(vd, vp, th_d, th_p)) {
-                            warp_insert<KPT, uint32_t>(dk, pk, vd, vp, lane);
-                            th_d = __shfl_sync(0xffffffffu, dk[KPT - 1], 31);
-                            th_p = __shfl_sync(0xffffffffu, pk[KPT - 1], 31);
-                        }
-                    }
-                }
-                // a full list bounds what the whole CTA still needs: publish its worst distance
-                // (clamped at 0 so that the integer minimum orders like the float)
-                if (lane == 0 && th_d < lim) atomicMin(&s_gth, __float_as_int(fmaxf(th_d, 0.f)));
-            }
-        };
-        Chunk ca, cb;
-        bool have = advance();
-        if (have) fetch(ca);
-        while (have) {
-            // the next chunk's loads are in flight while this one is processed
-            have = advance();
-            if (have) fetch(cb);
-            process(ca);
-            if (!have) break;
-            have = advance();
-            if (have) fetch(ca);
-            process(cb);
-        }
-    }
+    for (int s = 0; s < 16; ++s) sum.offb[s] = lut_base + 4u * (((s + lane) & 15) + (lane & 16));
+    StaticFeed feed(a, q, split + a.S * warp, a.S * kScanWarps, lane, visited);
+    scan_warp_probes<MT, KPT>(a, feed, lane, sum, &s_gth, dk, pk);
     if (a.scanned && visited) atomicAdd(a.scanned, visited);
 
     // merge the four warp lists, keep the kprime best of the CTA
@@ -527,6 +588,176 @@ ivfpq_fast_scan_kernel(const ScanArgs a) {
         // kept list is not full nothing was dropped.
         a.fth[q * a.S + split] = sp[KP - 1] != kNoPos ? sd[KP - 1] : __int_as_float(0x7f800000);
     }
+}
+
+// ---------------------------------------------------------------------------------------
+// 3a'. fast scan for large batches (M = 16): one persistent CTA per SM, four query slots
+// ---------------------------------------------------------------------------------------
+// A table row of 256 bytes holds the [32]-column rows of TWO queries side by side, and the table
+// starts on a 64 KB boundary of the shared window.  The address of an entry is then
+//   table | code << 8 | (query half * 128 + 4 * column)
+// -- the code value is exactly byte 1 -- so ONE byte-permute of the code word with a per-lane
+// constant forms it, against a permute and a multiply-add for 128-byte rows: three instructions
+// per lookup instead of four in a loop that is bound by instruction issue.  Two such tables (four
+// queries) fit beside the alignment gap; each query slot is worked by six warps, which take the
+// next query from a global counter when they are done, so slots never wait for one another.
+constexpr int kPsWarpsPerSlot = 6;
+constexpr int kPsSlots = 4;
+constexpr int kPsSlotThreads = kPsWarpsPerSlot * 32;              // 192
+constexpr int kPsThreads = kPsSlots * kPsSlotThreads;             // 768
+constexpr int kPsMaxProbe = 256;                                  // probes whose metadata is staged per slot
+constexpr int kPsMaxKpt = 2;                                      // k' <= 64 (k <= 48)
+constexpr int kPsScratchBytes = 33 * 1024;                        // slot control words, probe metadata, merge buffers
+constexpr int kPsSmemBytes = 3 * 65536 + 4096;                    // two aligned tables + gap + room for the scratch
+
+struct RowSum256 {
+    uint32_t offb[16];   // table base | (query half * 128 + 4 * this lane's column at step s)
+    __device__ __forceinline__ void operator()(const uint4 (&c)[1], float& acc) const {
+        const uint32_t w[4] = {c[0].x, c[0].y, c[0].z, c[0].w};
+#pragma unroll
+        for (int s = 0; s < 16; ++s) {
+            // bytes of the address: [offb.0, code byte s, offb.2, offb.3]
+            const uint32_t addr = __byte_perm(w[s >> 2], offb[s], 0x7604u | ((s & 3) << 4));
+            float val;
+            asm("ld.shared.f32 %0, [%1];" : "=f"(val) : "r"(addr));
+            acc = acc + val;
+        }
+    }
+};
+
+__device__ __forceinline__ void slot_barrier(int slot) {
+    asm volatile("bar.sync %0, %1;" ::"r"(slot + 1), "n"(kPsSlotThreads) : "memory");
+}
+
+// Bitonic sort of E pairs by the kPsSlotThreads threads of one slot.
+__device__ __forceinline__ void slot_sort_pairs(float* sd, uint32_t* sl, int E, int tid_s, int slot) {
+    for (int size = 2; size <= E; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int i = tid_s; i < E / 2; i += kPsSlotThreads) {
+                const int lo = 2 * i - (i & (stride - 1));
+                const int hi = lo + stride;
+                const bool up = (lo & size) == 0;
+                const float d1 = sd[lo], d2 = sd[hi];
+                const uint32_t l1 = sl[lo], l2 = sl[hi];
+                if (pair_less<uint32_t>(d2, l2, d1, l1) == up) {
+                    sd[lo] = d2; sd[hi] = d1;
+                    sl[lo] = l2; sl[hi] = l1;
+                }
+            }
+            slot_barrier(slot);
+        }
+    }
+}
+
+template <int KPT>
+__global__ void __launch_bounds__(kPsThreads, 1)
+ivfpq_scan_persist_kernel(const ScanArgs a) {
+    extern __shared__ __align__(16) uint8_t ps_smem[];
+    const uint32_t base = static_cast<uint32_t>(__cvta_generic_to_shared(ps_smem));
+    const uint32_t tab0 = (base + 0xFFFFu) & ~0xFFFFu;      // first 64 KB boundary of the shared window
+    const uint32_t gap = tab0 - base;
+    uint8_t* tabs = ps_smem + gap;                            // two tables of 64 KB
+    uint8_t* scratch = gap >= static_cast<uint32_t>(kPsScratchBytes) ? ps_smem : tabs + 2 * 65536;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slot = warp / kPsWarpsPerSlot, wslot = warp % kPsWarpsPerSlot;
+    const int tid_s = threadIdx.x - slot * kPsSlotThreads;
+    const int tbl = slot >> 1, half = slot & 1;
+    float* lut = reinterpret_cast<float*>(tabs + tbl * 65536) + half * 32;   // this query's half of the rows
+
+    // scratch: per slot {next query, bound}, then per slot the merge buffers
+    constexpr int E = 256 * KPT;                              // >= 192 * KPT entries, a power of two
+    constexpr int KP = 32 * KPT;
+    unsigned int* s_q = reinterpret_cast<unsigned int*>(scratch);            // [4]
+    int* s_gth = reinterpret_cast<int*>(scratch + 16);                       // [4]
+    int* s_next = reinterpret_cast<int*>(scratch + 32);                      // [4] next probe of the slot's query
+    uint32_t* s_pb = reinterpret_cast<uint32_t*>(scratch + 64) + slot * 3 * kPsMaxProbe;   // list begin
+    uint32_t* s_pe = s_pb + kPsMaxProbe;                                                   // list end
+    float* s_pbase = reinterpret_cast<float*>(s_pe + kPsMaxProbe);                         // coarse distance
+    uint32_t* sp = reinterpret_cast<uint32_t*>(scratch + 64 + kPsSlots * 3 * kPsMaxProbe * 4) + slot * 2 * E;
+    float* sd = reinterpret_cast<float*>(sp + E);
+
+    RowSum256 sum;
+#pragma unroll
+    for (int s = 0; s < 16; ++s)
+        sum.offb[s] = (tab0 + static_cast<uint32_t>(tbl) * 65536u) |
+                      (static_cast<uint32_t>(half) * 128u + 4u * (((s + lane) & 15) + (lane & 16)));
+
+    unsigned long long visited = 0;
+    for (;;) {
+        if (tid_s == 0) {
+            s_q[slot] = atomicAdd(a.work, 1u);
+            s_gth[slot] = 0x7f800000;
+            s_next[slot] = 0;
+        }
+        slot_barrier(slot);
+        const int64_t q = s_q[slot];
+        if (q >= a.nq) break;
+        // the probes' metadata: loads issued here, stored to shared memory after the table is built
+        uint32_t m_begin[(kPsMaxProbe + kPsSlotThreads - 1) / kPsSlotThreads] = {0, 0};
+        uint32_t m_end[(kPsMaxProbe + kPsSlotThreads - 1) / kPsSlotThreads] = {0, 0};
+        float m_base[(kPsMaxProbe + kPsSlotThreads - 1) / kPsSlotThreads] = {0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < (kPsMaxProbe + kPsSlotThreads - 1) / kPsSlotThreads; ++j) {
+            const int pidx = tid_s + j * kPsSlotThreads;
+            if (pidx < a.nprobe) {
+                const int64_t list = a.cI[q * a.nprobe + pidx];
+                if (list >= 0) {
+                    m_begin[j] = static_cast<uint32_t>(a.offsets[list]);
+                    m_end[j] = static_cast<uint32_t>(a.offsets[list + 1]);
+                    if (a.by_residual) m_base[j] = a.cD[q * a.nprobe + pidx];
+                }
+            }
+        }
+        switch (a.dsub) {
+            case 4: build_scan_table<4>(a, q, 1, lut, 64, wslot, kPsWarpsPerSlot); break;
+            case 8: build_scan_table<8>(a, q, 1, lut, 64, wslot, kPsWarpsPerSlot); break;
+            default: build_scan_table<0>(a, q, 1, lut, 64, wslot, kPsWarpsPerSlot); break;
+        }
+#pragma unroll
+        for (int j = 0; j < (kPsMaxProbe + kPsSlotThreads - 1) / kPsSlotThreads; ++j) {
+            const int pidx = tid_s + j * kPsSlotThreads;
+            if (pidx < a.nprobe) {
+                s_pb[pidx] = m_begin[j];
+                s_pe[pidx] = m_end[j];
+                s_pbase[pidx] = m_base[j];
+                visited += m_end[j] - m_begin[j];
+            }
+        }
+        slot_barrier(slot);
+
+        float dk[KPT];
+        uint32_t pk[KPT];
+#pragma unroll
+        for (int s = 0; s < KPT; ++s) {
+            dk[s] = __int_as_float(0x7f800000);
+            pk[s] = kNoPos;
+        }
+        SharedFeed feed{s_pb, s_pe, s_pbase, &s_next[slot], a.nprobe, lane};
+        scan_warp_probes<1, KPT>(a, feed, lane, sum, &s_gth[slot], dk, pk);
+
+        // merge the slot's six warp lists, keep the kprime best
+#pragma unroll
+        for (int s = 0; s < KPT; ++s) {
+            sd[tid_s * KPT + s] = dk[s];
+            sp[tid_s * KPT + s] = pk[s];
+        }
+        for (int i = kPsSlotThreads * KPT + tid_s; i < E; i += kPsSlotThreads) {
+            sd[i] = __int_as_float(0x7f800000);
+            sp[i] = kNoPos;
+        }
+        slot_barrier(slot);
+        slot_sort_pairs(sd, sp, E, tid_s, slot);
+        float* od = a.fd + q * KP;
+        uint32_t* op = a.fp + q * KP;
+        for (int i = tid_s; i < KP; i += kPsSlotThreads) {
+            od[i] = sd[i];
+            op[i] = sp[i];
+        }
+        if (tid_s == 0) a.fth[q] = sp[KP - 1] != kNoPos ? sd[KP - 1] : __int_as_float(0x7f800000);
+        slot_barrier(slot);   // the buffers and s_q are reused by the next query
+    }
+    if (a.scanned && visited) atomicAdd(a.scanned, visited);
 }
 
 // Canonical distance of the vector at `pos` (probed through list `list`).
@@ -776,6 +1007,25 @@ cudaError_t launch_fast(const ScanArgs& a, int kpt, cudaStream_t st) {
     }
 }
 
+cudaError_t launch_persist(const ScanArgs& a, int kpt, int num_sms, cudaStream_t st) {
+    cudaError_t e = cudaMemsetAsync(a.work, 0, sizeof(unsigned int), st);
+    if (e != cudaSuccess) return e;
+#define B200_PS_CASE(KP)                                                                       \
+    case KP: {                                                                                 \
+        auto kern = ivfpq_scan_persist_kernel<KP>;                                             \
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPsSmemBytes); \
+        if (e != cudaSuccess) return e;                                                        \
+        kern<<<num_sms, kPsThreads, kPsSmemBytes, st>>>(a);                                    \
+        return cudaGetLastError();                                                             \
+    }
+    switch (kpt) {
+        B200_PS_CASE(1)
+        B200_PS_CASE(2)
+        default: return cudaErrorInvalidValue;
+    }
+#undef B200_PS_CASE
+}
+
 cudaError_t launch_exact(const ScanArgs& a, int nq_launch, cudaStream_t st) {
     int kpt = 1;
     while (kpt * 32 < a.k) kpt <<= 1;
@@ -826,6 +1076,9 @@ IvfpqIndex::IvfpqIndex(int d, int nlist, int M, int nbits, bool by_residual, int
     B200_CUDA_CHECK(cudaMemset(w_tmp_.get(), 0, sizeof(unsigned long long)));
     const char* e = std::getenv("B200IDX_IVFPQ_EXACT");
     force_exact_ = e && std::strcmp(e, "1") == 0;
+    const char* np = std::getenv("B200IDX_IVFPQ_NO_PERSIST");   // development aid: always the per-query CTAs
+    no_persist_ = np && std::strcmp(np, "1") == 0;
+    w_work_.ensure(sizeof(unsigned int));
 }
 
 IvfpqIndex::~IvfpqIndex() {
@@ -1137,6 +1390,9 @@ void IvfpqIndex::search_device(int64_t nq, const float* xq, int k, float* D, int
         int S = static_cast<int>((16LL * num_sms_ + m - 1) / m);
         S = std::max(1, std::min(S, (nprobe + kScanWarps - 1) / kScanWarps));
         S = std::max(1, std::min(S, 4096 / kprime));
+        // large batches of 16-byte codes: persistent CTAs, four queries per SM at a time
+        const bool persist = M_ == 16 && kpt <= kPsMaxKpt && nprobe <= kPsMaxProbe && m >= 8LL * num_sms_ && !no_persist_;
+        if (persist) S = 1;
         a.S = S;
         a.kprime = kprime;
         a.fd = static_cast<float*>(w_fd_.ensure(static_cast<size_t>(m) * S * kprime * 4));
@@ -1153,7 +1409,12 @@ void IvfpqIndex::search_device(int64_t nq, const float* xq, int k, float* D, int
         const float cmax = coarse_->raw_view().max_norm;
         a.t2_bound = cb_norm_bound_ * cb_norm_bound_ + 2.f * cmax * cb_norm_bound_;
         timer_.begin(kStageScan, st);
-        B200_CUDA_CHECK(launch_fast(a, kpt, st));
+        if (persist) {
+            a.work = w_work_.as<unsigned int>();
+            B200_CUDA_CHECK(launch_persist(a, kpt, num_sms_, st));
+        } else {
+            B200_CUDA_CHECK(launch_fast(a, kpt, st));
+        }
         timer_.end(st);
         timer_.begin(kStageMerge, st);
         const int P = pow2_ceil_int(std::max(S * kprime, 32));

@@ -69,6 +69,7 @@ private:
     int nprobe_ = 1;
     int64_t n_ = 0;
     bool has_centroids_ = false, has_codebooks_ = false;
+    bool no_persist_ = false;
     int num_sms_ = 0;
     float cb_norm_bound_ = 0.f;           // sqrt(sum_m max_j |cb[m][j]|^2), for the filter's error bound
     bool force_exact_ = false;            // B200IDX_IVFPQ_EXACT=1: always use the exact scan kernels
@@ -81,7 +82,7 @@ private:
     std::vector<int64_t> offsets_host_;
     DeviceBuffer codes_, ids_, t2_;
     // scratch
-    DeviceBuffer w_cD_, w_cI_, w_fd_, w_fp_, w_fth_, w_flag_, w_qlist_, w_q_, w_D_, w_I_, w_assign_D_,
+    DeviceBuffer w_work_, w_cD_, w_cI_, w_fd_, w_fp_, w_fth_, w_flag_, w_qlist_, w_q_, w_D_, w_I_, w_assign_D_,
         w_assign_I_, w_list_, w_codes_, w_t2_, w_ids_, w_x_, w_tmp_;
     PinnedBuffer h_flag_;
     SearchStats stats_;

@@ -53,6 +53,8 @@ def test_golden_fixture(b200, tag, resid):
 @pytest.mark.parametrize("d,nlist,M,n,nq,nprobe,k,chunks", [
     (128, 256, 16, 60000, 50, 16, 10, 3),
     (128, 64, 16, 20000, 300, 64, 100, 1),
+    (128, 64, 16, 20000, 1500, 24, 10, 1),     # large batch of 16-byte codes: the persistent scan kernel
+    (64, 48, 16, 9000, 1300, 48, 40, 1),       # the same with k' = 64
     (96, 128, 48, 30000, 20, 32, 100, 2),
     (64, 32, 8, 5000, 9, 8, 320, 1),
     (128, 100, 32, 8000, 4, 100, 1, 1),
