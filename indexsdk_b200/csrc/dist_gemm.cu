@@ -1,15 +1,16 @@
 // tcgen05 / TMEM / TMA distance GEMM with fused selection epilogues, plus a plain CUDA-core
 // variant that shares the epilogue code and serves as an on-device cross-check.
 //
-// Pipeline of the tcgen05 variant (one persistent CTA per SM, 320 threads):
+// Pipeline of the tcgen05 variant (one persistent CTA per SM, 320 or 576 threads):
 //   warp 0 (one lane)  : TMA producer.  Per K chunk of 128 bytes: query box 128 x 128 B and base
 //                        box 256 x 128 B into a 4-stage ring of 48 KB stages (SWIZZLE_128B).
 //   warp 1 (one lane)  : issues tcgen05.mma 128 x 256 x (32 bytes of K) from shared-memory
 //                        descriptors into one of two 256-column TMEM accumulators; commits free
 //                        the stage (per chunk) and publish the accumulator (per tile).
-//   warps 2-9          : epilogue, two warps per scheduler.  Thread = (query row = TMEM lane, one
-//                        half of the tile's columns); reads 32 columns at a time with tcgen05.ld
-//                        (double-buffered) and applies the norm-add and the selection predicate.
+//   warps 2-9 / 2-17   : epilogue, two or four warps per scheduler (see epi_warps).  Thread = (query
+//                        row = TMEM lane, a half or a quarter of the tile's columns); reads 32
+//                        columns at a time with tcgen05.ld (double-buffered) and applies the
+//                        selection predicate (after the norm-add where the operands are not folded).
 // Work items are (query block, base tile) pairs, query block fastest, so the CTAs running at
 // the same time read the same base tiles and HBM sees each base tile about once per pass.
 #include "dist_gemm.cuh"
@@ -31,9 +32,12 @@ constexpr int kStageBBytes = kTileB * kChunkBytes;               // 32 KB
 constexpr int kStageBytes = kStageABytes + kStageBBytes;         // 48 KB
 constexpr int kGemmSmemBudget = 224 * 1024;                      // dynamic shared memory incl. 1 KB alignment slack
 constexpr int kResidentMaxChunks = 4;                            // query tile kept in shared memory up to 64 KB
-constexpr int kEpiWarps = 8;                                    // two per scheduler; pairs split the tile's columns
-constexpr int kEpiThreads = kEpiWarps * 32;
-constexpr int kGemmThreads = 64 + kEpiThreads;                   // producer warp + MMA warp + epilogue warps
+// Epilogue warps: two per scheduler, each thread draining half of a row's columns, where the
+// epilogue is bound by shared-memory norm loads (fp16, int8); four per scheduler and a quarter
+// of the columns each for the folded bf16 kind, whose short ALU-only epilogue is latency-bound
+// and scales with the number of warps.
+__host__ __device__ constexpr int epi_warps(int kind) { return kind == kKindBF16 ? 16 : 8; }
+__host__ __device__ constexpr int gemm_threads(int kind) { return 64 + 32 * epi_warps(kind); }   // + producer and MMA warps
 constexpr uint32_t kTmemCols = 512;
 
 template <typename AccT>
@@ -178,18 +182,25 @@ struct RowEpilogue {
     // Folded operands: r holds D for 32 columns.
     // ci: index of the chunk inside this thread's part of the tile (a constant after unrolling)
     __device__ __forceinline__ void chunk_fold(const uint32_t (&r)[32], int64_t col0, int nvalid, int ci) {
-        if (!row_ok) return;
+        if (!row_ok && (MODE == kModeBurstMin || a.direct)) return;
         if (MODE == kModeBurstMin) {
             constexpr int NB = 32 / BURST;
             const float ninf = __int_as_float(0xff800000);
+            // min / max and selects share the half-rate integer pipe, which is what bounds this
+            // epilogue: the test for rows past the end of the base is kept out of the common path.
+            const bool full = nvalid >= 32;
 #pragma unroll
             for (int b = 0; b < NB; ++b) {
                 float v[BURST];
+                if (full) {
 #pragma unroll
-                for (int j = 0; j < BURST; ++j) {
-                    const int c = b * BURST + j;
-                    v[j] = __uint_as_float(r[c]);
-                    if (nvalid < 32 && c >= nvalid) v[j] = ninf;   // rows past the end of the base
+                    for (int j = 0; j < BURST; ++j) v[j] = __uint_as_float(r[b * BURST + j]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < BURST; ++j) {
+                        const int c = b * BURST + j;
+                        v[j] = c < nvalid ? __uint_as_float(r[c]) : ninf;
+                    }
                 }
 #pragma unroll
                 for (int w = BURST / 2; w > 0; w >>= 1)
@@ -208,6 +219,7 @@ struct RowEpilogue {
                 if (c < nvalid && key <= tau) crow[c] = pack_cand(float_to_ord(key), static_cast<uint32_t>(col0 + c));
             }
         } else {
+            if (!row_ok) return;
             uint32_t t[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) t[i] = r[2 * i] & r[2 * i + 1];
@@ -270,11 +282,20 @@ struct RowEpilogue {
 #pragma unroll
             for (int b = 0; b < NB; ++b) {
                 AccT m[4] = {K::worst(), K::worst(), K::worst(), K::worst()};   // independent chains
+                if (nvalid >= 32) {
 #pragma unroll
-                for (int j = 0; j < BURST; ++j) {
-                    const int c = b * BURST + j;
-                    const AccT key = K::key(K::from_bits(r[c]), K::from_bits(bnb[c]), l2);
-                    if ((valid >> c) & 1u) m[j & 3] = key < m[j & 3] ? key : m[j & 3];
+                    for (int j = 0; j < BURST; ++j) {
+                        const int c = b * BURST + j;
+                        const AccT key = K::key(K::from_bits(r[c]), K::from_bits(bnb[c]), l2);
+                        m[j & 3] = key < m[j & 3] ? key : m[j & 3];
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < BURST; ++j) {
+                        const int c = b * BURST + j;
+                        const AccT key = K::key(K::from_bits(r[c]), K::from_bits(bnb[c]), l2);
+                        if ((valid >> c) & 1u) m[j & 3] = key < m[j & 3] ? key : m[j & 3];
+                    }
                 }
                 const AccT ma = m[0] < m[1] ? m[0] : m[1], mb = m[2] < m[3] ? m[2] : m[3];
                 dst[b] = K::ord(ma < mb ? ma : mb);
@@ -324,11 +345,17 @@ struct RowEpilogue {
             pre_ok = true;
         }
         if (MODE == kModeBurstMin && FOLD && row_ok) {
-            // one 16-byte store per four results instead of four scattered words
-            uint4* dst = reinterpret_cast<uint4*>(a.mins + static_cast<int64_t>(q) * a.mins_stride + hslot);
+            // 16-byte (or 8-byte) stores instead of scattered words
+            uint32_t* dst = a.mins + static_cast<int64_t>(q) * a.mins_stride + hslot;
+            constexpr int NW = NCH * (32 / BURST);
+            if (NW % 4 == 0) {
 #pragma unroll
-            for (int i = 0; i < static_cast<int>(sizeof(res) / 16); ++i)
-                dst[i] = make_uint4(res[4 * i], res[4 * i + 1], res[4 * i + 2], res[4 * i + 3]);
+                for (int i = 0; i < NW / 4; ++i)
+                    reinterpret_cast<uint4*>(dst)[i] = make_uint4(res[4 * i], res[4 * i + 1], res[4 * i + 2], res[4 * i + 3]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < NW / 2; ++i) reinterpret_cast<uint2*>(dst)[i] = make_uint2(res[2 * i], res[2 * i + 1]);
+            }
         }
     }
 
@@ -344,20 +371,35 @@ __device__ __forceinline__ int tile_of(const GemmArgs& a, int sel) {
 
 // Work of one CTA: a contiguous range of the (query block, base tile) items in query-block-major
 // order.  Consecutive items of a CTA share the query block, which is what lets the query tile stay
-// in shared memory and a thread keep one candidate block open across tiles; CTAs of different
-// query blocks walk the base tiles in step, so a base tile is read from HBM about once.
+// in shared memory and a thread keep one candidate block open across tiles.  With few query blocks
+// and a base larger than L2 the ranges are aligned (see below) so that CTAs of different query
+// blocks walk the same base tiles at the same time and a base tile is read from HBM about once;
+// otherwise the linearised item list is simply cut into equal pieces.
 struct ItemRange {
     int64_t count;       // items of this CTA
     int qb0, sel0;       // first item
     int n_sel;
     __device__ __forceinline__ ItemRange(const GemmArgs& a, int n_qb) {
-        const int64_t total = static_cast<int64_t>(n_qb) * a.n_tiles_sel;
-        const int64_t lo = total * blockIdx.x / gridDim.x;
-        const int64_t hi = total * (blockIdx.x + 1) / gridDim.x;
-        count = hi - lo;
         n_sel = a.n_tiles_sel;
-        qb0 = static_cast<int>(lo / n_sel);
-        sel0 = static_cast<int>(lo % n_sel);
+        const int G = gridDim.x, c = blockIdx.x;
+        if (a.aligned_ranges) {
+            // one query block per CTA; the CTAs of a query block split the tiles evenly, so CTAs of
+            // different query blocks sit on the same stretch of the base at the same time
+            const int qb = c % n_qb, j = c / n_qb;
+            const int nl = G / n_qb + (qb < G % n_qb ? 1 : 0);
+            const int64_t lo = static_cast<int64_t>(n_sel) * j / nl;
+            const int64_t hi = static_cast<int64_t>(n_sel) * (j + 1) / nl;
+            count = hi - lo;
+            qb0 = qb;
+            sel0 = static_cast<int>(lo);
+        } else {
+            const int64_t total = static_cast<int64_t>(n_qb) * n_sel;
+            const int64_t lo = total * c / G;
+            const int64_t hi = total * (c + 1) / G;
+            count = hi - lo;
+            qb0 = static_cast<int>(lo / n_sel);
+            sel0 = static_cast<int>(lo % n_sel);
+        }
     }
 };
 // Walks a range without divisions (the roles that run one thread deep cannot afford them).
@@ -383,7 +425,7 @@ struct ItemCursor {
 // the query tile is small enough (a.a_resident) it is therefore loaded once per query block and
 // only base chunks (32 KB) travel through the stage ring.
 template <int KIND, int MODE, int BURST>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(gemm_threads(KIND), 1)
 dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                     const GemmArgs a) {
     using AccT = typename std::conditional<KIND == kKindI8, int32_t, float>::type;
@@ -420,7 +462,7 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(&bar_acc_full[b], 1);
-            ptx::mbar_init(&bar_acc_empty[b], kEpiWarps);
+            ptx::mbar_init(&bar_acc_empty[b], epi_warps(KIND));
         }
         ptx::mbar_init(&bar_a_full, 1);
         ptx::mbar_init(&bar_a_free, 1);
@@ -548,10 +590,10 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         }
     } else {
         const int quarter = warp & 3;          // TMEM lane quarter this warp may read
-        const int half = (warp - 2) >> 2;      // which 128 columns of the tile this warp drains
+        const int half = (warp - 2) >> 2;      // which kCols columns of the tile this warp drains
         const int row_in_tile = quarter * 32 + lane;
-        const int et = threadIdx.x - 64;       // epilogue thread index, 0..255
-        constexpr int kCols = kTileB / 2;      // columns per epilogue thread
+        const int et = threadIdx.x - 64;       // epilogue thread index
+        constexpr int kCols = kTileB / (epi_warps(KIND) / 4);   // columns per epilogue thread
         RowEpilogue<AccT, MODE, BURST, FOLD, kCols / 32> epi(a);
         const bool l2 = a.metric == kMetricL2 && !FOLD;   // FOLD: no norms to fetch
         const uint32_t* gnorm = static_cast<const uint32_t*>(a.bnorm);
@@ -571,11 +613,11 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             const long long e0 = profiler ? clock64() : 0;
             // The tile's norms travel global -> registers while the MMA is still running.
             uint32_t n0 = 0;
-            if (l2) n0 = __ldg(gnorm + tile_col0 + et);
+            if (l2 && et < kTileB) n0 = __ldg(gnorm + tile_col0 + et);
             epi.begin_tile(q, q < a.nq);
             if (!ptx::mbar_wait_bounded(&bar_acc_full[ab], aph, &abort_flag)) {
                 // leave without stranding a sibling warp at the named barrier below
-                if (!FOLD) asm volatile("bar.arrive 1, 256;" ::: "memory");
+                if (!FOLD) asm volatile("bar.arrive 1, %0;" ::"n"(32 * epi_warps(KIND)) : "memory");
                 ok = false;
                 break;
             }
@@ -583,8 +625,8 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             ptx::tc_fence_after();
             const long long b0 = profiler ? clock64() : 0;
             if (!FOLD) {
-                epi_sh.norm[ab][et] = n0;
-                asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight epilogue warps
+                if (et < kTileB) epi_sh.norm[ab][et] = n0;
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * epi_warps(KIND)) : "memory");   // the epilogue warps
             }
             if (profiler) ebar += clock64() - b0;
             const uint32_t tacc =
@@ -751,7 +793,15 @@ cudaError_t launch_one(const GemmLaunch& L, GemmArgs a, const CUtensorMap* mapA,
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBudget);
     if (e != cudaSuccess) return e;
     const int grid = static_cast<int>(total < L.num_sms ? total : L.num_sms);
-    kern<<<grid, kGemmThreads, smem, stream>>>(*mapA, *mapB, a);
+    // aligned ranges when every query block gets at least one CTA and the split stays balanced
+    a.aligned_ranges = 0;
+    if (n_qb <= grid && a.n_tiles_sel >= grid / n_qb) {
+        const int nl_min = grid / n_qb;
+        const double worst = static_cast<double>((a.n_tiles_sel + nl_min - 1) / nl_min);
+        const double ideal = static_cast<double>(total) / grid;
+        if (worst <= 1.06 * ideal + 1.0) a.aligned_ranges = 1;
+    }
+    kern<<<grid, gemm_threads(KIND), smem, stream>>>(*mapA, *mapB, a);
     return cudaGetLastError();
 }
 

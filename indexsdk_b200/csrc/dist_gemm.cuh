@@ -57,6 +57,7 @@ struct GemmArgs {
     // filled in by launch_dist_gemm (tcgen05 variant): shared-memory plan
     int a_resident;       // 1: the query tile stays in shared memory for a whole query block
     int n_stages;         // ring stages (base chunks, or query + base chunks when not resident)
+    int aligned_ranges;   // 1: CTA = (query block, even share of the tiles); 0: equal cuts of the item list
 };
 
 struct GemmLaunch {

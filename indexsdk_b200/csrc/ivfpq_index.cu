@@ -797,6 +797,7 @@ __device__ __forceinline__ float exact_distance(const ScanArgs& a, int64_t q, in
 // ---------------------------------------------------------------------------------------
 // 3b. exact re-computation of the survivors, ordering by (distance, label), verification
 // ---------------------------------------------------------------------------------------
+constexpr int kRefMaxProbe = 256;
 __global__ void __launch_bounds__(kScanThreads)
 ivfpq_refine_kernel(const ScanArgs a, int P) {
     extern __shared__ __align__(16) uint8_t ref_smem[];
@@ -805,6 +806,20 @@ ivfpq_refine_kernel(const ScanArgs a, int P) {
     __shared__ float s_qn2;
     const int64_t q = blockIdx.x;
     const int n_c = a.S * a.kprime;
+    // The owning list of a survivor is one of the query's probed lists: their bounds go to shared
+    // memory once and the owner is found there, not by a search through the global offsets array.
+    __shared__ uint32_t s_lb[kRefMaxProbe], s_le[kRefMaxProbe];
+    __shared__ int32_t s_ll[kRefMaxProbe];
+    const bool probes_staged = a.by_residual && a.nprobe <= kRefMaxProbe;
+    if (probes_staged) {
+        for (int p = threadIdx.x; p < a.nprobe; p += kScanThreads) {
+            const int64_t list = a.cI[q * a.nprobe + p];
+            s_ll[p] = static_cast<int32_t>(list);
+            s_lb[p] = list >= 0 ? static_cast<uint32_t>(a.offsets[list]) : 0u;
+            s_le[p] = list >= 0 ? static_cast<uint32_t>(a.offsets[list + 1]) : 0u;
+        }
+        __syncthreads();
+    }
     for (int i = threadIdx.x; i < P; i += kScanThreads) {
         float dist = __int_as_float(0x7f800000);
         int64_t label = kNoLabel;
@@ -812,7 +827,10 @@ ivfpq_refine_kernel(const ScanArgs a, int P) {
             const uint32_t pos = a.fp[q * n_c + i];
             if (pos != kNoPos) {
                 int64_t list = 0;
-                if (a.by_residual) {          // owning list of the position
+                if (probes_staged) {
+                    for (int p = 0; p < a.nprobe; ++p)
+                        if (pos >= s_lb[p] && pos < s_le[p]) list = s_ll[p];
+                } else if (a.by_residual) {          // owning list of the position
                     int lo = 0, hi = a.nlist;
                     while (hi - lo > 1) {
                         const int mid = (lo + hi) >> 1;
