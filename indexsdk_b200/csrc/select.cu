@@ -179,6 +179,7 @@ select_topk_kernel(const uint64_t* cand, const uint32_t* counts, uint32_t n_fixe
             const uint64_t v = small[i];
             if (v == kCandInvalid) continue;
             uint32_t rank = 0;
+#pragma unroll 8
             for (uint32_t j = 0; j < n; ++j) rank += small[j] < v ? 1u : 0u;
             if (rank < static_cast<uint32_t>(k)) orow_fast[rank] = v;
         }
@@ -206,11 +207,11 @@ select_topk_kernel(const uint64_t* cand, const uint32_t* counts, uint32_t n_fixe
 // Canonical fp32 distances of the candidates (sequential fmaf over the dimensions, the arithmetic
 // of the CPU oracle).  The chain of one candidate cannot be split over lanes, so a lane owns a
 // candidate -- but the rows are fetched co-operatively: a warp reads the rows of its 32 candidates
-// kRefChunk floats at a time, each row as one contiguous piece spread over consecutive lanes
-// (a few cache lines per load instruction instead of 32), parks them in shared memory and every
-// lane then walks its own row there.  Rows are padded by 4 floats: 8 consecutive lanes reading one
-// float4 each fall into 8 different 16-byte bank groups.
-constexpr int kRefChunk = 64;
+// kRefChunk floats at a time, each row as one contiguous 128-byte piece spread over consecutive
+// lanes (four cache lines per load instruction instead of 32), parks them in shared memory and
+// every lane then walks its own row there.  Rows are padded by 4 floats: 8 consecutive lanes
+// reading one float4 each fall into 8 different 16-byte bank groups.
+constexpr int kRefChunk = 32;     // small, so that many warps fit an SM: the kernel lives on memory-level parallelism
 constexpr int kRefPitch = kRefChunk + 4;
 __global__ void __launch_bounds__(128)
 refine_f32_kernel(uint64_t* cand, const uint32_t* counts, uint32_t n_fixed, uint32_t cap, int d, int metric,
@@ -237,9 +238,9 @@ refine_f32_kernel(uint64_t* cand, const uint32_t* counts, uint32_t n_fixed, uint
             const int w = d - ch0 < kRefChunk ? d - ch0 : kRefChunk;
             const int lpr = w >> 2;                                  // float4 pieces per row
             if (lpr == kRefChunk / 4) {
-#pragma unroll 8
-                for (int it = 0; it < 16; ++it) {                    // two of the 32 rows per load instruction
-                    const int r = it * 2 + (lane >> 4), j = lane & 15;
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {                     // four of the 32 rows per load instruction
+                    const int r = it * 4 + (lane >> 3), j = lane & 7;
                     const uint32_t pr = __shfl_sync(0xffffffffu, pos, r);
                     const float4 v = __ldg(reinterpret_cast<const float4*>(xb + static_cast<int64_t>(pr) * d + ch0) + j);
                     *reinterpret_cast<float4*>(rows + r * kRefPitch + 4 * j) = v;
