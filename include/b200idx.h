@@ -119,6 +119,21 @@ int b200idx_ivfpq_add_codes(b200idx_t* h, int64_t n, const int32_t* list_no, con
                             const int64_t* ids);
 /* setNumProbes / getNumProbes: FR/ascend/AscendIndexIVF.h:93-96 */
 int b200idx_ivfpq_set_nprobe(b200idx_t* h, int nprobe);
+
+/* The two halves of an IVFPQ search, device-resident (the reference runs them back to back inside
+ * IndexIVFPQ::searchImpl: probe selection feature_retrieval/src/ascendfaiss/ascenddaemon/impl/
+ * IndexIVFPQ.cpp:2104-2164, code scan + top-k :2165-2411).  Split so that the ranks of a sharded
+ * index -- every rank holds the full coarse quantizer -- can each select the probes of a slice of
+ * the queries, exchange them, and scan their shard for all queries.
+ *   coarse      : probe_distances_dev / probe_lists_dev [n][nprobe] <- the nprobe nearest centroids
+ *                 (canonical fp32 distances, ascending; list -1 = none)
+ *   preassigned : searches the given probes; same results as b200idx_search_device when they come
+ *                 from coarse on the same queries */
+int b200idx_ivfpq_coarse_device(b200idx_t* h, int64_t n, const float* x_dev, float* probe_distances_dev,
+                                int64_t* probe_lists_dev);
+int b200idx_ivfpq_search_preassigned_device(b200idx_t* h, int64_t n, const float* x_dev, int k,
+                                            const float* probe_distances_dev, const int64_t* probe_lists_dev,
+                                            float* distances_dev, int64_t* labels_dev);
 int b200idx_ivfpq_get_nprobe(const b200idx_t* h);
 /* getListLength / getListCodesAndIds: FR/ascend/AscendIndexIVF.h:105-108 */
 int64_t b200idx_ivfpq_list_length(const b200idx_t* h, int list);

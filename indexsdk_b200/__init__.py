@@ -82,6 +82,8 @@ def load() -> C.CDLL:
         "b200idx_ivfpq_get_codebooks": (i32, [vp, vp]),
         "b200idx_ivfpq_add_codes": (i32, [vp, i64, vp, vp, vp]),
         "b200idx_ivfpq_set_nprobe": (i32, [vp, i32]),
+        "b200idx_ivfpq_coarse_device": (i32, [vp, i64, vp, vp, vp]),
+        "b200idx_ivfpq_search_preassigned_device": (i32, [vp, i64, vp, i32, vp, vp, vp, vp]),
         "b200idx_ivfpq_get_nprobe": (i32, [vp]),
         "b200idx_ivfpq_list_length": (i64, [vp, i32]),
         "b200idx_ivfpq_get_list": (i32, [vp, i32, vp, vp]),
@@ -106,7 +108,8 @@ EXPORTED_SYMBOLS = [
     "b200idx_search_multi", "b200idx_merge_topk_device", "b200idx_reset", "b200idx_remove_ids", "b200idx_ntotal",
     "b200idx_dim", "b200idx_device", "b200idx_get_base", "b200idx_get_ids", "b200idx_ivfpq_set_centroids",
     "b200idx_ivfpq_set_codebooks", "b200idx_ivfpq_get_centroids", "b200idx_ivfpq_get_codebooks",
-    "b200idx_ivfpq_add_codes", "b200idx_ivfpq_set_nprobe", "b200idx_ivfpq_get_nprobe", "b200idx_ivfpq_list_length",
+    "b200idx_ivfpq_add_codes", "b200idx_ivfpq_set_nprobe", "b200idx_ivfpq_coarse_device",
+    "b200idx_ivfpq_search_preassigned_device", "b200idx_ivfpq_get_nprobe", "b200idx_ivfpq_list_length",
     "b200idx_ivfpq_get_list", "b200idx_stats", "b200idx_set_timing", "b200idx_stream", "b200idx_last_error",
     "b200idx_version",
 ]
@@ -311,6 +314,17 @@ class IndexIVFPQ(_Index):
     @nprobe.setter
     def nprobe(self, v: int):
         _check(self._lib.b200idx_ivfpq_set_nprobe(self._h, int(v)), self._h)
+
+    def coarse_device(self, x_ptr: int, n: int, cD_ptr: int, cI_ptr: int):
+        """Probe selection only: [n][nprobe] distances and list ids (device pointers)."""
+        _check(self._lib.b200idx_ivfpq_coarse_device(self._h, n, C.c_void_p(x_ptr), C.c_void_p(cD_ptr),
+                                                     C.c_void_p(cI_ptr)), self._h)
+
+    def search_preassigned_device(self, x_ptr: int, n: int, k: int, cD_ptr: int, cI_ptr: int, D_ptr: int, I_ptr: int):
+        """Code scan + refinement for given probes (device pointers)."""
+        _check(self._lib.b200idx_ivfpq_search_preassigned_device(
+            self._h, n, C.c_void_p(x_ptr), k, C.c_void_p(cD_ptr), C.c_void_p(cI_ptr), C.c_void_p(D_ptr),
+            C.c_void_p(I_ptr)), self._h)
 
     def list_length(self, l: int) -> int:
         return int(self._lib.b200idx_ivfpq_list_length(self._h, l))

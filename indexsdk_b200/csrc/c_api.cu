@@ -405,6 +405,21 @@ int64_t b200idx_ivfpq_list_length(const b200idx_t* h, int list) {
     if (!h || h->kind != 2 || list < 0 || list >= h->ivfpq->nlist()) return -1;
     return h->ivfpq->list_length(list);
 }
+int b200idx_ivfpq_coarse_device(b200idx_t* h, int64_t n, const float* x, float* cD, int64_t* cI) {
+    B200_REQUIRE_IVFPQ(h)
+    return guarded(h, [&] {
+        if (n <= 0 || !x || !cD || !cI) throw std::invalid_argument("n must be > 0, pointers non-NULL");
+        h->ivfpq->coarse_device(n, x, cD, cI);
+    });
+}
+int b200idx_ivfpq_search_preassigned_device(b200idx_t* h, int64_t n, const float* x, int k, const float* cD,
+                                            const int64_t* cI, float* D, int64_t* I) {
+    B200_REQUIRE_IVFPQ(h)
+    return guarded(h, [&] {
+        check_search_args(h, n, x, k, D, I);
+        h->ivfpq->search_preassigned_device(n, x, k, cD, cI, D, I);
+    });
+}
 int b200idx_ivfpq_get_list(const b200idx_t* h, int list, uint8_t* codes, int64_t* ids) {
     B200_REQUIRE_IVFPQ(h)
     return guarded(h, [&] { h->ivfpq->get_list(list, codes, ids); });

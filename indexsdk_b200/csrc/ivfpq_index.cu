@@ -1348,7 +1348,37 @@ void IvfpqIndex::get_list(int list, uint8_t* codes, int64_t* ids) const {
     if (ids) B200_CUDA_CHECK(cudaMemcpy(ids, ids_.as<int64_t>() + b, static_cast<size_t>(len) * 8, cudaMemcpyDeviceToHost));
 }
 
+void IvfpqIndex::coarse_device(int64_t nq, const float* xq, float* cD, int64_t* cI) {
+    if (nq <= 0) return;
+    if (!is_trained()) throw std::invalid_argument("IVFPQ index is not trained (centroids / codebooks missing)");
+    DeviceGuard g(device_);
+    cudaStream_t st = stream();
+    const int nprobe = std::max(1, std::min(nprobe_, nlist_));
+    timer_.begin(kStageCoarse, st);
+    coarse_->search_device(nq, xq, false, nprobe, cD, cI, nprobe);
+    timer_.end(st);
+    B200_CUDA_CHECK(cudaStreamSynchronize(st));
+    timer_.collect(stats_);
+    stats_.kernel_launches += coarse_->stats().kernel_launches;
+    stats_.gemm_launches += coarse_->stats().gemm_launches;
+    coarse_->stats().kernel_launches = 0;
+    coarse_->stats().gemm_launches = 0;
+}
+
 void IvfpqIndex::search_device(int64_t nq, const float* xq, int k, float* D, int64_t* I) {
+    search_stages(nq, xq, k, D, I, nullptr, nullptr);
+}
+
+void IvfpqIndex::search_preassigned_device(int64_t nq, const float* xq, int k, const float* cD, const int64_t* cI,
+                                           float* D, int64_t* I) {
+    if (!cD || !cI) throw std::invalid_argument("search_preassigned needs the probe lists and their distances");
+    search_stages(nq, xq, k, D, I, cD, cI);
+}
+
+// pre_cD / pre_cI: [nq][nprobe] probe distances and list ids computed elsewhere (nullptr: run the
+// coarse stage here).
+void IvfpqIndex::search_stages(int64_t nq, const float* xq, int k, float* D, int64_t* I, const float* pre_cD,
+                               const int64_t* pre_cI) {
     if (nq <= 0) return;
     if (!is_trained()) throw std::invalid_argument("IVFPQ index is not trained (centroids / codebooks missing)");
     if (k > 1024) throw std::invalid_argument("IVFPQ search supports k <= 1024");
@@ -1366,11 +1396,21 @@ void IvfpqIndex::search_device(int64_t nq, const float* xq, int k, float* D, int
     for (int64_t q0 = 0; q0 < nq; q0 += page) {
         const int64_t m = std::min(page, nq - q0);
         const float* xp = xq + q0 * d_;
-        float* cD = static_cast<float*>(w_cD_.ensure(static_cast<size_t>(m) * nprobe * 4));
-        int64_t* cI = static_cast<int64_t*>(w_cI_.ensure(static_cast<size_t>(m) * nprobe * 8));
-        timer_.begin(kStageCoarse, st);
-        coarse_->search_device(m, xp, false, nprobe, cD, cI, nprobe);
-        timer_.end(st);
+        const float* cD;
+        const int64_t* cI;
+        if (pre_cI) {
+            cD = pre_cD + q0 * nprobe;
+            cI = pre_cI + q0 * nprobe;
+        } else {
+            float* wD = static_cast<float*>(w_cD_.ensure(static_cast<size_t>(m) * nprobe * 4));
+            int64_t* wI = static_cast<int64_t*>(w_cI_.ensure(static_cast<size_t>(m) * nprobe * 8));
+            timer_.begin(kStageCoarse, st);
+            coarse_->search_device(m, xp, false, nprobe, wD, wI, nprobe);
+            timer_.end(st);
+            cD = wD;
+            cI = wI;
+        }
+
         ScanArgs a{};
         a.cbT = codebooks_t_.as<float>();
         a.cI = cI;

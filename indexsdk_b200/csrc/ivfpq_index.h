@@ -55,6 +55,11 @@ public:
     void get_list(int list, uint8_t* codes_host, int64_t* ids_host) const;
 
     void search_device(int64_t nq, const float* xq, int k, float* D, int64_t* I);
+    // the two halves of a search: probe selection (k = nprobe on the coarse quantizer), and the
+    // code scan + refinement given the probes (device pointers, [nq][nprobe])
+    void coarse_device(int64_t nq, const float* xq, float* cD, int64_t* cI);
+    void search_preassigned_device(int64_t nq, const float* xq, int k, const float* cD, const int64_t* cI, float* D,
+                                   int64_t* I);
     void search_host(int64_t nq, const float* xq, int k, float* D, int64_t* I);
 
 private:
@@ -68,6 +73,8 @@ private:
     bool rotated_;                        // M % 16 == 0: rotated code storage + conflict-free scan
     int nprobe_ = 1;
     int64_t n_ = 0;
+    void search_stages(int64_t nq, const float* xq, int k, float* D, int64_t* I, const float* pre_cD,
+                       const int64_t* pre_cI);
     bool has_centroids_ = false, has_codebooks_ = false;
     bool no_persist_ = false;
     int num_sms_ = 0;

@@ -49,7 +49,10 @@ class ShardedSearcher:
         n = xq.shape[0]
         b = self._buffers(n, k)
         torch.cuda.current_stream(self.device).synchronize()   # xq produced on torch's stream
-        self.index.search_device(xq.data_ptr(), n, k, b["locD"].data_ptr(), b["locI"].data_ptr())
+        if self.world > 1 and hasattr(self.index, "coarse_device") and n >= 4 * self.world:
+            self._search_ivfpq_split_coarse(xq, n, k, b)
+        else:
+            self.index.search_device(xq.data_ptr(), n, k, b["locD"].data_ptr(), b["locI"].data_ptr())
         if self.world == 1:
             return b["locD"], b["locI"]
         dist.all_gather_into_tensor(b["allD"], b["locD"], group=self.group)
@@ -58,6 +61,35 @@ class ShardedSearcher:
         merge_topk_device(self.world, n, k, self.descending, b["allD"].data_ptr(), b["allI"].data_ptr(),
                           b["outD"].data_ptr(), b["outI"].data_ptr(), stream)
         return b["outD"], b["outI"]
+
+    def _search_ivfpq_split_coarse(self, xq, n, k, b):
+        """IVFPQ shards hold the full coarse quantizer, so probe selection would be repeated on every
+        rank: instead each rank selects the probes of an even slice of the queries, one all-gather
+        (n * nprobe * 12 bytes) makes them known everywhere, and every rank scans its shard for all
+        queries with the given probes.  Results are those of a plain search."""
+        nprobe = min(self.index.nprobe, self.index.nlist)
+        per = (n + self.world - 1) // self.world
+        key = ("probe", n, nprobe)
+        if key not in self._buf:
+            dev = self.device
+            self._buf[key] = dict(
+                myD=torch.empty((per, nprobe), dtype=torch.float32, device=dev),
+                myI=torch.empty((per, nprobe), dtype=torch.int64, device=dev),
+                allD=torch.empty((self.world * per, nprobe), dtype=torch.float32, device=dev),
+                allI=torch.empty((self.world * per, nprobe), dtype=torch.int64, device=dev))
+        p = self._buf[key]
+        lo = min(self.rank * per, n)
+        cnt = max(0, min(per, n - lo))
+        if cnt < per:                       # a short (or empty) last slice: defined padding
+            p["myD"].zero_()
+            p["myI"].fill_(-1)
+        if cnt:
+            self.index.coarse_device(xq[lo:lo + cnt].data_ptr(), cnt, p["myD"].data_ptr(), p["myI"].data_ptr())
+        dist.all_gather_into_tensor(p["allD"], p["myD"], group=self.group)
+        dist.all_gather_into_tensor(p["allI"], p["myI"], group=self.group)
+        torch.cuda.current_stream(self.device).synchronize()   # the index runs on its own stream
+        self.index.search_preassigned_device(xq.data_ptr(), n, k, p["allD"].data_ptr(), p["allI"].data_ptr(),
+                                             b["locD"].data_ptr(), b["locI"].data_ptr())
 
     def search(self, xq_host: torch.Tensor, k: int, out_D: torch.Tensor | None = None,
                out_I: torch.Tensor | None = None):

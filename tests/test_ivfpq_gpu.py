@@ -175,3 +175,34 @@ def test_untrained_index_is_rejected(b200):
     with pytest.raises(b200.B200IdxError) as e:
         ix.add(datasets.gaussian(10, 64, seed=1))
     assert e.value.code == 2001 and "not trained" in e.value.msg
+
+
+@pytest.mark.parametrize("resid", [False, True])
+def test_coarse_plus_preassigned_equals_search(b200, resid):
+    """The two halves of a search run apart -- probes selected for slices of the queries, as the
+    ranks of a sharded index do, then the scan with those probes -- give the plain search's result."""
+    import torch
+    d, nlist, M, n, nq, nprobe, k = 64, 64, 16, 20000, 257, 12, 10
+    xb, _ = datasets.mixture(n, d, 32, seed=14)
+    xq, _ = datasets.mixture(nq, d, 32, seed=15, centers_seed=14)
+    ids = np.arange(n, dtype=np.int64) * 3 + 1
+    cent, cb = datasets.train_ivfpq(xb[:8000], nlist, M, resid, niter=4)
+    ix = _build(b200, xb, ids, cent, cb, resid)
+    ix.nprobe = nprobe
+    D0, I0 = ix.search(xq, k)
+    dev = torch.device("cuda", ix.device)
+    xq_d = torch.from_numpy(xq).to(dev)
+    cD = torch.empty((nq, nprobe), dtype=torch.float32, device=dev)
+    cI = torch.empty((nq, nprobe), dtype=torch.int64, device=dev)
+    torch.cuda.synchronize(dev)
+    for lo, hi in ((0, 100), (100, 101), (101, nq)):            # three "ranks"
+        ix.coarse_device(xq_d[lo:hi].data_ptr(), hi - lo, cD[lo:hi].data_ptr(), cI[lo:hi].data_ptr())
+    D = torch.empty((nq, k), dtype=torch.float32, device=dev)
+    I = torch.empty((nq, k), dtype=torch.int64, device=dev)
+    ix.search_preassigned_device(xq_d.data_ptr(), nq, k, cD.data_ptr(), cI.data_ptr(), D.data_ptr(), I.data_ptr())
+    torch.cuda.synchronize(dev)
+    assert_exact(D.cpu().numpy(), I.cpu().numpy(), D0, I0)
+    # the probes themselves: the oracle's coarse quantizer (same lists in the same order)
+    off, cs, idl = _oracle_lists(xb, ids, cent, cb, resid)[2]
+    _, _, coarse = oracle.ivfpq_search(cent, cb, resid, off, cs, idl, xq, nprobe, k, return_coarse=True)
+    np.testing.assert_array_equal(cI.cpu().numpy(), coarse.astype(np.int64))
