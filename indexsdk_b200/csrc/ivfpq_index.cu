@@ -48,6 +48,7 @@ namespace b200 {
 namespace {
 
 constexpr int kKsub = 256;
+constexpr int kListPad = 32;     // lists are padded to a multiple of this many vectors
 constexpr int kScanThreads = 128;
 constexpr int kScanWarps = kScanThreads / 32;
 constexpr float kInf = 3.402823466e+38f;   // FLT_MAX used as padding distance
@@ -132,10 +133,35 @@ __global__ void hist_kernel(const int32_t* list_no, int64_t n, int64_t* hist) {
     const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i < n) atomicAdd(reinterpret_cast<unsigned long long*>(hist + list_no[i]), 1ull);
 }
-__global__ void add_counts_kernel(const int64_t* old_off, const int64_t* new_hist, int nlist, int64_t* total) {
+// Lists are stored padded to a multiple of kListPad vectors (the scan kernels read whole
+// 32-vector groups without a per-lane bounds check): new length and padded size per list.
+__global__ void add_counts_kernel(const int64_t* old_len, const int64_t* new_hist, int nlist, int64_t* new_len,
+                                  int64_t* padded) {
     const int l = blockIdx.x * blockDim.x + threadIdx.x;
-    if (l < nlist) total[l] = (old_off[l + 1] - old_off[l]) + new_hist[l];
-    if (l == nlist) total[l] = 0;
+    if (l < nlist) {
+        const int64_t t = old_len[l] + new_hist[l];
+        new_len[l] = t;
+        padded[l] = (t + kListPad - 1) / kListPad * kListPad;
+    }
+    if (l == nlist) {
+        new_len[l] = 0;
+        padded[l] = 0;
+    }
+}
+// Padding slots (and kListPad slots behind the last list): zero codes, label -1, NaN in the
+// per-vector term so that a padding slot can never enter a result.
+__global__ void fill_pads_kernel(int nlist, const int64_t* off, const int64_t* len, int M, uint8_t* codes,
+                                 int64_t* ids, float* t2) {
+    const int l = blockIdx.x * (blockDim.x / kListPad) + threadIdx.x / kListPad;
+    const int j = threadIdx.x % kListPad;
+    if (l > nlist) return;
+    const int64_t first = l < nlist ? off[l] + len[l] : off[nlist];
+    const int64_t last = l < nlist ? off[l + 1] : off[nlist] + kListPad;
+    const int64_t p = first + j;
+    if (p >= last) return;
+    for (int b = 0; b < M; ++b) codes[p * M + b] = 0;
+    ids[p] = -1;
+    t2[p] = __int_as_float(0x7fc00000);
 }
 __global__ void iota_i32_kernel(int32_t* p, int64_t n) {
     const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -153,9 +179,10 @@ __device__ __forceinline__ void copy_code(const uint8_t* from, uint8_t* to, int 
     for (int g = 0; g < M; g += 16)
         for (int s = 0; s < 16; ++s) to[dst * M + g + s] = from[src * M + g + ((s + delta) & 15)];
 }
-__global__ void scatter_old_kernel(int64_t n_old, int nlist, const int64_t* old_off, const int64_t* new_off, int M,
-                                   int rotated, const uint8_t* codes, const int64_t* ids, const float* t2,
-                                   uint8_t* ncodes, int64_t* nids, float* nt2) {
+// n_old: old padded size; padding slots of the old layout are skipped.
+__global__ void scatter_old_kernel(int64_t n_old, int nlist, const int64_t* old_off, const int64_t* old_len,
+                                   const int64_t* new_off, int M, int rotated, const uint8_t* codes, const int64_t* ids,
+                                   const float* t2, uint8_t* ncodes, int64_t* nids, float* nt2) {
     const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= n_old) return;
     int lo = 0, hi = nlist;  // largest l with old_off[l] <= i
@@ -164,23 +191,25 @@ __global__ void scatter_old_kernel(int64_t n_old, int nlist, const int64_t* old_
         if (old_off[mid] <= i) lo = mid;
         else hi = mid;
     }
-    const int64_t dst = new_off[lo] + (i - old_off[lo]);
+    const int64_t idx = i - old_off[lo];
+    if (idx >= old_len[lo]) return;
+    const int64_t dst = new_off[lo] + idx;
     copy_code(codes, ncodes, M, rotated != 0, i, static_cast<int>(i & 15), dst);
     nids[dst] = ids[i];
-    if (t2) nt2[dst] = t2[i];
+    nt2[dst] = t2[i];
 }
 __global__ void scatter_new_kernel(int64_t n_new, const int32_t* sorted_list, const int32_t* sorted_src,
-                                   const int64_t* old_off, const int64_t* new_off, const int64_t* new_first, int M,
+                                   const int64_t* old_len, const int64_t* new_off, const int64_t* new_first, int M,
                                    int rotated, const uint8_t* codes, const int64_t* ids, const float* t2,
                                    uint8_t* ncodes, int64_t* nids, float* nt2) {
     const int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (j >= n_new) return;
     const int l = sorted_list[j];
     const int64_t src = sorted_src[j];
-    const int64_t dst = new_off[l] + (old_off[l + 1] - old_off[l]) + (j - new_first[l]);
+    const int64_t dst = new_off[l] + old_len[l] + (j - new_first[l]);
     copy_code(codes, ncodes, M, rotated != 0, src, 0, dst);
     nids[dst] = ids[src];
-    if (t2) nt2[dst] = t2[src];
+    nt2[dst] = t2 ? t2[src] : 0.f;   // raw encoding: no per-vector term
 }
 
 // ---- top-k kept in a warp's registers ----
@@ -240,7 +269,8 @@ struct ScanArgs {
     const int64_t* cI;       // [nq][nprobe] probed list ids (-1 = none)
     const float* cD;         // [nq][nprobe] coarse distances
     int nprobe;
-    const int64_t* offsets;  // [nlist + 1]
+    const int64_t* offsets;  // [nlist + 1] first position of every list (multiples of 32: lists are padded)
+    const int64_t* lens;     // [nlist] vectors in every list
     const uint8_t* codes;
     const int64_t* ids;
     const float* t2;
@@ -386,7 +416,7 @@ struct StaticFeed {
                 const int64_t list = a.cI[q * a.nprobe + p];
                 if (list >= 0) {
                     my_begin = static_cast<uint32_t>(a.offsets[list]);
-                    my_end = static_cast<uint32_t>(a.offsets[list + 1]);
+                    my_end = my_begin + static_cast<uint32_t>(a.lens[list]);
                     if (a.by_residual) my_base = a.cD[q * a.nprobe + p];
                 }
             }
@@ -438,18 +468,19 @@ __device__ __forceinline__ void scan_warp_probes(const ScanArgs& a, Feed& feed, 
         v0 += 32 * U;
         while (v0 >= end) {
             if (!feed.next(begin, end, base)) return false;
-            v0 = begin & ~31u;
+            v0 = begin;                   // a multiple of 32: lists are stored padded
             if (begin == end) v0 = end;   // empty or absent list
         }
         return true;
     };
-    // One chunk in flight: codes, the per-vector term and where it came from.  Lanes outside
-    // the list read a clamped (valid) address and carry NaN, which fails every comparison, so
-    // the lookups and the threshold test run without any per-lane validity branch.
+    // One chunk in flight: codes, the per-vector term and where it came from.  Lists are padded to
+    // whole 32-vector groups whose padding slots carry NaN in the per-vector term, which fails every
+    // comparison, so there is no per-lane bounds check; a group past the end of the list (the
+    // chunk is two groups long) is switched off through the list's term.
     struct Chunk {
         uint4 c[U][MT];
         float t[U];      // per-vector term (loaded; consumed only when the chunk is processed)
-        float bias[U];   // the list's term, or NaN for a lane outside the list
+        float bias[U];   // the list's term, or NaN for a group outside the list
         uint32_t v0;
     };
     auto fetch = [&](Chunk& ch) {
@@ -457,13 +488,11 @@ __device__ __forceinline__ void scan_warp_probes(const ScanArgs& a, Feed& feed, 
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const uint32_t v = v0 + 32 * u + lane;
-            const bool valid = (v - begin) < (end - begin);
-            const uint32_t vc = min(max(v, begin), end - 1);
-            const uint4* cp = codes4 + static_cast<size_t>(vc) * MT;
+            const uint4* cp = codes4 + static_cast<size_t>(v) * MT;
 #pragma unroll
             for (int g = 0; g < MT; ++g) ch.c[u][g] = __ldg(cp + g);
-            ch.t[u] = a.by_residual ? __ldg(a.t2 + vc) : 0.f;
-            ch.bias[u] = valid ? base : __int_as_float(0x7fc00000);
+            ch.t[u] = __ldg(a.t2 + v);
+            ch.bias[u] = (u == 0 || v0 + 32 * u < end) ? base : __int_as_float(0x7fc00000);
         }
     };
     auto process = [&](const Chunk& ch) {
@@ -704,7 +733,7 @@ ivfpq_scan_persist_kernel(const ScanArgs a) {
                 const int64_t list = a.cI[q * a.nprobe + pidx];
                 if (list >= 0) {
                     m_begin[j] = static_cast<uint32_t>(a.offsets[list]);
-                    m_end[j] = static_cast<uint32_t>(a.offsets[list + 1]);
+                    m_end[j] = m_begin[j] + static_cast<uint32_t>(a.lens[list]);
                     if (a.by_residual) m_base[j] = a.cD[q * a.nprobe + pidx];
                 }
             }
@@ -816,7 +845,7 @@ ivfpq_refine_kernel(const ScanArgs a, int P) {
             const int64_t list = a.cI[q * a.nprobe + p];
             s_ll[p] = static_cast<int32_t>(list);
             s_lb[p] = list >= 0 ? static_cast<uint32_t>(a.offsets[list]) : 0u;
-            s_le[p] = list >= 0 ? static_cast<uint32_t>(a.offsets[list + 1]) : 0u;
+            s_le[p] = list >= 0 ? s_lb[p] + static_cast<uint32_t>(a.lens[list]) : 0u;
         }
         __syncthreads();
     }
@@ -929,7 +958,7 @@ ivfpq_exact_scan_kernel(const ScanArgs a) {
     for (int p = 0; p < a.nprobe; ++p) {
         const int64_t list = a.cI[q * a.nprobe + p];
         if (list < 0) continue;
-        const int64_t begin = a.offsets[list], end = a.offsets[list + 1];
+        const int64_t begin = a.offsets[list], end = begin + a.lens[list];
         if (begin == end) continue;
         __syncthreads();   // previous list fully scanned before the table changes
         if (a.by_residual) {
@@ -1090,6 +1119,9 @@ IvfpqIndex::IvfpqIndex(int d, int nlist, int M, int nbits, bool by_residual, int
     offsets_.ensure(static_cast<size_t>(nlist_ + 1) * 8);
     B200_CUDA_CHECK(cudaMemset(offsets_.get(), 0, static_cast<size_t>(nlist_ + 1) * 8));
     offsets_host_.assign(static_cast<size_t>(nlist_ + 1), 0);
+    lens_.ensure(static_cast<size_t>(nlist_ + 1) * 8);
+    B200_CUDA_CHECK(cudaMemset(lens_.get(), 0, static_cast<size_t>(nlist_ + 1) * 8));
+    lens_host_.assign(static_cast<size_t>(nlist_ + 1), 0);
     w_tmp_.ensure(sizeof(unsigned long long));
     B200_CUDA_CHECK(cudaMemset(w_tmp_.get(), 0, sizeof(unsigned long long)));
     const char* e = std::getenv("B200IDX_IVFPQ_EXACT");
@@ -1227,18 +1259,21 @@ void IvfpqIndex::add_codes(int64_t n, const int32_t* list_no, const uint8_t* cod
 void IvfpqIndex::merge_new(int64_t n, const int32_t* ln, const uint8_t* cd, const float* t2, const int64_t* idd) {
     cudaStream_t st = stream();
     const int64_t n_new_total = n_ + n;
-    if (n_new_total > 0x7FFFFFF0ll) throw std::invalid_argument("a single-device IVFPQ index holds at most 2^31 - 16 vectors");
-    DeviceBuffer hist, total, new_off, new_first, keys_out, vals_in, vals_out, cub_tmp;
+    // upper bound of the padded size; the exact value is known after the scan below
+    const int64_t pad_bound = n_new_total + static_cast<int64_t>(kListPad) * (nlist_ + 1);
+    if (pad_bound > 0x7FFFFFF0ll) throw std::invalid_argument("a single-device IVFPQ index holds at most 2^31 - 16 vectors (padding included)");
+    DeviceBuffer hist, new_len, padded, new_off, new_first, keys_out, vals_in, vals_out, cub_tmp;
     DeviceBuffer ncodes, nids, nt2;
     int64_t* h = static_cast<int64_t*>(hist.ensure(static_cast<size_t>(nlist_ + 1) * 8));
     B200_CUDA_CHECK(cudaMemsetAsync(h, 0, static_cast<size_t>(nlist_ + 1) * 8, st));
     hist_kernel<<<blocks_for(n, 256), 256, 0, st>>>(ln, n, h);
-    int64_t* tot = static_cast<int64_t*>(total.ensure(static_cast<size_t>(nlist_ + 1) * 8));
-    add_counts_kernel<<<blocks_for(nlist_ + 1, 256), 256, 0, st>>>(offsets_.as<int64_t>(), h, nlist_, tot);
+    int64_t* nlen = static_cast<int64_t*>(new_len.ensure(static_cast<size_t>(nlist_ + 1) * 8));
+    int64_t* pad = static_cast<int64_t*>(padded.ensure(static_cast<size_t>(nlist_ + 1) * 8));
+    add_counts_kernel<<<blocks_for(nlist_ + 1, 256), 256, 0, st>>>(lens_.as<int64_t>(), h, nlist_, nlen, pad);
     int64_t* noff = static_cast<int64_t*>(new_off.ensure(static_cast<size_t>(nlist_ + 1) * 8));
     int64_t* nfirst = static_cast<int64_t*>(new_first.ensure(static_cast<size_t>(nlist_ + 1) * 8));
     size_t tmp_bytes = 0, tb = 0;
-    cub::DeviceScan::ExclusiveSum(nullptr, tmp_bytes, tot, noff, nlist_ + 1, st);
+    cub::DeviceScan::ExclusiveSum(nullptr, tmp_bytes, pad, noff, nlist_ + 1, st);
     int32_t* kout = static_cast<int32_t*>(keys_out.ensure(static_cast<size_t>(n) * 4));
     int32_t* vin = static_cast<int32_t*>(vals_in.ensure(static_cast<size_t>(n) * 4));
     int32_t* vout = static_cast<int32_t*>(vals_out.ensure(static_cast<size_t>(n) * 4));
@@ -1248,40 +1283,48 @@ void IvfpqIndex::merge_new(int64_t n, const int32_t* ln, const uint8_t* cd, cons
     tmp_bytes = std::max(tmp_bytes, tb);
     void* tmp = cub_tmp.ensure(tmp_bytes + 16);
     size_t tsz = tmp_bytes;
-    B200_CUDA_CHECK(cub::DeviceScan::ExclusiveSum(tmp, tsz, tot, noff, nlist_ + 1, st));
+    B200_CUDA_CHECK(cub::DeviceScan::ExclusiveSum(tmp, tsz, pad, noff, nlist_ + 1, st));
     tsz = tmp_bytes;
     B200_CUDA_CHECK(cub::DeviceScan::ExclusiveSum(tmp, tsz, h, nfirst, nlist_ + 1, st));
     iota_i32_kernel<<<blocks_for(n, 256), 256, 0, st>>>(vin, n);
     tsz = tmp_bytes;
     B200_CUDA_CHECK(cub::DeviceRadixSort::SortPairs(tmp, tsz, ln, kout, vin, vout, static_cast<int>(n), 0, end_bit, st));
-
-    uint8_t* nc = static_cast<uint8_t*>(ncodes.ensure(static_cast<size_t>(n_new_total) * M_ + 64));
-    int64_t* ni = static_cast<int64_t*>(nids.ensure(static_cast<size_t>(n_new_total) * 8));
-    float* nt = by_residual_ ? static_cast<float*>(nt2.ensure(static_cast<size_t>(n_new_total) * 4)) : nullptr;
-    if (n_ > 0)
-        scatter_old_kernel<<<blocks_for(n_, 256), 256, 0, st>>>(n_, nlist_, offsets_.as<int64_t>(), noff, M_,
-                                                                rotated_ ? 1 : 0, codes_.as<uint8_t>(),
-                                                                ids_.as<int64_t>(),
-                                                                by_residual_ ? t2_.as<float>() : nullptr, nc, ni, nt);
-    scatter_new_kernel<<<blocks_for(n, 256), 256, 0, st>>>(n, kout, vout, offsets_.as<int64_t>(), noff, nfirst, M_,
+    uint8_t* nc = static_cast<uint8_t*>(ncodes.ensure(static_cast<size_t>(pad_bound) * M_ + 64));
+    int64_t* ni = static_cast<int64_t*>(nids.ensure(static_cast<size_t>(pad_bound) * 8));
+    float* nt = static_cast<float*>(nt2.ensure(static_cast<size_t>(pad_bound) * 4));
+    if (n_pad_ > 0)
+        scatter_old_kernel<<<blocks_for(n_pad_, 256), 256, 0, st>>>(n_pad_, nlist_, offsets_.as<int64_t>(),
+                                                                    lens_.as<int64_t>(), noff, M_, rotated_ ? 1 : 0,
+                                                                    codes_.as<uint8_t>(), ids_.as<int64_t>(),
+                                                                    t2_.as<float>(), nc, ni, nt);
+    scatter_new_kernel<<<blocks_for(n, 256), 256, 0, st>>>(n, kout, vout, lens_.as<int64_t>(), noff, nfirst, M_,
                                                            rotated_ ? 1 : 0, cd, idd, t2, nc, ni, nt);
+    fill_pads_kernel<<<blocks_for(static_cast<int64_t>(nlist_ + 1) * kListPad, 256), 256, 0, st>>>(nlist_, noff, nlen, M_,
+                                                                                               nc, ni, nt);
     B200_CUDA_CHECK(cudaGetLastError());
     B200_CUDA_CHECK(cudaMemcpyAsync(offsets_host_.data(), noff, static_cast<size_t>(nlist_ + 1) * 8,
                                     cudaMemcpyDeviceToHost, st));
+    B200_CUDA_CHECK(cudaMemcpyAsync(lens_host_.data(), nlen, static_cast<size_t>(nlist_ + 1) * 8,
+                                    cudaMemcpyDeviceToHost, st));
     B200_CUDA_CHECK(cudaStreamSynchronize(st));
     offsets_.swap(new_off);
+    lens_.swap(new_len);
     codes_.swap(ncodes);
     ids_.swap(nids);
-    if (by_residual_) t2_.swap(nt2);
+    t2_.swap(nt2);
     n_ = n_new_total;
+    n_pad_ = offsets_host_[static_cast<size_t>(nlist_)];
 }
 
 void IvfpqIndex::reset() {
     DeviceGuard g(device_);
     cudaStreamSynchronize(stream());
     n_ = 0;
+    n_pad_ = 0;
     cudaMemset(offsets_.get(), 0, static_cast<size_t>(nlist_ + 1) * 8);
+    cudaMemset(lens_.get(), 0, static_cast<size_t>(nlist_ + 1) * 8);
     offsets_host_.assign(static_cast<size_t>(nlist_ + 1), 0);
+    lens_host_.assign(static_cast<size_t>(nlist_ + 1), 0);
 }
 
 // codes: n stored codes starting at CSR position first_pos -> canonical byte order, in place.
@@ -1301,11 +1344,11 @@ void IvfpqIndex::unrotate_host(uint8_t* codes, int64_t first_pos, int64_t n) con
 int64_t IvfpqIndex::remove_ids(int64_t n, const int64_t* ids) {
     if (n <= 0 || n_ == 0) return 0;
     DeviceGuard g(device_);
-    std::vector<int64_t> hid(static_cast<size_t>(n_));
-    std::vector<uint8_t> hcodes(static_cast<size_t>(n_) * M_);
+    std::vector<int64_t> hid(static_cast<size_t>(n_pad_));
+    std::vector<uint8_t> hcodes(static_cast<size_t>(n_pad_) * M_);
     B200_CUDA_CHECK(cudaMemcpy(hid.data(), ids_.get(), hid.size() * 8, cudaMemcpyDeviceToHost));
     B200_CUDA_CHECK(cudaMemcpy(hcodes.data(), codes_.get(), hcodes.size(), cudaMemcpyDeviceToHost));
-    unrotate_host(hcodes.data(), 0, n_);
+    unrotate_host(hcodes.data(), 0, n_pad_);
     std::unordered_set<int64_t> rm(ids, ids + n);
     std::vector<int32_t> ln;
     std::vector<int64_t> kid;
@@ -1315,7 +1358,7 @@ int64_t IvfpqIndex::remove_ids(int64_t n, const int64_t* ids) {
     kc.reserve(hcodes.size());
     int64_t removed = 0;
     for (int l = 0; l < nlist_; ++l)
-        for (int64_t v = offsets_host_[l]; v < offsets_host_[l + 1]; ++v) {
+        for (int64_t v = offsets_host_[l]; v < offsets_host_[l] + lens_host_[l]; ++v) {
             if (rm.count(hid[static_cast<size_t>(v)])) {
                 ++removed;
                 continue;
@@ -1332,7 +1375,7 @@ int64_t IvfpqIndex::remove_ids(int64_t n, const int64_t* ids) {
 
 int64_t IvfpqIndex::list_length(int list) const {
     if (list < 0 || list >= nlist_) throw std::invalid_argument("list id out of range");
-    return offsets_host_[static_cast<size_t>(list) + 1] - offsets_host_[static_cast<size_t>(list)];
+    return lens_host_[static_cast<size_t>(list)];
 }
 
 void IvfpqIndex::get_list(int list, uint8_t* codes, int64_t* ids) const {
@@ -1417,6 +1460,7 @@ void IvfpqIndex::search_stages(int64_t nq, const float* xq, int k, float* D, int
         a.cD = cD;
         a.nprobe = nprobe;
         a.offsets = offsets_.as<int64_t>();
+        a.lens = lens_.as<int64_t>();
         a.codes = codes_.as<uint8_t>();
         a.ids = ids_.as<int64_t>();
         a.t2 = t2_.as<float>();

@@ -72,7 +72,8 @@ private:
     bool by_residual_;
     bool rotated_;                        // M % 16 == 0: rotated code storage + conflict-free scan
     int nprobe_ = 1;
-    int64_t n_ = 0;
+    int64_t n_ = 0;                       // vectors stored
+    int64_t n_pad_ = 0;                   // storage slots in use: every list padded to a multiple of 32
     void search_stages(int64_t nq, const float* xq, int k, float* D, int64_t* I, const float* pre_cD,
                        const int64_t* pre_cI);
     bool has_centroids_ = false, has_codebooks_ = false;
@@ -85,8 +86,9 @@ private:
     DeviceBuffer codebooks_;              // [M][256][dsub] float
     DeviceBuffer codebooks_t_;            // the same regrouped [M / 16][256][16][dsub] (M % 16 == 0)
     DeviceBuffer cbnorm_;                 // [M][256] float: canonical squared norm of each codeword
-    DeviceBuffer offsets_;                // int64 [nlist + 1]
-    std::vector<int64_t> offsets_host_;
+    DeviceBuffer offsets_;                // int64 [nlist + 1] first slot of every list (multiples of 32)
+    DeviceBuffer lens_;                   // int64 [nlist + 1] vectors per list
+    std::vector<int64_t> offsets_host_, lens_host_;
     DeviceBuffer codes_, ids_, t2_;
     // scratch
     DeviceBuffer w_work_, w_cD_, w_cI_, w_fd_, w_fp_, w_fth_, w_flag_, w_qlist_, w_q_, w_D_, w_I_, w_assign_D_,
