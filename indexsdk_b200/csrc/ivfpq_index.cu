@@ -789,36 +789,53 @@ ivfpq_scan_persist_kernel(const ScanArgs a) {
     if (a.scanned && visited) atomicAdd(a.scanned, visited);
 }
 
-// Canonical distance of the vector at `pos` (probed through list `list`).
+// Canonical distance of the vector at `pos` (probed through list `list`): sum over m, in
+// ascending m, of |(q - c_list)_m - cb[m][code_m]|^2 accumulated with sequential fmaf over the
+// sub-vector (c_list = 0 for raw encoding).  Rows are read as float4 where the sub-vector length
+// allows: the survivors of a query live in unrelated lists, so every lane streams its own
+// centroid row and codewords, and wide loads keep the number of cache transactions down.
 __device__ __forceinline__ float exact_distance(const ScanArgs& a, int64_t q, int64_t pos, int64_t list) {
     const uint8_t* code = a.codes + pos * a.M;
+    const float* qv = a.xq + q * a.d;
+    const float* cen = a.centroids + list * a.d;
+    const bool resid = a.by_residual != 0;
     float acc = 0.f;
-    if (!a.by_residual) {
-        const float* qv = a.xq + q * a.d;
+    if ((a.dsub & 3) == 0) {
+        const int d4 = a.dsub >> 2;
+        const float4* q4 = reinterpret_cast<const float4*>(qv);
+        const float4* c4 = reinterpret_cast<const float4*>(cen);
         for (int m = 0; m < a.M; ++m) {
-            const float* cw = a.codebooks +
-                              (static_cast<int64_t>(m) * kKsub + code[code_byte(a.rotated != 0, m, pos)]) * a.dsub;
+            const float4* w4 = reinterpret_cast<const float4*>(
+                a.codebooks + (static_cast<int64_t>(m) * kKsub + code[code_byte(a.rotated != 0, m, pos)]) * a.dsub);
             float e = 0.f;
-            for (int t = 0; t < a.dsub; ++t) {
-                const float df = qv[m * a.dsub + t] - cw[t];
-                e = fmaf(df, df, e);
+            for (int t = 0; t < d4; ++t) {
+                float4 r = __ldg(q4 + m * d4 + t);
+                if (resid) {
+                    const float4 c = __ldg(c4 + m * d4 + t);
+                    r.x -= c.x; r.y -= c.y; r.z -= c.z; r.w -= c.w;
+                }
+                const float4 w = __ldg(w4 + t);
+                float df;
+                df = r.x - w.x; e = fmaf(df, df, e);
+                df = r.y - w.y; e = fmaf(df, df, e);
+                df = r.z - w.z; e = fmaf(df, df, e);
+                df = r.w - w.w; e = fmaf(df, df, e);
             }
             acc = acc + e;
         }
-    } else {
-        const float* qv = a.xq + q * a.d;
-        const float* cen = a.centroids + list * a.d;
-        for (int m = 0; m < a.M; ++m) {
-            const float* cw = a.codebooks +
-                              (static_cast<int64_t>(m) * kKsub + code[code_byte(a.rotated != 0, m, pos)]) * a.dsub;
-            float e = 0.f;
-            for (int t = 0; t < a.dsub; ++t) {
-                const float r = qv[m * a.dsub + t] - cen[m * a.dsub + t];
-                const float df = r - cw[t];
-                e = fmaf(df, df, e);
-            }
-            acc = acc + e;
+        return acc;
+    }
+    for (int m = 0; m < a.M; ++m) {
+        const float* cw = a.codebooks +
+                          (static_cast<int64_t>(m) * kKsub + code[code_byte(a.rotated != 0, m, pos)]) * a.dsub;
+        float e = 0.f;
+        for (int t = 0; t < a.dsub; ++t) {
+            float r = qv[m * a.dsub + t];
+            if (resid) r -= cen[m * a.dsub + t];
+            const float df = r - cw[t];
+            e = fmaf(df, df, e);
         }
+        acc = acc + e;
     }
     return acc;
 }
@@ -907,6 +924,82 @@ ivfpq_refine_kernel(const ScanArgs a, int P) {
             const bool have_k = sl[kk - 1] != kNoLabel;
             // fewer than k survivors although something was dropped, or the k-th is too close
             if (!have_k || !(sd[kk - 1] < a_min - eps)) bad = 1;
+        }
+        a.flag[q] = bad;
+    }
+}
+
+// The same for 32 survivors per query (one split, k' = 32): one WARP per query, a lane per
+// survivor, the sort done with shuffles -- no block-wide barriers and four queries per CTA, which
+// is what the latency chain survivor -> code -> codewords needs to be hidden by other warps.
+constexpr int kRefWarpsPerBlock = 4;
+__global__ void __launch_bounds__(kRefWarpsPerBlock * 32)
+ivfpq_refine_warp_kernel(const ScanArgs a) {
+    __shared__ uint32_t s_lb[kRefWarpsPerBlock][kRefMaxProbe], s_le[kRefWarpsPerBlock][kRefMaxProbe];
+    __shared__ int32_t s_ll[kRefWarpsPerBlock][kRefMaxProbe];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t q = static_cast<int64_t>(blockIdx.x) * kRefWarpsPerBlock + warp;
+    if (q >= a.nq) return;
+    const uint32_t pos = a.fp[q * 32 + lane];
+    if (a.by_residual) {
+        for (int p = lane; p < a.nprobe; p += 32) {
+            const int64_t list = a.cI[q * a.nprobe + p];
+            s_ll[warp][p] = static_cast<int32_t>(list);
+            const uint32_t b = list >= 0 ? static_cast<uint32_t>(a.offsets[list]) : 0u;
+            s_lb[warp][p] = b;
+            s_le[warp][p] = list >= 0 ? b + static_cast<uint32_t>(a.lens[list]) : 0u;
+        }
+        __syncwarp();
+    }
+    float dist = __int_as_float(0x7f800000);
+    int64_t label = kNoLabel;
+    if (pos != kNoPos) {
+        int64_t list = 0;
+        if (a.by_residual)
+            for (int p = 0; p < a.nprobe; ++p)
+                if (pos >= s_lb[warp][p] && pos < s_le[warp][p]) list = s_ll[warp][p];
+        dist = exact_distance(a, q, pos, list);
+        label = a.ids[pos];
+    }
+    float qn2 = 0.f;   // |q|^2 for the residual error bound
+    if (a.by_residual)
+        for (int t = lane; t < a.d; t += 32) qn2 = fmaf(a.xq[q * a.d + t], a.xq[q * a.d + t], qn2);
+    for (int o = 16; o > 0; o >>= 1) qn2 += __shfl_xor_sync(0xffffffffu, qn2, o);
+    // bitonic sort of the 32 (distance, label) pairs across the lanes, ascending
+    for (int size = 2; size <= 32; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            const float od = __shfl_xor_sync(0xffffffffu, dist, stride);
+            const int64_t ol = __shfl_xor_sync(0xffffffffu, label, stride);
+            const bool lower = (lane & stride) == 0;              // this lane keeps the smaller of the two ...
+            const bool up = (lane & size) == 0;                   // ... in an ascending run
+            const bool other_less = pair_less<int64_t>(od, ol, dist, label);
+            const bool take = (lower == up) ? other_less : !other_less && !(od == dist && ol == label);
+            if (take) {
+                dist = od;
+                label = ol;
+            }
+        }
+    }
+    if (lane < a.k) {
+        const bool real = label != kNoLabel;
+        a.outD[q * a.k + lane] = real ? dist : kInf;
+        a.outI[q * a.k + lane] = real ? label : -1;
+    }
+    // verification (see ivfpq_refine_kernel): the k-th exact distance against the filter's threshold
+    const int kk = a.k <= 32 ? a.k : 32;
+    const float dk = __shfl_sync(0xffffffffu, dist, kk - 1);
+    const int64_t lk = __shfl_sync(0xffffffffu, label, kk - 1);
+    if (lane == 0) {
+        const float a_min = a.fth[q];
+        uint8_t bad = 0;
+        if (a_min != __int_as_float(0x7f800000)) {
+            float eps = a.err_rel * fabsf(a_min);
+            if (a.by_residual) {
+                const float coarse_max = a.cD[q * a.nprobe + a.nprobe - 1];
+                const float bound = fabsf(coarse_max) + a.t2_bound + 2.f * sqrtf(qn2) * a.cb_bound + fabsf(a_min);
+                eps = a.err_rel * bound;
+            }
+            if (lk == kNoLabel || !(dk < a_min - eps)) bad = 1;
         }
         a.flag[q] = bad;
     }
@@ -1521,8 +1614,12 @@ void IvfpqIndex::search_stages(int64_t nq, const float* xq, int k, float* D, int
         timer_.begin(kStageMerge, st);
         const int P = pow2_ceil_int(std::max(S * kprime, 32));
         const size_t rsmem = static_cast<size_t>(P) * 12;
-        B200_CUDA_CHECK(set_smem(ivfpq_refine_kernel, rsmem));
-        ivfpq_refine_kernel<<<static_cast<unsigned>(m), kScanThreads, rsmem, st>>>(a, P);
+        if (S * kprime == 32 && k <= 32 && nprobe <= kRefMaxProbe) {
+            ivfpq_refine_warp_kernel<<<blocks_for(m, kRefWarpsPerBlock), kRefWarpsPerBlock * 32, 0, st>>>(a);
+        } else {
+            B200_CUDA_CHECK(set_smem(ivfpq_refine_kernel, rsmem));
+            ivfpq_refine_kernel<<<static_cast<unsigned>(m), kScanThreads, rsmem, st>>>(a, P);
+        }
         B200_CUDA_CHECK(cudaGetLastError());
         timer_.end(st);
         stats_.kernel_launches += 3;
