@@ -10,7 +10,7 @@ namespace b200 {
 namespace {
 
 constexpr int kSelThreads = 256;
-constexpr int kSmallSet = 512;   // candidate sets up to this size are ranked by counting
+constexpr int kSmallSet = 512;   // candidate sets up to this size are sorted in shared memory
 
 // Inclusive scan of a 256-bin histogram held in shared memory; returns through `bucket`/`below`
 // the bin that contains rank r (1-based) and the number of elements in lower bins.
@@ -138,6 +138,54 @@ prune_candidates_kernel(uint64_t* cand, uint32_t* counts, uint32_t cap, int k, c
     }
 }
 
+// The same threshold for short rows (n <= 32 * NPL), one WARP per query: the minima sit in
+// registers, NPL per lane, and the k-th smallest is found bit by bit -- per bit every lane counts
+// its values that agree with the bits fixed so far and have a 0 there, one warp reduction adds the
+// counts.  About a third of the instructions of the block-wide byte-radix version at n = 512.
+template <int NPL>
+__global__ void __launch_bounds__(128)
+kth_threshold_warp_kernel(const uint32_t* mins, int stride, int n, int nq, int k, const float* eps, uint32_t tau_all,
+                          uint32_t* tau) {
+    const int lane = threadIdx.x & 31;
+    const int q = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (q >= nq) return;
+    if (n < k) {
+        if (lane == 0) tau[q] = tau_all;
+        return;
+    }
+    uint32_t v[NPL];
+    const uint32_t* row = mins + static_cast<int64_t>(q) * stride;
+#pragma unroll
+    for (int j = 0; j < NPL; ++j) {
+        const int i = j * 32 + lane;
+        v[j] = i < n ? row[i] : 0xFFFFFFFFu;
+    }
+    uint32_t prefix = 0, mask = 0, r = static_cast<uint32_t>(k);
+    for (int bit = 31; bit >= 0; --bit) {
+        const uint32_t b = 1u << bit;
+        uint32_t c = 0;
+#pragma unroll
+        for (int j = 0; j < NPL; ++j) c += ((v[j] & (mask | b)) == prefix) ? 1u : 0u;   // agrees so far, bit is 0
+        c = __reduce_add_sync(0xffffffffu, c);
+        if (r > c) {   // the k-th smallest has a 1 at this bit
+            prefix |= b;
+            r -= c;
+        }
+        mask |= b;
+    }
+    if (lane == 0) {
+        uint32_t kth = prefix;
+        if (eps) {
+            float f = ord_to_float(kth);
+            f = f + 2.f * eps[q];
+            f = f + fabsf(f) * 9.5367431640625e-07f;  // one part in 2^20 against the rounding of the adds
+            kth = (f != f) ? tau_all : float_to_ord(f);
+            if (kth > tau_all) kth = tau_all;
+        }
+        tau[q] = kth;
+    }
+}
+
 __device__ __forceinline__ void bitonic_sort_u64(uint64_t* s, int P) {
     for (int size = 2; size <= P; size <<= 1) {
         for (int stride = size >> 1; stride > 0; stride >>= 1) {
@@ -168,19 +216,25 @@ select_topk_kernel(const uint64_t* cand, const uint32_t* counts, uint32_t n_fixe
     if (n > cap) n = cap;
     uint64_t* orow_fast = out + static_cast<int64_t>(q) * k;
     if (n <= static_cast<uint32_t>(kSmallSet)) {
-        // Small candidate set (the common case after a tight threshold): stage it in shared
-        // memory and place every element by its rank, counted against all others.  Candidates
-        // are distinct (positions are unique), so ranks are a permutation.
+        // Small candidate set (the common case after a tight threshold): the real entries (unused
+        // reserved slots are dropped) are staged in shared memory and every one is placed by its
+        // rank, counted against all others.  Candidates are distinct (positions are unique), so
+        // the ranks are a permutation.
         __shared__ uint64_t small[kSmallSet];
-        for (uint32_t i = threadIdx.x; i < n; i += kSelThreads) small[i] = row[i];
+        if (threadIdx.x == 0) sh_fill = 0;
         for (int i = threadIdx.x; i < k; i += kSelThreads) orow_fast[i] = kCandInvalid;
         __syncthreads();
         for (uint32_t i = threadIdx.x; i < n; i += kSelThreads) {
+            const uint64_t v = row[i];
+            if (v != kCandInvalid) small[atomicAdd(&sh_fill, 1u)] = v;
+        }
+        __syncthreads();
+        const uint32_t m = sh_fill;
+        for (uint32_t i = threadIdx.x; i < m; i += kSelThreads) {
             const uint64_t v = small[i];
-            if (v == kCandInvalid) continue;
             uint32_t rank = 0;
 #pragma unroll 8
-            for (uint32_t j = 0; j < n; ++j) rank += small[j] < v ? 1u : 0u;
+            for (uint32_t j = 0; j < m; ++j) rank += small[j] < v ? 1u : 0u;
             if (rank < static_cast<uint32_t>(k)) orow_fast[rank] = v;
         }
         return;
@@ -233,6 +287,8 @@ refine_f32_kernel(uint64_t* cand, const uint32_t* counts, uint32_t n_fixed, uint
         const uint64_t c = i < n ? row[i] : kCandInvalid;
         const bool live = c != kCandInvalid;
         const uint32_t pos = live ? static_cast<uint32_t>(c) : 0u;
+        const uint32_t live_mask = __ballot_sync(0xffffffffu, live);
+        if (live_mask == 0) continue;
         float acc = 0.f;
         for (int ch0 = 0; ch0 < d; ch0 += kRefChunk) {
             const int w = d - ch0 < kRefChunk ? d - ch0 : kRefChunk;
@@ -242,8 +298,10 @@ refine_f32_kernel(uint64_t* cand, const uint32_t* counts, uint32_t n_fixed, uint
                 for (int it = 0; it < 8; ++it) {                     // four of the 32 rows per load instruction
                     const int r = it * 4 + (lane >> 3), j = lane & 7;
                     const uint32_t pr = __shfl_sync(0xffffffffu, pos, r);
-                    const float4 v = __ldg(reinterpret_cast<const float4*>(xb + static_cast<int64_t>(pr) * d + ch0) + j);
-                    *reinterpret_cast<float4*>(rows + r * kRefPitch + 4 * j) = v;
+                    if ((live_mask >> r) & 1u) {   // rows of unused slots are neither fetched nor read
+                        const float4 v = __ldg(reinterpret_cast<const float4*>(xb + static_cast<int64_t>(pr) * d + ch0) + j);
+                        *reinterpret_cast<float4*>(rows + r * kRefPitch + 4 * j) = v;
+                    }
                 }
             } else {
                 for (int idx = lane; idx < 32 * lpr; idx += 32) {
@@ -256,7 +314,9 @@ refine_f32_kernel(uint64_t* cand, const uint32_t* counts, uint32_t n_fixed, uint
             __syncwarp();
             const float4* mine = reinterpret_cast<const float4*>(rows + lane * kRefPitch);
             const float4* qv = reinterpret_cast<const float4*>(qs + ch0);
-            if (metric == kMetricL2) {
+            if (!live) {
+                // nothing to accumulate for an unused slot
+            } else if (metric == kMetricL2) {
 #pragma unroll 4
                 for (int j = 0; j < lpr; ++j) {
                     const float4 a = qv[j], b = mine[j];
@@ -557,7 +617,12 @@ inline int next_pow2(int v) {
 cudaError_t launch_kth_threshold(const uint32_t* mins, int stride, int n, int nq, int k, const float* eps,
                                  uint32_t tau_all, uint32_t* tau, cudaStream_t stream) {
     if (nq <= 0) return cudaSuccess;
-    kth_threshold_kernel<<<nq, kSelThreads, 0, stream>>>(mins, stride, n, k, eps, tau_all, tau);
+    if (n <= 512)
+        kth_threshold_warp_kernel<16><<<(nq + 3) / 4, 128, 0, stream>>>(mins, stride, n, nq, k, eps, tau_all, tau);
+    else if (n <= 1024)
+        kth_threshold_warp_kernel<32><<<(nq + 3) / 4, 128, 0, stream>>>(mins, stride, n, nq, k, eps, tau_all, tau);
+    else
+        kth_threshold_kernel<<<nq, kSelThreads, 0, stream>>>(mins, stride, n, k, eps, tau_all, tau);
     return cudaGetLastError();
 }
 
