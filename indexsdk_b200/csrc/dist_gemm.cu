@@ -116,7 +116,7 @@ struct RowEpilogue {
     uint32_t res[NCH * (32 / BURST)];   // burst-min results of this thread's part of the tile
 
     __device__ __forceinline__ explicit RowEpilogue(const GemmArgs& a_)
-        : a(a_), q(0), row_ok(false), l2(a_.metric == kMetricL2), tau(AccT(0)), tau_up(AccT(0)), tq(0.f),
+        : a(a_), q(-1), row_ok(false), l2(a_.metric == kMetricL2), tau(AccT(0)), tau_up(AccT(0)), tq(0.f),
           blk_q(-1), blk_next(0), blk_left(0), pre_base(0), pre_ok(false) {}
 
     // Fills what is left of the open block with the "invalid" marker.
@@ -135,11 +135,20 @@ struct RowEpilogue {
     }
 
     __device__ __forceinline__ void begin_tile(int q_, bool ok) {
+        const bool new_row = q_ != q || ok != row_ok;
         if (MODE == kModeAppend && !a.direct && (q_ != blk_q || !ok)) close_block();
         q = q_;
         row_ok = ok;
-        if (MODE == kModeAppend && ok) {
+        if (MODE == kModeAppend && ok && new_row) {
+            // once per run of tiles of the same row: the threshold, and (threshold mode) the first
+            // candidate block -- reserved now, while the accumulator is still being computed, so
+            // that the first candidate of the run does not wait for the atomic
             const uint32_t to = __ldg(a.tau + q);
+            if (!a.direct && blk_q != q) {
+                blk_next = atomicAdd(a.counts + q, kCandBlock);
+                blk_left = kCandBlock;
+                blk_q = q;
+            }
             if (FOLD && !a.direct) {
                 tq = ord_to_float(to);
             } else {

@@ -239,10 +239,11 @@ FlatIndex::Plan FlatIndex::make_plan(int k, int64_t nq) const {
         const double inv_f = static_cast<double>(n_tiles) / p.s_tiles;
         uint64_t want = static_cast<uint64_t>(4.0 * k * inv_f);
         // The append epilogue reserves slots in blocks of 8 per (thread, run of tiles of one query
-        // block); a row is shared by two threads in each of the CTAs that walk its query block, and
+        // block); a row is shared by up to four threads in each of the CTAs that walk its query block, and
         // every one of them may leave a block partly unused.
         const int64_t n_qb = (std::max<int64_t>(nq, 1) + kTileQ - 1) / kTileQ;
-        const uint64_t owners = 2 * static_cast<uint64_t>((num_sms_ + n_qb - 1) / n_qb + 1);
+        // (four threads per row in the 16-warp epilogue of the bf16 kind)
+        const uint64_t owners = 4 * static_cast<uint64_t>((num_sms_ + n_qb - 1) / n_qb + 1);
         want += owners * 16;   // an open block and one reserved ahead
         p.cap = pow2_ceil(std::max<uint64_t>(p.s_tiles == n_tiles ? 512 : 2048, want));
         if (p.cap >= static_cast<uint64_t>(n_pad)) p.sampled = false;

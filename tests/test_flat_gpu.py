@@ -48,7 +48,7 @@ def test_fp32_duplicates_ties_and_overflow_fallback(b200):
     """Heavy ties: many copies of the same vectors overflow the candidate buffers; the
     no-threshold re-run must still return the lowest positions first."""
     base = datasets.gaussian(16, 32, seed=5)
-    xb = np.tile(base, (8192, 1))          # 131072 rows, each distinct vector 8192 times
+    xb = np.tile(base, (32768, 1))         # 524288 rows, each distinct vector 32768 times
     xq = base[:3] + 0.0
     ix = b200.IndexFlat(32, L2)
     ix.add(xb)
