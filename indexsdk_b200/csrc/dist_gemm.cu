@@ -37,7 +37,11 @@ constexpr int kResidentMaxChunks = 4;                            // query tile k
 // of the columns each for the folded bf16 kind, whose short ALU-only epilogue is latency-bound
 // and scales with the number of warps.
 __host__ __device__ constexpr int epi_warps(int kind) { return kind == kKindBF16 ? 16 : 8; }
-__host__ __device__ constexpr int gemm_threads(int kind) { return 64 + 32 * epi_warps(kind); }   // + producer and MMA warps
+// + the producer warp, the MMA warp and, behind the epilogue warps, a second MMA warp and a second
+// producer warp (even and odd items have their own issuing threads and their own stage sub-ring)
+__host__ __device__ constexpr int gemm_threads(int kind) { return 64 + 32 * epi_warps(kind) + 64; }
+__host__ __device__ constexpr int mma2_warp(int kind) { return 2 + epi_warps(kind); }
+__host__ __device__ constexpr int prod2_warp(int kind) { return 3 + epi_warps(kind); }
 constexpr uint32_t kTmemCols = 512;
 
 template <typename AccT>
@@ -460,21 +464,22 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int nkc = (a.d + kChunkElems - 1) / kChunkElems;
     const bool resident = a.a_resident != 0;
-    const int nst = a.n_stages;
+    const int nst = a.n_stages / 2;          // stages per sub-ring (even / odd items)
     const uint32_t stage_bytes = resident ? kStageBBytes : kStageBytes;
     uint8_t* ring = smem + (resident ? nkc * kStageABytes : 0);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < nst; ++s) {
-            ptx::mbar_init(&bar_full[s], 1);
-            ptx::mbar_init(&bar_empty[s], 1);
-        }
+        for (int r = 0; r < 2; ++r)
+            for (int s = 0; s < nst; ++s) {
+                ptx::mbar_init(&bar_full[r * (kMaxStages / 2) + s], 1);
+                ptx::mbar_init(&bar_empty[r * (kMaxStages / 2) + s], 1);
+            }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(&bar_acc_full[b], 1);
             ptx::mbar_init(&bar_acc_empty[b], epi_warps(KIND));
         }
         ptx::mbar_init(&bar_a_full, 1);
-        ptx::mbar_init(&bar_a_free, 1);
+        ptx::mbar_init(&bar_a_free, 2);   // both MMA-issuing threads
         abort_flag = 0;
         ptx::mbar_fence_init();
         ptx::prefetch_tensormap(&mapA);
@@ -492,20 +497,26 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     const int n_qb = (a.nq + kTileQ - 1) / kTileQ;
     const ItemRange range(a, n_qb);
 
-    if (warp == 0) {
+    if (warp == 0 || warp == prod2_warp(KIND)) {
         if (lane == 0) {
-            int s = 0;
-            uint32_t ph = 0;
+            const uint32_t pidx = warp == 0 ? 0u : 1u;   // this producer serves the items of this parity
+            // Two sub-rings of nst / 2 stages: even items travel through the first, odd items through
+            // the second, so that each ring's barriers have exactly one consuming thread (a consumer a
+            // whole revolution ahead of the other would otherwise read a parity that has not happened).
+            // The resident query tile is loaded by producer 0.
+            int rs = 0;
+            uint32_t rph = 0;
             int cur_qb = -1;
-            uint32_t a_loads = 0;
+            uint32_t a_loads = 0, t = 0;
             bool ok = true;
             long long pw = 0;
-            const long long k0 = a.prof ? clock64() : 0;
+            const bool prof_on = a.prof && pidx == 0;
+            const long long k0 = prof_on ? clock64() : 0;
+            const uint32_t r = pidx;
             ItemCursor cur(range);
-            for (int64_t i = 0; i < range.count && ok; ++i, cur.next()) {
+            for (int64_t i = 0; i < range.count && ok; ++i, ++t, cur.next()) {
                 const int qb = cur.qb;
-                const int tile = tile_of(a, cur.sel);
-                if (resident && qb != cur_qb) {
+                if (resident && pidx == 0 && qb != cur_qb) {
                     // the previous query block's UMMAs must be done with the tile before it is overwritten
                     if (a_loads && !ptx::mbar_wait_bounded(&bar_a_free, (a_loads - 1u) & 1u, &abort_flag)) { ok = false; break; }
                     ptx::mbar_expect_tx(&bar_a_full, static_cast<uint32_t>(nkc) * kStageABytes);
@@ -514,27 +525,38 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                     ++a_loads;
                     cur_qb = qb;
                 }
+                if ((t & 1u) != pidx) continue;
+                const int tile = tile_of(a, cur.sel);
                 for (int kc = 0; kc < nkc; ++kc) {
-                    const long long w0 = a.prof ? clock64() : 0;
-                    if (!ptx::mbar_wait_bounded(&bar_empty[s], ph ^ 1u, &abort_flag)) { ok = false; break; }
-                    if (a.prof) pw += clock64() - w0;
-                    ptx::mbar_expect_tx(&bar_full[s], stage_bytes);
-                    uint8_t* st = ring + static_cast<size_t>(s) * stage_bytes;
+                    const int s = rs;
+                    uint64_t* full = &bar_full[r * (kMaxStages / 2) + s];
+                    const long long w0 = prof_on ? clock64() : 0;
+                    if (!ptx::mbar_wait_bounded(&bar_empty[r * (kMaxStages / 2) + s], rph ^ 1u, &abort_flag)) { ok = false; break; }
+                    if (prof_on) pw += clock64() - w0;
+                    ptx::mbar_expect_tx(full, stage_bytes);
+                    uint8_t* st = ring + static_cast<size_t>(r * nst + s) * stage_bytes;
                     if (!resident) {
-                        ptx::tma_load_2d(st, &mapA, &bar_full[s], kc * kChunkElems, qb * kTileQ);
+                        ptx::tma_load_2d(st, &mapA, full, kc * kChunkElems, qb * kTileQ);
                         st += kStageABytes;
                     }
-                    ptx::tma_load_2d(st, &mapB, &bar_full[s], kc * kChunkElems, tile * kTileB);
-                    if (++s == nst) { s = 0; ph ^= 1u; }
+                    ptx::tma_load_2d(st, &mapB, full, kc * kChunkElems, tile * kTileB);
+                    if (++rs == nst) { rs = 0; rph ^= 1u; }
                 }
             }
-            if (a.prof) {
+            if (prof_on) {
                 atomicAdd(a.prof + 0, static_cast<unsigned long long>(pw));
                 atomicAdd(a.prof + 7, static_cast<unsigned long long>(clock64() - k0));
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == mma2_warp(KIND)) {
+        // Two threads issue the UMMAs, one for the even items (accumulator 0) and one for the odd
+        // items (accumulator 1), on different schedulers: a single issuing thread, sharing its
+        // scheduler with busy epilogue warps, could not keep the tensor pipe fed.  Both walk the
+        // whole item list so that their view of the query-block runs agrees; each consumes its own
+        // sub-ring of stages.
         if (lane == 0) {
+            const uint32_t parity = warp == 1 ? 0u : 1u;
+            const bool prof_on = a.prof && parity == 0;
             int s = 0;
             uint32_t ph = 0, t = 0;
             int cur_qb = -1;
@@ -557,19 +579,25 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                     ++a_seen;
                     cur_qb = qb;
                 }
-                const uint32_t ab = t & 1u;
+                const bool run_ends = resident && (i + 1 == range.count || cur.last_of_qb());
+                if ((t & 1u) != parity) {
+                    // the other thread's item (it travels through the other sub-ring)
+                    if (run_ends) ptx::umma_commit(&bar_a_free);   // nothing of this run left on this thread
+                    continue;
+                }
+                const uint32_t ab = parity;
                 const uint32_t aph = (t >> 1) & 1u;
-                long long w0 = a.prof ? clock64() : 0;
+                long long w0 = prof_on ? clock64() : 0;
                 if (!ptx::mbar_wait_bounded(&bar_acc_empty[ab], aph ^ 1u, &abort_flag)) { ok = false; break; }
-                if (a.prof) mw0 += clock64() - w0;
+                if (prof_on) mw0 += clock64() - w0;
                 ptx::tc_fence_after();
                 const uint32_t tacc = tmem_base + ab * kTileB;
                 for (int kc = 0; kc < nkc; ++kc) {
-                    w0 = a.prof ? clock64() : 0;
-                    if (!ptx::mbar_wait_bounded(&bar_full[s], ph, &abort_flag)) { ok = false; break; }
-                    if (a.prof) mw1 += clock64() - w0;
+                    w0 = prof_on ? clock64() : 0;
+                    if (!ptx::mbar_wait_bounded(&bar_full[parity * (kMaxStages / 2) + s], ph, &abort_flag)) { ok = false; break; }
+                    if (prof_on) mw1 += clock64() - w0;
                     ptx::tc_fence_after();
-                    const uint32_t st_lo = ring_lo + static_cast<uint32_t>(s) * stage_lo;
+                    const uint32_t st_lo = ring_lo + (parity * static_cast<uint32_t>(nst) + static_cast<uint32_t>(s)) * stage_lo;
                     const uint32_t sa_lo = resident ? a_res_lo + static_cast<uint32_t>(kc) * (kStageABytes >> 4) : st_lo;
                     const uint32_t sb_lo = resident ? st_lo : st_lo + (kStageABytes >> 4);
                     // the last chunk may hold fewer than four 32-byte K steps (the rest is zero fill)
@@ -583,16 +611,16 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                         if (KIND == kKindI8) ptx::umma_i8(tacc, da, db, kIdesc, accum);
                         else ptx::umma_f16(tacc, da, db, kIdesc, accum);
                     }
-                    ptx::umma_commit(&bar_empty[s]);
+                    ptx::umma_commit(&bar_empty[parity * (kMaxStages / 2) + s]);
                     if (++s == nst) { s = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
                 ptx::umma_commit(&bar_acc_full[ab]);
                 // last item of this CTA for the query block: the resident tile may be replaced once
-                // everything issued so far has completed
-                if (resident && (i + 1 == range.count || cur.last_of_qb())) ptx::umma_commit(&bar_a_free);
+                // everything both threads issued so far has completed
+                if (run_ends) ptx::umma_commit(&bar_a_free);
             }
-            if (a.prof) {
+            if (prof_on) {
                 atomicAdd(a.prof + 1, static_cast<unsigned long long>(mw0));
                 atomicAdd(a.prof + 2, static_cast<unsigned long long>(mw1));
             }
@@ -795,6 +823,8 @@ cudaError_t launch_one(const GemmLaunch& L, GemmArgs a, const CUtensorMap* mapA,
     const int stage_bytes = a.a_resident ? kStageBBytes : kStageBytes;
     int nst = (kGemmSmemBudget - 1024 - a_bytes) / stage_bytes;
     if (nst > kMaxStages) nst = kMaxStages;
+    nst &= ~1;                       // two sub-rings of equal depth
+    if (nst < 2) return cudaErrorInvalidConfiguration;
     a.n_stages = nst;
     const int smem = a_bytes + nst * stage_bytes + 1024;
     auto kern = dist_gemm_tc_kernel<KIND, MODE, BURST>;
