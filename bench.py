@@ -42,9 +42,9 @@ FALLBACK_BF16_TFLOPS = 1590.0
 # DRAM bytes per launch of the dominant kernel taken from an ncu capture (see profiles/);
 # None until a capture exists for the workload.
 NCU_TRAFFIC_BYTES = {
-    "ivfpq10m": 1.546e9,     # profiles/ivfpq_scan_kernels_ivfpq10m.md (full-size launch)
-    "flat1m": 2.69e8,        # profiles/dist_gemm_tc_kernel_flat_quarter.md, 67.3 MB at N = 250 k, x4
-    "int8flat4m": None,
+    "ivfpq10m": 1.616e9,     # profiles/ivfpq_scan_kernels_ivfpq10m.md (full-size launch)
+    "flat1m": 3.21e8,        # profiles/dist_gemm_tc_kernel_flat_quarter.md, 80.2 MB at N = 250 k, x4
+    "int8flat4m": 1.049e9,   # profiles/dist_gemm_tc_kernel_flat_quarter.md, 262.3 MB at N = 1 M, x4
 }
 
 
