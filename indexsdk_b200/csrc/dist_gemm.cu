@@ -378,7 +378,7 @@ struct RowEpilogue {
 };
 
 __device__ __forceinline__ int tile_of(const GemmArgs& a, int sel) {
-    if (a.n_tiles_sel == a.n_tiles_total) return sel;   // full pass: no 64-bit division on the hot path
+    if (a.tile_first >= 0) return a.tile_first + sel;   // a contiguous stretch of tiles (whole base: first = 0)
     return static_cast<int>(static_cast<int64_t>(sel) * a.n_tiles_total / a.n_tiles_sel);
 }
 

@@ -37,7 +37,9 @@ struct GemmArgs {
     int nq;
     int64_t N;
     int n_tiles_total;    // ceil(N / kTileB)
-    int n_tiles_sel;      // tiles visited by this pass; tile(i) = i * n_tiles_total / n_tiles_sel
+    int n_tiles_sel;      // tiles visited by this pass
+    int tile_first;       // >= 0: tiles tile_first .. tile_first + n_tiles_sel - 1;
+                          // -1: n_tiles_sel tiles spread evenly, tile(i) = i * n_tiles_total / n_tiles_sel
     int metric;           // kMetricIP / kMetricL2
     const void* bnorm;    // float* (f16/bf16 kinds) or int32_t* (i8): squared norm per base row, L2 only
     // kModeBurstMin

@@ -244,7 +244,7 @@ FlatIndex::Plan FlatIndex::make_plan(int k, int64_t nq) const {
         const int64_t n_qb = (std::max<int64_t>(nq, 1) + kTileQ - 1) / kTileQ;
         // (four threads per row in the 16-warp epilogue of the bf16 kind)
         const uint64_t owners = 4 * static_cast<uint64_t>((num_sms_ + n_qb - 1) / n_qb + 1);
-        want += owners * 16;   // an open block and one reserved ahead
+        want += owners * 32;   // an open block and one reserved ahead, in each of the two stretches of the pass
         p.cap = pow2_ceil(std::max<uint64_t>(p.s_tiles == n_tiles ? 512 : 2048, want));
         if (p.cap >= static_cast<uint64_t>(n_pad)) p.sampled = false;
     }
@@ -325,6 +325,7 @@ void FlatIndex::run_page(int nq, const void* xq_raw, const void* xq_op_in, int k
         const int stride = plan.s_tiles * (kTileB / plan.burst);
         uint32_t* mins = static_cast<uint32_t*>(w_mins_.ensure(static_cast<size_t>(nq) * stride * 4));
         a.n_tiles_sel = plan.s_tiles;
+        a.tile_first = plan.s_tiles == a.n_tiles_total ? 0 : -1;
         a.mins = mins;
         a.mins_stride = stride;
         L.mode = kModeBurstMin;
@@ -350,8 +351,10 @@ void FlatIndex::run_page(int nq, const void* xq_raw, const void* xq_op_in, int k
     }
     timer_.end(stream_);
     timer_.begin(kStageFullGemm, stream_);
-    // 4. full pass: append every key <= tau
-    a.n_tiles_sel = a.n_tiles_total;
+    // 4. full pass: append every key <= tau.  With a threshold from a small sample the pass runs
+    //    in two stretches: after the first fifth of the tiles the candidates found so far give a
+    //    much tighter threshold for the rest (their k-th smallest key bounds the final k-th key),
+    //    which roughly halves the candidates and with them the epilogue's and the refinement's work.
     a.tau = tau;
     a.cand = cand;
     a.counts = counts;
@@ -359,9 +362,38 @@ void FlatIndex::run_page(int nq, const void* xq_raw, const void* xq_op_in, int k
     L.mode = kModeAppend;
     L.burst = 32;
     a.prof = prof_ ? w_prof_.as<unsigned long long>() + 16 : nullptr;
+    const int n_tiles = a.n_tiles_total;
+    const bool two_stretches = plan.sampled && !force_full && plan.s_tiles * 4 <= n_tiles && n_tiles >= 512;
+    int first_stretch = two_stretches ? std::max(n_tiles / 5, 2 * plan.s_tiles) : n_tiles;
+    a.tile_first = 0;
+    a.n_tiles_sel = first_stretch;
     B200_CUDA_CHECK(launch_dist_gemm(L, a, &map_a, &map_b_, stream_));
     stats_.gemm_launches += 1;
     stats_.kernel_launches += 1;
+    auto report_counts = [&](const char* what) {   // development aid (B200IDX_PROF=1)
+        if (!prof_ || !plan.sampled) return;
+        std::vector<uint32_t> hc(static_cast<size_t>(nq));
+        cudaMemcpyAsync(hc.data(), counts, static_cast<size_t>(nq) * 4, cudaMemcpyDeviceToHost, stream_);
+        cudaStreamSynchronize(stream_);
+        double sum = 0;
+        uint32_t mx = 0;
+        for (uint32_t c : hc) { sum += c; mx = std::max(mx, c); }
+        fprintf(stderr, "[b200idx prof] reserved candidate slots %s: mean %.1f max %u (cap %u)\n", what, sum / nq, mx, plan.cap);
+    };
+    report_counts(two_stretches ? "after the first stretch" : "after the full pass");
+    if (two_stretches) {
+        B200_CUDA_CHECK(launch_tighten_tau(cand, counts, plan.cap, nq, k, eps, tau, stream_));
+        if (dtype_ == kF32)
+            B200_CUDA_CHECK(launch_fold_tau(tau, static_cast<const float*>(qnorm), max_norm_, nq, d_, metric_,
+                                            const_cast<void*>(xq_op), stream_));
+        a.tile_first = first_stretch;
+        a.n_tiles_sel = n_tiles - first_stretch;
+        a.prof = nullptr;
+        B200_CUDA_CHECK(launch_dist_gemm(L, a, &map_a, &map_b_, stream_));
+        stats_.gemm_launches += 1;
+        stats_.kernel_launches += 3;
+        report_counts("after the second stretch");
+    }
     timer_.end(stream_);
 
     const uint32_t* counts_arg = plan.sampled ? counts : nullptr;

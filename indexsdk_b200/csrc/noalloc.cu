@@ -139,6 +139,7 @@ extern "C" int b200idx_search_device_noalloc(b200idx_t* h, int64_t n, const void
         a.N = v.n;
         a.n_tiles_total = static_cast<int>(n_pad / kTileB);
         a.n_tiles_sel = a.n_tiles_total;
+        a.tile_first = 0;
         a.metric = ix->metric();
         a.bnorm = v.norms;
         a.tau = tau;

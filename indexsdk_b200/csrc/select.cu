@@ -89,6 +89,36 @@ kth_threshold_kernel(const uint32_t* mins, int stride, int n, int k, const float
 // cancels out of this argument.
 constexpr int kPruneKeys = 4096;    // keys staged in shared memory for the rank search
 constexpr int kPruneKeep = 2048;    // survivors staged for the in-place compaction
+
+// Tightens a threshold part-way through the full pass: the candidates found so far (in the tiles
+// already visited) contain k keys <= their k-th smallest key A_k, so A_k bounds the final k-th key
+// from above and the remaining tiles need only admit keys <= min(tau, A_k (+ 2 eps where keys are
+// approximate)).  Rows whose list overflowed or holds fewer than k candidates keep their threshold.
+__global__ void __launch_bounds__(kSelThreads)
+tighten_tau_kernel(const uint64_t* cand, const uint32_t* counts, uint32_t cap, int k, const float* eps,
+                   uint32_t* tau) {
+    __shared__ uint32_t hist[256], scan[256], sh_bucket, sh_below;
+    __shared__ uint32_t keys[kPruneKeys];
+    const int q = blockIdx.x;
+    const uint64_t* row = cand + static_cast<int64_t>(q) * cap;
+    const uint32_t n = counts[q];
+    if (n > cap || n > static_cast<uint32_t>(kPruneKeys) || n < static_cast<uint32_t>(k)) return;
+    for (uint32_t i = threadIdx.x; i < n; i += kSelThreads) keys[i] = static_cast<uint32_t>(row[i] >> 32);
+    __syncthreads();
+    uint32_t kth = block_radix_kth<uint32_t>(keys, n, static_cast<uint32_t>(k), hist, scan, &sh_bucket, &sh_below);
+    if (kth == 0xFFFFFFFFu) return;   // fewer than k real candidates (the rest are unused slots)
+    if (threadIdx.x == 0) {
+        if (eps) {
+            float f = ord_to_float(kth);
+            f = f + 2.f * eps[q] + eps[q] * 0.125f;
+            f = f + fabsf(f) * 9.5367431640625e-07f;
+            if (f != f) return;
+            kth = float_to_ord(f);
+        }
+        if (kth < tau[q]) tau[q] = kth;
+    }
+}
+
 __global__ void __launch_bounds__(kSelThreads)
 prune_candidates_kernel(uint64_t* cand, uint32_t* counts, uint32_t cap, int k, const float* eps) {
     __shared__ uint32_t hist[256], scan[256], sh_bucket, sh_below, sh_fill;
@@ -637,6 +667,13 @@ cudaError_t launch_select_topk(const uint64_t* cand, const uint32_t* counts, uin
         if (e != cudaSuccess) return e;
     }
     select_topk_kernel<<<nq, kSelThreads, smem, stream>>>(cand, counts, n_fixed, cap, k, P, out, overflow);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_tighten_tau(const uint64_t* cand, const uint32_t* counts, uint32_t cap, int nq, int k,
+                               const float* eps, uint32_t* tau, cudaStream_t stream) {
+    if (nq <= 0) return cudaSuccess;
+    tighten_tau_kernel<<<nq, kSelThreads, 0, stream>>>(cand, counts, cap, k, eps, tau);
     return cudaGetLastError();
 }
 

@@ -24,6 +24,10 @@ cudaError_t launch_select_topk(const uint64_t* cand, const uint32_t* counts, uin
 // fp32 refinement: replaces the key of every candidate by the canonical fp32 distance
 // (sequential fmaf over the dimension) computed from the fp32 rows; L2 -> distance,
 // IP -> negated dot product.
+// thresholded path, between two stretches of the full pass: tau[row] = min(tau[row], k-th smallest
+// key among the row's candidates so far (+ 2 eps[row] where eps is given: approximate keys))
+cudaError_t launch_tighten_tau(const uint64_t* cand, const uint32_t* counts, uint32_t cap, int nq, int k,
+                               const float* eps, uint32_t* tau, cudaStream_t stream);
 // fp32 index, thresholded path: removes candidates whose approximate key exceeds the k-th smallest
 // approximate key of the row by more than 2 eps[row] (they cannot be in the exact top-k); the row
 // is compacted and counts[row] updated
