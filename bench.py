@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the search hot path on seeded synthetic data.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload ivfpq10m|flat1m|int8flat4m]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload ivfpq10m|flat1m|int8flat4m|ivfpq100m]
                     [--impl ours|reference] [--by-residual 0|1]
 
 One "step" is one pass of the search path over one batch of queries.  The default workload is
@@ -150,12 +150,13 @@ def torch_kmeans(x, k, niter, seed, plusplus=False):
         cent = farthest_first(x, k, seed)
     else:
         cent = x[torch.randperm(n, generator=g, device=x.device)[:k]].clone()
+    step = max(4096, min(131072, (1 << 29) // max(k, 1)))     # rows per distance block (<= 2 GiB of fp32)
     for _ in range(niter):
         cn = (cent * cent).sum(1)
         assign = torch.empty(n, dtype=torch.int64, device=x.device)
-        for s in range(0, n, 131072):
-            xs = x[s:s + 131072]
-            assign[s:s + 131072] = (cn[None, :] - 2.0 * (xs @ cent.T)).argmin(1)
+        for s in range(0, n, step):
+            xs = x[s:s + step]
+            assign[s:s + step] = (cn[None, :] - 2.0 * (xs @ cent.T)).argmin(1)
         counts = torch.bincount(assign, minlength=k)
         sums = torch.zeros_like(cent).index_add_(0, assign, x)
         nz = counts > 0
@@ -170,8 +171,9 @@ def assign_torch(x, cent):
     import torch
     cn = (cent * cent).sum(1)
     out = torch.empty(x.shape[0], dtype=torch.int64, device=x.device)
-    for s in range(0, x.shape[0], 131072):
-        out[s:s + 131072] = (cn[None, :] - 2.0 * (x[s:s + 131072] @ cent.T)).argmin(1)
+    step = max(4096, min(131072, (1 << 29) // max(cent.shape[0], 1)))
+    for s in range(0, x.shape[0], step):
+        out[s:s + step] = (cn[None, :] - 2.0 * (x[s:s + step] @ cent.T)).argmin(1)
     return out
 
 
@@ -184,21 +186,29 @@ class Workload:
 
 
 class IvfpqWorkload(Workload):
-    """IVFPQ, d=128, N=10 M Gaussian mixture (16384 centres ~ N(0,1), sigma 0.1), nlist=16384,
-    M=16 x 8 bit trained by seeded k-means (25 iterations) on a 500 k sample, 10 000 queries from
-    the same mixture, nprobe=64, k=10."""
+    """IVFPQ on a Gaussian mixture (centres ~ N(0,1), sigma 0.1), coarse centroids and PQ codebooks
+    trained by seeded k-means (25 iterations) on a 500 k sample, 10 000 queries from the same
+    mixture.  `ivfpq10m`: d=128, N=10 M, 16384 centres / lists, M=16 x 8 bit, nprobe=64, k=10.
+    `ivfpq100m`: d=96, N=100 M, 65536 centres / lists, M=48 x 8 bit, nprobe=128, k=100 (the sharded
+    configuration: base vectors round-robin by id over the ranks)."""
     name = "ivfpq10m"
+    CONFIGS = {
+        "ivfpq10m": dict(d=128, nlist=16384, M=16, nprobe=64, k=10, N=10_000_000, seed=4, qseed=5),
+        "ivfpq100m": dict(d=96, nlist=65536, M=48, nprobe=128, k=100, N=100_000_000, seed=6, qseed=7),
+    }
 
-    def __init__(self, b, dev, rank, world, by_residual, scale=1.0):
+    def __init__(self, b, dev, rank, world, by_residual, scale=1.0, name="ivfpq10m"):
         import torch
-        self.d, self.nlist, self.M, self.nprobe, self.k = 128, 16384, 16, 64, 10
-        self.N = int(10_000_000 * scale)
+        self.name = name
+        cfg = self.CONFIGS[name]
+        self.d, self.nlist, self.M, self.nprobe, self.k = cfg["d"], cfg["nlist"], cfg["M"], cfg["nprobe"], cfg["k"]
+        self.N = int(cfg["N"] * scale)
         self.nq = 10_000
         self.by_residual = bool(by_residual)
         self.dtype = "f32"
-        nc = 16384
+        nc = self.nlist
         g = torch.Generator(device=dev)
-        g.manual_seed(4)
+        g.manual_seed(cfg["seed"])
         centers = torch.randn(nc, self.d, generator=g, device=dev)
         chunk = 1_000_000
 
@@ -209,7 +219,8 @@ class IvfpqWorkload(Workload):
             return centers[which] + 0.1 * torch.randn(n, self.d, generator=gg, device=dev)
 
         t0 = time.time()
-        sample = gen(4000, min(chunk, self.N))[:500_000]
+        base_seed = 1000 * cfg["seed"]
+        sample = gen(base_seed, min(chunk, self.N))[:500_000]
         cent = torch_kmeans(sample, self.nlist, 25, seed=41, plusplus=True)
         train = sample
         if self.by_residual:
@@ -226,7 +237,7 @@ class IvfpqWorkload(Workload):
         t0 = time.time()
         for c in range((self.N + chunk - 1) // chunk):
             n = min(chunk, self.N - c * chunk)
-            x = gen(4000 + c, n)
+            x = gen(base_seed + c, n)
             ids = np.arange(c * chunk, c * chunk + n, dtype=np.int64)
             if world > 1:
                 x = x[rank::world].contiguous()
@@ -237,11 +248,12 @@ class IvfpqWorkload(Workload):
         self.add_s = time.time() - t0
         ix.nprobe = self.nprobe
         self.index = ix
-        self.xq = gen(5, self.nq).cpu().pin_memory()
+        self.xq = gen(cfg["qseed"], self.nq).cpu().pin_memory()
         self.units_bytes_per_query = self.nprobe * (self.N / self.nlist) * self.M   # algorithmic scan bytes
         lens = np.array([ix.list_length(l) for l in range(self.nlist)], np.float64)
-        self.desc = dict(workload="IVFPQ d=128 N=%d nlist=16384 M=16x8bit nprobe=64 k=10 nq=10000 "
-                                  "(Gaussian mixture, seeded k-means++ init + 25 Lloyd it on 500k sample)" % self.N,
+        self.desc = dict(workload="IVFPQ d=%d N=%d nlist=%d M=%dx8bit nprobe=%d k=%d nq=10000 "
+                                  "(Gaussian mixture, seeded k-means++ init + 25 Lloyd it on 500k sample)"
+                                  % (self.d, self.N, self.nlist, self.M, self.nprobe, self.k),
                          by_residual=self.by_residual,
                          list_len_mean=float(lens.mean()), list_len_max=float(lens.max()),
                          list_len_size_biased_mean=float((lens * lens).sum() / max(lens.sum(), 1)))
@@ -251,7 +263,8 @@ class IvfpqWorkload(Workload):
         alg = self.units_bytes_per_query * self.nq / max(1, self.world_size)
         ach = alg / (ms * 1e-3) / 1e9 if ms > 0 else None
         visited = stats["scan_codes_delta"] * self.M / max(1, stats["stage_launches"]["scan"])
-        return dict(bound="hbm", kernel="ivfpq_scan_persist_kernel", achieved=ach, peak=peaks["hbm"], unit="GB/s",
+        kern = "ivfpq_scan_persist_kernel" if self.M == 16 else "ivfpq_fast_scan_kernel"
+        return dict(bound="hbm", kernel=kern, achieved=ach, peak=peaks["hbm"], unit="GB/s",
                     frac=(ach / peaks["hbm"]) if ach else None, peak_source=peaks["source"],
                     traffic=NCU_TRAFFIC_BYTES.get(self.name), algorithmic_bytes_per_launch=alg,
                     visited_code_bytes_per_launch=visited, ms_per_launch=ms)
@@ -372,8 +385,8 @@ class Int8Workload(Workload):
 
 
 def make_workload(name, b, dev, rank, world, args):
-    if name == "ivfpq10m":
-        w = IvfpqWorkload(b, dev, rank, world, args.by_residual, args.scale)
+    if name in IvfpqWorkload.CONFIGS:
+        w = IvfpqWorkload(b, dev, rank, world, args.by_residual, args.scale, name=name)
     elif name == "flat1m":
         w = FlatWorkload(b, dev, rank, world, args.scale)
     elif name == "int8flat4m":
