@@ -554,8 +554,10 @@ struct RowSum128 {
     }
 };
 
-template <int MT, int KPT>
-__global__ void __launch_bounds__(kScanThreads, (MT == 1 && KPT <= 2) ? 6 : 1)
+// NT threads per CTA: 128, or 256 when the table (MT x 32 KB) leaves room for only one or two CTAs
+// per SM and the warps of a CTA are what hides the load latency.
+template <int MT, int KPT, int NT>
+__global__ void __launch_bounds__(NT, (MT == 1 && KPT <= 2) ? 6 : 1)
 ivfpq_fast_scan_kernel(const ScanArgs a) {
     extern __shared__ __align__(16) uint8_t scan_smem[];
     float* lut = reinterpret_cast<float*>(scan_smem);   // [MT][256][32]
@@ -569,9 +571,9 @@ ivfpq_fast_scan_kernel(const ScanArgs a) {
     int& s_gth = *reinterpret_cast<int*>(scan_smem + static_cast<size_t>(MT) * kKsub * 32 * 4);
     if (threadIdx.x == 0) s_gth = 0x7f800000;
     switch (a.dsub) {
-        case 4: build_scan_table<4>(a, q, MT, lut, 32, warp, kScanWarps); break;
-        case 8: build_scan_table<8>(a, q, MT, lut, 32, warp, kScanWarps); break;
-        default: build_scan_table<0>(a, q, MT, lut, 32, warp, kScanWarps); break;
+        case 4: build_scan_table<4>(a, q, MT, lut, 32, warp, NT / 32); break;
+        case 8: build_scan_table<8>(a, q, MT, lut, 32, warp, NT / 32); break;
+        default: build_scan_table<0>(a, q, MT, lut, 32, warp, NT / 32); break;
     }
     __syncthreads();
 
@@ -589,13 +591,13 @@ ivfpq_fast_scan_kernel(const ScanArgs a) {
     RowSum128<MT> sum;
 #pragma unroll
     for (int s = 0; s < 16; ++s) sum.offb[s] = lut_base + 4u * (((s + lane) & 15) + (lane & 16));
-    StaticFeed feed(a, q, split + a.S * warp, a.S * kScanWarps, lane, visited);
+    StaticFeed feed(a, q, split + a.S * warp, a.S * (NT / 32), lane, visited);
     scan_warp_probes<MT, KPT>(a, feed, lane, sum, &s_gth, dk, pk);
     if (a.scanned && visited) atomicAdd(a.scanned, visited);
 
     // merge the four warp lists, keep the kprime best of the CTA
     __syncthreads();
-    constexpr int E = kScanThreads * KPT;
+    constexpr int E = NT * KPT;
     constexpr int KP = 32 * KPT;
     uint32_t* sp = reinterpret_cast<uint32_t*>(scan_smem);
     float* sd = reinterpret_cast<float*>(scan_smem + static_cast<size_t>(E) * 4);
@@ -608,7 +610,7 @@ ivfpq_fast_scan_kernel(const ScanArgs a) {
     block_sort_pairs<uint32_t>(sd, sp, E);
     float* od = a.fd + (q * a.S + split) * KP;
     uint32_t* op = a.fp + (q * a.S + split) * KP;
-    for (int i = threadIdx.x; i < KP; i += kScanThreads) {
+    for (int i = threadIdx.x; i < KP; i += NT) {
         od[i] = sd[i];
         op[i] = sp[i];
     }
@@ -1112,17 +1114,20 @@ cudaError_t set_smem(Kern kern, size_t smem) {
     return cudaSuccess;
 }
 
+constexpr int fast_scan_threads(int mt) { return mt >= 2 ? 256 : 128; }
+
 template <int MT>
 cudaError_t launch_fast_mt(const ScanArgs& a, int kpt, cudaStream_t st) {
+    constexpr int NT = fast_scan_threads(MT);
     // table + the CTA-wide bound; reused for the final merge
-    const size_t smem = std::max(static_cast<size_t>(MT) * kKsub * 32 * 4 + 16, static_cast<size_t>(kScanThreads) * kpt * 8);
+    const size_t smem = std::max(static_cast<size_t>(MT) * kKsub * 32 * 4 + 16, static_cast<size_t>(NT) * kpt * 8);
     dim3 grid(static_cast<unsigned>(a.nq), static_cast<unsigned>(a.S));
 #define B200_FAST_CASE(KP)                                           \
     case KP: {                                                       \
-        auto kern = ivfpq_fast_scan_kernel<MT, KP>;                  \
+        auto kern = ivfpq_fast_scan_kernel<MT, KP, NT>;              \
         cudaError_t e = set_smem(kern, smem);                        \
         if (e != cudaSuccess) return e;                              \
-        kern<<<grid, kScanThreads, smem, st>>>(a);                   \
+        kern<<<grid, NT, smem, st>>>(a);                             \
         return cudaGetLastError();                                   \
     }
     switch (kpt) {
@@ -1583,7 +1588,8 @@ void IvfpqIndex::search_stages(int64_t nq, const float* xq, int k, float* D, int
         // probe splits: enough CTAs to fill the machine, bounded so that the refine kernel's
         // candidate set (S * k') stays within shared memory
         int S = static_cast<int>((16LL * num_sms_ + m - 1) / m);
-        S = std::max(1, std::min(S, (nprobe + kScanWarps - 1) / kScanWarps));
+        const int scan_warps = fast_scan_threads(M_ / 16) / 32;
+        S = std::max(1, std::min(S, (nprobe + scan_warps - 1) / scan_warps));
         S = std::max(1, std::min(S, 4096 / kprime));
         // large batches of 16-byte codes: persistent CTAs, four queries per SM at a time
         const bool persist = M_ == 16 && kpt <= kPsMaxKpt && nprobe <= kPsMaxProbe && m >= 8LL * num_sms_ && !no_persist_;
