@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the search hot path on seeded synthetic data.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload ivfpq10m|flat1m|int8flat4m|ivfpq100m]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload ivfpq10m|flat1m|int8flat4m|ivfpq100m|multiflat20m]
                     [--impl ours|reference] [--by-residual 0|1]
 
 One "step" is one pass of the search path over one batch of queries.  The default workload is
@@ -384,6 +384,124 @@ class Int8Workload(Workload):
         return run
 
 
+class MultiIndexAdapter:
+    """Several indexes on one device behind the interface the bench drives: every search runs on
+    all of them and merges on the device -- what b200idx_search_multi(..., merged) does for host
+    pointers, with device pointers for the device-resident figure."""
+
+    def __init__(self, b, indexes, dev, descending):
+        import torch
+        self.b, self.indexes, self.dev, self.descending = b, indexes, dev, descending
+        self.device = indexes[0].device
+        self.stream_ptr = indexes[0].stream_ptr
+        self._tmp = None
+        self._torch = torch
+
+    def set_timing(self, on):
+        for ix in self.indexes:
+            ix.set_timing(on)
+
+    def stats(self):
+        out = None
+        for ix in self.indexes:
+            s = ix.stats()
+            if out is None:
+                out = s
+                continue
+            for key, v in s.items():
+                if isinstance(v, dict):
+                    for n2 in v:
+                        out[key][n2] += v[n2]
+                else:
+                    out[key] += v
+        return out
+
+    def search_device(self, x_ptr, n, k, D_ptr, I_ptr):
+        torch = self._torch
+        nh = len(self.indexes)
+        if self._tmp is None or self._tmp[0].shape != (nh, n, k):
+            self._tmp = (torch.empty((nh, n, k), dtype=torch.float32, device=self.dev),
+                         torch.empty((nh, n, k), dtype=torch.int64, device=self.dev))
+        tD, tI = self._tmp
+        for i, ix in enumerate(self.indexes):
+            ix.search_device(x_ptr, n, k, tD[i].data_ptr(), tI[i].data_ptr())   # returns when its stream is idle
+        self.b.merge_topk_device(nh, n, k, self.descending, tD.data_ptr(), tI.data_ptr(), D_ptr, I_ptr, self.stream_ptr)
+        torch.cuda.ExternalStream(self.stream_ptr, device=self.dev).synchronize()
+
+    def search_into(self, x, k, D, I):
+        Dm, Im = self.b.search_multi(self.indexes, x, k, merged=True)
+        D[...] = Dm
+        I[...] = Im
+
+
+class MultiFlatWorkload(Workload):
+    """Eight fp16 Flat inner-product indexes of 2 500 000 x 768 L2-normalised N(0,1) rows each,
+    4096 normalised queries, k=1000 merged over all indexes; the indexes are dealt to the ranks
+    round-robin (one per GPU at 8 GPUs)."""
+    name = "multiflat20m"
+    descending = True
+
+    def __init__(self, b, dev, rank, world, scale=1.0):
+        import torch
+        self.d, self.k, self.nq, self.n_indexes = 768, 1000, 4096, 8
+        self.n_each = int(2_500_000 * scale)
+        self.N = self.n_each * self.n_indexes
+        self.dtype = "fp16 -> f32"
+        chunk = 250_000
+
+        def gen(seed, n):
+            g = torch.Generator(device=dev)
+            g.manual_seed(seed)
+            x = torch.randn(n, self.d, generator=g, device=dev)
+            return x / x.norm(dim=1, keepdim=True)
+
+        mine = [i for i in range(self.n_indexes) if i % world == rank]
+        self.indexes, self.first_base = [], None
+        for i in mine:
+            ix = b.IndexFlat(self.d, b.METRIC_INNER_PRODUCT, dtype=b.F16, device=dev.index)
+            for c in range((self.n_each + chunk - 1) // chunk):
+                n = min(chunk, self.n_each - c * chunk)
+                x = gen(8000 + 100 * i + c, n)
+                ids = np.arange(i * self.n_each + c * chunk, i * self.n_each + c * chunk + n, dtype=np.int64)
+                torch.cuda.synchronize(dev)
+                ix.add_device(x.data_ptr(), n, ids)
+                if rank == 0 and i == mine[0]:
+                    part = x.half().float().cpu().numpy()     # the values the index holds
+                    self.first_base = part if self.first_base is None else np.concatenate([self.first_base, part])
+                del x
+            self.indexes.append(ix)
+        self.index = MultiIndexAdapter(b, self.indexes, dev, True)
+        self.xq = gen(9, self.nq).cpu().pin_memory()
+        self.flops_per_query = 2.0 * self.N * self.d
+        self.desc = dict(workload="8 x Flat IP fp16 N=%d each d=768 nq=4096 k=1000 merged (L2-normalised N(0,1) rows)"
+                                  % self.n_each, indexes_on_this_rank=len(mine))
+
+    def roofline(self, stats, steps, peaks):
+        launches = max(1, stats["stage_launches"]["full_gemm"])
+        ms = stats["stage_ms"]["full_gemm"] / launches
+        alg = self.flops_per_query * self.nq / self.n_indexes          # one index's pass
+        ach = alg / (ms * 1e-3) / 1e12 if ms > 0 else None
+        return dict(bound="tensor", kernel="dist_gemm_tc_kernel<f16> (append pass, one index)", achieved=ach,
+                    peak=peaks["tflops"], unit="TFLOP/s", frac=(ach / peaks["tflops"]) if ach else None,
+                    peak_source=peaks["source"], traffic=None, algorithmic_flops_per_launch=alg, ms_per_launch=ms)
+
+    def parity_results(self, m):
+        """GPU results of the first index alone, to set against the oracle on that index."""
+        return self.indexes[0].search(np.ascontiguousarray(self.xq.numpy()[:m]), self.k)
+
+    def cpu_reference(self, oracle, nsample):
+        # The CPU arm searches ONE index (7.7 GB of fp32 rows; all eight would not fit the host) and
+        # its rate is divided by the number of indexes: exact search is linear in the base size.
+        xq = np.ascontiguousarray(self.xq.numpy().astype(np.float16).astype(np.float32))
+        self.cpu_note = "; one of the 8 indexes searched, time multiplied by 8"
+
+        def run(n):
+            t0 = time.perf_counter()
+            D, I = oracle.flat_search(oracle.METRIC_IP, self.first_base, xq[:n], self.k)
+            return (time.perf_counter() - t0) * self.n_indexes, D, I
+        return run
+
+
 def make_workload(name, b, dev, rank, world, args):
     if name in IvfpqWorkload.CONFIGS:
         w = IvfpqWorkload(b, dev, rank, world, args.by_residual, args.scale, name=name)
@@ -391,6 +509,8 @@ def make_workload(name, b, dev, rank, world, args):
         w = FlatWorkload(b, dev, rank, world, args.scale)
     elif name == "int8flat4m":
         w = Int8Workload(b, dev, rank, world, args.scale)
+    elif name == "multiflat20m":
+        w = MultiFlatWorkload(b, dev, rank, world, args.scale)
     else:
         raise SystemExit(f"unknown workload {name}")
     w.world_size = world
@@ -569,12 +689,14 @@ def main():
         qps, n, t = time_cpu(run, nq)
         line["cpu_baseline"] = dict(value=qps, unit="queries/s", cores=oracle.num_threads(), kind="port",
                                     sample="%d queries (the batch of %d, repeated), %.1f s, CPU oracle port with "
-                                           "OpenMP on all host threads (Faiss is not installed)" % (n, nq, t))
+                                           "OpenMP on all host threads (Faiss is not installed)%s"
+                                           % (n, nq, t, getattr(wl, "cpu_note", "")))
         # parity of the timed GPU results against the same oracle run
         _, Dr, Ir = run(min(n, 64))
         m = Dr.shape[0]
-        same = float((outI_np[:m] == Ir).mean())
-        relerr = float(np.max(np.abs(outD_np[:m] - Dr) / np.maximum(np.abs(Dr), 1e-30)))
+        Dg, Ig = wl.parity_results(m) if hasattr(wl, "parity_results") else (outD_np[:m], outI_np[:m])
+        same = float((Ig == Ir).mean())
+        relerr = float(np.max(np.abs(Dg - Dr) / np.maximum(np.abs(Dr), 1e-30)))
         line["parity_check"] = dict(queries=m, id_agreement=same, max_rel_distance_error=relerr)
     if rank == 0:
         print(json.dumps(line))

@@ -63,6 +63,14 @@ int b200idx_add_device(b200idx_t* h, int64_t n, const void* x_dev, const int64_t
  *      (FR/ascend/impl/AscendIndexImpl.cpp:628-633). ---- */
 int b200idx_search(b200idx_t* h, int64_t n, const void* x, int k, float* distances, int64_t* labels);
 int b200idx_search_f16(b200idx_t* h, int64_t n, const uint16_t* x, int k, float* distances, int64_t* labels);
+/* Search restricted by a filter: `mask` holds n rows of ceil(ntotal / 8) bytes; bit (i % 8) of byte
+ * i / 8 of a row is 1 when base position i (add order) may appear in that query's result (replaces
+ * AscendIndexFlat::search_with_masks, feature_retrieval/src/ascendfaiss/ascend/AscendIndexFlat.h:78-82;
+ * device predicate feature_retrieval/src/ascendfaiss/ops/ascendc/op_kernel/distance_flat_l2.cpp:487-533).
+ * Flat and Int8Flat indexes; queries in the index's input dtype (float for F32 / F16 indexes). */
+int b200idx_search_with_masks(b200idx_t* h, int64_t n, const void* x, int k, const uint8_t* mask, float* distances,
+                              int64_t* labels);
+
 /* Device-resident variant: x, distances, labels are device pointers on the index's device; the
  * call returns after the index's stream has been synchronised. */
 int b200idx_search_device(b200idx_t* h, int64_t n, const void* x_dev, int k, float* distances_dev,

@@ -81,6 +81,7 @@ def load() -> C.CDLL:
         "b200idx_ivfpq_get_centroids": (i32, [vp, vp]),
         "b200idx_ivfpq_get_codebooks": (i32, [vp, vp]),
         "b200idx_ivfpq_add_codes": (i32, [vp, i64, vp, vp, vp]),
+        "b200idx_search_with_masks": (i32, [vp, i64, vp, i32, vp, vp, vp]),
         "b200idx_ivfpq_set_nprobe": (i32, [vp, i32]),
         "b200idx_ivfpq_coarse_device": (i32, [vp, i64, vp, vp, vp]),
         "b200idx_ivfpq_search_preassigned_device": (i32, [vp, i64, vp, i32, vp, vp, vp, vp]),
@@ -108,7 +109,7 @@ EXPORTED_SYMBOLS = [
     "b200idx_search_multi", "b200idx_merge_topk_device", "b200idx_reset", "b200idx_remove_ids", "b200idx_ntotal",
     "b200idx_dim", "b200idx_device", "b200idx_get_base", "b200idx_get_ids", "b200idx_ivfpq_set_centroids",
     "b200idx_ivfpq_set_codebooks", "b200idx_ivfpq_get_centroids", "b200idx_ivfpq_get_codebooks",
-    "b200idx_ivfpq_add_codes", "b200idx_ivfpq_set_nprobe", "b200idx_ivfpq_coarse_device",
+    "b200idx_search_with_masks", "b200idx_ivfpq_add_codes", "b200idx_ivfpq_set_nprobe", "b200idx_ivfpq_coarse_device",
     "b200idx_ivfpq_search_preassigned_device", "b200idx_ivfpq_get_nprobe", "b200idx_ivfpq_list_length",
     "b200idx_ivfpq_get_list", "b200idx_stats", "b200idx_set_timing", "b200idx_stream", "b200idx_last_error",
     "b200idx_version",
@@ -180,6 +181,19 @@ class _Index:
         D = np.empty((n, k), np.float32)
         I = np.empty((n, k), np.int64)
         _check(self._lib.b200idx_search(self._h, n, _ptr(x), k, _ptr(D), _ptr(I)), self._h)
+        return D, I
+
+    def search_with_masks(self, x, k: int, mask):
+        """mask: uint8 [n][ceil(ntotal / 8)], bit (i % 8) of byte i / 8 = 1 keeps base position i
+        (np.packbits(keep, axis=1, bitorder="little"))."""
+        x = self._prep(x)
+        n = x.shape[0]
+        mask = np.ascontiguousarray(mask, dtype=np.uint8)
+        if mask.shape != (n, (self.ntotal + 7) // 8):
+            raise ValueError("mask must have shape [n][ceil(ntotal / 8)]")
+        D = np.empty((n, k), np.float32)
+        I = np.empty((n, k), np.int64)
+        _check(self._lib.b200idx_search_with_masks(self._h, n, _ptr(x), k, _ptr(mask), _ptr(D), _ptr(I)), self._h)
         return D, I
 
     def search_into(self, x, k: int, D, I):

@@ -198,6 +198,16 @@ int b200idx_search_f16(b200idx_t* h, int64_t n, const uint16_t* x, int k, float*
     });
 }
 
+int b200idx_search_with_masks(b200idx_t* h, int64_t n, const void* x, int k, const uint8_t* mask, float* D,
+                              int64_t* I) {
+    return guarded(h, [&] {
+        check_search_args(h, n, x, k, D, I);
+        if (h->kind == 2) throw std::invalid_argument("search_with_masks applies to Flat and Int8Flat indexes");
+        if (!mask) throw std::invalid_argument("mask can not be nullptr.");
+        h->flat->search_host_masked(n, x, false, k, mask, D, I);
+    });
+}
+
 int b200idx_search_device(b200idx_t* h, int64_t n, const void* x, int k, float* D, int64_t* I) {
     return guarded(h, [&] {
         check_search_args(h, n, x, k, D, I);

@@ -123,6 +123,11 @@ struct RowEpilogue {
         : a(a_), q(-1), row_ok(false), l2(a_.metric == kMetricL2), tau(AccT(0)), tau_up(AccT(0)), tq(0.f),
           blk_q(-1), blk_next(0), blk_left(0), pre_base(0), pre_ok(false) {}
 
+    // 32 filter bits of this row for base positions col0 .. col0 + 31 (col0 is a multiple of 32).
+    __device__ __forceinline__ uint32_t mask_word(int64_t col0) const {
+        return __ldg(a.qmask + static_cast<int64_t>(q) * a.qmask_stride + (col0 >> 5));
+    }
+
     // Fills what is left of the open block with the "invalid" marker.
     __device__ __forceinline__ void close_block() {
         if (blk_q >= 0) {
@@ -201,7 +206,9 @@ struct RowEpilogue {
             const float ninf = __int_as_float(0xff800000);
             // min / max and selects share the half-rate integer pipe, which is what bounds this
             // epilogue: the test for rows past the end of the base is kept out of the common path.
-            const bool full = nvalid >= 32;
+            uint32_t keep = nvalid >= 32 ? 0xFFFFFFFFu : ((1u << nvalid) - 1u);   // bit c: column c takes part
+            if (a.qmask) keep &= mask_word(col0);
+            const bool full = keep == 0xFFFFFFFFu;
 #pragma unroll
             for (int b = 0; b < NB; ++b) {
                 float v[BURST];
@@ -212,7 +219,7 @@ struct RowEpilogue {
 #pragma unroll
                     for (int j = 0; j < BURST; ++j) {
                         const int c = b * BURST + j;
-                        v[j] = c < nvalid ? __uint_as_float(r[c]) : ninf;
+                        v[j] = ((keep >> c) & 1u) ? __uint_as_float(r[c]) : ninf;
                     }
                 }
 #pragma unroll
@@ -224,12 +231,14 @@ struct RowEpilogue {
             }
         } else if (a.direct) {
             uint64_t* crow = a.cand + static_cast<int64_t>(q) * a.cap + col0;
+            uint32_t keep = nvalid >= 32 ? 0xFFFFFFFFu : ((1u << nvalid) - 1u);
+            if (a.qmask) keep &= mask_word(col0);
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
                 const float dv = __uint_as_float(r[c]);
                 const float key = l2 ? -2.f * dv : -dv;
                 // NaN keys are left at the buffer's "invalid" fill
-                if (c < nvalid && key <= tau) crow[c] = pack_cand(float_to_ord(key), static_cast<uint32_t>(col0 + c));
+                if (((keep >> c) & 1u) && key <= tau) crow[c] = pack_cand(float_to_ord(key), static_cast<uint32_t>(col0 + c));
             }
         } else {
             if (!row_ok) return;
@@ -249,6 +258,7 @@ struct RowEpilogue {
             }
             uint32_t mask = ~((m0 << 16) | (m1 & 0xFFFFu));
             mask &= nvalid >= 32 ? 0xFFFFFFFFu : ~(0xFFFFFFFFu >> nvalid);
+            if (a.qmask) mask &= __brev(mask_word(col0));   // column c is bit (31 - c) here, bit c in the filter
             while (mask) {
                 const uint32_t c = __clz(mask);
                 mask &= ~(0x80000000u >> c);
@@ -288,14 +298,15 @@ struct RowEpilogue {
 #pragma unroll
             for (int j = 0; j < 32; ++j) bnb[j] = 0u;   // +0.0f / 0
         }
-        const uint32_t valid = nvalid >= 32 ? 0xFFFFFFFFu : ((1u << nvalid) - 1u);
+        uint32_t valid = nvalid >= 32 ? 0xFFFFFFFFu : ((1u << nvalid) - 1u);
+        if (a.qmask) valid &= mask_word(col0);
         if (MODE == kModeBurstMin) {
             constexpr int NB = 32 / BURST;
             uint32_t* dst = a.mins + static_cast<int64_t>(q) * a.mins_stride + bslot;
 #pragma unroll
             for (int b = 0; b < NB; ++b) {
                 AccT m[4] = {K::worst(), K::worst(), K::worst(), K::worst()};   // independent chains
-                if (nvalid >= 32) {
+                if (valid == 0xFFFFFFFFu) {
 #pragma unroll
                     for (int j = 0; j < BURST; ++j) {
                         const int c = b * BURST + j;
@@ -340,7 +351,7 @@ struct RowEpilogue {
                 }
             }
             uint32_t mask = (m0 << 16) | (m1 & 0xFFFFu);
-            mask &= nvalid >= 32 ? 0xFFFFFFFFu : ~(0xFFFFFFFFu >> nvalid);
+            mask &= __brev(valid);   // rows past the end of the base, rows the filter excludes
             while (mask) {
                 const uint32_t c = __clz(mask);
                 mask &= ~(0x80000000u >> c);

@@ -51,6 +51,10 @@ struct GemmArgs {
     uint32_t* counts;     // [nq] slots reserved (blocks of 8 per thread and query block run): >= candidates
     uint32_t cap;
     int direct;           // 1: slot = position (cap >= N, no atomics); 0: slot = atomic counter
+    // optional per-(query, base row) filter: bit (row % 32) of qmask[q * qmask_stride + row / 32] = 1
+    // lets the row take part (nullptr: every row does)
+    const uint32_t* qmask;
+    int64_t qmask_stride;
     int* err;             // device error word
     // optional phase profile (nullptr = off): 8 counters of SM cycles summed over CTAs
     //   0 producer wait-empty   1 mma wait-acc-empty   2 mma wait-full   3 epilogue wait-acc-full

@@ -310,6 +310,8 @@ void FlatIndex::run_page(int nq, const void* xq_raw, const void* xq_op_in, int k
     a.metric = metric_;
     a.bnorm = norms_.get();
     a.err = w_err_.as<int>();
+    a.qmask = mask_cur_;
+    a.qmask_stride = mask_stride_;
     a.prof = nullptr;
     GemmLaunch L{};
     L.kind = kind;
@@ -470,6 +472,7 @@ void FlatIndex::search_device(int64_t nq, const void* xq, bool q_is_f16, int k, 
     for (int64_t q0 = 0; q0 < nq; q0 += page) {
         const int nqp = static_cast<int>(std::min<int64_t>(page, nq - q0));
         const uint8_t* xp = static_cast<const uint8_t*>(xq_in) + q0 * in_row;
+        mask_cur_ = mask_dev_ ? mask_dev_ + q0 * mask_stride_ : nullptr;
         run_page(nqp, xp, xp, k, D + q0 * ldk, I + q0 * ldk, ldk, nullptr, false);
         uint8_t* h = static_cast<uint8_t*>(h_over_.ensure(static_cast<size_t>(nqp) + sizeof(int)));
         B200_CUDA_CHECK(cudaMemcpyAsync(h, w_over_.get(), static_cast<size_t>(nqp), cudaMemcpyDeviceToHost, stream_));
@@ -513,6 +516,12 @@ void FlatIndex::search_device(int64_t nq, const void* xq, bool q_is_f16, int k, 
             void* fq = w_fb_q_.ensure(static_cast<size_t>(m) * in_row);
             B200_CUDA_CHECK(launch_gather_rows(xq_in, qmap + o0, m, static_cast<int>(in_row), fq, stream_));
             stats_.kernel_launches += 1;
+            mask_cur_ = nullptr;
+            if (mask_dev_) {
+                void* fm = w_fb_mask_.ensure(static_cast<size_t>(m) * mask_stride_ * 4);
+                B200_CUDA_CHECK(launch_gather_rows(mask_dev_, qmap + o0, m, static_cast<int>(mask_stride_ * 4), fm, stream_));
+                mask_cur_ = static_cast<const uint32_t*>(fm);
+            }
             run_page(m, fq, fq, k, D, I, ldk, qmap + o0, true);
             B200_CUDA_CHECK(cudaStreamSynchronize(stream_));
             timer_.collect(stats_);
@@ -521,11 +530,24 @@ void FlatIndex::search_device(int64_t nq, const void* xq, bool q_is_f16, int k, 
 }
 
 void FlatIndex::search_host(int64_t nq, const void* xq, bool q_is_f16, int k, float* D, int64_t* I) {
+    search_host_masked(nq, xq, q_is_f16, k, nullptr, D, I);
+}
+
+void FlatIndex::search_host_masked(int64_t nq, const void* xq, bool q_is_f16, int k, const uint8_t* mask, float* D,
+                                   int64_t* I) {
     if (nq <= 0) return;
     DeviceGuard g(device_);
+    // the filter travels as 32-bit words, one row per query, rows padded with zeros to whole tiles
+    const size_t mask_bytes = static_cast<size_t>((n_ + 7) / 8);
+    const int64_t mstride = round_up(std::max<int64_t>(n_, 1), kTileB) / 32;
+    struct MaskScope {   // the members describe the search in progress only
+        FlatIndex* self;
+        ~MaskScope() { self->mask_dev_ = self->mask_cur_ = nullptr; self->mask_stride_ = 0; }
+    } scope{this};
     const size_t in_row = static_cast<size_t>(d_) * ((dtype_ == kI8) ? 1 : (q_is_f16 ? 2 : 4));
     // Page so that staging stays bounded.
-    const int64_t page = std::max<int64_t>(1, std::min<int64_t>(nq, (size_t(1) << 30) / std::max<size_t>(in_row, size_t(k) * 12)));
+    const size_t per_query = std::max<size_t>(std::max<size_t>(in_row, size_t(k) * 12), mask ? static_cast<size_t>(mstride) * 4 : 0);
+    const int64_t page = std::max<int64_t>(1, std::min<int64_t>(nq, (size_t(1) << 30) / per_query));
     for (int64_t q0 = 0; q0 < nq; q0 += page) {
         const int64_t m = std::min<int64_t>(page, nq - q0);
         void* dq = w_stage_in_.ensure(static_cast<size_t>(m) * in_row);
@@ -533,6 +555,14 @@ void FlatIndex::search_host(int64_t nq, const void* xq, bool q_is_f16, int k, fl
         int64_t* dI = static_cast<int64_t*>(w_stage_I_.ensure(static_cast<size_t>(m) * k * 8));
         B200_CUDA_CHECK(cudaMemcpyAsync(dq, static_cast<const uint8_t*>(xq) + q0 * in_row,
                                         static_cast<size_t>(m) * in_row, cudaMemcpyHostToDevice, stream_));
+        if (mask && n_ > 0) {
+            void* dm = w_mask_.ensure(static_cast<size_t>(m) * mstride * 4);
+            B200_CUDA_CHECK(cudaMemsetAsync(dm, 0, static_cast<size_t>(m) * mstride * 4, stream_));
+            B200_CUDA_CHECK(cudaMemcpy2DAsync(dm, static_cast<size_t>(mstride) * 4, mask + q0 * mask_bytes, mask_bytes,
+                                              mask_bytes, static_cast<size_t>(m), cudaMemcpyHostToDevice, stream_));
+            mask_dev_ = static_cast<const uint32_t*>(dm);
+            mask_stride_ = mstride;
+        }
         search_device(m, dq, q_is_f16, k, dD, dI, k);
         B200_CUDA_CHECK(cudaMemcpyAsync(D + q0 * k, dD, static_cast<size_t>(m) * k * 4, cudaMemcpyDeviceToHost,
                                         stream_));

@@ -120,6 +120,8 @@ public:
     void search_device(int64_t nq, const void* xq, bool q_is_f16, int k, float* D, int64_t* I, int ldk);
     // Host-pointer search: pinned staging, H2D, search_device, D2H.
     void search_host(int64_t nq, const void* xq, bool q_is_f16, int k, float* D, int64_t* I);
+    // mask: nq rows of ceil(ntotal / 8) bytes, bit (i % 8) of byte i / 8 = 1 lets base position i take part
+    void search_host_masked(int64_t nq, const void* xq, bool q_is_f16, int k, const uint8_t* mask, float* D, int64_t* I);
 
     // Raw access for composite indexes (IVFPQ coarse quantizer).
     const float* rows_f32() const { return x32_.as<float>(); }
@@ -169,6 +171,12 @@ private:
     cudaStream_t stream_ = nullptr;
 
     DeviceBuffer x32_;     // kF32: fp32 rows
+    // filter of the search in progress (device, one row of mask_stride_ words per query of the current
+    // host page; nullptr = none) and the rows of the page run_page is working on
+    const uint32_t* mask_dev_ = nullptr;
+    const uint32_t* mask_cur_ = nullptr;
+    int64_t mask_stride_ = 0;
+    DeviceBuffer w_mask_, w_fb_mask_;
     DeviceBuffer xop_;     // GEMM operand rows: bf16 (kF32), fp16 (kF16), int8 (kI8)
     DeviceBuffer norms_;   // float (kF32/kF16) or int32 (kI8), padded to a multiple of 256 rows
     DeviceBuffer labels_;  // int64 per row

@@ -434,8 +434,17 @@ void AscendIndexFlat::copyTo(faiss::IndexIDMap* index) const {
     index->metric_type = metric_type;
 }
 
-void AscendIndexFlat::search_with_masks(idx_t, const float*, idx_t, float*, idx_t*, const void*) const {
-    FAISS_THROW_MSG("search_with_masks is not implemented in the B200 build yet");
+void AscendIndexFlat::search_with_masks(idx_t n, const float* x, idx_t k, float* distances, idx_t* labels,
+                                        const void* mask) const {
+    RwGuard g(AscendIndex::impl_->mutex, false);
+    check_search_args(n, x, k, distances, labels, is_trained);
+    FAISS_THROW_IF_NOT_MSG(mask, "mask can not be nullptr.");
+    // bit i of a query's row refers to the i-th vector in add order, which is one device's storage order
+    FAISS_THROW_IF_NOT_MSG(AscendIndex::impl_->handles.size() == 1,
+                           "search_with_masks is implemented for an index on one device");
+    b200idx_t* h = AscendIndex::impl_->handles[0];
+    AscendIndex::impl_->rc(b200idx_search_with_masks(h, n, x, static_cast<int>(k), static_cast<const uint8_t*>(mask),
+                                                     distances, labels), h, "search_with_masks");
 }
 void AscendIndexFlat::search_with_masks(idx_t, const uint16_t*, idx_t, float*, idx_t*, const void*) const {
     FAISS_THROW_MSG("search_with_masks is not implemented in the B200 build yet");
@@ -624,8 +633,17 @@ void AscendIndexInt8Flat::copyTo(faiss::IndexIDMap* index) const {
     }
     index->ntotal = sq->ntotal;
 }
-void AscendIndexInt8Flat::search_with_masks(idx_t, const int8_t*, idx_t, float*, idx_t*, const void*) const {
-    FAISS_THROW_MSG("search_with_masks is not implemented in the B200 build yet");
+void AscendIndexInt8Flat::search_with_masks(idx_t n, const int8_t* x, idx_t k, float* distances, idx_t* labels,
+                                            const void* mask) const {
+    FAISS_THROW_IF_NOT_MSG(n > 0 && x && distances && labels && k > 0, "invalid search arguments");
+    FAISS_THROW_IF_NOT_MSG(mask, "mask can not be nullptr.");
+    AscendIndexInt8Impl& core = *AscendIndexInt8::impl_;
+    RwGuard g(core.mutex, false);
+    FAISS_THROW_IF_NOT_MSG(core.handles.size() == 1, "search_with_masks is implemented for an index on one device");
+    b200idx_t* h = core.handles[0];
+    const int code = b200idx_search_with_masks(h, n, x, static_cast<int>(k), static_cast<const uint8_t*>(mask),
+                                               distances, labels);
+    if (code != B200IDX_OK) FAISS_THROW_FMT("search_with_masks failed (%d): %s", code, b200idx_last_error(h));
 }
 void AscendIndexInt8Flat::setPageSize(uint16_t pageBlockNum) {
     FAISS_THROW_IF_NOT_MSG(pageBlockNum > 0 && pageBlockNum <= 144, "pageBlockNum should be in range (0, 144]");
