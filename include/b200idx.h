@@ -147,6 +147,14 @@ int b200idx_ivfpq_get_nprobe(const b200idx_t* h);
 int64_t b200idx_ivfpq_list_length(const b200idx_t* h, int list);
 int b200idx_ivfpq_get_list(const b200idx_t* h, int list, uint8_t* codes, int64_t* ids);
 
+/* Persistence in this library's own file format: everything needed to search again -- vectors in the
+ * index's storage dtype and labels (Flat, Int8Flat), or the trained state, list contents and nprobe
+ * (IVFPQ).  Replaces the reference's route through a CPU Faiss index, index_ascend_to_cpu +
+ * faiss::write_index / read_index + index_cpu_to_ascend (feature_retrieval/src/ascendfaiss/ascend/
+ * AscendCloner.cpp:64-99,159-196,232-281).  load creates the index on `device`. */
+int b200idx_save(const b200idx_t* h, const char* path);
+int b200idx_load(const char* path, int device, b200idx_t** out);
+
 /* ---- counters (the reference has none; APP_LOG timings only) ---- */
 enum {
     B200IDX_STAGE_SAMPLE = 0,    /* query prep + sample GEMM pass + threshold selection */

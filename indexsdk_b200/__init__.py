@@ -82,6 +82,8 @@ def load() -> C.CDLL:
         "b200idx_ivfpq_get_codebooks": (i32, [vp, vp]),
         "b200idx_ivfpq_add_codes": (i32, [vp, i64, vp, vp, vp]),
         "b200idx_search_with_masks": (i32, [vp, i64, vp, i32, vp, vp, vp]),
+        "b200idx_save": (i32, [vp, C.c_char_p]),
+        "b200idx_load": (i32, [C.c_char_p, i32, C.POINTER(vp)]),
         "b200idx_ivfpq_set_nprobe": (i32, [vp, i32]),
         "b200idx_ivfpq_coarse_device": (i32, [vp, i64, vp, vp, vp]),
         "b200idx_ivfpq_search_preassigned_device": (i32, [vp, i64, vp, i32, vp, vp, vp, vp]),
@@ -109,7 +111,7 @@ EXPORTED_SYMBOLS = [
     "b200idx_search_multi", "b200idx_merge_topk_device", "b200idx_reset", "b200idx_remove_ids", "b200idx_ntotal",
     "b200idx_dim", "b200idx_device", "b200idx_get_base", "b200idx_get_ids", "b200idx_ivfpq_set_centroids",
     "b200idx_ivfpq_set_codebooks", "b200idx_ivfpq_get_centroids", "b200idx_ivfpq_get_codebooks",
-    "b200idx_search_with_masks", "b200idx_ivfpq_add_codes", "b200idx_ivfpq_set_nprobe", "b200idx_ivfpq_coarse_device",
+    "b200idx_search_with_masks", "b200idx_save", "b200idx_load", "b200idx_ivfpq_add_codes", "b200idx_ivfpq_set_nprobe", "b200idx_ivfpq_coarse_device",
     "b200idx_ivfpq_search_preassigned_device", "b200idx_ivfpq_get_nprobe", "b200idx_ivfpq_list_length",
     "b200idx_ivfpq_get_list", "b200idx_stats", "b200idx_set_timing", "b200idx_stream", "b200idx_last_error",
     "b200idx_version",
@@ -182,6 +184,10 @@ class _Index:
         I = np.empty((n, k), np.int64)
         _check(self._lib.b200idx_search(self._h, n, _ptr(x), k, _ptr(D), _ptr(I)), self._h)
         return D, I
+
+    def save(self, path: str):
+        """Writes the index in the library's own file format (see b200idx_save)."""
+        _check(self._lib.b200idx_save(self._h, str(path).encode()), self._h)
 
     def search_with_masks(self, x, k: int, mask):
         """mask: uint8 [n][ceil(ntotal / 8)], bit (i % 8) of byte i / 8 = 1 keeps base position i
@@ -350,6 +356,32 @@ class IndexIVFPQ(_Index):
         if n:
             _check(self._lib.b200idx_ivfpq_get_list(self._h, l, _ptr(codes), _ptr(ids)), self._h)
         return codes, ids
+
+
+def load_index(path: str, device: int = 0):
+    """Reads an index written by ``save`` onto ``device`` (b200idx_load) and returns the matching
+    Python object."""
+    import struct
+    with open(path, "rb") as f:
+        head = f.read(4 + 4 + 4 + 12 + 8 + 16)
+    if len(head) < 32 or head[:4] != b"B2IX":
+        raise B200IdxError(2001, "not an index file of this library")
+    _, kind, d, metric, dtype, _ = struct.unpack_from("<IIiiiq", head, 4)
+    if kind == 0:
+        ix = IndexFlat.__new__(IndexFlat)
+        _Index.__init__(ix)
+        ix.metric, ix.dtype = metric, (F16 if dtype == 1 else F32)
+    elif kind == 1:
+        ix = IndexInt8Flat.__new__(IndexInt8Flat)
+        _Index.__init__(ix)
+        ix.metric = metric
+    else:
+        nlist, M, _, by_res = struct.unpack_from("<iiii", head, 32)
+        ix = IndexIVFPQ.__new__(IndexIVFPQ)
+        _Index.__init__(ix)
+        ix.nlist, ix.M, ix.by_residual = nlist, M, bool(by_res)
+    _check(ix._lib.b200idx_load(str(path).encode(), device, C.byref(ix._h)))
+    return ix
 
 
 def search_multi(indexes, x, k: int, merged: bool = True):

@@ -2,6 +2,7 @@
 // translation, and the multi-index / multi-device fan-out.
 #include "../../include/b200idx.h"
 
+#include <cstdio>
 #include <cstring>
 #include <map>
 #include <memory>
@@ -433,6 +434,178 @@ int b200idx_ivfpq_search_preassigned_device(b200idx_t* h, int64_t n, const float
 int b200idx_ivfpq_get_list(const b200idx_t* h, int list, uint8_t* codes, int64_t* ids) {
     B200_REQUIRE_IVFPQ(h)
     return guarded(h, [&] { h->ivfpq->get_list(list, codes, ids); });
+}
+
+// ---------------------------------------------------------------------------------------
+// Native file format (little-endian):
+//   "B2IX" | u32 version = 1 | u32 kind (0 Flat, 1 Int8Flat, 2 IVFPQ) | i32 d | i32 metric | i32 dtype | i64 ntotal
+//   Flat / Int8Flat : ntotal rows in the index's storage dtype (fp32, fp16 or int8) | ntotal int64 labels
+//   IVFPQ           : i32 nlist | i32 M | i32 nbits | i32 by_residual | i32 nprobe | i32 trained |
+//                     centroids [nlist][d] fp32 | codebooks [M][256][d/M] fp32 |
+//                     per list: i64 length | codes [length][M] (canonical byte order) | ids [length]
+// ---------------------------------------------------------------------------------------
+}  // extern "C"
+namespace {
+struct FileCloser {
+    void operator()(FILE* f) const { if (f) std::fclose(f); }
+};
+using FilePtr = std::unique_ptr<FILE, FileCloser>;
+
+void put(FILE* f, const void* p, size_t n) {
+    if (n && std::fwrite(p, 1, n, f) != n) throw std::runtime_error("write failed");
+}
+void get(FILE* f, void* p, size_t n) {
+    if (n && std::fread(p, 1, n, f) != n) throw std::runtime_error("file is truncated");
+}
+template <typename T>
+void put_v(FILE* f, T v) { put(f, &v, sizeof(T)); }
+template <typename T>
+T get_v(FILE* f) { T v; get(f, &v, sizeof(T)); return v; }
+size_t storage_elem_bytes(int dtype) { return dtype == kI8 ? 1 : (dtype == kF16 ? 2 : 4); }
+}  // namespace
+extern "C" {
+
+int b200idx_save(const b200idx_t* h, const char* path) {
+    if (!h || !path) return B200IDX_ERR_INVALID_PARAM;
+    return guarded(h, [&] {
+        FilePtr f(std::fopen(path, "wb"));
+        if (!f) throw std::invalid_argument(std::string("cannot open for writing: ") + path);
+        put(f.get(), "B2IX", 4);
+        put_v<uint32_t>(f.get(), 1u);
+        put_v<uint32_t>(f.get(), static_cast<uint32_t>(h->kind));
+        if (h->kind != 2) {
+            const FlatIndex& ix = *h->flat;
+            put_v<int32_t>(f.get(), ix.d());
+            put_v<int32_t>(f.get(), ix.metric());
+            put_v<int32_t>(f.get(), ix.dtype());
+            put_v<int64_t>(f.get(), ix.ntotal());
+            const size_t row = static_cast<size_t>(ix.d()) * storage_elem_bytes(ix.dtype());
+            const int64_t chunk = std::max<int64_t>(1, (int64_t(64) << 20) / static_cast<int64_t>(row));
+            std::vector<uint8_t> buf;
+            for (int64_t o = 0; o < ix.ntotal(); o += chunk) {
+                const int64_t m = std::min(chunk, ix.ntotal() - o);
+                buf.resize(static_cast<size_t>(m) * row);
+                ix.get_base(o, m, buf.data());
+                put(f.get(), buf.data(), buf.size());
+            }
+            std::vector<int64_t> ids(static_cast<size_t>(ix.ntotal()));
+            if (!ids.empty()) ix.get_labels(0, ix.ntotal(), ids.data());
+            put(f.get(), ids.data(), ids.size() * 8);
+        } else {
+            const IvfpqIndex& ix = *h->ivfpq;
+            put_v<int32_t>(f.get(), ix.d());
+            put_v<int32_t>(f.get(), B200IDX_METRIC_L2);
+            put_v<int32_t>(f.get(), 0);
+            put_v<int64_t>(f.get(), ix.ntotal());
+            put_v<int32_t>(f.get(), ix.nlist());
+            put_v<int32_t>(f.get(), ix.M());
+            put_v<int32_t>(f.get(), 8);
+            put_v<int32_t>(f.get(), ix.by_residual() ? 1 : 0);
+            put_v<int32_t>(f.get(), ix.nprobe());
+            put_v<int32_t>(f.get(), ix.is_trained() ? 1 : 0);
+            if (ix.is_trained()) {
+                std::vector<float> c(static_cast<size_t>(ix.nlist()) * ix.d()), cb(static_cast<size_t>(256) * ix.d());
+                ix.get_centroids(c.data());
+                ix.get_codebooks(cb.data());
+                put(f.get(), c.data(), c.size() * 4);
+                put(f.get(), cb.data(), cb.size() * 4);
+                std::vector<uint8_t> codes;
+                std::vector<int64_t> ids;
+                for (int l = 0; l < ix.nlist(); ++l) {
+                    const int64_t len = ix.list_length(l);
+                    put_v<int64_t>(f.get(), len);
+                    codes.resize(static_cast<size_t>(len) * ix.M());
+                    ids.resize(static_cast<size_t>(len));
+                    if (len) ix.get_list(l, codes.data(), ids.data());
+                    put(f.get(), codes.data(), codes.size());
+                    put(f.get(), ids.data(), ids.size() * 8);
+                }
+            }
+        }
+        if (std::fflush(f.get()) != 0) throw std::runtime_error("write failed");
+    });
+}
+
+int b200idx_load(const char* path, int device, b200idx_t** out) {
+    if (!path || !out) return B200IDX_ERR_INVALID_PARAM;
+    *out = nullptr;
+    b200idx_t* h = nullptr;
+    const int code = guarded_create([&] {
+        FilePtr f(std::fopen(path, "rb"));
+        if (!f) throw std::invalid_argument(std::string("cannot open for reading: ") + path);
+        char magic[4];
+        get(f.get(), magic, 4);
+        if (std::memcmp(magic, "B2IX", 4) != 0 || get_v<uint32_t>(f.get()) != 1u)
+            throw std::invalid_argument("not an index file of this library (or an unknown version)");
+        const uint32_t kind = get_v<uint32_t>(f.get());
+        const int d = get_v<int32_t>(f.get());
+        const int metric = get_v<int32_t>(f.get());
+        const int dtype = get_v<int32_t>(f.get());
+        const int64_t ntotal = get_v<int64_t>(f.get());
+        if (kind > 2 || ntotal < 0) throw std::invalid_argument("corrupt index file");
+        int rc;
+        if (kind == 0) rc = b200idx_create_flat(d, metric, dtype == kF16 ? B200IDX_F16 : B200IDX_F32, device, &h);
+        else if (kind == 1) rc = b200idx_create_int8flat(d, metric, device, &h);
+        else {
+            const int nlist = get_v<int32_t>(f.get()), M = get_v<int32_t>(f.get()), nbits = get_v<int32_t>(f.get());
+            const int by_res = get_v<int32_t>(f.get());
+            rc = b200idx_create_ivfpq(d, metric, nlist, M, nbits, by_res, device, &h);
+        }
+        if (rc != B200IDX_OK) throw std::invalid_argument(std::string("corrupt index file: ") + b200idx_last_error(nullptr));
+        if (kind != 2) {
+            const size_t row = static_cast<size_t>(d) * storage_elem_bytes(h->flat->dtype());
+            const int64_t chunk = std::max<int64_t>(1, (int64_t(64) << 20) / static_cast<int64_t>(row));
+            std::vector<uint8_t> rows(static_cast<size_t>(std::min<int64_t>(chunk, std::max<int64_t>(ntotal, 1))) * row);
+            // labels follow the rows: read them first
+            const long rows_at = std::ftell(f.get());
+            if (std::fseek(f.get(), rows_at + static_cast<long>(static_cast<size_t>(ntotal) * row), SEEK_SET) != 0)
+                throw std::runtime_error("file is truncated");
+            std::vector<int64_t> ids(static_cast<size_t>(ntotal));
+            get(f.get(), ids.data(), ids.size() * 8);
+            if (std::fseek(f.get(), rows_at, SEEK_SET) != 0) throw std::runtime_error("seek failed");
+            for (int64_t o = 0; o < ntotal; o += chunk) {
+                const int64_t m = std::min(chunk, ntotal - o);
+                get(f.get(), rows.data(), static_cast<size_t>(m) * row);
+                h->flat->add(m, rows.data(), h->flat->dtype() == kF16, ids.data() + o, false);
+            }
+        } else {
+            IvfpqIndex& ix = *h->ivfpq;
+            ix.set_nprobe(get_v<int32_t>(f.get()));
+            const int trained = get_v<int32_t>(f.get());
+            if (trained) {
+                std::vector<float> c(static_cast<size_t>(ix.nlist()) * d), cb(static_cast<size_t>(256) * d);
+                get(f.get(), c.data(), c.size() * 4);
+                get(f.get(), cb.data(), cb.size() * 4);
+                ix.set_centroids(c.data());
+                ix.set_codebooks(cb.data());
+                std::vector<uint8_t> codes;
+                std::vector<int64_t> ids;
+                std::vector<int32_t> ln;
+                for (int l = 0; l < ix.nlist(); ++l) {
+                    const int64_t len = get_v<int64_t>(f.get());
+                    if (len < 0) throw std::invalid_argument("corrupt index file");
+                    const size_t at = ln.size();
+                    ln.resize(at + static_cast<size_t>(len), l);
+                    codes.resize((at + static_cast<size_t>(len)) * ix.M());
+                    ids.resize(at + static_cast<size_t>(len));
+                    get(f.get(), codes.data() + at * ix.M(), static_cast<size_t>(len) * ix.M());
+                    get(f.get(), ids.data() + at, static_cast<size_t>(len) * 8);
+                    if (ln.size() >= (size_t(1) << 22) || l + 1 == ix.nlist()) {   // add in batches, list order kept
+                        if (!ln.empty()) ix.add_codes(static_cast<int64_t>(ln.size()), ln.data(), codes.data(), ids.data());
+                        ln.clear();
+                        codes.clear();
+                        ids.clear();
+                    }
+                }
+            }
+        }
+    });
+    if (code != B200IDX_OK) {
+        if (h) b200idx_destroy(h);
+        return code;
+    }
+    *out = h;
+    return B200IDX_OK;
 }
 
 int b200idx_stats(b200idx_t* h, b200idx_stats_t* out, int reset) {
