@@ -128,6 +128,17 @@ int b200idx_ivfpq_add_codes(b200idx_t* h, int64_t n, const int32_t* list_no, con
 /* setNumProbes / getNumProbes: FR/ascend/AscendIndexIVF.h:93-96 */
 int b200idx_ivfpq_set_nprobe(b200idx_t* h, int nprobe);
 
+/* Training on the device.  b200idx_kmeans: Lloyd k-means of n host vectors into k centroids (start:
+ * centroid c = x[(floor(c n / k) + seed) mod n]; nearest centroid under the canonical fp32 L2
+ * distance, ties to the lower centroid; mean of the members summed in fp64 in increasing vector
+ * index; a centroid without members keeps its value).  b200idx_ivfpq_train: coarse centroids with
+ * k = nlist, then one 256-entry codebook per sub-space (seed + 1 + m), on the residuals to the
+ * assigned centroid when the index encodes residuals; the index must be empty.  Replaces the
+ * reference's NPU training (feature_retrieval/src/ascendfaiss/ascenddaemon/impl/IndexIVFPQ.cpp:
+ * 810-1135,1340-1430; ascend/impl/AscendIndexIVFPQImpl.cpp:962-1252). */
+int b200idx_kmeans(int device, int d, int64_t n, const float* x, int k, int niter, uint64_t seed, float* centroids);
+int b200idx_ivfpq_train(b200idx_t* h, int64_t n, const float* x, int niter, uint64_t seed);
+
 /* The two halves of an IVFPQ search, device-resident (the reference runs them back to back inside
  * IndexIVFPQ::searchImpl: probe selection feature_retrieval/src/ascendfaiss/ascenddaemon/impl/
  * IndexIVFPQ.cpp:2104-2164, code scan + top-k :2165-2411).  Split so that the ranks of a sharded

@@ -82,6 +82,8 @@ def load() -> C.CDLL:
         "b200idx_ivfpq_get_codebooks": (i32, [vp, vp]),
         "b200idx_ivfpq_add_codes": (i32, [vp, i64, vp, vp, vp]),
         "b200idx_search_with_masks": (i32, [vp, i64, vp, i32, vp, vp, vp]),
+        "b200idx_kmeans": (i32, [i32, i32, i64, vp, i32, i32, C.c_uint64, vp]),
+        "b200idx_ivfpq_train": (i32, [vp, i64, vp, i32, C.c_uint64]),
         "b200idx_save": (i32, [vp, C.c_char_p]),
         "b200idx_load": (i32, [C.c_char_p, i32, C.POINTER(vp)]),
         "b200idx_ivfpq_set_nprobe": (i32, [vp, i32]),
@@ -111,7 +113,7 @@ EXPORTED_SYMBOLS = [
     "b200idx_search_multi", "b200idx_merge_topk_device", "b200idx_reset", "b200idx_remove_ids", "b200idx_ntotal",
     "b200idx_dim", "b200idx_device", "b200idx_get_base", "b200idx_get_ids", "b200idx_ivfpq_set_centroids",
     "b200idx_ivfpq_set_codebooks", "b200idx_ivfpq_get_centroids", "b200idx_ivfpq_get_codebooks",
-    "b200idx_search_with_masks", "b200idx_save", "b200idx_load", "b200idx_ivfpq_add_codes", "b200idx_ivfpq_set_nprobe", "b200idx_ivfpq_coarse_device",
+    "b200idx_search_with_masks", "b200idx_save", "b200idx_load", "b200idx_kmeans", "b200idx_ivfpq_train", "b200idx_ivfpq_add_codes", "b200idx_ivfpq_set_nprobe", "b200idx_ivfpq_coarse_device",
     "b200idx_ivfpq_search_preassigned_device", "b200idx_ivfpq_get_nprobe", "b200idx_ivfpq_list_length",
     "b200idx_ivfpq_get_list", "b200idx_stats", "b200idx_set_timing", "b200idx_stream", "b200idx_last_error",
     "b200idx_version",
@@ -335,6 +337,21 @@ class IndexIVFPQ(_Index):
     def nprobe(self, v: int):
         _check(self._lib.b200idx_ivfpq_set_nprobe(self._h, int(v)), self._h)
 
+    def get_centroids(self):
+        out = np.empty((self.nlist, self.d), np.float32)
+        _check(self._lib.b200idx_ivfpq_get_centroids(self._h, _ptr(out)), self._h)
+        return out
+
+    def get_codebooks(self):
+        out = np.empty((self.M, 256, self.d // self.M), np.float32)
+        _check(self._lib.b200idx_ivfpq_get_codebooks(self._h, _ptr(out)), self._h)
+        return out
+
+    def train(self, x, niter: int = 10, seed: int = 0):
+        """Coarse centroids and PQ codebooks by k-means on the device (b200idx_ivfpq_train)."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        _check(self._lib.b200idx_ivfpq_train(self._h, x.shape[0], _ptr(x), int(niter), C.c_uint64(seed)), self._h)
+
     def coarse_device(self, x_ptr: int, n: int, cD_ptr: int, cI_ptr: int):
         """Probe selection only: [n][nprobe] distances and list ids (device pointers)."""
         _check(self._lib.b200idx_ivfpq_coarse_device(self._h, n, C.c_void_p(x_ptr), C.c_void_p(cD_ptr),
@@ -356,6 +373,14 @@ class IndexIVFPQ(_Index):
         if n:
             _check(self._lib.b200idx_ivfpq_get_list(self._h, l, _ptr(codes), _ptr(ids)), self._h)
         return codes, ids
+
+
+def kmeans(x, k: int, niter: int = 10, seed: int = 0, device: int = 0):
+    """Lloyd k-means on the device (b200idx_kmeans); returns the [k][d] centroids."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty((k, x.shape[1]), np.float32)
+    _check(load().b200idx_kmeans(device, x.shape[1], x.shape[0], _ptr(x), k, int(niter), C.c_uint64(seed), _ptr(out)))
+    return out
 
 
 def load_index(path: str, device: int = 0):

@@ -14,6 +14,7 @@
 #include "c_api_internal.h"
 #include "flat_index.h"
 #include "ivfpq_index.h"
+#include "kmeans.h"
 #include "select.cuh"
 
 using namespace b200;
@@ -429,6 +430,28 @@ int b200idx_ivfpq_search_preassigned_device(b200idx_t* h, int64_t n, const float
     return guarded(h, [&] {
         check_search_args(h, n, x, k, D, I);
         h->ivfpq->search_preassigned_device(n, x, k, cD, cI, D, I);
+    });
+}
+int b200idx_kmeans(int device, int d, int64_t n, const float* x, int k, int niter, uint64_t seed, float* centroids) {
+    return guarded_create([&] {
+        if (!x || !centroids) throw std::invalid_argument("x and centroids can not be nullptr.");
+        if (d <= 0 || n <= 0 || k <= 0 || niter < 0 || k > n) throw std::invalid_argument("k-means: need d > 0, 0 < k <= n, niter >= 0");
+        DeviceGuard g(device);
+        DeviceBuffer xd, cd;
+        float* xdev = static_cast<float*>(xd.ensure(static_cast<size_t>(n) * d * 4));
+        float* cdev = static_cast<float*>(cd.ensure(static_cast<size_t>(k) * d * 4));
+        B200_CUDA_CHECK(cudaMemcpy(xdev, x, static_cast<size_t>(n) * d * 4, cudaMemcpyHostToDevice));
+        kmeans_device(device, d, n, xdev, k, niter, seed, cdev, nullptr);
+        B200_CUDA_CHECK(cudaMemcpy(centroids, cdev, static_cast<size_t>(k) * d * 4, cudaMemcpyDeviceToHost));
+    });
+}
+int b200idx_ivfpq_train(b200idx_t* h, int64_t n, const float* x, int niter, uint64_t seed) {
+    B200_REQUIRE_IVFPQ(h)
+    return guarded(h, [&] {
+        if (n <= 0 || !x) throw std::invalid_argument("n must be > 0, x non-NULL");
+        if (niter < 0) throw std::invalid_argument("niter must be >= 0");
+        if (h->ivfpq->ntotal() != 0) throw std::invalid_argument("train: the index already holds vectors");
+        h->ivfpq->train(n, x, niter, seed);
     });
 }
 int b200idx_ivfpq_get_list(const b200idx_t* h, int list, uint8_t* codes, int64_t* ids) {

@@ -42,6 +42,7 @@
 #include <cub/cub.cuh>
 #include <unordered_set>
 
+#include "kmeans.h"
 #include "select.cuh"
 
 namespace b200 {
@@ -1275,6 +1276,46 @@ void IvfpqIndex::set_codebooks(const float* cb) {
         B200_CUDA_CHECK(cudaMemcpy(codebooks_t_.get(), t.data(), bytes, cudaMemcpyHostToDevice));
     }
     has_codebooks_ = true;
+}
+
+namespace {
+// sub[i][t] = x[i][m * dsub + t] - (cent ? cent[assign[i]][m * dsub + t] : 0)
+__global__ void train_subspace_kernel(const float* x, int64_t n, int d, int m, int dsub, const float* cent,
+                                      const int32_t* assign, float* sub) {
+    const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= n * dsub) return;
+    const int64_t i = idx / dsub;
+    const int t = static_cast<int>(idx % dsub);
+    float v = x[i * d + m * dsub + t];
+    if (cent) v = v - cent[static_cast<int64_t>(assign[i]) * d + m * dsub + t];
+    sub[idx] = v;
+}
+}  // namespace
+
+void IvfpqIndex::train(int64_t n, const float* x_host, int niter, uint64_t seed) {
+    if (n < std::max(nlist_, kKsub)) throw std::invalid_argument("training needs at least max(nlist, 256) vectors");
+    DeviceGuard g(device_);
+    DeviceBuffer xd, cd, ad, sd, cbd;
+    float* x = static_cast<float*>(xd.ensure(static_cast<size_t>(n) * d_ * 4));
+    float* cent = static_cast<float*>(cd.ensure(static_cast<size_t>(nlist_) * d_ * 4));
+    int32_t* assign = static_cast<int32_t*>(ad.ensure(static_cast<size_t>(n) * 4));
+    float* sub = static_cast<float*>(sd.ensure(static_cast<size_t>(n) * dsub_ * 4));
+    float* cb = static_cast<float*>(cbd.ensure(static_cast<size_t>(kKsub) * dsub_ * 4));
+    B200_CUDA_CHECK(cudaMemcpy(x, x_host, static_cast<size_t>(n) * d_ * 4, cudaMemcpyHostToDevice));
+    kmeans_device(device_, d_, n, x, nlist_, niter, seed, cent, assign);
+    std::vector<float> hc(static_cast<size_t>(nlist_) * d_), hcb(static_cast<size_t>(M_) * kKsub * dsub_);
+    B200_CUDA_CHECK(cudaMemcpy(hc.data(), cent, hc.size() * 4, cudaMemcpyDeviceToHost));
+    for (int m = 0; m < M_; ++m) {
+        train_subspace_kernel<<<blocks_for(n * dsub_, 256), 256>>>(x, n, d_, m, dsub_, by_residual_ ? cent : nullptr,
+                                                                   assign, sub);
+        B200_CUDA_CHECK(cudaGetLastError());
+        B200_CUDA_CHECK(cudaDeviceSynchronize());
+        kmeans_device(device_, dsub_, n, sub, kKsub, niter, seed + 1 + static_cast<uint64_t>(m), cb, nullptr);
+        B200_CUDA_CHECK(cudaMemcpy(hcb.data() + static_cast<size_t>(m) * kKsub * dsub_, cb,
+                                   static_cast<size_t>(kKsub) * dsub_ * 4, cudaMemcpyDeviceToHost));
+    }
+    set_centroids(hc.data());
+    set_codebooks(hcb.data());
 }
 
 void IvfpqIndex::get_centroids(float* out) const { coarse_->get_base(0, nlist_, out); }

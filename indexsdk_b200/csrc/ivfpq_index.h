@@ -42,6 +42,9 @@ public:
 
     void set_centroids(const float* centroids_host);  // [nlist][d]
     void set_codebooks(const float* codebooks_host);  // [M][256][d / M]
+    // Trains coarse centroids (k-means, k = nlist) and the M sub-space codebooks (k-means, k = 256, on
+    // the residuals to the assigned centroid when the index encodes residuals) on the device.
+    void train(int64_t n, const float* x_host, int niter, uint64_t seed);
     void get_centroids(float* out_host) const;
     void get_codebooks(float* out_host) const;
 

@@ -670,64 +670,6 @@ void push_trained_state(AscendIndexImpl& im) {
         im.rc(b200idx_ivfpq_set_codebooks(h, im.codebooks.data()), h, "set_codebooks");
     }
 }
-// Lloyd k-means; assignment on the GPU when the sub-space dimension allows a Flat index,
-// otherwise on the host.  Seeded, deterministic.
-std::vector<float> kmeans(int dev, int dim, idx_t n, const float* x, int k, int niter, unsigned seed) {
-    std::mt19937_64 rng(seed);
-    std::vector<float> cent(static_cast<size_t>(k) * dim);
-    std::vector<idx_t> perm(static_cast<size_t>(n));
-    for (idx_t i = 0; i < n; ++i) perm[static_cast<size_t>(i)] = i;
-    std::shuffle(perm.begin(), perm.end(), rng);
-    for (int c = 0; c < k; ++c)
-        std::memcpy(&cent[static_cast<size_t>(c) * dim], x + perm[static_cast<size_t>(c % n)] * dim, sizeof(float) * dim);
-    std::vector<idx_t> assign(static_cast<size_t>(n));
-    std::vector<float> dist(static_cast<size_t>(n));
-    const bool on_gpu = dim % 16 == 0;
-    for (int it = 0; it < niter; ++it) {
-        if (on_gpu) {
-            b200idx_t* h = nullptr;
-            if (b200idx_create_flat(dim, B200IDX_METRIC_L2, B200IDX_F32, dev, &h) != B200IDX_OK)
-                FAISS_THROW_FMT("k-means: %s", b200idx_last_error(nullptr));
-            int code = b200idx_add(h, k, cent.data(), nullptr);
-            if (code == B200IDX_OK) code = b200idx_search(h, n, x, 1, dist.data(), assign.data());
-            std::string msg = code ? b200idx_last_error(h) : "";
-            b200idx_destroy(h);
-            if (code) FAISS_THROW_FMT("k-means assignment failed: %s", msg.c_str());
-        } else {
-            for (idx_t i = 0; i < n; ++i) {
-                float best = 3.4e38f;
-                idx_t arg = 0;
-                for (int c = 0; c < k; ++c) {
-                    float acc = 0.f;
-                    for (int t = 0; t < dim; ++t) {
-                        const float df = x[i * dim + t] - cent[static_cast<size_t>(c) * dim + t];
-                        acc += df * df;
-                    }
-                    if (acc < best) { best = acc; arg = c; }
-                }
-                assign[static_cast<size_t>(i)] = arg;
-            }
-        }
-        std::vector<double> sum(static_cast<size_t>(k) * dim, 0.0);
-        std::vector<idx_t> cnt(static_cast<size_t>(k), 0);
-        for (idx_t i = 0; i < n; ++i) {
-            const size_t c = static_cast<size_t>(assign[static_cast<size_t>(i)]);
-            cnt[c] += 1;
-            for (int t = 0; t < dim; ++t) sum[c * dim + t] += x[i * dim + t];
-        }
-        for (int c = 0; c < k; ++c) {
-            if (cnt[static_cast<size_t>(c)] == 0) {   // empty cluster: re-seed from a random point
-                const idx_t p = static_cast<idx_t>(rng() % static_cast<uint64_t>(n));
-                std::memcpy(&cent[static_cast<size_t>(c) * dim], x + p * dim, sizeof(float) * dim);
-                continue;
-            }
-            for (int t = 0; t < dim; ++t)
-                cent[static_cast<size_t>(c) * dim + t] =
-                    static_cast<float>(sum[static_cast<size_t>(c) * dim + t] / cnt[static_cast<size_t>(c)]);
-        }
-    }
-    return cent;
-}
 }  // namespace
 
 AscendIndexIVF::AscendIndexIVF(int dims, faiss::MetricType metric, int nlist, AscendIndexIVFConfig config)
@@ -813,31 +755,14 @@ void AscendIndexIVFPQ::train(idx_t n, const float* x) {
                            "training needs at least max(msubs * 256, nlist) = %d vectors",
                            std::max(im.msubs * 256, im.nlist));
     if (is_trained) return;
-    const int dev = im.devices[0], dsub = d / im.msubs;
-    im.centroids = kmeans(dev, d, n, x, im.nlist, 10, 1234);
-    // PQ codebooks on (at most 65536) training vectors, residuals when the index encodes residuals
-    const idx_t ns = std::min<idx_t>(n, 65536);
-    std::vector<float> tr(x, x + ns * d);
-    if (im.by_residual) {
-        b200idx_t* h = nullptr;
-        if (b200idx_create_flat(d, B200IDX_METRIC_L2, B200IDX_F32, dev, &h) != B200IDX_OK)
-            FAISS_THROW_FMT("train: %s", b200idx_last_error(nullptr));
-        std::vector<float> dist(static_cast<size_t>(ns));
-        std::vector<idx_t> as(static_cast<size_t>(ns));
-        int code = b200idx_add(h, im.nlist, im.centroids.data(), nullptr);
-        if (code == B200IDX_OK) code = b200idx_search(h, ns, tr.data(), 1, dist.data(), as.data());
-        b200idx_destroy(h);
-        FAISS_THROW_IF_NOT_MSG(code == B200IDX_OK, "train: residual assignment failed");
-        for (idx_t i = 0; i < ns; ++i)
-            for (int t = 0; t < d; ++t) tr[i * d + t] -= im.centroids[static_cast<size_t>(as[static_cast<size_t>(i)]) * d + t];
-    }
-    im.codebooks.assign(static_cast<size_t>(im.msubs) * 256 * dsub, 0.f);
-    std::vector<float> sub(static_cast<size_t>(ns) * dsub);
-    for (int m = 0; m < im.msubs; ++m) {
-        for (idx_t i = 0; i < ns; ++i) std::memcpy(&sub[i * dsub], &tr[i * d + m * dsub], sizeof(float) * dsub);
-        std::vector<float> cb = kmeans(dev, dsub, ns, sub.data(), 256, 10, 4321u + m);
-        std::memcpy(&im.codebooks[static_cast<size_t>(m) * 256 * dsub], cb.data(), sizeof(float) * 256 * dsub);
-    }
+    // Lloyd k-means for the coarse centroids and for each sub-space codebook runs on the first
+    // device (10 iterations, fixed seed); the other devices receive the trained state.
+    b200idx_t* h0 = im.handles[0];
+    im.rc(b200idx_ivfpq_train(h0, n, x, 10, 1234), h0, "train");
+    im.centroids.resize(static_cast<size_t>(im.nlist) * d);
+    im.codebooks.resize(static_cast<size_t>(d) * 256);
+    im.rc(b200idx_ivfpq_get_centroids(h0, im.centroids.data()), h0, "get_centroids");
+    im.rc(b200idx_ivfpq_get_codebooks(h0, im.codebooks.data()), h0, "get_codebooks");
     push_trained_state(im);
     is_trained = true;
 }

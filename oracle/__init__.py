@@ -154,6 +154,18 @@ def ivfpq_search(centroids, codebooks, by_residual, list_offsets, codes, ids, xq
     return (D, I, coarse) if return_coarse else (D, I)
 
 
+def kmeans(x, k, niter, seed=0):
+    """Lloyd k-means in the trainer's canonical arithmetic (see orc_kmeans)."""
+    x = _f32(x)
+    n, d = x.shape
+    out = np.empty((k, d), np.float32)
+    rc = lib().orc_kmeans(C.c_int(d), C.c_int64(n), _p(x, C.c_float), C.c_int(k), C.c_int(niter),
+                          C.c_uint64(seed), _p(out, C.c_float))
+    if rc:
+        raise RuntimeError(f"orc_kmeans rc={rc}")
+    return out
+
+
 def merge_topk(Din, Iin, descending=False):
     """Din/Iin: [nsrc, nq, k] -> merged [nq, k]."""
     Din = np.ascontiguousarray(Din, dtype=np.float32)

@@ -466,3 +466,41 @@ int orc_num_threads(void) {
     return 1;
 #endif
 }
+
+/*
+ * Lloyd k-means in the arithmetic the GPU trainer reproduces bit for bit (the reference trains on
+ * the NPU with the same structure -- distance operator, arg-min, centroid update --
+ * feature_retrieval/src/ascendfaiss/ascenddaemon/impl/IndexIVFPQ.cpp:810-1135; its random choices
+ * are not pinned, so this is a restatement of the algorithm, not of its bits):
+ *   start   : centroid c = x[(floor(c * n / k) + seed) mod n]
+ *   assign  : nearest centroid under the canonical fp32 L2 distance, ties -> lower centroid
+ *   update  : mean of the members, summed in fp64 in increasing vector index, rounded to fp32 once;
+ *             a centroid without members keeps its value
+ */
+int orc_kmeans(int d, int64_t n, const float* x, int k, int niter, uint64_t seed, float* cent) {
+    if (d <= 0 || n <= 0 || k <= 0 || niter < 0) return -1;
+    for (int c = 0; c < k; ++c) {
+        int64_t src = (int64_t)(((__int128)c * n) / k);
+        src = (int64_t)(((uint64_t)src + seed) % (uint64_t)n);
+        memcpy(cent + (int64_t)c * d, x + src * d, sizeof(float) * (size_t)d);
+    }
+    int32_t* assign = (int32_t*)malloc(sizeof(int32_t) * (size_t)n);
+    double* sum = (double*)malloc(sizeof(double) * (size_t)k * d);
+    int64_t* cnt = (int64_t*)malloc(sizeof(int64_t) * (size_t)k);
+    if (!assign || !sum || !cnt) { free(assign); free(sum); free(cnt); return -2; }
+    for (int it = 0; it < niter; ++it) {
+        orc_ivf_assign(d, k, cent, n, x, assign);
+        memset(sum, 0, sizeof(double) * (size_t)k * d);
+        memset(cnt, 0, sizeof(int64_t) * (size_t)k);
+        for (int64_t i = 0; i < n; ++i) {          /* increasing vector index: the summation order */
+            const int32_t c = assign[i];
+            cnt[c] += 1;
+            for (int t = 0; t < d; ++t) sum[(int64_t)c * d + t] += (double)x[i * d + t];
+        }
+        for (int c = 0; c < k; ++c)
+            if (cnt[c] > 0)
+                for (int t = 0; t < d; ++t) cent[(int64_t)c * d + t] = (float)(sum[(int64_t)c * d + t] / (double)cnt[c]);
+    }
+    free(assign); free(sum); free(cnt);
+    return 0;
+}

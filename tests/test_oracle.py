@@ -145,3 +145,19 @@ def test_rounding_helpers():
     b = oracle.round_bf16(y)
     assert b[0] == 1.0 and b[1] == 1.0 + 2 ** -7 or b[1] == 1.0  # ties to even
     assert np.all((b.view(np.uint32) & 0xFFFF) == 0)
+
+
+def test_kmeans_restatement_properties():
+    """orc_kmeans: deterministic, start points as documented, every iteration lowers the objective."""
+    x, _ = datasets.mixture(3000, 16, 8, seed=3)
+    c0 = oracle.kmeans(x, 10, 0, seed=5)
+    n = x.shape[0]
+    np.testing.assert_array_equal(c0, x[[(c * n // 10 + 5) % n for c in range(10)]])
+    prev = None
+    for it in (1, 2, 4, 8):
+        c = oracle.kmeans(x, 10, it, seed=5)
+        a = oracle.ivf_assign(c, x)
+        obj = float(((x - c[a]) ** 2).sum())
+        assert prev is None or obj <= prev * (1 + 1e-6)
+        prev = obj
+    np.testing.assert_array_equal(oracle.kmeans(x, 10, 4, seed=5), oracle.kmeans(x, 10, 4, seed=5))
