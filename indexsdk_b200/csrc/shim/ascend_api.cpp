@@ -446,8 +446,15 @@ void AscendIndexFlat::search_with_masks(idx_t n, const float* x, idx_t k, float*
     AscendIndex::impl_->rc(b200idx_search_with_masks(h, n, x, static_cast<int>(k), static_cast<const uint8_t*>(mask),
                                                      distances, labels), h, "search_with_masks");
 }
-void AscendIndexFlat::search_with_masks(idx_t, const uint16_t*, idx_t, float*, idx_t*, const void*) const {
-    FAISS_THROW_MSG("search_with_masks is not implemented in the B200 build yet");
+// fp16 queries: widened on the host (exact), then the float entry point; an fp16-storage index
+// rounds them back to the same bits.
+void AscendIndexFlat::search_with_masks(idx_t n, const uint16_t* x, idx_t k, float* distances, idx_t* labels,
+                                        const void* mask) const {
+    FAISS_THROW_IF_NOT_MSG(x != nullptr, "x cannot be nullptr.");
+    FAISS_THROW_IF_NOT_FMT((n > 0) && (n < MAX_N), "n must be > 0 and < %ld", static_cast<long>(MAX_N));
+    std::vector<float> xf(static_cast<size_t>(n) * d);
+    for (size_t i = 0; i < xf.size(); ++i) xf[i] = half_bits_to_float(x[i]);
+    search_with_masks(n, xf.data(), k, distances, labels, mask);
 }
 
 AscendIndexFlatL2::AscendIndexFlatL2(faiss::IndexFlatL2* index, AscendIndexFlatConfig config)

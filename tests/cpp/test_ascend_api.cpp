@@ -163,6 +163,33 @@ static void test_flat_gpu() {
         ix.search(static_cast<idx_t>(nq), xq.data(), k, D.data(), I.data());
         ix2.search(static_cast<idx_t>(nq), xq.data(), k, D2.data(), I2.data());
         CHECK(I == I2 && D == D2);
+        // search_with_masks: only rows whose bit is set may appear (every third row kept); the
+        // fp16-query overload answers like the float one on fp16-rounded queries
+        {
+            const size_t mrow = (nb + 7) / 8;
+            std::vector<uint8_t> mask(nq * mrow, 0);
+            for (size_t q = 0; q < nq; ++q)
+                for (size_t i = q % 3; i < nb; i += 3) mask[q * mrow + i / 8] |= static_cast<uint8_t>(1u << (i % 8));
+            std::vector<float> Dm(nq * k), Dh(nq * k);
+            std::vector<idx_t> Im(nq * k), Ih(nq * k);
+            ix.search_with_masks(static_cast<idx_t>(nq), xq.data(), k, Dm.data(), Im.data(), mask.data());
+            bool kept_only = true, sorted = true;
+            for (size_t q = 0; q < nq; ++q)
+                for (int j = 0; j < k; ++j) {
+                    kept_only = kept_only && Im[q * k + j] >= 0 && static_cast<size_t>(Im[q * k + j]) % 3 == q % 3;
+                    if (j) sorted = sorted && (metric == METRIC_L2 ? Dm[q * k + j - 1] <= Dm[q * k + j]
+                                                                 : Dm[q * k + j - 1] >= Dm[q * k + j]);
+                }
+            CHECK(kept_only && sorted);
+            std::vector<uint16_t> xh(nq * d);
+            for (size_t i = 0; i < xh.size(); ++i) {
+                const _Float16 hv = static_cast<_Float16>(xq[i]);
+                std::memcpy(&xh[i], &hv, 2);
+            }
+            ix.search_with_masks(static_cast<idx_t>(nq), xh.data(), k, Dh.data(), Ih.data(), mask.data());
+            CHECK(Ih == Im && Dh == Dm);
+            CHECK(throws_with([&] { ix.search_with_masks(1, xq.data(), k, Dm.data(), Im.data(), nullptr); }, "mask can not be nullptr."));
+        }
         // remove + reset
         IDSelectorRange sel(0, 100);
         CHECK(ix.remove_ids(sel) == 100 && ix.ntotal == static_cast<idx_t>(nb - 100));
