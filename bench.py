@@ -59,28 +59,97 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock/throttle sampling during the timed region (reads only)."""
+    """SM clock / throttle-reason sampling while the steps run (reads only, nothing is set).
+
+    A thread polls NVML every 2 ms (the timed regions last tens of milliseconds, too short for an
+    external nvidia-smi loop to see) and stamps each sample with time.perf_counter(); `mark()`
+    brackets the timed regions, and the summary prefers the samples inside them.  The steps are
+    repeated untimed for a short hold phase afterwards so that the driver's own clock counters,
+    which refresh more slowly than the poll, are read at least a few times under the same load.
+    Without NVML the nvidia-smi loop is the fallback."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index: int, uuid: str | None = None):
         self.gpu = gpu_index
+        self.uuid = uuid
         self.proc = None
         self.path = None
+        self.thread = None
+        self.samples = []          # (t, sm_mhz, power_w, reasons bitmask)
+        self.windows = []          # [(t0, t1)] timed regions
+        self.smax = None
+        self._stop = False
+        self.source = None
+
+    def _nvml_loop(self, nv, h):
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self._stop:
+            try:
+                sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                pw = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+                rs = int(get_reasons(h))
+                self.samples.append((time.perf_counter(), float(sm), pw, rs))
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def start(self):
+        try:
+            import threading
+            import pynvml as nv
+            nv.nvmlInit()
+            h = None
+            if self.uuid:
+                try:
+                    h = nv.nvmlDeviceGetHandleByUUID(self.uuid if self.uuid.startswith("GPU-") else "GPU-" + self.uuid)
+                except Exception:
+                    h = None
+            if h is None:
+                h = nv.nvmlDeviceGetHandleByIndex(self.gpu)
+            self.smax = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            self._nv = nv
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, h), daemon=True)
+            self.thread.start()
+            self.source = "nvml, 2 ms poll"
+            return
+        except Exception:
+            self.thread = None
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
                  "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+            self.source = "nvidia-smi -lms 100"
         except Exception:
             self.proc = None
 
+    def mark(self, t0, t1):
+        self.windows.append((t0, t1))
+
+    def _summarise(self, sm, power, masks, smax, where):
+        names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+                 0x80: "hw_power_brake_slowdown"}
+        reasons = sorted({n for m in masks for bit, n in names.items() if m & bit})
+        busy = [c for c, pw in zip(sm, power) if pw >= 0.6 * max(power)] or sm
+        return {"sm_mhz": float(np.median(busy)), "sm_max_mhz": smax, "reasons": reasons, "samples": len(sm),
+                "power_w_max": max(power), "source": self.source, "window": where}
+
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.thread is not None:
+            self._stop = True
+            self.thread.join(timeout=2)
+            inside = [x for x in self.samples if any(t0 <= x[0] <= t1 for t0, t1 in self.windows)]
+            use, where = (inside, "timed regions") if len(inside) >= 3 else \
+                (self.samples, "warm-up, timed regions and the untimed hold phase of identical steps")
+            if use:
+                out = self._summarise([x[1] for x in use], [x[2] for x in use], [x[3] for x in use], self.smax, where)
+                out["samples_in_timed_regions"] = len(inside)
+            return out
         if self.proc is None:
             return out
         self.proc.terminate()
@@ -88,7 +157,7 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, reasons, smax, power = [], set(), None, []
+        sm, masks, smax, power = [], [], None, []
         try:
             for line in open(self.path):
                 f = [t.strip() for t in line.split(",")]
@@ -100,19 +169,18 @@ class ClockSampler:
                     power.append(float(f[3]))
                 except ValueError:
                     continue
-                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
-                                   f[5:9]):
+                m = 0
+                for bit, v in zip((0x8, 0x40, 0x20, 0x4), f[5:9]):
                     if v.lower().startswith("active"):
-                        reasons.add(name)
+                        m |= bit
+                masks.append(m)
         finally:
             try:
                 os.unlink(self.path)
             except OSError:
                 pass
         if sm:
-            busy = [c for c, p in zip(sm, power) if p >= 0.6 * max(power)] or sm
-            out.update(sm_mhz=float(np.median(busy)), sm_max_mhz=smax, reasons=sorted(reasons), samples=len(sm),
-                       power_w_max=max(power))
+            out = self._summarise(sm, power, masks, smax, "whole run of the sampler")
         return out
 
 
@@ -633,7 +701,9 @@ def main():
         e1.record(lib_stream)
         e1.synchronize()
         torch.cuda.synchronize(dev)
-        wall = time.perf_counter() - t0
+        t1 = time.perf_counter()
+        wall = t1 - t0
+        sampler.mark(t0, t1)
         dev_ms = e0.elapsed_time(e1)
         # the library stream is idle between the host-side stages of a step; wall clock covers
         # the NCCL / copy work issued on torch's stream.  Take the larger of the two.
@@ -643,18 +713,27 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()) / steps, wall * 1e3 / steps
 
+    try:
+        gpu_uuid = str(torch.cuda.get_device_properties(dev).uuid)
+    except Exception:
+        gpu_uuid = None
+    sampler = ClockSampler(local_rank, gpu_uuid)
+    if rank == 0:
+        sampler.start()
     for _ in range(args.warmup):
         step_device()
         step_e2e()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     wl.index.set_timing(True)
     s0 = wl.index.stats()
     ms_dev, wall_dev = timed(step_device, args.steps)
     s1 = wl.index.stats()
     wl.index.set_timing(False)
     ms_e2e, wall_e2e = timed(step_e2e, args.steps)
+    # hold phase: the same steps, untimed, for about half a second, so that the clock counters are
+    # read several times under the load that was just timed (same count on every rank)
+    for _ in range(min(2000, max(1, int(500.0 / max(ms_dev, 1e-3))))):
+        step_device()
+    barrier()
     clocks = sampler.stop() if rank == 0 else None
     s2 = wl.index.stats()
 
