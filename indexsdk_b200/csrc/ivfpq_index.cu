@@ -37,11 +37,13 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <cub/cub.cuh>
 #include <unordered_set>
 
+#include "ivfpq_tc_scan.cuh"
 #include "kmeans.h"
 #include "select.cuh"
 
@@ -300,6 +302,9 @@ struct ScanArgs {
     const int32_t* qlist;    // exact scan: indices of the queries to process
     unsigned long long* scanned;
     unsigned int* work;      // persistent scan: next query to hand out (zeroed before the launch)
+    // > 0: fd / fth come from the tensor-core filter, which already subtracted the error bound of
+    // its fp16 product from every value; only fp32 rounding slack remains (twice the table scan's)
+    float tc_rel, tc_abs;
 };
 
 // ---------------------------------------------------------------------------------------
@@ -922,6 +927,7 @@ ivfpq_refine_kernel(const ScanArgs a, int P) {
                 const float coarse_max = a.cD[q * a.nprobe + a.nprobe - 1];
                 const float bound = fabsf(coarse_max) + a.t2_bound + 2.f * sqrtf(s_qn2) * a.cb_bound + fabsf(a_min);
                 eps = a.err_rel * bound;
+                if (a.tc_rel > 0.f) eps = 2.f * eps;   // the kept values are lower bounds already (see ivfpq_tc_scan.cu)
             }
             const int kk = a.k <= P ? a.k : P;
             const bool have_k = sl[kk - 1] != kNoLabel;
@@ -1001,6 +1007,7 @@ ivfpq_refine_warp_kernel(const ScanArgs a) {
                 const float coarse_max = a.cD[q * a.nprobe + a.nprobe - 1];
                 const float bound = fabsf(coarse_max) + a.t2_bound + 2.f * sqrtf(qn2) * a.cb_bound + fabsf(a_min);
                 eps = a.err_rel * bound;
+                if (a.tc_rel > 0.f) eps = 2.f * eps;   // the kept values are lower bounds already (see ivfpq_tc_scan.cu)
             }
             if (lk == kNoLabel || !(dk < a_min - eps)) bad = 1;
         }
@@ -1227,6 +1234,8 @@ IvfpqIndex::IvfpqIndex(int d, int nlist, int M, int nbits, bool by_residual, int
     force_exact_ = e && std::strcmp(e, "1") == 0;
     const char* np = std::getenv("B200IDX_IVFPQ_NO_PERSIST");   // development aid: always the per-query CTAs
     no_persist_ = np && std::strcmp(np, "1") == 0;
+    const char* tc = std::getenv("B200IDX_IVFPQ_TC");
+    tc_scan_ = tc && std::strcmp(tc, "1") == 0;
     w_work_.ensure(sizeof(unsigned int));
 }
 
@@ -1264,6 +1273,15 @@ void IvfpqIndex::set_codebooks(const float* cb) {
         acc += mx;
     }
     cb_norm_bound_ = static_cast<float>(std::sqrt(acc) * 1.0001);
+    {   // fp16 copy for the tensor-core scan; usable while every entry stays inside the fp16 range
+        float amax = 0.f;
+        const size_t ne = static_cast<size_t>(M_) * kKsub * dsub_;
+        for (size_t i = 0; i < ne; ++i) amax = std::max(amax, std::fabs(cb[i]));
+        tc_cb_ok_ = amax < 3.0e4f;
+        cb16_.ensure(ne * 2);
+        B200_CUDA_CHECK(launch_tc_cb16(codebooks_.as<float>(), static_cast<int64_t>(ne), cb16_.as<uint16_t>(), stream()));
+        B200_CUDA_CHECK(cudaStreamSynchronize(stream()));
+    }
     if (rotated_) {
         // [M / 16][256][16][dsub]: the 16 codewords (one per sub-quantizer of a group) that share a
         // code value lie together, the order in which the scan kernel builds its table
@@ -1650,8 +1668,88 @@ void IvfpqIndex::search_stages(int64_t nq, const float* xq, int k, float* D, int
         a.cb_bound = cb_norm_bound_;
         const float cmax = coarse_->raw_view().max_norm;
         a.t2_bound = cb_norm_bound_ * cb_norm_bound_ + 2.f * cmax * cb_norm_bound_;
+        // very large batches of residual codes: every probed list is decoded once and multiplied with
+        // all of its queries on the tensor cores (ivfpq_tc_scan.cu)
+        const bool tc = persist && tc_scan_ && tc_cb_ok_ && by_residual_ && d_ == kTcDim && M_ == kTcM && kpt == 1 &&
+                        nprobe >= 16 && m * nprobe < (1LL << 30);
+        unsigned int* tc_err = nullptr;
         timer_.begin(kStageScan, st);
-        if (persist) {
+        if (tc) {
+            const int64_t npairs = m * nprobe;
+            int32_t* keys = static_cast<int32_t*>(w_tc_keys_.ensure(static_cast<size_t>(npairs) * 4));
+            int32_t* vals = static_cast<int32_t*>(w_tc_vals_.ensure(static_cast<size_t>(npairs) * 4));
+            int32_t* keys2 = static_cast<int32_t*>(w_tc_keys2_.ensure(static_cast<size_t>(npairs) * 4));
+            int32_t* vals2 = static_cast<int32_t*>(w_tc_vals2_.ensure(static_cast<size_t>(npairs) * 4));
+            int32_t* first = static_cast<int32_t*>(w_tc_first_.ensure(static_cast<size_t>(nlist_) * 4));
+            int32_t* last = static_cast<int32_t*>(w_tc_last_.ensure(static_cast<size_t>(nlist_) * 4));
+            B200_CUDA_CHECK(launch_tc_keys(cI, npairs, nlist_, keys, vals, st));
+            int end_bit = 1;
+            while ((1 << end_bit) <= nlist_) ++end_bit;
+            size_t sort_bytes = 0;
+            B200_CUDA_CHECK(cub::DeviceRadixSort::SortPairs(nullptr, sort_bytes, keys, keys2, vals, vals2,
+                                                            static_cast<int>(npairs), 0, end_bit, st));
+            void* sort_tmp = w_tc_sort_.ensure(sort_bytes);
+            B200_CUDA_CHECK(cub::DeviceRadixSort::SortPairs(sort_tmp, sort_bytes, keys, keys2, vals, vals2,
+                                                            static_cast<int>(npairs), 0, end_bit, st));
+            B200_CUDA_CHECK(launch_tc_bounds(keys2, npairs, nlist_, first, last, st));
+            float* tau = static_cast<float*>(w_tc_tau_.ensure(static_cast<size_t>(m) * 4));
+            TcScanArgs t{};
+            t.cb16 = cb16_.as<uint16_t>();
+            t.cbnorm = cbnorm_.as<float>();
+            t.xq = xp;
+            t.centroids = coarse_->rows_f32();
+            t.cD = cD;
+            t.nprobe = nprobe;
+            t.nlist = nlist_;
+            t.nq = m;
+            t.sorted_pair = vals2;
+            t.first = first;
+            t.last = last;
+            t.offsets = offsets_.as<int64_t>();
+            t.lens = lens_.as<int64_t>();
+            t.codes = codes_.as<uint8_t>();
+            t.tau = tau;
+            t.cap = 256;
+            t.cb_bound = a.cb_bound;
+            t.cand_d = static_cast<float*>(w_tc_cd_.ensure(static_cast<size_t>(m) * t.cap * 4));
+            t.cand_p = static_cast<uint32_t*>(w_tc_cp_.ensure(static_cast<size_t>(m) * t.cap * 4));
+            t.cand_n = static_cast<unsigned int*>(w_tc_cn_.ensure(static_cast<size_t>(m) * 4));
+            t.work = w_work_.as<unsigned int>();
+            t.scanned = a.scanned;
+            if (!w_tc_err_.get()) {
+                w_tc_err_.ensure(4);
+                B200_CUDA_CHECK(cudaMemsetAsync(w_tc_err_.get(), 0, 4, st));
+            }
+            t.err = tc_err = w_tc_err_.as<unsigned int>();
+            const char* pe = std::getenv("B200IDX_PROF");
+            const bool tc_prof = pe && std::strcmp(pe, "1") == 0;
+            if (tc_prof) {
+                w_tc_prof_.ensure(64 + static_cast<size_t>(m) * 4);
+                B200_CUDA_CHECK(cudaMemsetAsync(w_tc_prof_.get(), 0, 64, st));
+                t.prof = w_tc_prof_.as<unsigned long long>();
+            }
+            // threshold: one warp per query over the codes of its nearest list
+            B200_CUDA_CHECK(launch_tc_head_tau(t, cI, a.err_rel, a.t2_bound, tau, st));
+            B200_CUDA_CHECK(launch_tc_scan(t, num_sms_, st));
+            B200_CUDA_CHECK(launch_tc_select(t, a.fd, a.fp, a.fth, st));
+            if (tc_prof) {   // development aid: phase cycles of thread 0 (sum over CTAs), candidates per query
+                unsigned long long hp[8];
+                std::vector<unsigned int> cn(static_cast<size_t>(m));
+                B200_CUDA_CHECK(cudaMemcpyAsync(hp, t.prof, 64, cudaMemcpyDeviceToHost, st));
+                B200_CUDA_CHECK(cudaMemcpyAsync(cn.data(), t.cand_n, cn.size() * 4, cudaMemcpyDeviceToHost, st));
+                B200_CUDA_CHECK(cudaStreamSynchronize(st));
+                unsigned long long tot = 0, mx = 0;
+                for (unsigned int c : cn) { tot += c; mx = std::max<unsigned long long>(mx, c); }
+                std::fprintf(stderr, "[tc scan] per-CTA kcycles: ctx_wait %.0f decode %.0f barrier %.0f issue %.0f mma_wait %.0f "
+                             "epilogue %.0f release %.0f; tiles/CTA %.0f; candidates/query avg %.1f max %llu\n",
+                             hp[0] / 1e3 / num_sms_, hp[1] / 1e3 / num_sms_, hp[2] / 1e3 / num_sms_, hp[3] / 1e3 / num_sms_,
+                             hp[4] / 1e3 / num_sms_, hp[5] / 1e3 / num_sms_, hp[6] / 1e3 / num_sms_,
+                             static_cast<double>(hp[7]) / num_sms_, static_cast<double>(tot) / m, mx);
+            }
+            a.tc_rel = kTcErrRel;
+            a.tc_abs = kTcErrAbs;
+            stats_.kernel_launches += 7;
+        } else if (persist) {
             a.work = w_work_.as<unsigned int>();
             B200_CUDA_CHECK(launch_persist(a, kpt, num_sms_, st));
         } else {
@@ -1672,7 +1770,14 @@ void IvfpqIndex::search_stages(int64_t nq, const float* xq, int k, float* D, int
         stats_.kernel_launches += 3;
         uint8_t* hf = static_cast<uint8_t*>(h_flag_.ensure(static_cast<size_t>(m)));
         B200_CUDA_CHECK(cudaMemcpyAsync(hf, a.flag, static_cast<size_t>(m), cudaMemcpyDeviceToHost, st));
+        unsigned int tc_err_host = 0;
+        if (tc_err) B200_CUDA_CHECK(cudaMemcpyAsync(&tc_err_host, tc_err, 4, cudaMemcpyDeviceToHost, st));
         B200_CUDA_CHECK(cudaStreamSynchronize(st));
+        if (tc_err_host) {
+            cudaMemsetAsync(tc_err, 0, 4, st);
+            throw std::runtime_error("IVFPQ tensor-core scan reported error word " + std::to_string(tc_err_host) +
+                                     " (bounded wait ran out)");
+        }
         std::vector<int32_t> bad;
         for (int64_t i = 0; i < m; ++i)
             if (hf[i]) bad.push_back(static_cast<int32_t>(i));

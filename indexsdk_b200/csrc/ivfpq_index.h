@@ -81,6 +81,8 @@ private:
                        const int64_t* pre_cI);
     bool has_centroids_ = false, has_codebooks_ = false;
     bool no_persist_ = false;
+    bool tc_scan_ = false;                // list-major tensor-core filter scan (large batches, residual encoding)
+    bool tc_cb_ok_ = false;               // codebook entries inside the fp16 range
     int num_sms_ = 0;
     float cb_norm_bound_ = 0.f;           // sqrt(sum_m max_j |cb[m][j]|^2), for the filter's error bound
     bool force_exact_ = false;            // B200IDX_IVFPQ_EXACT=1: always use the exact scan kernels
@@ -89,6 +91,7 @@ private:
     DeviceBuffer codebooks_;              // [M][256][dsub] float
     DeviceBuffer codebooks_t_;            // the same regrouped [M / 16][256][16][dsub] (M % 16 == 0)
     DeviceBuffer cbnorm_;                 // [M][256] float: canonical squared norm of each codeword
+    DeviceBuffer cb16_;                   // [M][256][dsub] fp16 bits of the codebooks (tensor-core scan)
     DeviceBuffer offsets_;                // int64 [nlist + 1] first slot of every list (multiples of 32)
     DeviceBuffer lens_;                   // int64 [nlist + 1] vectors per list
     std::vector<int64_t> offsets_host_, lens_host_;
@@ -96,6 +99,8 @@ private:
     // scratch
     DeviceBuffer w_work_, w_cD_, w_cI_, w_fd_, w_fp_, w_fth_, w_flag_, w_qlist_, w_q_, w_D_, w_I_, w_assign_D_,
         w_assign_I_, w_list_, w_codes_, w_t2_, w_ids_, w_x_, w_tmp_;
+    DeviceBuffer w_tc_keys_, w_tc_vals_, w_tc_keys2_, w_tc_vals2_, w_tc_first_, w_tc_last_, w_tc_cI0_, w_tc_cD0_,
+        w_tc_fd0_, w_tc_fp0_, w_tc_fth0_, w_tc_tau_, w_tc_cd_, w_tc_cp_, w_tc_cn_, w_tc_sort_, w_tc_err_, w_tc_prof_;
     PinnedBuffer h_flag_;
     SearchStats stats_;
     StageTimer timer_;

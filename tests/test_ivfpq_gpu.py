@@ -206,3 +206,30 @@ def test_coarse_plus_preassigned_equals_search(b200, resid):
     off, cs, idl = _oracle_lists(xb, ids, cent, cb, resid)[2]
     _, _, coarse = oracle.ivfpq_search(cent, cb, resid, off, cs, idl, xq, nprobe, k, return_coarse=True)
     np.testing.assert_array_equal(cI.cpu().numpy(), coarse.astype(np.int64))
+
+
+@pytest.mark.parametrize("nlist,n,nq,nprobe,k", [
+    (64, 20000, 1500, 24, 10),       # ~560 queries per list: several query chunks per list
+    (256, 60000, 1300, 16, 16),      # shorter lists, tails of the 128-code tiles
+    (1024, 50000, 2000, 64, 1),      # few queries per list, lists shorter than one tile
+])
+def test_tensor_core_scan_vs_oracle(b200, monkeypatch, nlist, n, nq, nprobe, k):
+    """B200IDX_IVFPQ_TC=1: large batches on a residual-encoded d = 128, M = 16 index take the
+    list-major tensor-core filter (decode once per list, fp16 two-term product, threshold from a
+    table scan of the nearest lists).  Results must stay bit-identical to the oracle, and only a
+    small part of the queries may need the exact re-scan."""
+    monkeypatch.setenv("B200IDX_IVFPQ_TC", "1")
+    d, M = 128, 16
+    xb, _ = datasets.mixture(n, d, max(nlist // 2, 4), seed=14)
+    xq, _ = datasets.mixture(nq, d, max(nlist // 2, 4), seed=15, centers_seed=14)
+    ids = (np.arange(n, dtype=np.int64) * 3 + 7)
+    cent, cb = datasets.train_ivfpq(xb[:8000], nlist, M, True, niter=4)
+    ix = _build(b200, xb, ids, cent, cb, True, 2)
+    ln, codes, (off, cs, idl) = _oracle_lists(xb, ids, cent, cb, True)
+    ix.nprobe = nprobe
+    D, I = ix.search(xq, k)
+    Dr, Ir = oracle.ivfpq_search(cent, cb, True, off, cs, idl, xq, nprobe, k)
+    assert_exact(D, I, Dr, Ir)
+    st = ix.stats()
+    assert st["fallback_queries"] <= nq // 10
+    assert st["scan_codes"] > 0
