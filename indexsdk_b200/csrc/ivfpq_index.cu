@@ -721,15 +721,19 @@ ivfpq_scan_persist_kernel(const ScanArgs a) {
                       (static_cast<uint32_t>(half) * 128u + 4u * (((s + lane) & 15) + (lane & 16)));
 
     unsigned long long visited = 0;
+    // the slot's next query is drawn from the global counter one query ahead, so that the round
+    // trip of the atomic hides behind the scan
+    if (tid_s == 0) {
+        s_q[slot] = atomicAdd(a.work, 1u);
+        s_gth[slot] = 0x7f800000;
+        s_next[slot] = 0;
+    }
     for (;;) {
-        if (tid_s == 0) {
-            s_q[slot] = atomicAdd(a.work, 1u);
-            s_gth[slot] = 0x7f800000;
-            s_next[slot] = 0;
-        }
         slot_barrier(slot);
         const int64_t q = s_q[slot];
         if (q >= a.nq) break;
+        unsigned int q_next = 0;
+        if (tid_s == 0) q_next = atomicAdd(a.work, 1u);
         // the probes' metadata: loads issued here, stored to shared memory after the table is built
         uint32_t m_begin[(kPsMaxProbe + kPsSlotThreads - 1) / kPsSlotThreads] = {0, 0};
         uint32_t m_end[(kPsMaxProbe + kPsSlotThreads - 1) / kPsSlotThreads] = {0, 0};
@@ -779,20 +783,55 @@ ivfpq_scan_persist_kernel(const ScanArgs a) {
             sd[tid_s * KPT + s] = dk[s];
             sp[tid_s * KPT + s] = pk[s];
         }
-        for (int i = kPsSlotThreads * KPT + tid_s; i < E; i += kPsSlotThreads) {
-            sd[i] = __int_as_float(0x7f800000);
-            sp[i] = kNoPos;
+        // Every warp's segment [wslot * KP, +KP) is sorted; positions are unique, so the rank of an
+        // entry in the merged order is its index in its own segment plus, for every other segment,
+        // the number of entries below it (binary search).  Ranks below KP are scattered into the
+        // output area behind the segments.
+        float* so_d = sd + kPsSlotThreads * KPT;
+        uint32_t* so_p = sp + kPsSlotThreads * KPT;
+        for (int i = tid_s; i < KP; i += kPsSlotThreads) {
+            so_d[i] = __int_as_float(0x7f800000);
+            so_p[i] = kNoPos;
         }
         slot_barrier(slot);
-        slot_sort_pairs(sd, sp, E, tid_s, slot);
+#pragma unroll
+        for (int s = 0; s < KPT; ++s) {
+            const float md = dk[s];
+            const uint32_t mp = pk[s];
+            if (mp == kNoPos) continue;
+            int rank = lane * KPT + s;
+            for (int w = 0; w < kPsWarpsPerSlot; ++w) {
+                if (w == wslot) continue;
+                const float* wd = sd + w * KP;
+                const uint32_t* wp = sp + w * KP;
+                int lo = 0, hi = KP;                  // first index whose entry is not below (md, mp)
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if (pair_less<uint32_t>(wd[mid], wp[mid], md, mp)) lo = mid + 1;
+                    else hi = mid;
+                }
+                rank += lo;
+            }
+            if (rank < KP) {
+                so_d[rank] = md;
+                so_p[rank] = mp;
+            }
+        }
+        slot_barrier(slot);
         float* od = a.fd + q * KP;
         uint32_t* op = a.fp + q * KP;
         for (int i = tid_s; i < KP; i += kPsSlotThreads) {
-            od[i] = sd[i];
-            op[i] = sp[i];
+            od[i] = so_d[i];
+            op[i] = so_p[i];
         }
-        if (tid_s == 0) a.fth[q] = sp[KP - 1] != kNoPos ? sd[KP - 1] : __int_as_float(0x7f800000);
-        slot_barrier(slot);   // the buffers and s_q are reused by the next query
+        if (tid_s == 0) {
+            a.fth[q] = so_p[KP - 1] != kNoPos ? so_d[KP - 1] : __int_as_float(0x7f800000);
+            s_q[slot] = q_next;
+            s_gth[slot] = 0x7f800000;
+            s_next[slot] = 0;
+        }
+        // the barrier at the top of the loop orders these writes (and the merge buffers) before the
+        // next query
     }
     if (a.scanned && visited) atomicAdd(a.scanned, visited);
 }
