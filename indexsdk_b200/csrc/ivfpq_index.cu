@@ -666,26 +666,6 @@ __device__ __forceinline__ void slot_barrier(int slot) {
     asm volatile("bar.sync %0, %1;" ::"r"(slot + 1), "n"(kPsSlotThreads) : "memory");
 }
 
-// Bitonic sort of E pairs by the kPsSlotThreads threads of one slot.
-__device__ __forceinline__ void slot_sort_pairs(float* sd, uint32_t* sl, int E, int tid_s, int slot) {
-    for (int size = 2; size <= E; size <<= 1) {
-        for (int stride = size >> 1; stride > 0; stride >>= 1) {
-            for (int i = tid_s; i < E / 2; i += kPsSlotThreads) {
-                const int lo = 2 * i - (i & (stride - 1));
-                const int hi = lo + stride;
-                const bool up = (lo & size) == 0;
-                const float d1 = sd[lo], d2 = sd[hi];
-                const uint32_t l1 = sl[lo], l2 = sl[hi];
-                if (pair_less<uint32_t>(d2, l2, d1, l1) == up) {
-                    sd[lo] = d2; sd[hi] = d1;
-                    sl[lo] = l2; sl[hi] = l1;
-                }
-            }
-            slot_barrier(slot);
-        }
-    }
-}
-
 template <int KPT>
 __global__ void __launch_bounds__(kPsThreads, 1)
 ivfpq_scan_persist_kernel(const ScanArgs a) {
