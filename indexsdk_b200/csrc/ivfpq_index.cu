@@ -1733,6 +1733,9 @@ void IvfpqIndex::search_stages(int64_t nq, const float* xq, int k, float* D, int
             t.cand_d = static_cast<float*>(w_tc_cd_.ensure(static_cast<size_t>(m) * t.cap * 4));
             t.cand_p = static_cast<uint32_t*>(w_tc_cp_.ensure(static_cast<size_t>(m) * t.cap * 4));
             t.cand_n = static_cast<unsigned int*>(w_tc_cn_.ensure(static_cast<size_t>(m) * 4));
+            t.stage_cap = kTcStageCap;
+            t.stage = static_cast<uint4*>(w_tc_stage_.ensure(static_cast<size_t>(num_sms_) * kTcStageCap * 16));
+            t.stage_n = static_cast<unsigned int*>(w_tc_stage_n_.ensure(static_cast<size_t>(num_sms_) * 4));
             t.work = w_work_.as<unsigned int>();
             t.scanned = a.scanned;
             if (!w_tc_err_.get()) {
@@ -1767,7 +1770,7 @@ void IvfpqIndex::search_stages(int64_t nq, const float* xq, int k, float* D, int
             }
             a.tc_rel = kTcErrRel;
             a.tc_abs = kTcErrAbs;
-            stats_.kernel_launches += 7;
+            stats_.kernel_launches += 8;
         } else if (persist) {
             a.work = w_work_.as<unsigned int>();
             B200_CUDA_CHECK(launch_persist(a, kpt, num_sms_, st));
@@ -1792,8 +1795,10 @@ void IvfpqIndex::search_stages(int64_t nq, const float* xq, int k, float* D, int
         unsigned int tc_err_host = 0;
         if (tc_err) B200_CUDA_CHECK(cudaMemcpyAsync(&tc_err_host, tc_err, 4, cudaMemcpyDeviceToHost, st));
         B200_CUDA_CHECK(cudaStreamSynchronize(st));
-        if (tc_err_host) {
-            cudaMemsetAsync(tc_err, 0, 4, st);
+        if (tc_err_host) cudaMemsetAsync(tc_err, 0, 4, st);
+        if (tc_err_host & 2u)                       // a staging area overflowed: candidates were lost,
+            std::memset(hf, 1, static_cast<size_t>(m));   // every query of the page takes the exact path
+        if (tc_err_host & 1u) {
             throw std::runtime_error("IVFPQ tensor-core scan reported error word " + std::to_string(tc_err_host) +
                                      " (bounded wait ran out)");
         }

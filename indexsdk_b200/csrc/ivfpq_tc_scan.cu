@@ -387,6 +387,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) ivfpq_tc_scan_kernel(const TcSc
     __shared__ TcCtx ctx[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
+    __shared__ unsigned int s_stage_n;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     for (int i = tid; i < kCbBytes / 16; i += kTcThreads)
@@ -401,6 +402,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) ivfpq_tc_scan_kernel(const TcSc
             ptx::mbar_init(&a_full[i], 1);
         }
         abort_flag = 0;
+        s_stage_n = 0;
         ptx::mbar_fence_init();
     }
     if (warp == 1) {
@@ -494,12 +496,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) ivfpq_tc_scan_kernel(const TcSc
                         const int col = b * 32 + j;
                         const float v = fmaf(-2.f, __uint_as_float(acc[j]), rn);
                         if (v <= s_u[col]) {
-                            const int64_t q = s_q[col];
-                            const unsigned int sl = atomicAdd(a.cand_n + q, 1u);
-                            if (sl < static_cast<unsigned int>(a.cap)) {
-                                a.cand_d[q * a.cap + sl] = s_cd[col] + v;
-                                a.cand_p[q * a.cap + sl] = pos;
-                            }
+                            // staged per CTA (shared-memory counter, one 16-byte store): the per-query
+                            // slots are handed out later by tc_scatter_kernel, where the round trip of
+                            // a global atomic does not stall an epilogue warp
+                            const unsigned int sl = atomicAdd(&s_stage_n, 1u);
+                            if (sl < static_cast<unsigned int>(a.stage_cap))
+                                a.stage[static_cast<size_t>(blockIdx.x) * a.stage_cap + sl] =
+                                    make_uint4(static_cast<uint32_t>(s_q[col]), pos, __float_as_uint(s_cd[col] + v), 0u);
                         }
                     }
                 }
@@ -630,7 +633,29 @@ __global__ void __launch_bounds__(kTcThreads, 1) ivfpq_tc_scan_kernel(const TcSc
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, kTcTmemCols);
     }
-    if (tid == 0 && abort_flag) atomicOr(a.err, 1u);
+    if (tid == 0) {
+        a.stage_n[blockIdx.x] = s_stage_n;
+        if (abort_flag) atomicOr(a.err, 1u);
+    }
+}
+
+// Moves the staged candidates of CTA blockIdx.x into the per-query arrays.
+__global__ void tc_scatter_kernel(const TcScanArgs a) {
+    const unsigned int n_all = a.stage_n[blockIdx.x];
+    if (n_all > static_cast<unsigned int>(a.stage_cap)) {
+        if (threadIdx.x == 0) atomicOr(a.err, 2u);
+        return;
+    }
+    const uint4* st = a.stage + static_cast<size_t>(blockIdx.x) * a.stage_cap;
+    for (unsigned int i = threadIdx.x; i < n_all; i += blockDim.x) {
+        const uint4 e = st[i];
+        const int64_t q = e.x;
+        const unsigned int sl = atomicAdd(a.cand_n + q, 1u);
+        if (sl < static_cast<unsigned int>(a.cap)) {
+            a.cand_d[q * a.cap + sl] = __uint_as_float(e.z);
+            a.cand_p[q * a.cap + sl] = e.y;
+        }
+    }
 }
 
 }  // namespace
@@ -672,6 +697,9 @@ cudaError_t launch_tc_scan(const TcScanArgs& a, int num_sms, cudaStream_t st) {
     e = cudaFuncSetAttribute(ivfpq_tc_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes);
     if (e != cudaSuccess) return e;
     ivfpq_tc_scan_kernel<<<num_sms, kTcThreads, kTcSmemBytes, st>>>(a);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    tc_scatter_kernel<<<num_sms, 512, 0, st>>>(a);
     return cudaGetLastError();
 }
 

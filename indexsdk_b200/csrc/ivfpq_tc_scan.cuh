@@ -29,6 +29,7 @@ constexpr int kTcMaxN = 64;          // queries per chunk (UMMA N, TMEM columns 
 constexpr int kTcMainThreads = 256;  // decode + epilogue warps (warp 0 lane 0 issues the MMAs)
 constexpr int kTcThreads = kTcMainThreads + 96;   // + two warps that prepare the next (list, chunk) + the MMA warp
 constexpr int kTcKeep = 32;          // k' of the filter
+constexpr int kTcStageCap = 16384;   // candidates one CTA can stage per launch
 
 // Relative and absolute error of the fp16 two-term product against (q - c) . r in exact arithmetic:
 //   |err| <= kTcErrRel * |q - c| * |r| + kTcErrAbs * (|q - c| + |r|)
@@ -57,9 +58,12 @@ struct TcScanArgs {
     uint32_t* cand_p;            // [nq][cap] their slots
     unsigned int* cand_n;        // [nq] candidates found (may exceed cap: overflow)
     int cap;
+    uint4* stage;                // [CTAs][stage_cap] (query, slot, distance bits, -) as the epilogues find them
+    unsigned int* stage_n;       // [CTAs] entries each CTA produced (may exceed stage_cap: overflow)
+    int stage_cap;
     unsigned int* work;          // next list to hand out (zeroed before the launch)
     unsigned long long* scanned; // += (query, code) pairs visited
-    unsigned int* err;           // != 0: a bounded wait ran out
+    unsigned int* err;           // bit 0: a bounded wait ran out; bit 1: a CTA's staging area overflowed
     unsigned long long* prof;    // optional [8]: cycles of thread 0 per phase, summed over CTAs (development aid)
 };
 
