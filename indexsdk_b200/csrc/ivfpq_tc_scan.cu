@@ -340,27 +340,42 @@ __device__ __forceinline__ void scout_loop(const TcScanArgs& a, uint8_t* sm, int
         }
         __syncwarp();
         // (q - c) rows as fp16 high + low terms; a lane keeps one 16-byte chunk (8 dims) and walks the rows
+        // The loads of eight rows are issued together, ahead of the conversions and stores: a load
+        // that follows a shared-memory store in program order would wait for it.
         const int c = lane & 15;
-#pragma unroll 8
-        for (int j = lane >> 4; j < n_mma; j += 2) {
-            uint4 hi = make_uint4(0, 0, 0, 0), lo = make_uint4(0, 0, 0, 0);
-            if (j < cnt) {
-                const float4* xp = reinterpret_cast<const float4*>(a.xq + static_cast<int64_t>(s_q[j]) * kTcDim + c * 8);
-                const float4 x0 = __ldg(xp), x1 = __ldg(xp + 1);
-                const float v[8] = {x0.x - e0.x, x0.y - e0.y, x0.z - e0.z, x0.w - e0.w,
-                                    x1.x - e1.x, x1.y - e1.y, x1.z - e1.z, x1.w - e1.w};
-                __half h[8], l[8];
+        for (int j0 = lane >> 4; j0 < n_mma; j0 += 16) {
+            float4 x0[8], x1[8];
 #pragma unroll
-                for (int t = 0; t < 8; ++t) {
-                    h[t] = __float2half_rn(v[t]);
-                    l[t] = __float2half_rn(v[t] - __half2float(h[t]));
+            for (int k = 0; k < 8; ++k) {
+                const int j = j0 + 2 * k;
+                x0[k] = x1[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (j < cnt) {
+                    const float4* xp = reinterpret_cast<const float4*>(a.xq + static_cast<int64_t>(s_q[j]) * kTcDim + c * 8);
+                    x0[k] = __ldg(xp);
+                    x1[k] = __ldg(xp + 1);
                 }
-                hi = make_uint4(pack_h2(h[0], h[1]), pack_h2(h[2], h[3]), pack_h2(h[4], h[5]), pack_h2(h[6], h[7]));
-                lo = make_uint4(pack_h2(l[0], l[1]), pack_h2(l[2], l[3]), pack_h2(l[4], l[5]), pack_h2(l[6], l[7]));
             }
-            const uint32_t off = sw_off(static_cast<uint32_t>(j), static_cast<uint32_t>(c & 7));
-            *reinterpret_cast<uint4*>(bbase + (c >> 3) * kBAtomBytes + off) = hi;
-            *reinterpret_cast<uint4*>(bbase + (2 + (c >> 3)) * kBAtomBytes + off) = lo;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int j = j0 + 2 * k;
+                if (j >= n_mma) break;
+                uint4 hi = make_uint4(0, 0, 0, 0), lo = make_uint4(0, 0, 0, 0);
+                if (j < cnt) {
+                    const float v[8] = {x0[k].x - e0.x, x0[k].y - e0.y, x0[k].z - e0.z, x0[k].w - e0.w,
+                                        x1[k].x - e1.x, x1[k].y - e1.y, x1[k].z - e1.z, x1[k].w - e1.w};
+                    __half h[8], l[8];
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) {
+                        h[t] = __float2half_rn(v[t]);
+                        l[t] = __float2half_rn(v[t] - __half2float(h[t]));
+                    }
+                    hi = make_uint4(pack_h2(h[0], h[1]), pack_h2(h[2], h[3]), pack_h2(h[4], h[5]), pack_h2(h[6], h[7]));
+                    lo = make_uint4(pack_h2(l[0], l[1]), pack_h2(l[2], l[3]), pack_h2(l[4], l[5]), pack_h2(l[6], l[7]));
+                }
+                const uint32_t off = sw_off(static_cast<uint32_t>(j), static_cast<uint32_t>(c & 7));
+                *reinterpret_cast<uint4*>(bbase + (c >> 3) * kBAtomBytes + off) = hi;
+                *reinterpret_cast<uint4*>(bbase + (2 + (c >> 3)) * kBAtomBytes + off) = lo;
+            }
         }
         if (lane == 0) {
             ctx->begin = begin;
@@ -399,7 +414,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) ivfpq_tc_scan_kernel(const TcSc
             ptx::mbar_init(&mbar[i], 1);
             ptx::mbar_init(&ctx_full[i], 1);
             ptx::mbar_init(&ctx_free[i], 1);
-            ptx::mbar_init(&a_full[i], 1);
+            ptx::mbar_init(&a_full[i], kTcMainThreads);
         }
         abort_flag = 0;
         s_stage_n = 0;
@@ -463,12 +478,28 @@ __global__ void __launch_bounds__(kTcThreads, 1) ivfpq_tc_scan_kernel(const TcSc
 
         const bool prof_on = a.prof != nullptr && tid == 0;
         long long pc[8] = {0, 0, 0, 0, 0, 0, 0, 0};   // ctx wait, decode, barrier, issue, mma wait, epilogue, release, tiles
-        auto epilogue = [&]() {
-            const uint32_t ge = g - 1, buf = ge & 1u;
+        // The epilogue of a tile in two steps.  epi_load brings the warp's 32 accumulator columns
+        // into registers and must run BEFORE the next tile is handed to the MMA warp: a TMEM load
+        // issued behind 16 queued UMMAs waits for them.  epi_compute works on the registers while
+        // the tensor core runs.  (kTcMaxN = 64: a warp owns at most one block of 32 columns.)
+        uint32_t acc[32];
+        bool acc_ok = false;
+        auto epi_load = [&](uint32_t ge) {
+            acc_ok = false;
+            const uint32_t buf = ge & 1u;
             const long long w0 = prof_on ? clock64() : 0;
             if (!ptx::mbar_wait_bounded(&mbar[buf], (ge >> 1) & 1u, &abort_flag)) return;
             if (prof_on) pc[4] += clock64() - w0;
             ptx::tc_fence_after();
+            if (static_cast<int>(cb0) * 32 < p_nld) {
+                ptx::tmem_ld_32x32(tmem_base + buf * kTcMaxN + cb0 * 32 + ((quarter * 32u) << 16), acc);
+                ptx::tmem_ld_wait(acc);
+                acc_ok = true;
+            }
+            ptx::tc_fence_before();
+        };
+        auto epi_compute = [&](uint32_t ge) {
+            if (!acc_ok) return;
             const float* s_u = reinterpret_cast<const float*>(sm + kOffCol + p_slot * kColBytes);
             const float* s_cd = s_u + kTcMaxN;
             const int* s_q = reinterpret_cast<const int*>(s_cd + kTcMaxN);
@@ -476,38 +507,40 @@ __global__ void __launch_bounds__(kTcThreads, 1) ivfpq_tc_scan_kernel(const TcSc
             const bool valid = rr < p_len;
             const float rn = s_rn[(ge & 3u) * 256 + row] + s_rn[(ge & 3u) * 256 + 128 + row];
             const uint32_t pos = static_cast<uint32_t>(p_begin + rr);
-            for (int b = static_cast<int>(cb0); b * 32 < p_nld; b += 2) {
-                uint32_t acc[32];
-                ptx::tmem_ld_32x32(tmem_base + buf * kTcMaxN + b * 32 + ((quarter * 32u) << 16), acc);
-                ptx::tmem_ld_wait(acc);
-                const float4* up = reinterpret_cast<const float4*>(s_u + b * 32);
-                bool any = false;
+            const int b = static_cast<int>(cb0);
+            const float4* up = reinterpret_cast<const float4*>(s_u + b * 32);
+            uint32_t hits = 0;                 // bit j: column j of the block passes
 #pragma unroll
-                for (int j4 = 0; j4 < 8; ++j4) {
-                    const float4 u = up[j4];
-                    any |= fmaf(-2.f, __uint_as_float(acc[4 * j4 + 0]), rn) <= u.x;
-                    any |= fmaf(-2.f, __uint_as_float(acc[4 * j4 + 1]), rn) <= u.y;
-                    any |= fmaf(-2.f, __uint_as_float(acc[4 * j4 + 2]), rn) <= u.z;
-                    any |= fmaf(-2.f, __uint_as_float(acc[4 * j4 + 3]), rn) <= u.w;
-                }
-                if (any && valid) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int col = b * 32 + j;
-                        const float v = fmaf(-2.f, __uint_as_float(acc[j]), rn);
-                        if (v <= s_u[col]) {
-                            // staged per CTA (shared-memory counter, one 16-byte store): the per-query
-                            // slots are handed out later by tc_scatter_kernel, where the round trip of
-                            // a global atomic does not stall an epilogue warp
-                            const unsigned int sl = atomicAdd(&s_stage_n, 1u);
-                            if (sl < static_cast<unsigned int>(a.stage_cap))
-                                a.stage[static_cast<size_t>(blockIdx.x) * a.stage_cap + sl] =
-                                    make_uint4(static_cast<uint32_t>(s_q[col]), pos, __float_as_uint(s_cd[col] + v), 0u);
-                        }
-                    }
-                }
+            for (int j4 = 0; j4 < 8; ++j4) {
+                const float4 u = up[j4];
+                hits |= (fmaf(-2.f, __uint_as_float(acc[4 * j4 + 0]), rn) <= u.x ? 1u : 0u) << (4 * j4 + 0);
+                hits |= (fmaf(-2.f, __uint_as_float(acc[4 * j4 + 1]), rn) <= u.y ? 1u : 0u) << (4 * j4 + 1);
+                hits |= (fmaf(-2.f, __uint_as_float(acc[4 * j4 + 2]), rn) <= u.z ? 1u : 0u) << (4 * j4 + 2);
+                hits |= (fmaf(-2.f, __uint_as_float(acc[4 * j4 + 3]), rn) <= u.w ? 1u : 0u) << (4 * j4 + 3);
             }
-            ptx::tc_fence_before();
+            if (!valid) hits = 0;
+            // rare: about one pair in a thousand passes.  The accumulator of a hit is fetched from the
+            // register array through a select chain only here.
+            while (hits) {
+                const int j = __ffs(hits) - 1;
+                hits &= hits - 1;
+                float av = 0.f;
+#pragma unroll
+                for (int t = 0; t < 32; ++t) av = t == j ? __uint_as_float(acc[t]) : av;
+                const int col = b * 32 + j;
+                const float v = fmaf(-2.f, av, rn);
+                // staged per CTA (shared-memory counter, one 16-byte store): the per-query slots are
+                // handed out later by tc_scatter_kernel, where the round trip of a global atomic does
+                // not stall an epilogue warp
+                const unsigned int sl = atomicAdd(&s_stage_n, 1u);
+                if (sl < static_cast<unsigned int>(a.stage_cap))
+                    a.stage[static_cast<size_t>(blockIdx.x) * a.stage_cap + sl] =
+                        make_uint4(static_cast<uint32_t>(s_q[col]), pos, __float_as_uint(s_cd[col] + v), 0u);
+            }
+        };
+        auto epilogue = [&]() {            // both steps, for the pending tile g - 1
+            epi_load(g - 1);
+            epi_compute(g - 1);
         };
 
         while (!aborted) {
@@ -555,14 +588,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) ivfpq_tc_scan_kernel(const TcSc
                     const uint8_t* cbm = sm + kOffCb + half * 8u * 256u * 16u;
                     const float* cbn = s_cbn + half * 8u * 256u;
                     float rn = 0.f;
+                    uint4 v[8];                      // all lookups first, then the stores
 #pragma unroll
                     for (uint32_t i = 0; i < 8; ++i) {
                         const uint32_t byte = ((i < 4 ? lo_w : hi_w) >> ((i & 3u) * 8u)) & 0xFFu;
                         const uint32_t e = i * 256u + byte;
-                        const uint4 v = *reinterpret_cast<const uint4*>(cbm + e * 16u);
-                        *reinterpret_cast<uint4*>(arow + ((i ^ (row & 7u)) << 4)) = v;
+                        v[i] = *reinterpret_cast<const uint4*>(cbm + e * 16u);
                         rn += cbn[e];
                     }
+#pragma unroll
+                    for (uint32_t i = 0; i < 8; ++i) *reinterpret_cast<uint4*>(arow + ((i ^ (row & 7u)) << 4)) = v[i];
                     s_rn[(g & 3u) * 256 + half * 128 + row] = rn;
                 }
                 const long long d1 = prof_on ? clock64() : 0;
@@ -571,18 +606,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) ivfpq_tc_scan_kernel(const TcSc
                 main_barrier();
                 const long long d2 = prof_on ? clock64() : 0;
                 if (abort_flag) { aborted = true; break; }
-                if (tid == 0) {
-                    tile_info[buf] = static_cast<uint32_t>(n_mma) | (static_cast<uint32_t>(slot) << 16);
-                    ptx::mbar_arrive(&a_full[buf]);
-                }
+                if (pend) epi_load(g - 1);           // before the UMMAs of this tile enter the pipe
+                if (tid == 0) tile_info[buf] = static_cast<uint32_t>(n_mma) | (static_cast<uint32_t>(slot) << 16);
+                ptx::mbar_arrive(&a_full[buf]);      // every main thread: its rows are written and its load is done
                 ++g;
                 const long long d3 = prof_on ? clock64() : 0;
                 cw = load_code(t + 1);               // in flight behind the epilogue
                 if (pend) {
-                    // g - 1 is the tile just issued; the pending one is g - 2
-                    --g;
-                    epilogue();
-                    ++g;
+                    epi_compute(g - 2);
                     const long long d4 = prof_on ? clock64() : 0;
                     if (p_last) {                    // the context of the pending tile is finished: hand its slot back
                         main_barrier();
@@ -614,10 +645,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) ivfpq_tc_scan_kernel(const TcSc
             main_barrier();
             if (tid == 0 && p_last) ptx::mbar_arrive(&ctx_free[p_slot]);
         }
-        if (tid == 0) {                         // release the MMA warp
-            tile_info[g & 1u] = kTileStop;
-            ptx::mbar_arrive(&a_full[g & 1u]);
-        }
+        if (tid == 0) tile_info[g & 1u] = kTileStop;     // release the MMA warp
+        ptx::mbar_arrive(&a_full[g & 1u]);
         if (prof_on)
             for (int i = 0; i < 8; ++i) atomicAdd(a.prof + i, static_cast<unsigned long long>(pc[i]));
     }
