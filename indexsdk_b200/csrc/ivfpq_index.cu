@@ -1711,6 +1711,17 @@ void IvfpqIndex::search_stages(int64_t nq, const float* xq, int k, float* D, int
             B200_CUDA_CHECK(cub::DeviceRadixSort::SortPairs(sort_tmp, sort_bytes, keys, keys2, vals, vals2,
                                                             static_cast<int>(npairs), 0, end_bit, st));
             B200_CUDA_CHECK(launch_tc_bounds(keys2, npairs, nlist_, first, last, st));
+            // lists with the most probing queries are handed out first, so that no long list is
+            // left for the end of the launch
+            int32_t* okeys = static_cast<int32_t*>(w_tc_okeys_.ensure(static_cast<size_t>(nlist_) * 16));
+            int32_t* ovals = okeys + nlist_;
+            int32_t* okeys2 = ovals + nlist_;
+            int32_t* order = okeys2 + nlist_;
+            B200_CUDA_CHECK(launch_tc_order_keys(first, last, nlist_, okeys, ovals, st));
+            size_t osort_bytes = 0;
+            B200_CUDA_CHECK(cub::DeviceRadixSort::SortPairs(nullptr, osort_bytes, okeys, okeys2, ovals, order, nlist_, 0, 31, st));
+            void* osort_tmp = w_tc_osort_.ensure(osort_bytes);
+            B200_CUDA_CHECK(cub::DeviceRadixSort::SortPairs(osort_tmp, osort_bytes, okeys, okeys2, ovals, order, nlist_, 0, 31, st));
             float* tau = static_cast<float*>(w_tc_tau_.ensure(static_cast<size_t>(m) * 4));
             TcScanArgs t{};
             t.cb16 = cb16_.as<uint16_t>();
@@ -1724,6 +1735,7 @@ void IvfpqIndex::search_stages(int64_t nq, const float* xq, int k, float* D, int
             t.sorted_pair = vals2;
             t.first = first;
             t.last = last;
+            t.order = order;
             t.offsets = offsets_.as<int64_t>();
             t.lens = lens_.as<int64_t>();
             t.codes = codes_.as<uint8_t>();

@@ -147,6 +147,14 @@ tc_head_tau_kernel(const TcScanArgs a, const int64_t* cI, float err_rel, float t
     if (lane == 0) tau[q] = out;
 }
 
+__global__ void tc_order_keys_kernel(const int32_t* first, const int32_t* last, int nlist, int32_t* keys,
+                                     int32_t* vals) {
+    const int l = blockIdx.x * blockDim.x + threadIdx.x;
+    if (l >= nlist) return;
+    keys[l] = 0x40000000 - (last[l] - first[l]);      // ascending sort: most queries first
+    vals[l] = l;
+}
+
 __global__ void tc_cb16_kernel(const float* cb, int64_t n, uint16_t* out) {
     const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i < n) out[i] = __half_as_ushort(__float2half_rn(cb[i]));
@@ -282,6 +290,7 @@ __device__ __forceinline__ void scout_loop(const TcScanArgs& a, uint8_t* sm, int
                 list = -1;
                 break;
             }
+            if (a.order) l = static_cast<unsigned int>(a.order[l]);
             list = l;
             f = a.first[l];
             np = a.last[l] - f;
@@ -533,9 +542,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) ivfpq_tc_scan_kernel(const TcSc
                 // handed out later by tc_scatter_kernel, where the round trip of a global atomic does
                 // not stall an epilogue warp
                 const unsigned int sl = atomicAdd(&s_stage_n, 1u);
-                if (sl < static_cast<unsigned int>(a.stage_cap))
+                if (sl < static_cast<unsigned int>(a.stage_cap)) {
                     a.stage[static_cast<size_t>(blockIdx.x) * a.stage_cap + sl] =
                         make_uint4(static_cast<uint32_t>(s_q[col]), pos, __float_as_uint(s_cd[col] + v), 0u);
+                } else {                            // staging area full: append directly
+                    const int64_t q = s_q[col];
+                    const unsigned int qs = atomicAdd(a.cand_n + q, 1u);
+                    if (qs < static_cast<unsigned int>(a.cap)) {
+                        a.cand_d[q * a.cap + qs] = s_cd[col] + v;
+                        a.cand_p[q * a.cap + qs] = pos;
+                    }
+                }
             }
         };
         auto epilogue = [&]() {            // both steps, for the pending tile g - 1
@@ -670,11 +687,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) ivfpq_tc_scan_kernel(const TcSc
 
 // Moves the staged candidates of CTA blockIdx.x into the per-query arrays.
 __global__ void tc_scatter_kernel(const TcScanArgs a) {
-    const unsigned int n_all = a.stage_n[blockIdx.x];
-    if (n_all > static_cast<unsigned int>(a.stage_cap)) {
-        if (threadIdx.x == 0) atomicOr(a.err, 2u);
-        return;
-    }
+    // entries beyond the staging capacity were appended by the scan kernel itself
+    const unsigned int n_all = min(a.stage_n[blockIdx.x], static_cast<unsigned int>(a.stage_cap));
     const uint4* st = a.stage + static_cast<size_t>(blockIdx.x) * a.stage_cap;
     for (unsigned int i = threadIdx.x; i < n_all; i += blockDim.x) {
         const uint4 e = st[i];
@@ -715,6 +729,12 @@ cudaError_t launch_tc_bounds(const int32_t* sorted_keys, int64_t npairs, int nli
 cudaError_t launch_tc_head_tau(const TcScanArgs& a, const int64_t* cI, float err_rel, float t2_bound, float* tau,
                                cudaStream_t st) {
     tc_head_tau_kernel<<<blocks(a.nq, kHeadWarps), kHeadWarps * 32, 0, st>>>(a, cI, err_rel, t2_bound, tau);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_tc_order_keys(const int32_t* first, const int32_t* last, int nlist, int32_t* keys, int32_t* vals,
+                                 cudaStream_t st) {
+    tc_order_keys_kernel<<<blocks(nlist, 256), 256, 0, st>>>(first, last, nlist, keys, vals);
     return cudaGetLastError();
 }
 

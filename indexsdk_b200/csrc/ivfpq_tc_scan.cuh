@@ -49,6 +49,7 @@ struct TcScanArgs {
     const int32_t* sorted_pair;  // [nq * nprobe] pair index q * nprobe + p, ordered by list
     const int32_t* first;        // [nlist] first entry of the list's pairs in sorted_pair
     const int32_t* last;         // [nlist] one past its last entry (first == last: not probed)
+    const int32_t* order;        // [nlist] lists in the order they are handed out (most queries first), or null
     const int64_t* offsets;      // [nlist + 1] first slot of every list
     const int64_t* lens;         // [nlist] vectors per list
     const uint8_t* codes;        // 16 bytes per slot, rotated by (slot mod 16)
@@ -59,11 +60,11 @@ struct TcScanArgs {
     unsigned int* cand_n;        // [nq] candidates found (may exceed cap: overflow)
     int cap;
     uint4* stage;                // [CTAs][stage_cap] (query, slot, distance bits, -) as the epilogues find them
-    unsigned int* stage_n;       // [CTAs] entries each CTA produced (may exceed stage_cap: overflow)
+    unsigned int* stage_n;       // [CTAs] entries each CTA produced (beyond stage_cap they went straight to cand_*)
     int stage_cap;
     unsigned int* work;          // next list to hand out (zeroed before the launch)
     unsigned long long* scanned; // += (query, code) pairs visited
-    unsigned int* err;           // bit 0: a bounded wait ran out; bit 1: a CTA's staging area overflowed
+    unsigned int* err;           // bit 0: a bounded wait ran out
     unsigned long long* prof;    // optional [8]: cycles of thread 0 per phase, summed over CTAs (development aid)
 };
 
@@ -77,6 +78,9 @@ cudaError_t launch_tc_bounds(const int32_t* sorted_keys, int64_t npairs, int nli
 // fp16-decoded distances to the codes of its nearest list(s); -inf: exact path (fp16 range)
 cudaError_t launch_tc_head_tau(const TcScanArgs& a, const int64_t* cI, float err_rel, float t2_bound, float* tau,
                                cudaStream_t st);
+// sort keys that put the lists with the most probing queries first (keys[l] = -queries, vals[l] = l)
+cudaError_t launch_tc_order_keys(const int32_t* first, const int32_t* last, int nlist, int32_t* keys, int32_t* vals,
+                                 cudaStream_t st);
 cudaError_t launch_tc_scan(const TcScanArgs& a, int num_sms, cudaStream_t st);
 // per query: the kTcKeep best candidates -> fd / fp ([nq][32]) and fth ([nq])
 cudaError_t launch_tc_select(const TcScanArgs& a, float* fd, uint32_t* fp, float* fth, cudaStream_t st);
