@@ -2,6 +2,7 @@
 // translation, and the multi-index / multi-device fan-out.
 #include "../../include/b200idx.h"
 
+#include <algorithm>
 #include <cstdio>
 #include <cstring>
 #include <map>
@@ -24,6 +25,11 @@ struct b200idx_index {
     std::unique_ptr<FlatIndex> flat;
     std::unique_ptr<IvfpqIndex> ivfpq;
     mutable std::string last_error;
+    // An index owns ONE stream and ONE set of scratch buffers, so its entry points are not
+    // re-entrant: every call on a handle runs under this mutex.  Host threads may share a handle
+    // (the reference's MX_INDEX_MULTITHREAD=1 mode lets several threads search one index); their
+    // calls are serialised here, calls on different handles run concurrently.
+    mutable std::mutex mu;
 };
 
 namespace {
@@ -34,8 +40,16 @@ std::mutex g_create_mutex;
 constexpr int kMaxK = 4096;        // FR/ascend/AscendIndex.h:36
 constexpr int64_t kMaxN = 1000000000;  // FR/ascend/AscendIndex.h:35
 
+// status_of_error: message of a thrown exception -> status code.  A bounded device-side wait that
+// ran out is reported by the index classes as a runtime_error whose text contains "bounded wait".
+int status_of_error(const char* what) {
+    return std::strstr(what, "bounded wait") != nullptr ? B200IDX_ERR_TIMEOUT : B200IDX_ERR_INNER;
+}
+
 template <typename F>
-int guarded(const b200idx_index* h, F&& f) {
+int guarded(const b200idx_index* h, F&& f, bool lock = true) {
+    std::unique_lock<std::mutex> guard;
+    if (h && lock) guard = std::unique_lock<std::mutex>(h->mu);
     try {
         f();
         return B200IDX_OK;
@@ -44,9 +58,8 @@ int guarded(const b200idx_index* h, F&& f) {
         return B200IDX_ERR_INVALID_PARAM;
     } catch (const std::exception& e) {
         if (h) h->last_error = e.what();
-        const bool timeout = std::strstr(e.what(), "bounded wait") != nullptr;
         cudaGetLastError();
-        return timeout ? B200IDX_ERR_TIMEOUT : B200IDX_ERR_INNER;
+        return status_of_error(e.what());
     } catch (...) {
         if (h) h->last_error = "unknown error";
         return B200IDX_ERR_INNER;
@@ -91,6 +104,20 @@ void check_search_args(const b200idx_index* h, int64_t n, const void* x, int k, 
     if (!x) throw std::invalid_argument("Invalid x: nullptr.");
     if (!D) throw std::invalid_argument("Invalid distances: nullptr.");
     if (!I) throw std::invalid_argument("Invalid labels: nullptr.");
+}
+
+// Device buffers of b200idx_search_multi, one set per device, grown on demand and kept.
+struct MultiScratch {
+    std::mutex mu;           // held for a whole multi-index search that uses this device
+    DeviceBuffer q, D, I, allD, allI, mD, mI;
+};
+MultiScratch& multi_scratch(int device) {
+    static std::mutex table_mu;
+    static std::map<int, std::unique_ptr<MultiScratch>> table;
+    std::lock_guard<std::mutex> l(table_mu);
+    std::unique_ptr<MultiScratch>& p = table[device];
+    if (!p) p.reset(new MultiScratch);
+    return *p;
 }
 
 int dev_of(const b200idx_index* h) { return h->kind == 2 ? h->ivfpq->device() : h->flat->device(); }
@@ -222,6 +249,7 @@ int b200idx_search_multi(b200idx_t* const* hs, int nh, int64_t n, const void* x,
                          int merged) {
     if (!hs || nh <= 0 || !hs[0]) return B200IDX_ERR_INVALID_PARAM;
     b200idx_index* h0 = hs[0];
+    // the member handles are locked below (all of them, in address order), not by guarded()
     return guarded(h0, [&] {
         if (nh > 10000) throw std::invalid_argument("size of indexes must be > 0 and <= 10000.");
         check_search_args(h0, n, x, k, D, I);
@@ -231,6 +259,14 @@ int b200idx_search_multi(b200idx_t* const* hs, int nh, int64_t n, const void* x,
                 descending_of(hs[i]) != descending_of(h0))
                 throw std::invalid_argument("the indexes of a multi-index search must share type, dims and metric");
         }
+        // FR/ascend/AscendMultiIndexSearch.cpp:213-228 takes every index's lock before searching
+        std::vector<b200idx_index*> uniq(hs, hs + nh);
+        std::sort(uniq.begin(), uniq.end());
+        uniq.erase(std::unique(uniq.begin(), uniq.end()), uniq.end());
+        std::vector<std::unique_lock<std::mutex>> locks;
+        locks.reserve(uniq.size());
+        for (b200idx_index* u : uniq) locks.emplace_back(u->mu);
+
         const size_t row = query_row_bytes(h0);
         const size_t per = static_cast<size_t>(n) * k;
         const int dev0 = dev_of(h0);
@@ -238,14 +274,22 @@ int b200idx_search_multi(b200idx_t* const* hs, int nh, int64_t n, const void* x,
         std::map<int, std::vector<int>> groups;
         for (int i = 0; i < nh; ++i) groups[dev_of(hs[i])].push_back(i);
 
+        // Scratch is per device, grow-only and kept between calls (a steady-state call allocates
+        // nothing); every buffer is owned by the scratch object, so no exit path leaks.
+        MultiScratch& s0 = multi_scratch(dev0);
+        std::vector<MultiScratch*> held;
+        for (auto& kv : groups) held.push_back(&multi_scratch(kv.first));
+        if (std::find(held.begin(), held.end(), &s0) == held.end()) held.push_back(&s0);
+        std::sort(held.begin(), held.end());
+        std::vector<std::unique_lock<std::mutex>> scratch_locks;
+        for (MultiScratch* m : held) scratch_locks.emplace_back(m->mu);
+
         float* allD = nullptr;   // [nh][n][k] on dev0 when merged
         int64_t* allI = nullptr;
-        {
+        if (merged) {
             DeviceGuard g(dev0);
-            if (merged) {
-                B200_CUDA_CHECK(cudaMalloc(&allD, per * nh * 4));
-                B200_CUDA_CHECK(cudaMalloc(&allI, per * nh * 8));
-            }
+            allD = static_cast<float*>(s0.allD.ensure(per * nh * 4));
+            allI = static_cast<int64_t*>(s0.allI.ensure(per * nh * 8));
         }
         std::vector<std::string> errors(groups.size());
         std::vector<std::thread> workers;
@@ -257,58 +301,52 @@ int b200idx_search_multi(b200idx_t* const* hs, int nh, int64_t n, const void* x,
             auto body = [=, &hs]() {
                 try {
                     DeviceGuard g(dev);
-                    void* dq = nullptr;
-                    float* dD = nullptr;
-                    int64_t* dI = nullptr;
-                    B200_CUDA_CHECK(cudaMalloc(&dq, static_cast<size_t>(n) * row));
-                    B200_CUDA_CHECK(cudaMalloc(&dD, per * 4));
-                    B200_CUDA_CHECK(cudaMalloc(&dI, per * 8));
-                    B200_CUDA_CHECK(cudaMemcpy(dq, x, static_cast<size_t>(n) * row, cudaMemcpyHostToDevice));
+                    MultiScratch& sc = multi_scratch(dev);
+                    void* dq = sc.q.ensure(static_cast<size_t>(n) * row);
+                    float* dD = static_cast<float*>(sc.D.ensure(per * 4));
+                    int64_t* dI = static_cast<int64_t*>(sc.I.ensure(per * 8));
+                    cudaStream_t st = static_cast<cudaStream_t>(b200idx_stream(hs[members[0]]));
+                    B200_CUDA_CHECK(cudaMemcpyAsync(dq, x, static_cast<size_t>(n) * row, cudaMemcpyHostToDevice, st));
+                    B200_CUDA_CHECK(cudaStreamSynchronize(st));
                     for (int i : members) {
                         b200idx_index* h = hs[i];
-                        if (h->kind == 2) h->ivfpq->search_device(n, static_cast<const float*>(dq), k, dD, dI);
-                        else h->flat->search_device(n, dq, false, k, dD, dI, k);
-                        if (merged) {
-                            B200_CUDA_CHECK(cudaMemcpy(allD + per * i, dD, per * 4, cudaMemcpyDefault));
-                            B200_CUDA_CHECK(cudaMemcpy(allI + per * i, dI, per * 8, cudaMemcpyDefault));
-                        } else {
-                            B200_CUDA_CHECK(cudaMemcpy(D + per * i, dD, per * 4, cudaMemcpyDeviceToHost));
-                            B200_CUDA_CHECK(cudaMemcpy(I + per * i, dI, per * 8, cudaMemcpyDeviceToHost));
+                        // with merged results on this device the member writes its slice directly
+                        float* oD = (merged && dev == dev0) ? allD + per * i : dD;
+                        int64_t* oI = (merged && dev == dev0) ? allI + per * i : dI;
+                        if (h->kind == 2) h->ivfpq->search_device(n, static_cast<const float*>(dq), k, oD, oI);
+                        else h->flat->search_device(n, dq, false, k, oD, oI, k);
+                        if (merged && dev != dev0) {
+                            B200_CUDA_CHECK(cudaMemcpyAsync(allD + per * i, dD, per * 4, cudaMemcpyDefault, st));
+                            B200_CUDA_CHECK(cudaMemcpyAsync(allI + per * i, dI, per * 8, cudaMemcpyDefault, st));
+                            B200_CUDA_CHECK(cudaStreamSynchronize(st));
+                        } else if (!merged) {
+                            B200_CUDA_CHECK(cudaMemcpyAsync(D + per * i, dD, per * 4, cudaMemcpyDeviceToHost, st));
+                            B200_CUDA_CHECK(cudaMemcpyAsync(I + per * i, dI, per * 8, cudaMemcpyDeviceToHost, st));
+                            B200_CUDA_CHECK(cudaStreamSynchronize(st));
                         }
                     }
-                    cudaFree(dq);
-                    cudaFree(dD);
-                    cudaFree(dI);
                 } catch (const std::exception& e) {
                     *err = e.what();
+                    cudaGetLastError();
                 }
             };
             if (groups.size() == 1) body();
             else workers.emplace_back(body);
         }
         for (auto& w : workers) w.join();
-        std::string first_err;
         for (auto& e : errors)
-            if (!e.empty() && first_err.empty()) first_err = e;
-        if (first_err.empty() && merged) {
+            if (!e.empty()) throw std::runtime_error(e);
+        if (merged) {
             DeviceGuard g(dev0);
-            float* mD = nullptr;
-            int64_t* mI = nullptr;
-            B200_CUDA_CHECK(cudaMalloc(&mD, per * 4));
-            B200_CUDA_CHECK(cudaMalloc(&mI, per * 8));
-            B200_CUDA_CHECK(launch_merge_topk(nh, n, k, descending_of(h0) ? 1 : 0, allD, allI, mD, mI, nullptr));
-            B200_CUDA_CHECK(cudaMemcpy(D, mD, per * 4, cudaMemcpyDeviceToHost));
-            B200_CUDA_CHECK(cudaMemcpy(I, mI, per * 8, cudaMemcpyDeviceToHost));
-            cudaFree(mD);
-            cudaFree(mI);
+            cudaStream_t st = static_cast<cudaStream_t>(b200idx_stream(h0));
+            float* mD = static_cast<float*>(s0.mD.ensure(per * 4));
+            int64_t* mI = static_cast<int64_t*>(s0.mI.ensure(per * 8));
+            B200_CUDA_CHECK(launch_merge_topk(nh, n, k, descending_of(h0) ? 1 : 0, allD, allI, mD, mI, st));
+            B200_CUDA_CHECK(cudaMemcpyAsync(D, mD, per * 4, cudaMemcpyDeviceToHost, st));
+            B200_CUDA_CHECK(cudaMemcpyAsync(I, mI, per * 8, cudaMemcpyDeviceToHost, st));
+            B200_CUDA_CHECK(cudaStreamSynchronize(st));
         }
-        {
-            DeviceGuard g(dev0);
-            if (allD) cudaFree(allD);
-            if (allI) cudaFree(allI);
-        }
-        if (!first_err.empty()) throw std::runtime_error(first_err);
-    });
+    }, /*lock=*/false);
 }
 
 int b200idx_merge_topk_device(int nsrc, int64_t n, int k, int descending, const float* Din, const int64_t* Iin,

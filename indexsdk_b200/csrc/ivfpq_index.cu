@@ -246,6 +246,82 @@ __device__ __forceinline__ void warp_insert(float (&dk)[KPT], L (&lb)[KPT], floa
     }
 }
 
+// Bitonic sort of 32 (distance, position) pairs, one per lane, ascending.
+__device__ __forceinline__ void warp_sort32(float& d, uint32_t& p, int lane) {
+#pragma unroll
+    for (int size = 2; size <= 32; size <<= 1) {
+#pragma unroll
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            const float od = __shfl_xor_sync(0xffffffffu, d, stride);
+            const uint32_t op = __shfl_xor_sync(0xffffffffu, p, stride);
+            const bool keep_min = ((lane & stride) == 0) == ((lane & size) == 0);
+            const bool other_less = pair_less<uint32_t>(od, op, d, p);
+            if (keep_min ? other_less : !other_less) {
+                d = od;
+                p = op;
+            }
+        }
+    }
+}
+
+// First 32 candidates of a warp whose sorted list is still empty: one bitonic sort instead of 32
+// insertions.  (d, p): one candidate per lane, (+inf, kNoPos) where the lane has none.
+template <int KPT>
+__device__ __forceinline__ void warp_fill_sorted(float (&dk)[KPT], uint32_t (&pk)[KPT], float d, uint32_t p, int lane) {
+    warp_sort32(d, p, lane);
+#pragma unroll
+    for (int s = 0; s < KPT; ++s) {
+        const int r = lane * KPT + s;          // rank held in this register
+        const float fd = __shfl_sync(0xffffffffu, d, r & 31);
+        const uint32_t fp = __shfl_sync(0xffffffffu, p, r & 31);
+        dk[s] = r < 32 ? fd : __int_as_float(0x7f800000);
+        pk[s] = r < 32 ? fp : kNoPos;
+    }
+}
+
+// (dk, pk) and (od, op): two sorted lists of 32 * KPT pairs in the layout of warp_insert, KPT = 1 or 2.
+// Leaves the 32 * KPT smallest of their union, sorted, in (dk, pk): the second list is reversed, the
+// element-wise minimum is a bitonic sequence holding the winners, and log2 compare-exchange steps
+// sort it.
+template <int KPT>
+__device__ __forceinline__ void warp_merge_sorted(float (&dk)[KPT], uint32_t (&pk)[KPT], const float (&od)[KPT],
+                                                  const uint32_t (&op)[KPT], int lane) {
+    static_assert(KPT == 1 || KPT == 2, "register merge is written for k' = 32 and 64");
+#pragma unroll
+    for (int s = 0; s < KPT; ++s) {
+        const float rd = __shfl_sync(0xffffffffu, od[KPT - 1 - s], 31 - lane);
+        const uint32_t rp = __shfl_sync(0xffffffffu, op[KPT - 1 - s], 31 - lane);
+        if (pair_less<uint32_t>(rd, rp, dk[s], pk[s])) {
+            dk[s] = rd;
+            pk[s] = rp;
+        }
+    }
+#pragma unroll
+    for (int stride = 16; stride > 0; stride >>= 1) {
+#pragma unroll
+        for (int s = 0; s < KPT; ++s) {
+            const float xd = __shfl_xor_sync(0xffffffffu, dk[s], stride);
+            const uint32_t xp = __shfl_xor_sync(0xffffffffu, pk[s], stride);
+            const bool keep_min = (lane & stride) == 0;
+            const bool other_less = pair_less<uint32_t>(xd, xp, dk[s], pk[s]);
+            if (keep_min ? other_less : !other_less) {
+                dk[s] = xd;
+                pk[s] = xp;
+            }
+        }
+    }
+    if (KPT == 2) {
+        if (pair_less<uint32_t>(dk[KPT - 1], pk[KPT - 1], dk[0], pk[0])) {
+            const float td = dk[0];
+            const uint32_t tp = pk[0];
+            dk[0] = dk[KPT - 1];
+            pk[0] = pk[KPT - 1];
+            dk[KPT - 1] = td;
+            pk[KPT - 1] = tp;
+        }
+    }
+}
+
 // Bitonic sort of E (power of two) pairs held in shared memory, ascending by (distance, payload).
 template <typename L>
 __device__ __forceinline__ void block_sort_pairs(float* sd, L* sl, int E) {
@@ -420,7 +496,7 @@ struct StaticFeed {
             const int p = next_p0 + lane * stride;
             if (p < a.nprobe) {
                 const int64_t list = a.cI[q * a.nprobe + p];
-                if (list >= 0) {
+                if (list >= 0 && list < a.nlist) {
                     my_begin = static_cast<uint32_t>(a.offsets[list]);
                     my_end = my_begin + static_cast<uint32_t>(a.lens[list]);
                     if (a.by_residual) my_base = a.cD[q * a.nprobe + p];
@@ -442,9 +518,26 @@ struct SharedFeed {
     const uint32_t* s_begin;   // [nprobe]
     const uint32_t* s_end;
     const float* s_base;
-    int* s_next;               // next probe to hand out
+    int* s_next;               // next probe to hand out (starts at 1)
     int nprobe, lane;
+    int wslot, nwarps;         // this warp's place among the warps that share the query
+    bool first;
+    // The nearest list comes first and is split evenly (in 32-vector groups) over the warps of the
+    // query: it is where most of the final neighbours sit, so every warp's kept list -- and with it
+    // the bound the warps share -- is tight before the remaining lists are handed out.
     __device__ __forceinline__ bool next(uint32_t& begin, uint32_t& end, float& base) {
+        if (first) {
+            first = false;
+            const uint32_t b = s_begin[0], e = s_end[0];
+            const uint32_t groups = (e - b + 31u) >> 5;
+            const uint32_t lo = groups * static_cast<uint32_t>(wslot) / static_cast<uint32_t>(nwarps);
+            const uint32_t hi = groups * static_cast<uint32_t>(wslot + 1) / static_cast<uint32_t>(nwarps);
+            begin = b + 32u * lo;
+            end = min(e, b + 32u * hi);
+            if (begin > end) begin = end;
+            base = s_base[0];
+            return true;
+        }
         int p = 0;
         if (lane == 0) p = atomicAdd(s_next, 1);
         p = __shfl_sync(0xffffffffu, p, 0);
@@ -458,55 +551,83 @@ struct SharedFeed {
 
 // The filter loop of one warp over the probes its feed hands out.  `sum` adds the table entries of
 // one vector's codes to an accumulator; `gth` is the bound shared by the warps that work on the
-// same query (float bits, >= 0).  dk / pk: the warp's sorted k' best so far.  The code loads are
-// software-pipelined across list boundaries.  Positions fit 32 bits (an index holds fewer than
-// 2^31 vectors).
-template <int MT, int KPT, typename Sum, typename Feed>
+// same query (float bits, >= 0).  dk / pk: the warp's sorted k' best so far (empty on entry).
+// The unit of work is a group of 32 consecutive vectors (lists are stored padded to whole groups);
+// U groups, possibly of different lists, form a chunk, and the loads of the next chunk are in flight
+// while the current one is processed.  Positions fit 32 bits (an index holds fewer than 2^31
+// vectors).  RESID: residual encoding (per-vector term in a.t2, per-list term = coarse distance).
+template <int MT, int KPT, bool RESID, typename Sum, typename Feed>
 __device__ __forceinline__ void scan_warp_probes(const ScanArgs& a, Feed& feed, int lane, const Sum& sum, int* gth,
                                                  float (&dk)[KPT], uint32_t (&pk)[KPT]) {
-    float th_d = __shfl_sync(0xffffffffu, dk[KPT - 1], 31);
-    uint32_t th_p = __shfl_sync(0xffffffffu, pk[KPT - 1], 31);
+    const float kNaN = __int_as_float(0x7fc00000);
+    float th_d = __int_as_float(0x7f800000);
+    uint32_t th_p = kNoPos;
+    bool cold = true;                    // nothing kept yet: the first group is sorted, not inserted
     const uint4* codes4 = reinterpret_cast<const uint4*>(a.codes);
     uint32_t begin = 0, end = 0, v0 = 0;
     float base = 0.f;
-    constexpr int U = 2;                 // 32-vector sub-chunks per chunk
-    auto advance = [&]() -> bool {      // moves to the next chunk; false when the feed has run dry
-        v0 += 32 * U;
-        while (v0 >= end) {
-            if (!feed.next(begin, end, base)) return false;
-            v0 = begin;                   // a multiple of 32: lists are stored padded
-            if (begin == end) v0 = end;   // empty or absent list
-        }
-        return true;
-    };
-    // One chunk in flight: codes, the per-vector term and where it came from.  Lists are padded to
-    // whole 32-vector groups whose padding slots carry NaN in the per-vector term, which fails every
-    // comparison, so there is no per-lane bounds check; a group past the end of the list (the
-    // chunk is two groups long) is switched off through the list's term.
+    constexpr int U = 2;                 // 32-vector groups per chunk
+    // One chunk in flight: codes, the per-vector term and where it came from.  A padding slot
+    // carries NaN in its term (residual encoding: stored in t2; raw encoding: from the list's end),
+    // which fails every comparison, so the lookups need no per-lane bounds logic; a group that does
+    // not exist (the feed ran dry inside a chunk) is all NaN.
     struct Chunk {
         uint4 c[U][MT];
         float t[U];      // per-vector term (loaded; consumed only when the chunk is processed)
-        float bias[U];   // the list's term, or NaN for a group outside the list
-        uint32_t v0;
+        float bias[U];   // the list's term, or NaN
+        uint32_t v0[U];
     };
-    auto fetch = [&](Chunk& ch) {
-        ch.v0 = v0;
+    // next group of 32 vectors; false when the feed has run dry
+    auto next_group = [&](uint32_t& gv0, float& gbias) -> bool {
+        while (v0 >= end) {
+            if (!feed.next(begin, end, base)) return false;
+            v0 = begin;                   // a multiple of 32: lists are stored padded
+        }
+        gv0 = v0;
+        gbias = RESID ? base : ((v0 + lane < end) ? 0.f : kNaN);
+        v0 += 32;
+        return true;
+    };
+    auto fetch = [&](Chunk& ch) -> bool {
+        bool any = false;
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const uint32_t v = v0 + 32 * u + lane;
+            uint32_t gv0 = u > 0 ? ch.v0[0] : 0u;   // an absent group re-reads a valid address
+            float gb = kNaN;
+            const bool ok = next_group(gv0, gb);
+            if (u == 0 && !ok) return false;
+            any = true;
+            ch.v0[u] = gv0;
+            ch.bias[u] = ok ? gb : kNaN;
+            const uint32_t v = gv0 + lane;
             const uint4* cp = codes4 + static_cast<size_t>(v) * MT;
 #pragma unroll
             for (int g = 0; g < MT; ++g) ch.c[u][g] = __ldg(cp + g);
-            ch.t[u] = __ldg(a.t2 + v);
-            ch.bias[u] = (u == 0 || v0 + 32 * u < end) ? base : __int_as_float(0x7fc00000);
+            if (RESID) ch.t[u] = __ldg(a.t2 + v);
+        }
+        return any;
+    };
+    auto insert_group = [&](float acc, uint32_t v, float lim) {
+        const bool pass = acc <= lim && pair_less<uint32_t>(acc, v, th_d, th_p);
+        unsigned bal = __ballot_sync(0xffffffffu, pass);
+        while (bal) {
+            const int src = __ffs(bal) - 1;
+            bal &= bal - 1;
+            const float vd = __shfl_sync(0xffffffffu, acc, src);
+            const uint32_t vp = __shfl_sync(0xffffffffu, v, src);
+            if (pair_less<uint32_t>(vd, vp, th_d, th_p)) {
+                warp_insert<KPT, uint32_t>(dk, pk, vd, vp, lane);
+                th_d = __shfl_sync(0xffffffffu, dk[KPT - 1], 31);
+                th_p = __shfl_sync(0xffffffffu, pk[KPT - 1], 31);
+            }
         }
     };
     auto process = [&](const Chunk& ch) {
-        // the CTA-wide bound is read before the lookups and used after them
+        // the bound shared with the other warps is read before the lookups and used after them
         const float lim = fminf(th_d, __int_as_float(*reinterpret_cast<volatile int*>(gth)));
         float acc[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) acc[u] = ch.bias[u] + ch.t[u];
+        for (int u = 0; u < U; ++u) acc[u] = RESID ? ch.bias[u] + ch.t[u] : ch.bias[u];
 #pragma unroll
         for (int u = 0; u < U; ++u) sum(ch.c[u], acc[u]);
         bool maybe = false;
@@ -515,37 +636,30 @@ __device__ __forceinline__ void scan_warp_probes(const ScanArgs& a, Feed& feed, 
         if (__any_sync(0xffffffffu, maybe)) {
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const uint32_t v = ch.v0 + 32 * u + lane;   // v & 15 == lane & 15: the stored rotation
-                const bool pass = acc[u] <= lim && pair_less<uint32_t>(acc[u], v, th_d, th_p);
-                unsigned bal = __ballot_sync(0xffffffffu, pass);
-                while (bal) {
-                    const int src = __ffs(bal) - 1;
-                    bal &= bal - 1;
-                    const float vd = __shfl_sync(0xffffffffu, acc[u], src);
-                    const uint32_t vp = __shfl_sync(0xffffffffu, v, src);
-                    if (pair_less<uint32_t>(vd, vp, th_d, th_p)) {
-                        warp_insert<KPT, uint32_t>(dk, pk, vd, vp, lane);
-                        th_d = __shfl_sync(0xffffffffu, dk[KPT - 1], 31);
-                        th_p = __shfl_sync(0xffffffffu, pk[KPT - 1], 31);
-                    }
+                const uint32_t v = ch.v0[u] + lane;   // v & 15 == lane & 15: the stored rotation
+                if (u == 0 && cold) {
+                    const bool ok = acc[u] <= lim;    // false for NaN
+                    warp_fill_sorted<KPT>(dk, pk, ok ? acc[u] : __int_as_float(0x7f800000), ok ? v : kNoPos, lane);
+                    th_d = __shfl_sync(0xffffffffu, dk[KPT - 1], 31);
+                    th_p = __shfl_sync(0xffffffffu, pk[KPT - 1], 31);
+                    cold = false;
+                } else {
+                    insert_group(acc[u], v, fminf(lim, th_d));
                 }
             }
-            // a full list bounds what the whole CTA still needs: publish its worst distance
+            // a full list bounds what the whole query still needs: publish its worst distance
             // (clamped at 0 so that the integer minimum orders like the float)
             if (lane == 0 && th_d < lim) atomicMin(gth, __float_as_int(fmaxf(th_d, 0.f)));
         }
     };
     Chunk ca, cb;
-    bool have = advance();
-    if (have) fetch(ca);
+    bool have = fetch(ca);
     while (have) {
         // the next chunk's loads are in flight while this one is processed
-        have = advance();
-        if (have) fetch(cb);
+        have = fetch(cb);
         process(ca);
         if (!have) break;
-        have = advance();
-        if (have) fetch(ca);
+        have = fetch(ca);
         process(cb);
     }
 }
@@ -598,7 +712,8 @@ ivfpq_fast_scan_kernel(const ScanArgs a) {
 #pragma unroll
     for (int s = 0; s < 16; ++s) sum.offb[s] = lut_base + 4u * (((s + lane) & 15) + (lane & 16));
     StaticFeed feed(a, q, split + a.S * warp, a.S * (NT / 32), lane, visited);
-    scan_warp_probes<MT, KPT>(a, feed, lane, sum, &s_gth, dk, pk);
+    if (a.by_residual) scan_warp_probes<MT, KPT, true>(a, feed, lane, sum, &s_gth, dk, pk);
+    else scan_warp_probes<MT, KPT, false>(a, feed, lane, sum, &s_gth, dk, pk);
     if (a.scanned && visited) atomicAdd(a.scanned, visited);
 
     // merge the four warp lists, keep the kprime best of the CTA
@@ -644,7 +759,7 @@ constexpr int kPsSlotThreads = kPsWarpsPerSlot * 32;              // 192
 constexpr int kPsThreads = kPsSlots * kPsSlotThreads;             // 768
 constexpr int kPsMaxProbe = 256;                                  // probes whose metadata is staged per slot
 constexpr int kPsMaxKpt = 2;                                      // k' <= 64 (k <= 48)
-constexpr int kPsScratchBytes = 33 * 1024;                        // slot control words, probe metadata, merge buffers
+constexpr int kPsScratchBytes = 24 * 1024;                        // slot control words, probe metadata, merge buffers
 constexpr int kPsSmemBytes = 3 * 65536 + 4096;                    // two aligned tables + gap + room for the scratch
 
 struct RowSum256 {
@@ -666,7 +781,10 @@ __device__ __forceinline__ void slot_barrier(int slot) {
     asm volatile("bar.sync %0, %1;" ::"r"(slot + 1), "n"(kPsSlotThreads) : "memory");
 }
 
-template <int KPT>
+// Per query a slot goes through: table build (all six warps) | barrier | scan | barrier | merge of
+// the six kept lists in the registers of the slot's first warp, which also writes the result, while
+// the other five warps already build the next query's table.
+template <int KPT, bool RESID>
 __global__ void __launch_bounds__(kPsThreads, 1)
 ivfpq_scan_persist_kernel(const ScanArgs a) {
     extern __shared__ __align__(16) uint8_t ps_smem[];
@@ -682,8 +800,8 @@ ivfpq_scan_persist_kernel(const ScanArgs a) {
     const int tbl = slot >> 1, half = slot & 1;
     float* lut = reinterpret_cast<float*>(tabs + tbl * 65536) + half * 32;   // this query's half of the rows
 
-    // scratch: per slot {next query, bound}, then per slot the merge buffers
-    constexpr int E = 256 * KPT;                              // >= 192 * KPT entries, a power of two
+    // scratch: per slot {next query, bound, next probe}, the probes' metadata, the kept lists of
+    // warps 1 .. 5 of every slot
     constexpr int KP = 32 * KPT;
     unsigned int* s_q = reinterpret_cast<unsigned int*>(scratch);            // [4]
     int* s_gth = reinterpret_cast<int*>(scratch + 16);                       // [4]
@@ -691,8 +809,9 @@ ivfpq_scan_persist_kernel(const ScanArgs a) {
     uint32_t* s_pb = reinterpret_cast<uint32_t*>(scratch + 64) + slot * 3 * kPsMaxProbe;   // list begin
     uint32_t* s_pe = s_pb + kPsMaxProbe;                                                   // list end
     float* s_pbase = reinterpret_cast<float*>(s_pe + kPsMaxProbe);                         // coarse distance
-    uint32_t* sp = reinterpret_cast<uint32_t*>(scratch + 64 + kPsSlots * 3 * kPsMaxProbe * 4) + slot * 2 * E;
-    float* sd = reinterpret_cast<float*>(sp + E);
+    uint32_t* sp = reinterpret_cast<uint32_t*>(scratch + 64 + kPsSlots * 3 * kPsMaxProbe * 4) +
+                   slot * 2 * (kPsWarpsPerSlot - 1) * KP;
+    float* sd = reinterpret_cast<float*>(sp + (kPsWarpsPerSlot - 1) * KP);
 
     RowSum256 sum;
 #pragma unroll
@@ -706,27 +825,28 @@ ivfpq_scan_persist_kernel(const ScanArgs a) {
     if (tid_s == 0) {
         s_q[slot] = atomicAdd(a.work, 1u);
         s_gth[slot] = 0x7f800000;
-        s_next[slot] = 0;
+        s_next[slot] = 1;
     }
+    slot_barrier(slot);
     for (;;) {
-        slot_barrier(slot);
         const int64_t q = s_q[slot];
         if (q >= a.nq) break;
         unsigned int q_next = 0;
         if (tid_s == 0) q_next = atomicAdd(a.work, 1u);
         // the probes' metadata: loads issued here, stored to shared memory after the table is built
-        uint32_t m_begin[(kPsMaxProbe + kPsSlotThreads - 1) / kPsSlotThreads] = {0, 0};
-        uint32_t m_end[(kPsMaxProbe + kPsSlotThreads - 1) / kPsSlotThreads] = {0, 0};
-        float m_base[(kPsMaxProbe + kPsSlotThreads - 1) / kPsSlotThreads] = {0.f, 0.f};
+        constexpr int kMeta = (kPsMaxProbe + kPsSlotThreads - 1) / kPsSlotThreads;
+        uint32_t m_begin[kMeta] = {0, 0};
+        uint32_t m_end[kMeta] = {0, 0};
+        float m_base[kMeta] = {0.f, 0.f};
 #pragma unroll
-        for (int j = 0; j < (kPsMaxProbe + kPsSlotThreads - 1) / kPsSlotThreads; ++j) {
+        for (int j = 0; j < kMeta; ++j) {
             const int pidx = tid_s + j * kPsSlotThreads;
             if (pidx < a.nprobe) {
                 const int64_t list = a.cI[q * a.nprobe + pidx];
-                if (list >= 0) {
+                if (list >= 0 && list < a.nlist) {
                     m_begin[j] = static_cast<uint32_t>(a.offsets[list]);
                     m_end[j] = m_begin[j] + static_cast<uint32_t>(a.lens[list]);
-                    if (a.by_residual) m_base[j] = a.cD[q * a.nprobe + pidx];
+                    if (RESID) m_base[j] = a.cD[q * a.nprobe + pidx];
                 }
             }
         }
@@ -736,7 +856,7 @@ ivfpq_scan_persist_kernel(const ScanArgs a) {
             default: build_scan_table<0>(a, q, 1, lut, 64, wslot, kPsWarpsPerSlot); break;
         }
 #pragma unroll
-        for (int j = 0; j < (kPsMaxProbe + kPsSlotThreads - 1) / kPsSlotThreads; ++j) {
+        for (int j = 0; j < kMeta; ++j) {
             const int pidx = tid_s + j * kPsSlotThreads;
             if (pidx < a.nprobe) {
                 s_pb[pidx] = m_begin[j];
@@ -745,7 +865,7 @@ ivfpq_scan_persist_kernel(const ScanArgs a) {
                 visited += m_end[j] - m_begin[j];
             }
         }
-        slot_barrier(slot);
+        slot_barrier(slot);   // table and metadata complete (and the previous query's merge has read its lists)
 
         float dk[KPT];
         uint32_t pk[KPT];
@@ -754,64 +874,45 @@ ivfpq_scan_persist_kernel(const ScanArgs a) {
             dk[s] = __int_as_float(0x7f800000);
             pk[s] = kNoPos;
         }
-        SharedFeed feed{s_pb, s_pe, s_pbase, &s_next[slot], a.nprobe, lane};
-        scan_warp_probes<1, KPT>(a, feed, lane, sum, &s_gth[slot], dk, pk);
+        SharedFeed feed{s_pb, s_pe, s_pbase, &s_next[slot], a.nprobe, lane, wslot, kPsWarpsPerSlot, true};
+        scan_warp_probes<1, KPT, RESID>(a, feed, lane, sum, &s_gth[slot], dk, pk);
 
-        // merge the slot's six warp lists, keep the kprime best
+        if (wslot > 0) {
 #pragma unroll
-        for (int s = 0; s < KPT; ++s) {
-            sd[tid_s * KPT + s] = dk[s];
-            sp[tid_s * KPT + s] = pk[s];
+            for (int s = 0; s < KPT; ++s) {
+                sd[(wslot - 1) * KP + lane * KPT + s] = dk[s];
+                sp[(wslot - 1) * KP + lane * KPT + s] = pk[s];
+            }
         }
-        // Every warp's segment [wslot * KP, +KP) is sorted; positions are unique, so the rank of an
-        // entry in the merged order is its index in its own segment plus, for every other segment,
-        // the number of entries below it (binary search).  Ranks below KP are scattered into the
-        // output area behind the segments.
-        float* so_d = sd + kPsSlotThreads * KPT;
-        uint32_t* so_p = sp + kPsSlotThreads * KPT;
-        for (int i = tid_s; i < KP; i += kPsSlotThreads) {
-            so_d[i] = __int_as_float(0x7f800000);
-            so_p[i] = kNoPos;
-        }
-        slot_barrier(slot);
+        if (tid_s == 0) s_q[slot] = q_next;   // read by everybody after the barrier
+        slot_barrier(slot);   // every warp of the slot is done with the table, the bound and the probe counter
+        if (wslot == 0) {
+            if (lane == 0) {
+                s_gth[slot] = 0x7f800000;
+                s_next[slot] = 1;
+            }
+#pragma unroll 1
+            for (int w = 0; w < kPsWarpsPerSlot - 1; ++w) {
+                float od[KPT];
+                uint32_t op[KPT];
 #pragma unroll
-        for (int s = 0; s < KPT; ++s) {
-            const float md = dk[s];
-            const uint32_t mp = pk[s];
-            if (mp == kNoPos) continue;
-            int rank = lane * KPT + s;
-            for (int w = 0; w < kPsWarpsPerSlot; ++w) {
-                if (w == wslot) continue;
-                const float* wd = sd + w * KP;
-                const uint32_t* wp = sp + w * KP;
-                int lo = 0, hi = KP;                  // first index whose entry is not below (md, mp)
-                while (lo < hi) {
-                    const int mid = (lo + hi) >> 1;
-                    if (pair_less<uint32_t>(wd[mid], wp[mid], md, mp)) lo = mid + 1;
-                    else hi = mid;
+                for (int s = 0; s < KPT; ++s) {
+                    od[s] = sd[w * KP + lane * KPT + s];
+                    op[s] = sp[w * KP + lane * KPT + s];
                 }
-                rank += lo;
+                warp_merge_sorted<KPT>(dk, pk, od, op, lane);
             }
-            if (rank < KP) {
-                so_d[rank] = md;
-                so_p[rank] = mp;
+            float* outd = a.fd + q * KP;
+            uint32_t* outp = a.fp + q * KP;
+#pragma unroll
+            for (int s = 0; s < KPT; ++s) {
+                outd[lane * KPT + s] = dk[s];
+                outp[lane * KPT + s] = pk[s];
             }
+            // everything the slot dropped has an approximate distance >= the worst kept one; if the
+            // kept list is not full nothing was dropped
+            if (lane == 31) a.fth[q] = pk[KPT - 1] != kNoPos ? dk[KPT - 1] : __int_as_float(0x7f800000);
         }
-        slot_barrier(slot);
-        float* od = a.fd + q * KP;
-        uint32_t* op = a.fp + q * KP;
-        for (int i = tid_s; i < KP; i += kPsSlotThreads) {
-            od[i] = so_d[i];
-            op[i] = so_p[i];
-        }
-        if (tid_s == 0) {
-            a.fth[q] = so_p[KP - 1] != kNoPos ? so_d[KP - 1] : __int_as_float(0x7f800000);
-            s_q[slot] = q_next;
-            s_gth[slot] = 0x7f800000;
-            s_next[slot] = 0;
-        }
-        // the barrier at the top of the loop orders these writes (and the merge buffers) before the
-        // next query
     }
     if (a.scanned && visited) atomicAdd(a.scanned, visited);
 }
@@ -1184,7 +1285,7 @@ cudaError_t launch_persist(const ScanArgs& a, int kpt, int num_sms, cudaStream_t
     if (e != cudaSuccess) return e;
 #define B200_PS_CASE(KP)                                                                       \
     case KP: {                                                                                 \
-        auto kern = ivfpq_scan_persist_kernel<KP>;                                             \
+        auto kern = a.by_residual ? ivfpq_scan_persist_kernel<KP, true> : ivfpq_scan_persist_kernel<KP, false>; \
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPsSmemBytes); \
         if (e != cudaSuccess) return e;                                                        \
         kern<<<num_sms, kPsThreads, kPsSmemBytes, st>>>(a);                                    \
@@ -1339,7 +1440,7 @@ void IvfpqIndex::train(int64_t n, const float* x_host, int niter, uint64_t seed)
     float* sub = static_cast<float*>(sd.ensure(static_cast<size_t>(n) * dsub_ * 4));
     float* cb = static_cast<float*>(cbd.ensure(static_cast<size_t>(kKsub) * dsub_ * 4));
     B200_CUDA_CHECK(cudaMemcpy(x, x_host, static_cast<size_t>(n) * d_ * 4, cudaMemcpyHostToDevice));
-    kmeans_device(device_, d_, n, x, nlist_, niter, seed, cent, assign);
+    kmeans_device(device_, d_, n, x, nlist_, niter, seed, cent, assign);   // refuses non-finite input
     std::vector<float> hc(static_cast<size_t>(nlist_) * d_), hcb(static_cast<size_t>(M_) * kKsub * dsub_);
     B200_CUDA_CHECK(cudaMemcpy(hc.data(), cent, hc.size() * 4, cudaMemcpyDeviceToHost));
     for (int m = 0; m < M_; ++m) {
@@ -1374,6 +1475,25 @@ void IvfpqIndex::add(int64_t n, const float* x, const int64_t* ids, bool x_on_de
     if (!is_trained()) throw std::invalid_argument("IVFPQ index is not trained (centroids / codebooks missing)");
     DeviceGuard g(device_);
     cudaStream_t st = stream();
+    // A vector with a NaN or an infinite component has no nearest centroid (its assignment would be
+    // -1): the whole batch is refused before anything changes.
+    int* vflag = static_cast<int*>(w_vflag_.ensure(sizeof(int)));
+    auto read_flag = [&]() {
+        int hf = 0;
+        B200_CUDA_CHECK(cudaMemcpyAsync(&hf, vflag, sizeof(int), cudaMemcpyDeviceToHost, st));
+        B200_CUDA_CHECK(cudaStreamSynchronize(st));
+        return hf;
+    };
+    if (x_on_device) {
+        B200_CUDA_CHECK(cudaMemsetAsync(vflag, 0, sizeof(int), st));
+        B200_CUDA_CHECK(launch_check_finite(x, n * d_, vflag, st));
+        if (read_flag()) throw std::invalid_argument("add: x holds NaN or infinite values");
+    } else {
+        const uint32_t* bits = reinterpret_cast<const uint32_t*>(x);
+        uint32_t bad = 0;
+        for (int64_t i = 0; i < n * d_; ++i) bad |= static_cast<uint32_t>((bits[i] & 0x7f800000u) == 0x7f800000u);
+        if (bad) throw std::invalid_argument("add: x holds NaN or infinite values");
+    }
     const int64_t chunk = 1 << 20;
     for (int64_t off = 0; off < n; off += chunk) {
         const int64_t m = std::min(chunk, n - off);
@@ -1391,6 +1511,10 @@ void IvfpqIndex::add(int64_t n, const float* x, const int64_t* ids, bool x_on_de
         coarse_->search_device(m, xd, false, 1, aD, aI, 1);
         int32_t* ln = static_cast<int32_t*>(w_list_.ensure(static_cast<size_t>(m) * 4));
         i64_to_i32_kernel<<<blocks_for(m, 256), 256, 0, st>>>(aI, m, ln);
+        // finite input can still overflow to an infinite distance: no assignment may leave [0, nlist)
+        B200_CUDA_CHECK(cudaMemsetAsync(vflag, 0, sizeof(int), st));
+        B200_CUDA_CHECK(launch_check_range_i32(ln, m, nlist_, vflag, st));
+        if (read_flag()) throw std::invalid_argument("add: a vector could not be assigned to a list (distance overflow)");
         uint8_t* cd = static_cast<uint8_t*>(w_codes_.ensure(static_cast<size_t>(m) * M_));
         encode_kernel<<<blocks_for(m * M_, 8), 256, 0, st>>>(xd, m, d_, M_, dsub_, codebooks_.as<float>(),
                                                              by_residual_ ? 1 : 0, coarse_->rows_f32(), ln, cd);

@@ -19,6 +19,7 @@
 #include "common.cuh"
 #include "device_mem.h"
 #include "flat_index.h"
+#include "select.cuh"
 
 namespace b200 {
 namespace {
@@ -121,11 +122,27 @@ void kmeans_device(int device, int d, int64_t n, const float* x_dev, int k, int 
     const size_t tbytes = std::max(t1, t2);
     void* tp = tmp.ensure(tbytes + 16);
 
+    // A non-finite training vector has no nearest centroid; an assignment outside [0, k) must never
+    // reach the histogram or the update below.
+    DeviceBuffer vflag_buf;
+    int* vflag = static_cast<int*>(vflag_buf.ensure(sizeof(int)));
+    auto read_flag = [&]() {
+        int hf = 0;
+        B200_CUDA_CHECK(cudaMemcpyAsync(&hf, vflag, sizeof(int), cudaMemcpyDeviceToHost, st));
+        B200_CUDA_CHECK(cudaStreamSynchronize(st));
+        return hf;
+    };
+    B200_CUDA_CHECK(cudaMemsetAsync(vflag, 0, sizeof(int), st));
+    B200_CUDA_CHECK(launch_check_finite(x_dev, n * d, vflag, st));
+    if (read_flag()) throw std::invalid_argument("k-means: the training vectors hold NaN or infinite values");
+
     km_init_kernel<<<nblk(static_cast<int64_t>(k) * d, 256), 256, 0, st>>>(x_dev, n, d, k, seed, cent_dev);
     km_iota_kernel<<<nblk(n, 256), 256, 0, st>>>(vin, n);
     B200_CUDA_CHECK(cudaGetLastError());
     for (int it = 0; it < niter; ++it) {
         kmeans_assign_device(flat.get(), st, x_dev, n, d, cent_dev, k, assign, scratch);
+        B200_CUDA_CHECK(launch_check_range_i32(assign, n, k, vflag, st));
+        if (read_flag()) throw std::invalid_argument("k-means: a vector could not be assigned (distance overflow)");
         B200_CUDA_CHECK(cudaMemsetAsync(h, 0, static_cast<size_t>(k + 1) * 8, st));
         km_hist_kernel<<<nblk(n, 256), 256, 0, st>>>(assign, n, h);
         size_t tb = tbytes;
@@ -135,8 +152,11 @@ void kmeans_device(int device, int d, int64_t n, const float* x_dev, int k, int 
         km_update_kernel<<<nblk(static_cast<int64_t>(k) * d, 128), 128, 0, st>>>(x_dev, d, k, o, vout, cent_dev);
         B200_CUDA_CHECK(cudaGetLastError());
     }
-    if (assign_out_dev)   // assignment to the FINAL centroids
+    if (assign_out_dev) {   // assignment to the FINAL centroids
         kmeans_assign_device(flat.get(), st, x_dev, n, d, cent_dev, k, assign, scratch);
+        B200_CUDA_CHECK(launch_check_range_i32(assign, n, k, vflag, st));
+        if (read_flag()) throw std::invalid_argument("k-means: a vector could not be assigned (distance overflow)");
+    }
     B200_CUDA_CHECK(cudaStreamSynchronize(st));
 }
 

@@ -33,6 +33,7 @@ namespace {
 constexpr size_t kMaxCandidates = size_t(1) << 20;   // n * padded ntotal
 constexpr int kMaxKNoAlloc = 1024;
 constexpr int kMaxQueries = 1024;
+constexpr size_t kMaxQueryElems = size_t(1) << 19;                // n * d
 constexpr size_t kCandBytes = kMaxCandidates * 8;                 // 8 MiB of (key, position) pairs
 constexpr size_t kSelBudget = size_t(1) << 20;                    // n * k <= 128 Ki selected pairs (1 MiB)
 constexpr size_t kQopBytes = (size_t(1) << 20) + (size_t(32) << 10);   // n * d * 2 <= 1 MiB operand copy + 16 folded columns per row
@@ -79,7 +80,10 @@ extern "C" int b200idx_search_device_noalloc(b200idx_t* h, int64_t n, const void
         const int64_t n_pad = (v.n + kTileB - 1) / kTileB * kTileB;
         if (n > kMaxQueries || static_cast<size_t>(n) * static_cast<size_t>(n_pad) > kMaxCandidates)
             throw std::invalid_argument("request exceeds the static scratch: n * round_up(ntotal, 256) must be <= 2^20");
-        if (static_cast<size_t>(n) * k * 8 > kSelBudget || static_cast<size_t>(n) * d * 2 > kQopBytes)
+        // The operand copy of an fp32 index is op_cols() = d + 16 bf16 values wide (the folded columns), so
+        // n * d <= 2^19 together with n <= 1024 keeps n * op_cols() * 2 within kQopBytes.
+        if (static_cast<size_t>(n) * k * 8 > kSelBudget || static_cast<size_t>(n) * d > kMaxQueryElems ||
+            static_cast<size_t>(n) * ix->op_cols() * 2 > kQopBytes)
             throw std::invalid_argument("request exceeds the static scratch: n * k <= 131072 and n * d <= 524288");
 
         DeviceGuard g(ix->device());

@@ -780,6 +780,37 @@ cudaError_t launch_f16_to_f32(const void* x, int64_t count, float* out, cudaStre
     return cudaGetLastError();
 }
 
+namespace {
+// flag |= 1 when x holds a NaN or an infinity
+__global__ void check_finite_kernel(const float* x, int64_t count, int* flag) {
+    bool bad = false;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        bad |= (__float_as_uint(x[i]) & 0x7f800000u) == 0x7f800000u;
+    if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(flag, 1);
+}
+// flag |= 2 when a value lies outside [0, bound)
+__global__ void check_range_i32_kernel(const int32_t* v, int64_t count, int32_t bound, int* flag) {
+    bool bad = false;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        bad |= v[i] < 0 || v[i] >= bound;
+    if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(flag, 2);
+}
+}  // namespace
+cudaError_t launch_check_finite(const float* x, int64_t count, int* flag, cudaStream_t stream) {
+    if (count <= 0) return cudaSuccess;
+    int grid = static_cast<int>((count + 255) / 256 < 2048 ? (count + 255) / 256 : 2048);
+    check_finite_kernel<<<grid, 256, 0, stream>>>(x, count, flag);
+    return cudaGetLastError();
+}
+cudaError_t launch_check_range_i32(const int32_t* v, int64_t count, int32_t bound, int* flag, cudaStream_t stream) {
+    if (count <= 0) return cudaSuccess;
+    int grid = static_cast<int>((count + 255) / 256 < 2048 ? (count + 255) / 256 : 2048);
+    check_range_i32_kernel<<<grid, 256, 0, stream>>>(v, count, bound, flag);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_fill_u32(uint32_t* p, int64_t count, uint32_t value, cudaStream_t stream) {
     if (count <= 0) return cudaSuccess;
     int grid = static_cast<int>((count + 255) / 256 < 4096 ? (count + 255) / 256 : 4096);

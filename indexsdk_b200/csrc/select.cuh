@@ -74,6 +74,12 @@ cudaError_t launch_base_prep_i8(const int8_t* x, int64_t n, int d, int32_t* norm
 cudaError_t launch_f32_to_f16(const float* x, int64_t count, void* out, cudaStream_t stream);
 cudaError_t launch_f16_to_f32(const void* x, int64_t count, float* out, cudaStream_t stream);
 
+// Input validation on the device.  *flag (an int the caller zeroed) gets bit 0 when x holds a NaN or
+// an infinity, bit 1 when an assignment lies outside [0, bound): a non-finite vector has no nearest
+// centroid, and an assignment of -1 must never reach a histogram or a gather.
+cudaError_t launch_check_finite(const float* x, int64_t count, int* flag, cudaStream_t stream);
+cudaError_t launch_check_range_i32(const int32_t* v, int64_t count, int32_t bound, int* flag, cudaStream_t stream);
+
 // Small utilities.
 cudaError_t launch_fill_u32(uint32_t* p, int64_t count, uint32_t value, cudaStream_t stream);
 cudaError_t launch_iota_i64(int64_t* p, int64_t count, int64_t start, cudaStream_t stream);

@@ -70,3 +70,30 @@ def test_noalloc_rejects_requests_beyond_the_static_scratch(b200):
     Dr, Ir = _run(ix, ix.search_device, xq[:8], 10)
     np.testing.assert_array_equal(In, Ir)
     np.testing.assert_array_equal(Dn, Dr)
+
+
+def test_noalloc_query_operand_limit_is_enforced_as_documented(b200, oracle_lib):
+    """n * d <= 524288 is the documented limit for the query operand copy.  An fp32 index writes
+    rows of d + 16 bf16 values there, so the largest admitted request (n = 1024, d = 512) must
+    still fit -- checked against the CPU oracle, which shares no scratch with anything -- and the
+    first shape beyond the limit (d = 528) must be refused instead of overrunning the region."""
+    import torch
+    n, k, n_base = 1024, 10, 1000
+    for d, ok in ((512, True), (528, False)):
+        ix = b200.IndexFlat(d, b200.METRIC_L2)
+        xb = datasets.gaussian(n_base, d, seed=11)
+        ix.add(xb)
+        xq_np = datasets.gaussian(n, d, seed=12)
+        xq = torch.from_numpy(xq_np).cuda()
+        if ok:
+            for _ in range(2):
+                Dn, In = _run(ix, ix.search_device_noalloc, xq, k)
+                Dr, Ir = oracle_lib.flat_search(oracle_lib.METRIC_L2, xb, xq_np, k)
+                np.testing.assert_array_equal(In, Ir)
+                np.testing.assert_array_equal(Dn.view(np.uint32), Dr.view(np.uint32))
+        else:
+            D = torch.empty((n, k), dtype=torch.float32, device="cuda")
+            I = torch.empty((n, k), dtype=torch.int64, device="cuda")
+            with pytest.raises(b200.B200IdxError) as e:
+                ix.search_device_noalloc(xq.data_ptr(), n, k, D.data_ptr(), I.data_ptr())
+            assert e.value.code == 2001 and "n * d <= 524288" in e.value.msg
