@@ -42,6 +42,7 @@ def _digest() -> str:
                 with open(p, "rb") as f:
                     h.update(f.read())
     h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(os.environ.get("B200IDX_NVCC_EXTRA", "").encode())
     return h.hexdigest()
 
 
@@ -53,6 +54,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         return LIB_PATH
     nvcc = _nvcc()
     extra = ["-Xptxas", "-v"] if verbose else []
+    # extra nvcc arguments for development builds (e.g. -DB200IDX_DEV_PROF: phase cycle counters)
+    extra += os.environ.get("B200IDX_NVCC_EXTRA", "").split()
 
     def compile_one(src: str) -> str:
         obj = os.path.join(BUILD_DIR, src.replace(".cu", ".o"))

@@ -45,6 +45,7 @@
 
 #include "ivfpq_tc_scan.cuh"
 #include "kmeans.h"
+#include "ptx_sm100.cuh"
 #include "select.cuh"
 
 namespace b200 {
@@ -53,7 +54,6 @@ namespace {
 constexpr int kKsub = 256;
 constexpr int kListPad = 32;     // lists are padded to a multiple of this many vectors
 constexpr int kScanThreads = 128;
-constexpr int kScanWarps = kScanThreads / 32;
 constexpr float kInf = 3.402823466e+38f;   // FLT_MAX used as padding distance
 constexpr uint32_t kNoPos = 0xFFFFFFFFu;
 constexpr int64_t kNoLabel = 0x7fffffffffffffffll;
@@ -378,6 +378,7 @@ struct ScanArgs {
     const int32_t* qlist;    // exact scan: indices of the queries to process
     unsigned long long* scanned;
     unsigned int* work;      // persistent scan: next query to hand out (zeroed before the launch)
+    unsigned long long* prof;   // development builds (-DB200IDX_DEV_PROF): phase cycle counters, else unused
     // > 0: fd / fth come from the tensor-core filter, which already subtracted the error bound of
     // its fp16 product from every value; only fp32 rounding slack remains (twice the table scan's)
     float tc_rel, tc_abs;
@@ -430,26 +431,48 @@ __device__ __forceinline__ void build_scan_table(const ScanArgs& a, int64_t q, i
 #pragma unroll
             for (int t = 0; t < DS; ++t) qr[t] = __ldg(qrow + t);
         }
-#pragma unroll 4
-        for (int c = 2 * warp + half; c < kKsub; c += 2 * nwarps) {
-            const float* cw = a.cbT + (static_cast<size_t>(g * kKsub + c) * 16 + mm) * dsub;
-            float acc = 0.f;
-            if (DS > 0 && DS % 4 == 0) {
+        if (DS > 0 && DS % 4 == 0) {
+            // Four table entries per step, their codeword loads (L2 hits, several hundred cycles
+            // each) issued together: entry after entry this loop is one latency chain per entry.
+            constexpr int B = 4, V = DS > 0 ? DS / 4 : 1;
+            for (int c0 = 2 * warp + half; c0 < kKsub; c0 += 2 * nwarps * B) {
+                float4 cv[B][V];
 #pragma unroll
-                for (int t4 = 0; t4 < DS / 4; ++t4) {
-                    const float4 cv = __ldg(reinterpret_cast<const float4*>(cw) + t4);
-                    const float c4[4] = {cv.x, cv.y, cv.z, cv.w};
+                for (int j = 0; j < B; ++j) {
+                    const int c = min(c0 + 2 * nwarps * j, kKsub - 1);
+                    const float4* cw4 = reinterpret_cast<const float4*>(
+                        a.cbT + (static_cast<size_t>(g * kKsub + c) * 16 + mm) * dsub);
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        if (a.by_residual) {
-                            acc = fmaf(qr[t4 * 4 + u], c4[u], acc);
-                        } else {
-                            const float df = qr[t4 * 4 + u] - c4[u];
-                            acc = fmaf(df, df, acc);
+                    for (int t4 = 0; t4 < V; ++t4) cv[j][t4] = __ldg(cw4 + t4);
+                }
+#pragma unroll
+                for (int j = 0; j < B; ++j) {
+                    const int c = c0 + 2 * nwarps * j;
+                    if (c >= kKsub) break;
+                    float acc = 0.f;
+#pragma unroll
+                    for (int t4 = 0; t4 < V; ++t4) {
+                        const float c4[4] = {cv[j][t4].x, cv[j][t4].y, cv[j][t4].z, cv[j][t4].w};
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            if (a.by_residual) {
+                                acc = fmaf(qr[t4 * 4 + u], c4[u], acc);
+                            } else {
+                                const float df = qr[t4 * 4 + u] - c4[u];
+                                acc = fmaf(df, df, acc);
+                            }
                         }
                     }
+                    if (a.by_residual) acc = -2.f * acc;
+                    float* row = lut + (g * kKsub + c) * pitch;
+                    row[mm + 16 * half] = acc;
+                    row[mm + 16 * (half ^ 1)] = acc;
                 }
-            } else {
+            }
+        } else {
+            for (int c = 2 * warp + half; c < kKsub; c += 2 * nwarps) {
+                const float* cw = a.cbT + (static_cast<size_t>(g * kKsub + c) * 16 + mm) * dsub;
+                float acc = 0.f;
                 for (int t = 0; t < dsub; ++t) {
                     const float qt = __ldg(qrow + t);
                     const float ct = __ldg(cw + t);
@@ -460,11 +483,11 @@ __device__ __forceinline__ void build_scan_table(const ScanArgs& a, int64_t q, i
                         acc = fmaf(df, df, acc);
                     }
                 }
+                if (a.by_residual) acc = -2.f * acc;
+                float* row = lut + (g * kKsub + c) * pitch;
+                row[mm + 16 * half] = acc;
+                row[mm + 16 * (half ^ 1)] = acc;
             }
-            if (a.by_residual) acc = -2.f * acc;
-            float* row = lut + (g * kKsub + c) * pitch;
-            row[mm + 16 * half] = acc;
-            row[mm + 16 * (half ^ 1)] = acc;
         }
     }
 }
@@ -514,13 +537,24 @@ struct StaticFeed {
     }
 };
 
+// L2 prefetch of the codes (and per-vector terms) of list slots [begin, end): one thread, two bulk
+// requests.  begin is a multiple of 32, so both addresses are 128-byte aligned.
+__device__ __forceinline__ void prefetch_list_l2(const ScanArgs& a, uint32_t begin, uint32_t end, bool resid) {
+    if (end <= begin) return;
+    const uint32_t n = end - begin;
+    ptx::bulk_prefetch_l2(a.codes + static_cast<size_t>(begin) * a.M, n * static_cast<uint32_t>(a.M));
+    if (resid) ptx::bulk_prefetch_l2(a.t2 + begin, ((n + 3u) & ~3u) * 4u);
+}
+
 struct SharedFeed {
+    const ScanArgs& a;
     const uint32_t* s_begin;   // [nprobe]
     const uint32_t* s_end;
     const float* s_base;
     int* s_next;               // next probe to hand out (starts at 1)
     int nprobe, lane;
     int wslot, nwarps;         // this warp's place among the warps that share the query
+    bool resid;
     bool first;
     // The nearest list comes first and is split evenly (in 32-vector groups) over the warps of the
     // query: it is where most of the final neighbours sit, so every warp's kept list -- and with it
@@ -539,7 +573,11 @@ struct SharedFeed {
             return true;
         }
         int p = 0;
-        if (lane == 0) p = atomicAdd(s_next, 1);
+        if (lane == 0) {
+            p = atomicAdd(s_next, 1);
+            // the whole list is asked into L2 now; the warp's own loads run a few groups ahead only
+            if (p < nprobe) prefetch_list_l2(a, s_begin[p], s_end[p], resid);
+        }
         p = __shfl_sync(0xffffffffu, p, 0);
         if (p >= nprobe) return false;
         begin = s_begin[p];
@@ -610,6 +648,19 @@ __device__ __forceinline__ void scan_warp_probes(const ScanArgs& a, Feed& feed, 
     auto insert_group = [&](float acc, uint32_t v, float lim) {
         const bool pass = acc <= lim && pair_less<uint32_t>(acc, v, th_d, th_p);
         unsigned bal = __ballot_sync(0xffffffffu, pass);
+        if constexpr (KPT <= 2) {
+            // several candidates at once (the first groups of a near list): sort them and merge the
+            // two sorted lists -- a fixed cost, where insertions form one long dependent chain each
+            if (__popc(bal) >= 4) {
+                float od[KPT];
+                uint32_t op[KPT];
+                warp_fill_sorted<KPT>(od, op, pass ? acc : __int_as_float(0x7f800000), pass ? v : kNoPos, lane);
+                warp_merge_sorted<KPT>(dk, pk, od, op, lane);
+                th_d = __shfl_sync(0xffffffffu, dk[KPT - 1], 31);
+                th_p = __shfl_sync(0xffffffffu, pk[KPT - 1], 31);
+                return;
+            }
+        }
         while (bal) {
             const int src = __ffs(bal) - 1;
             bal &= bal - 1;
@@ -684,8 +735,6 @@ ivfpq_fast_scan_kernel(const ScanArgs a) {
     const int64_t q = blockIdx.x;
     const int split = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr int M = MT * 16;
-
     // Smallest "worst kept distance" of any warp of this CTA whose list is full (float bits, >= 0):
     // nothing above it can reach the CTA's k' best, so every warp also filters with it.
     int& s_gth = *reinterpret_cast<int*>(scan_smem + static_cast<size_t>(MT) * kKsub * 32 * 4);
@@ -781,6 +830,21 @@ __device__ __forceinline__ void slot_barrier(int slot) {
     asm volatile("bar.sync %0, %1;" ::"r"(slot + 1), "n"(kPsSlotThreads) : "memory");
 }
 
+#ifdef B200IDX_DEV_PROF
+// Development build: cycles per phase of the second warp (0-3: table build, wait for the table
+// barrier, scan, wait for the scan barrier) and of the first warp (4-8: the same four, then merge and
+// output) of every slot, summed over slots; 9: queries.
+#define PS_PROF_DECL long long ps_t = clock64(); const int ps_who = tid_s == 32 ? 0 : (tid_s == 0 ? 4 : -1); long long ps_c[5] = {0, 0, 0, 0, 0}; long long ps_n = 0;
+#define PS_PROF_MARK(i) do { if (ps_who >= 0) { const long long ps_now = clock64(); ps_c[i] += ps_now - ps_t; ps_t = ps_now; } } while (0)
+#define PS_PROF_COUNT() do { ++ps_n; } while (0)
+#define PS_PROF_FLUSH() do { if (ps_who >= 0 && a.prof) { for (int i = 0; i < 5; ++i) atomicAdd(a.prof + ps_who + i, static_cast<unsigned long long>(ps_c[i])); if (ps_who == 0) atomicAdd(a.prof + 9, static_cast<unsigned long long>(ps_n)); } } while (0)
+#else
+#define PS_PROF_DECL
+#define PS_PROF_MARK(i) do { } while (0)
+#define PS_PROF_COUNT() do { } while (0)
+#define PS_PROF_FLUSH() do { } while (0)
+#endif
+
 // Per query a slot goes through: table build (all six warps) | barrier | scan | barrier | merge of
 // the six kept lists in the registers of the slot's first warp, which also writes the result, while
 // the other five warps already build the next query's table.
@@ -813,12 +877,6 @@ ivfpq_scan_persist_kernel(const ScanArgs a) {
                    slot * 2 * (kPsWarpsPerSlot - 1) * KP;
     float* sd = reinterpret_cast<float*>(sp + (kPsWarpsPerSlot - 1) * KP);
 
-    RowSum256 sum;
-#pragma unroll
-    for (int s = 0; s < 16; ++s)
-        sum.offb[s] = (tab0 + static_cast<uint32_t>(tbl) * 65536u) |
-                      (static_cast<uint32_t>(half) * 128u + 4u * (((s + lane) & 15) + (lane & 16)));
-
     unsigned long long visited = 0;
     // the slot's next query is drawn from the global counter one query ahead, so that the round
     // trip of the atomic hides behind the scan
@@ -828,9 +886,12 @@ ivfpq_scan_persist_kernel(const ScanArgs a) {
         s_next[slot] = 1;
     }
     slot_barrier(slot);
+    PS_PROF_DECL
+    bool first_query = true;
     for (;;) {
         const int64_t q = s_q[slot];
         if (q >= a.nq) break;
+        PS_PROF_COUNT();
         unsigned int q_next = 0;
         if (tid_s == 0) q_next = atomicAdd(a.work, 1u);
         // the probes' metadata: loads issued here, stored to shared memory after the table is built
@@ -847,14 +908,23 @@ ivfpq_scan_persist_kernel(const ScanArgs a) {
                     m_begin[j] = static_cast<uint32_t>(a.offsets[list]);
                     m_end[j] = m_begin[j] + static_cast<uint32_t>(a.lens[list]);
                     if (RESID) m_base[j] = a.cD[q * a.nprobe + pidx];
+                    // the nearest list is scanned first, by all warps: fetch it while the table is built
+                    if (pidx == 0) prefetch_list_l2(a, m_begin[j], m_end[j], RESID);
                 }
             }
         }
-        switch (a.dsub) {
-            case 4: build_scan_table<4>(a, q, 1, lut, 64, wslot, kPsWarpsPerSlot); break;
-            case 8: build_scan_table<8>(a, q, 1, lut, 64, wslot, kPsWarpsPerSlot); break;
-            default: build_scan_table<0>(a, q, 1, lut, 64, wslot, kPsWarpsPerSlot); break;
+        // The first warp of the slot is busy merging the previous query's lists (below, at the end of
+        // the loop body): the table is built by the other five, by all six for the slot's first query.
+        const int bw = first_query ? wslot : wslot - 1;
+        const int bn = first_query ? kPsWarpsPerSlot : kPsWarpsPerSlot - 1;
+        if (bw >= 0) {
+            switch (a.dsub) {
+                case 4: build_scan_table<4>(a, q, 1, lut, 64, bw, bn); break;
+                case 8: build_scan_table<8>(a, q, 1, lut, 64, bw, bn); break;
+                default: build_scan_table<0>(a, q, 1, lut, 64, bw, bn); break;
+            }
         }
+        first_query = false;
 #pragma unroll
         for (int j = 0; j < kMeta; ++j) {
             const int pidx = tid_s + j * kPsSlotThreads;
@@ -865,7 +935,9 @@ ivfpq_scan_persist_kernel(const ScanArgs a) {
                 visited += m_end[j] - m_begin[j];
             }
         }
+        PS_PROF_MARK(0);
         slot_barrier(slot);   // table and metadata complete (and the previous query's merge has read its lists)
+        PS_PROF_MARK(1);
 
         float dk[KPT];
         uint32_t pk[KPT];
@@ -874,8 +946,18 @@ ivfpq_scan_persist_kernel(const ScanArgs a) {
             dk[s] = __int_as_float(0x7f800000);
             pk[s] = kNoPos;
         }
-        SharedFeed feed{s_pb, s_pe, s_pbase, &s_next[slot], a.nprobe, lane, wslot, kPsWarpsPerSlot, true};
+        // The 16 lookup address constants are formed here, per query, from a value the compiler cannot
+        // see through: kept live across the table build they would push its loads out of registers.
+        uint32_t lv = static_cast<uint32_t>(lane);
+        asm volatile("" : "+r"(lv));
+        RowSum256 sum;
+#pragma unroll
+        for (int s = 0; s < 16; ++s)
+            sum.offb[s] = (tab0 + static_cast<uint32_t>(tbl) * 65536u) |
+                          (static_cast<uint32_t>(half) * 128u + 4u * (((s + lv) & 15u) + (lv & 16u)));
+        SharedFeed feed{a, s_pb, s_pe, s_pbase, &s_next[slot], a.nprobe, lane, wslot, kPsWarpsPerSlot, RESID, true};
         scan_warp_probes<1, KPT, RESID>(a, feed, lane, sum, &s_gth[slot], dk, pk);
+        PS_PROF_MARK(2);
 
         if (wslot > 0) {
 #pragma unroll
@@ -886,6 +968,7 @@ ivfpq_scan_persist_kernel(const ScanArgs a) {
         }
         if (tid_s == 0) s_q[slot] = q_next;   // read by everybody after the barrier
         slot_barrier(slot);   // every warp of the slot is done with the table, the bound and the probe counter
+        PS_PROF_MARK(3);
         if (wslot == 0) {
             if (lane == 0) {
                 s_gth[slot] = 0x7f800000;
@@ -912,8 +995,10 @@ ivfpq_scan_persist_kernel(const ScanArgs a) {
             // everything the slot dropped has an approximate distance >= the worst kept one; if the
             // kept list is not full nothing was dropped
             if (lane == 31) a.fth[q] = pk[KPT - 1] != kNoPos ? dk[KPT - 1] : __int_as_float(0x7f800000);
+            PS_PROF_MARK(4);
         }
     }
+    PS_PROF_FLUSH();
     if (a.scanned && visited) atomicAdd(a.scanned, visited);
 }
 
@@ -1909,7 +1994,22 @@ void IvfpqIndex::search_stages(int64_t nq, const float* xq, int k, float* D, int
             stats_.kernel_launches += 8;
         } else if (persist) {
             a.work = w_work_.as<unsigned int>();
+#ifdef B200IDX_DEV_PROF
+            a.prof = static_cast<unsigned long long*>(w_tc_prof_.ensure(128));
+            B200_CUDA_CHECK(cudaMemsetAsync(a.prof, 0, 128, st));
+#endif
             B200_CUDA_CHECK(launch_persist(a, kpt, num_sms_, st));
+#ifdef B200IDX_DEV_PROF
+            {
+                unsigned long long hp[16];
+                B200_CUDA_CHECK(cudaMemcpyAsync(hp, a.prof, 128, cudaMemcpyDeviceToHost, st));
+                B200_CUDA_CHECK(cudaStreamSynchronize(st));
+                const double nq_s = hp[9] ? static_cast<double>(hp[9]) : 1.0;
+                std::fprintf(stderr, "[persist scan] cycles per query of a slot -- warp 1: build %.0f wait %.0f scan %.0f wait %.0f | "
+                             "warp 0: build %.0f wait %.0f scan %.0f wait %.0f merge %.0f\n", hp[0] / nq_s, hp[1] / nq_s,
+                             hp[2] / nq_s, hp[3] / nq_s, hp[4] / nq_s, hp[5] / nq_s, hp[6] / nq_s, hp[7] / nq_s, hp[8] / nq_s);
+            }
+#endif
         } else {
             B200_CUDA_CHECK(launch_fast(a, kpt, st));
         }
