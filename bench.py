@@ -39,12 +39,13 @@ if ROOT not in sys.path:
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 
-# DRAM bytes per launch of the dominant kernel taken from an ncu capture (see profiles/);
-# None until a capture exists for the workload.
+# DRAM bytes (read + write) per launch of the dominant kernel on ONE GPU, from an ncu capture of
+# that kernel: full-size launch for the IVFPQ scan; quarter-size captures scaled by four for the
+# exact-search GEMMs (their traffic grows with the base).  None until a capture exists.
 NCU_TRAFFIC_BYTES = {
-    "ivfpq10m": 1.616e9,     # profiles/ivfpq_scan_kernels_ivfpq10m.md (full-size launch)
-    "flat1m": 3.21e8,        # profiles/dist_gemm_tc_kernel_flat_quarter.md, 80.2 MB at N = 250 k, x4
-    "int8flat4m": 1.049e9,   # profiles/dist_gemm_tc_kernel_flat_quarter.md, 262.3 MB at N = 1 M, x4
+    "ivfpq10m": 1.616e9,
+    "flat1m": 3.21e8,
+    "int8flat4m": 1.049e9,
 }
 
 
@@ -251,6 +252,7 @@ class Workload:
     nq = 0
     dtype = "f32"
     descending = False
+    full_index = None      # unsharded copy of the index (IVFPQ at N > 1 only)
 
 
 class IvfpqWorkload(Workload):
@@ -265,7 +267,7 @@ class IvfpqWorkload(Workload):
         "ivfpq100m": dict(d=96, nlist=65536, M=48, nprobe=128, k=100, N=100_000_000, seed=6, qseed=7),
     }
 
-    def __init__(self, b, dev, rank, world, by_residual, scale=1.0, name="ivfpq10m"):
+    def __init__(self, b, dev, rank, world, by_residual, scale=1.0, name="ivfpq10m", full_copy=False):
         import torch
         self.name = name
         cfg = self.CONFIGS[name]
@@ -299,14 +301,24 @@ class IvfpqWorkload(Workload):
         self.train_s = time.time() - t0
         self.centroids = cent.cpu().numpy()
         self.codebooks = cb.cpu().numpy()
-        ix = b.IndexIVFPQ(self.d, self.nlist, self.M, 8, by_residual=self.by_residual, device=dev.index)
-        ix.set_centroids(self.centroids)
-        ix.set_codebooks(self.codebooks)
+        def new_index():
+            ix = b.IndexIVFPQ(self.d, self.nlist, self.M, 8, by_residual=self.by_residual, device=dev.index)
+            ix.set_centroids(self.centroids)
+            ix.set_codebooks(self.codebooks)
+            ix.nprobe = self.nprobe
+            return ix
+        ix = new_index()
+        # the unsharded index beside the shard: the replicated (query-parallel) layout, and on rank 0
+        # the lists the CPU oracle searches when the merged sharded result is checked
+        self.full_index = new_index() if (full_copy and world > 1) else None
         t0 = time.time()
         for c in range((self.N + chunk - 1) // chunk):
             n = min(chunk, self.N - c * chunk)
             x = gen(base_seed + c, n)
             ids = np.arange(c * chunk, c * chunk + n, dtype=np.int64)
+            torch.cuda.synchronize(dev)
+            if self.full_index is not None:
+                self.full_index.add_device(x.data_ptr(), n, ids)
             if world > 1:
                 x = x[rank::world].contiguous()
                 ids = ids[rank::world].copy()
@@ -314,17 +326,17 @@ class IvfpqWorkload(Workload):
             ix.add_device(x.data_ptr(), x.shape[0], ids)
             del x
         self.add_s = time.time() - t0
-        ix.nprobe = self.nprobe
         self.index = ix
+        self._gen, self._base_seed, self._chunk = gen, base_seed, chunk
         self.xq = gen(cfg["qseed"], self.nq).cpu().pin_memory()
         self.units_bytes_per_query = self.nprobe * (self.N / self.nlist) * self.M   # algorithmic scan bytes
         lens = np.array([ix.list_length(l) for l in range(self.nlist)], np.float64)
         self.desc = dict(workload="IVFPQ d=%d N=%d nlist=%d M=%dx8bit nprobe=%d k=%d nq=10000 "
                                   "(Gaussian mixture, seeded k-means++ init + 25 Lloyd it on 500k sample)"
                                   % (self.d, self.N, self.nlist, self.M, self.nprobe, self.k),
-                         by_residual=self.by_residual,
-                         list_len_mean=float(lens.mean()), list_len_max=float(lens.max()),
-                         list_len_size_biased_mean=float((lens * lens).sum() / max(lens.sum(), 1)))
+                         by_residual=self.by_residual)
+        self.run_info = dict(list_len_mean=float(lens.mean()), list_len_max=float(lens.max()),
+                             list_len_size_biased_mean=float((lens * lens).sum() / max(lens.sum(), 1)))
 
     def roofline(self, stats, steps, peaks):
         ms = stats["stage_ms"]["scan"] / max(1, stats["stage_launches"]["scan"])
@@ -337,8 +349,15 @@ class IvfpqWorkload(Workload):
                     traffic=NCU_TRAFFIC_BYTES.get(self.name), algorithmic_bytes_per_launch=alg,
                     visited_code_bytes_per_launch=visited, ms_per_launch=ms)
 
+    def first_rows(self, n):
+        """The first n base vectors (ids 0 .. n-1), regenerated."""
+        return self._gen(self._base_seed, min(self._chunk, self.N))[:n].cpu().numpy()
+
     def cpu_reference(self, oracle, nsample):
-        ix = self.index
+        ix = self.full_index if self.full_index is not None else self.index
+        if getattr(self, "_lists", None) is not None:
+            offs, codes, ids = self._lists
+            return self._cpu_run(oracle, offs, codes, ids)
         offs = np.zeros(self.nlist + 1, np.int64)
         lens = np.array([ix.list_length(l) for l in range(self.nlist)], np.int64)
         np.cumsum(lens, out=offs[1:])
@@ -349,6 +368,10 @@ class IvfpqWorkload(Workload):
                 c, i = ix.get_list(l)
                 codes[offs[l]:offs[l + 1]] = c
                 ids[offs[l]:offs[l + 1]] = i
+        self._lists = (offs, codes, ids)
+        return self._cpu_run(oracle, offs, codes, ids)
+
+    def _cpu_run(self, oracle, offs, codes, ids):
         xq = self.xq.numpy()
         variant = 1 if self.by_residual else 0
 
@@ -570,9 +593,10 @@ class MultiFlatWorkload(Workload):
         return run
 
 
-def make_workload(name, b, dev, rank, world, args):
+def make_workload(name, b, dev, rank, world, args, full_copy=False):
     if name in IvfpqWorkload.CONFIGS:
-        w = IvfpqWorkload(b, dev, rank, world, args.by_residual, args.scale, name=name)
+        w = IvfpqWorkload(b, dev, rank, world, args.by_residual, args.scale, name=name,
+                          full_copy=full_copy and IvfpqWorkload.CONFIGS[name]["N"] * args.scale <= 20_000_000)
     elif name == "flat1m":
         w = FlatWorkload(b, dev, rank, world, args.scale)
     elif name == "int8flat4m":
@@ -600,6 +624,186 @@ def time_cpu(run, nq_total, target_s=12.0, first=16):
     return n * reps / total, n * reps, total
 
 
+def probe_faiss():
+    """Is Faiss (the reference's CPU ground truth) importable on this box?  Recorded in the line;
+    when it is, the CPU oracle is cross-checked against it."""
+    try:
+        import faiss  # noqa: F401
+        return dict(importable=True, version=getattr(faiss, "__version__", "?"))
+    except Exception as e:  # ImportError on this image
+        return dict(importable=False, why=type(e).__name__)
+
+
+def faiss_cross_check(wl, oracle):
+    """Only reached when Faiss is importable: the oracle against Faiss' own Flat search on 64 queries."""
+    try:
+        import faiss
+        if not isinstance(wl, FlatWorkload) or wl.xb_host is None:
+            return None
+        ix = faiss.IndexFlatL2(wl.d)
+        ix.add(wl.xb_host)
+        xq = wl.xq.numpy()[:64]
+        Df, If = ix.search(xq, wl.k)
+        Do, Io = oracle.flat_search(oracle.METRIC_L2, wl.xb_host, xq, wl.k)
+        return dict(queries=64, id_agreement=float((If == Io).mean()),
+                    max_rel_distance_error=float(np.max(np.abs(Df - Do) / np.maximum(np.abs(Do), 1e-30))))
+    except Exception as e:
+        return dict(error=str(e)[:200])
+
+
+def parity_against_oracle(wl, oracle, Dg, Ig, m):
+    """The merged GPU results of the first m queries against the CPU oracle on the WHOLE base."""
+    run = wl.cpu_reference(oracle, None)
+    _, Dr, Ir = run(m)
+    if hasattr(wl, "parity_results"):
+        Dg, Ig = wl.parity_results(m)
+    same = float((Ig[:m] == Ir).mean())
+    relerr = float(np.max(np.abs(Dg[:m] - Dr) / np.maximum(np.abs(Dr), 1e-30)))
+    return dict(queries=int(m), id_agreement=same, max_rel_distance_error=relerr,
+                checked="merged result of all ranks against the CPU oracle on the whole base")
+
+
+def encode_check(wl, oracle, nsample=4096):
+    """IVFPQ: the lists the product built (GPU assignment + PQ encoding) against the oracle's own
+    assignment and encoding of the first vectors of the base."""
+    if not isinstance(wl, IvfpqWorkload):
+        return None
+    ix = wl.full_index if wl.full_index is not None else wl.index
+    x = wl.first_rows(nsample)
+    ln = oracle.ivf_assign(wl.centroids, x)
+    codes = oracle.pq_encode(wl.codebooks, x, wl.by_residual, wl.centroids, ln)
+    ok_list = ok_code = 0
+    cache = {}
+    for i in range(x.shape[0]):
+        l = int(ln[i])
+        if l not in cache:
+            cache[l] = ix.get_list(l)
+        c, ids = cache[l]
+        pos = np.flatnonzero(ids == i)
+        if pos.size == 1:
+            ok_list += 1
+            ok_code += int(np.array_equal(c[pos[0]], codes[i]))
+    return dict(vectors=int(x.shape[0]), list_agreement=ok_list / x.shape[0], code_agreement=ok_code / x.shape[0])
+
+
+def reference_arm(wl, args, oracle):
+    """The CPU arm: the oracle port on all host threads, a bounded sample per step."""
+    cores = oracle.use_all_host_threads()
+    nq = wl.nq
+    run = wl.cpu_reference(oracle, None)
+    # each step: a bounded sample sized so that warmup + steps stay within a few minutes
+    budget = 120.0 / max(1, args.steps + args.warmup)
+    t, _, _ = run(min(8, nq))
+    n = int(max(8, min(nq, budget / max(t / min(8, nq), 1e-9))))
+    for _ in range(args.warmup):
+        run(n)
+    times = []
+    for _ in range(args.steps):
+        t, _, _ = run(n)
+        times.append(t)
+    ms = 1e3 * sum(times) / len(times)
+    val = n / (ms * 1e-3)
+    sample = "%d of %d queries per step%s" % (n, nq, getattr(wl, "cpu_note", ""))
+    return dict(metric="QPS", value=val, unit="queries/s", n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, ms_per_step=ms, higher_is_better=True, scaling="strong", vs_baseline=None,
+                dtype=wl.dtype, data="synthetic", impl="reference", config=dict(wl.desc),
+                cpu_baseline=dict(value=val, unit="queries/s", cores=cores, kind="port",
+                                  sample=sample + ", all host threads (OpenMP), CPU oracle port; Faiss is not installed"),
+                e2e=dict(value=val, unit="queries/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                encode_check=encode_check(wl, oracle))
+
+
+def measure(wl, args, b, dev, rank, world, dist, sampler, peaks, mode):
+    """Device-resident and end-to-end timing of one workload; returns the JSON line as a dict."""
+    import torch
+    from indexsdk_b200.sharded import ShardedSearcher
+    k, nq = wl.k, wl.nq
+    index = wl.full_index if (mode == "replica" and wl.full_index is not None) else wl.index
+    searcher = ShardedSearcher(index, descending=wl.descending, mode=mode)
+    xq_host = wl.xq                                            # pinned CPU tensor
+    xq_dev = xq_host.to(dev)
+    outD = torch.empty((nq, k), dtype=torch.float32, pin_memory=True)
+    outI = torch.empty((nq, k), dtype=torch.int64, pin_memory=True)
+    xq_np, outD_np, outI_np = xq_host.numpy(), outD.numpy(), outI.numpy()
+    lib_stream = torch.cuda.ExternalStream(index.stream_ptr, device=dev)
+
+    def step_device():
+        searcher.search_device(xq_dev, k)
+
+    def step_e2e():
+        if world == 1:
+            index.search_into(xq_np, k, outD_np, outI_np)      # host pointers through the C ABI
+        else:
+            searcher.search(xq_host, k, outD, outI)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def timed(fn, steps):
+        # every stage of a step is queued on the index's own stream: two events on it bracket the steps
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record(lib_stream)
+        for _ in range(steps):
+            fn()
+        e1.record(lib_stream)
+        e1.synchronize()
+        torch.cuda.synchronize(dev)
+        t1 = time.perf_counter()
+        sampler.mark(t0, t1)
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / steps
+
+    for _ in range(args.warmup):
+        step_device()
+        step_e2e()
+    index.set_timing(True)
+    s0 = index.stats()
+    ms_dev = timed(step_device, args.steps)
+    s1 = index.stats()
+    index.set_timing(False)
+    ms_e2e = timed(step_e2e, args.steps)
+    # hold phase: the same steps, untimed, for about half a second, so that the clock counters are
+    # read several times under the load that was just timed (same count on every rank)
+    for _ in range(min(2000, max(1, int(500.0 / max(ms_dev, 1e-3))))):
+        step_device()
+    barrier()
+
+    # counters are cumulative: everything below is the difference over the device-resident region
+    stats = dict(s1)
+    stats["scan_codes_delta"] = s1["scan_codes"] - s0["scan_codes"]
+    stats["stage_ms"] = {n: s1["stage_ms"][n] - s0["stage_ms"][n] for n in s1["stage_ms"]}
+    stats["stage_launches"] = {n: s1["stage_launches"][n] - s0["stage_launches"][n] for n in s1["stage_launches"]}
+    # per step at N > 1: + the merge kernel and the unpack copies of the exchange
+    launches = s1["kernel_launches"] - s0["kernel_launches"] + (3 * args.steps if world > 1 else 0)
+    roof = wl.roofline(stats, args.steps, peaks)
+    if world > 1:
+        roof["traffic"] = None           # the ncu capture behind the constant was taken on one GPU
+    par = {"shard": ("single GPU" if world == 1 else
+                     "base sharded over %d ranks (IVFPQ: id mod N, Flat: contiguous slices), one packed NCCL "
+                     "all-gather of per-rank top-k + merge kernel" % world),
+           "replica": "index replicated on %d ranks, queries split evenly, one packed NCCL all-gather of the "
+                      "result slices (the reference's query-parallel search)" % world}[mode]
+    line = dict(metric="QPS", value=nq / (ms_dev * 1e-3), unit="queries/s", n_gpus=world, steps=args.steps,
+                warmup=args.warmup, ms_per_step=ms_dev, higher_is_better=True, scaling="strong", vs_baseline=None,
+                dtype=wl.dtype, data="synthetic", config=dict(wl.desc),
+                run=dict(nq_per_step=nq, l2_flush="inputs larger than L2 (codes/base >> 126 MB)", parallelism=par,
+                         **getattr(wl, "run_info", {})),
+                e2e=dict(value=nq / (ms_e2e * 1e-3), unit="queries/s", ms_per_step=ms_e2e,
+                         h2d_bytes_per_step=int(xq_host.numel() * xq_host.element_size()),
+                         d2h_bytes_per_step=int(nq * k * 12)),
+                gpu_launches=int(launches),
+                roofline=roof,
+                stage_ms_per_step={n: v / args.steps for n, v in stats["stage_ms"].items() if v > 0},
+                fallback_queries_per_step=(s1["fallback_queries"] - s0["fallback_queries"]) / args.steps)
+    return line, (outD_np, outI_np)
+
+
 # --------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -609,8 +813,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="ivfpq10m")
     ap.add_argument("--by-residual", type=int, default=1)
+    ap.add_argument("--parallelism", default="shard", choices=["shard", "replica"],
+                    help="N > 1: shard the base (default) or replicate it and split the queries")
     ap.add_argument("--scale", type=float, default=1.0, help="shrinks the base (development only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra-blocks", action="store_true",
+                    help="default workload only: skip the Flat-1M block (and the replica block at N > 1)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -624,7 +832,6 @@ def main():
     import torch
     import torch.distributed as dist
     import indexsdk_b200 as b
-    from indexsdk_b200.sharded import ShardedSearcher
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
@@ -635,83 +842,21 @@ def main():
     if world > 1 and not ref_arm:
         dist.init_process_group("nccl", device_id=dev)
     eff_world = 1 if ref_arm else world
-
-    t_setup = time.time()
-    wl = make_workload(args.workload, b, dev, 0 if ref_arm else rank, eff_world, args)
-    setup_s = time.time() - t_setup
     peaks = measured_peaks()
-    k, nq = wl.k, wl.nq
+    default_run = args.workload == "ivfpq10m" and not args.no_extra_blocks and args.scale == 1.0
 
     if ref_arm:
         import oracle
-        run = wl.cpu_reference(oracle, None)
-        # each step: a bounded sample sized so that warmup + steps stay within a few minutes
-        budget = 150.0 / max(1, args.steps + args.warmup)
-        t, _, _ = run(min(8, nq))
-        n = int(max(8, min(nq, budget / max(t / min(8, nq), 1e-9))))
-        for _ in range(args.warmup):
-            run(n)
-        times = []
-        for _ in range(args.steps):
-            t, _, _ = run(n)
-            times.append(t)
-        ms = 1e3 * sum(times) / len(times)
-        val = n / (ms * 1e-3)
-        line = dict(metric="QPS", value=val, unit="queries/s", n_gpus=args.gpus, steps=args.steps,
-                    warmup=args.warmup, ms_per_step=ms, higher_is_better=True, scaling="strong", vs_baseline=None,
-                    dtype=wl.dtype, data="synthetic", impl="reference",
-                    config=dict(wl.desc, sample="%d of %d queries per step" % (n, nq)),
-                    cpu_baseline=dict(value=val, unit="queries/s", cores=oracle.num_threads(), kind="port",
-                                      sample="%d queries per step, all host threads (OpenMP), CPU oracle port; "
-                                             "Faiss is not installed" % n),
-                    e2e=dict(value=val, unit="queries/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+        wl = make_workload(args.workload, b, dev, 0, 1, args)
+        line = reference_arm(wl, args, oracle)
+        line["faiss"] = probe_faiss()
+        if default_run:
+            del wl
+            wf = make_workload("flat1m", b, dev, 0, 1, args)
+            fl = reference_arm(wf, args, oracle)
+            line["flat1m"] = {n: fl[n] for n in ("metric", "value", "unit", "ms_per_step", "config", "cpu_baseline")}
         print(json.dumps(line))
         return
-
-    searcher = ShardedSearcher(wl.index, descending=wl.descending)
-    xq_host = wl.xq                                            # pinned CPU tensor
-    xq_dev = xq_host.to(dev)
-    outD = torch.empty((nq, k), dtype=torch.float32, pin_memory=True)
-    outI = torch.empty((nq, k), dtype=torch.int64, pin_memory=True)
-    xq_np, outD_np, outI_np = xq_host.numpy(), outD.numpy(), outI.numpy()
-    lib_stream = torch.cuda.ExternalStream(wl.index.stream_ptr, device=dev)
-
-    def step_device():
-        searcher.search_device(xq_dev, k)
-
-    def step_e2e():
-        if world == 1:
-            wl.index.search_into(xq_np, k, outD_np, outI_np)   # host pointers through the C ABI
-        else:
-            searcher.search(xq_host, k, outD, outI)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
-
-    def timed(fn, steps):
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0 = time.perf_counter()
-        e0.record(lib_stream)
-        for _ in range(steps):
-            fn()
-        torch.cuda.current_stream(dev).synchronize()
-        e1.record(lib_stream)
-        e1.synchronize()
-        torch.cuda.synchronize(dev)
-        t1 = time.perf_counter()
-        wall = t1 - t0
-        sampler.mark(t0, t1)
-        dev_ms = e0.elapsed_time(e1)
-        # the library stream is idle between the host-side stages of a step; wall clock covers
-        # the NCCL / copy work issued on torch's stream.  Take the larger of the two.
-        ms = max(dev_ms, wall * 1e3) if world > 1 else dev_ms
-        t = torch.tensor([ms], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()) / steps, wall * 1e3 / steps
 
     try:
         gpu_uuid = str(torch.cuda.get_device_properties(dev).uuid)
@@ -720,64 +865,56 @@ def main():
     sampler = ClockSampler(local_rank, gpu_uuid)
     if rank == 0:
         sampler.start()
-    for _ in range(args.warmup):
-        step_device()
-        step_e2e()
-    wl.index.set_timing(True)
-    s0 = wl.index.stats()
-    ms_dev, wall_dev = timed(step_device, args.steps)
-    s1 = wl.index.stats()
-    wl.index.set_timing(False)
-    ms_e2e, wall_e2e = timed(step_e2e, args.steps)
-    # hold phase: the same steps, untimed, for about half a second, so that the clock counters are
-    # read several times under the load that was just timed (same count on every rank)
-    for _ in range(min(2000, max(1, int(500.0 / max(ms_dev, 1e-3))))):
-        step_device()
-    barrier()
-    clocks = sampler.stop() if rank == 0 else None
-    s2 = wl.index.stats()
 
-    # counters are cumulative: everything below is the difference over the device-resident region
-    stats = dict(s1)
-    stats["scan_codes_delta"] = s1["scan_codes"] - s0["scan_codes"]
-    stats["stage_ms"] = {n: s1["stage_ms"][n] - s0["stage_ms"][n] for n in s1["stage_ms"]}
-    stats["stage_launches"] = {n: s1["stage_launches"][n] - s0["stage_launches"][n] for n in s1["stage_launches"]}
-    launches = s1["kernel_launches"] - s0["kernel_launches"] + (args.steps if world > 1 else 0)
-    roof = wl.roofline(stats, args.steps, peaks)
+    def one(name, mode, cpu_leg):
+        t_setup = time.time()
+        want_full = world > 1 and (rank == 0 or mode == "replica" or default_run)
+        wl = make_workload(name, b, dev, rank, eff_world, args, full_copy=want_full)
+        setup_s = time.time() - t_setup
+        line, (oD, oI) = measure(wl, args, b, dev, rank, world, dist, sampler, peaks, mode)
+        line["run"]["setup_s"] = round(setup_s, 1)
+        if rank == 0 and not args.no_cpu_baseline:
+            import oracle
+            cores = oracle.use_all_host_threads()
+            m = min(64, wl.nq)
+            if world > 1 and isinstance(wl, IvfpqWorkload) and wl.full_index is None:
+                line["parity_check"] = None      # the whole base is not held by any one rank at this size
+            else:
+                line["parity_check"] = parity_against_oracle(wl, oracle, oD, oI, m)
+            if cpu_leg:
+                run = wl.cpu_reference(oracle, None)
+                qps, n, t = time_cpu(run, wl.nq)
+                line["cpu_baseline"] = dict(value=qps, unit="queries/s", cores=cores, kind="port",
+                                            sample="%d queries (the batch of %d, repeated), %.1f s, CPU oracle port "
+                                                   "with OpenMP on all host threads (Faiss is not installed)%s"
+                                                   % (n, wl.nq, t, getattr(wl, "cpu_note", "")))
+                fx = faiss_cross_check(wl, oracle) if probe_faiss()["importable"] else None
+                if fx:
+                    line["faiss_cross_check"] = fx
+        return line, wl
 
-    # parity spot check inside the bench (rank 0): the timed results against the oracle on a few queries
-    line = dict(metric="QPS", value=nq / (ms_dev * 1e-3), unit="queries/s", n_gpus=world, steps=args.steps,
-                warmup=args.warmup, ms_per_step=ms_dev, higher_is_better=True, scaling="strong", vs_baseline=None,
-                dtype=wl.dtype, data="synthetic",
-                config=dict(wl.desc, nq_per_step=nq, l2_flush="inputs larger than L2 (codes/base >> 126 MB)",
-                            parallelism=("single GPU" if world == 1 else "base sharded by id mod %d, NCCL all-gather "
-                                         "of per-rank top-k + merge kernel" % world),
-                            setup_s=round(setup_s, 1)),
-                e2e=dict(value=nq / (ms_e2e * 1e-3), unit="queries/s", ms_per_step=ms_e2e,
-                         h2d_bytes_per_step=int(xq_host.numel() * xq_host.element_size()),
-                         d2h_bytes_per_step=int(nq * k * 12)),
-                gpu_launches=int(launches),
-                roofline=roof,
-                stage_ms_per_step={n: v / args.steps for n, v in stats["stage_ms"].items() if v > 0},
-                fallback_queries_per_step=(s1["fallback_queries"] - s0["fallback_queries"]) / args.steps,
-                clocks=clocks)
-
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        import oracle
-        run = wl.cpu_reference(oracle, None)
-        qps, n, t = time_cpu(run, nq)
-        line["cpu_baseline"] = dict(value=qps, unit="queries/s", cores=oracle.num_threads(), kind="port",
-                                    sample="%d queries (the batch of %d, repeated), %.1f s, CPU oracle port with "
-                                           "OpenMP on all host threads (Faiss is not installed)%s"
-                                           % (n, nq, t, getattr(wl, "cpu_note", "")))
-        # parity of the timed GPU results against the same oracle run
-        _, Dr, Ir = run(min(n, 64))
-        m = Dr.shape[0]
-        Dg, Ig = wl.parity_results(m) if hasattr(wl, "parity_results") else (outD_np[:m], outI_np[:m])
-        same = float((Ig == Ir).mean())
-        relerr = float(np.max(np.abs(Dg - Dr) / np.maximum(np.abs(Dr), 1e-30)))
-        line["parity_check"] = dict(queries=m, id_agreement=same, max_rel_distance_error=relerr)
+    line, wl = one(args.workload, args.parallelism, cpu_leg=(world == 1))
     if rank == 0:
+        line["faiss"] = probe_faiss()
+    if default_run:
+        # The metric names two workloads; the exact-search one follows as its own block, and at
+        # N > 1 the replicated (query-parallel) layout of the IVFPQ index next to the sharded one.
+        if world > 1 and args.parallelism == "shard":
+            rl, _ = measure(wl, args, b, dev, rank, world, dist, sampler, peaks, "replica")
+            if rank == 0:
+                line["replica"] = {n: rl[n] for n in ("value", "unit", "ms_per_step", "e2e", "run", "stage_ms_per_step")}
+        del wl
+        torch.cuda.empty_cache()
+        fl, _ = one("flat1m", "shard", cpu_leg=(world == 1))
+        if rank == 0:
+            keep = ("metric", "value", "unit", "n_gpus", "ms_per_step", "dtype", "config", "run", "e2e", "gpu_launches",
+                    "roofline", "stage_ms_per_step", "fallback_queries_per_step", "parity_check", "cpu_baseline")
+            line["flat1m"] = {n: fl[n] for n in keep if n in fl}
+    if rank == 0:
+        line["clocks"] = sampler.stop()
+        # the exact-search block goes last so that it survives in a truncated tail of the output
+        if "flat1m" in line:
+            line["flat1m"] = line.pop("flat1m")
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

@@ -103,6 +103,14 @@ int b200idx_search_multi(b200idx_t* const* hs, int nh, int64_t n, const void* x,
 int b200idx_merge_topk_device(int nsrc, int64_t n, int k, int descending, const float* Din_dev,
                               const int64_t* Iin_dev, float* D_dev, int64_t* I_dev, void* stream);
 
+/* The same for sources that are src_stride_bytes apart (a multiple of 8): source s has its distances
+ * at Din_dev + s * src_stride_bytes and its labels at Iin_dev + s * src_stride_bytes (byte offsets).
+ * This is the layout one all-gather of packed per-rank blocks [n*k distances | n*k labels] leaves in
+ * local memory, so the results of all ranks are exchanged with ONE collective and merged in place. */
+int b200idx_merge_topk_device_strided(int nsrc, int64_t n, int k, int descending, const float* Din_dev,
+                                      const int64_t* Iin_dev, int64_t src_stride_bytes, float* D_dev,
+                                      int64_t* I_dev, void* stream);
+
 /* ---- reset / remove_ids / bookkeeping: FR/ascend/AscendIndex.h:77,91;
  *      getBaseSize / getBase / getIdxMap FR/ascend/AscendIndexFlat.h:69-75,
  *      FR/ascend/AscendIndexInt8Flat.h:78-84. ---- */
@@ -197,6 +205,12 @@ void* b200idx_stream(const b200idx_t* h);
 
 /* Message of the last failing call on this handle (h = NULL: last failing create). */
 const char* b200idx_last_error(const b200idx_t* h);
+/* The status code this library returns for an internal failure with the given message: a device-side
+ * wait that ran out of its bound (the kernels give every mbarrier / flag wait a limit and report
+ * through an error word) maps to B200IDX_ERR_TIMEOUT, anything else to B200IDX_ERR_INNER -- the
+ * reference's APP_ERR_TIMEOUT for its bounded flag wait, FR/ops/cpukernel/impl/utils/kernel_utils.h:105-155,
+ * FR/common/ErrorCode.h:62.  Host-only; lets the translation be checked without a device fault. */
+int b200idx_status_of_message(const char* message);
 const char* b200idx_version(void);
 
 #ifdef __cplusplus

@@ -69,6 +69,7 @@ def load() -> C.CDLL:
         "b200idx_search_device_noalloc": (i32, [vp, i64, vp, i32, vp, vp]),
         "b200idx_search_multi": (i32, [pp, i32, i64, vp, i32, vp, vp, i32]),
         "b200idx_merge_topk_device": (i32, [i32, i64, i32, i32, vp, vp, vp, vp, vp]),
+        "b200idx_merge_topk_device_strided": (i32, [i32, i64, i32, i32, vp, vp, i64, vp, vp, vp]),
         "b200idx_reset": (i32, [vp]),
         "b200idx_remove_ids": (i32, [vp, i64, vp, C.POINTER(i64)]),
         "b200idx_ntotal": (i64, [vp]),
@@ -96,6 +97,7 @@ def load() -> C.CDLL:
         "b200idx_set_timing": (i32, [vp, i32]),
         "b200idx_stream": (vp, [vp]),
         "b200idx_last_error": (C.c_char_p, [vp]),
+        "b200idx_status_of_message": (i32, [C.c_char_p]),
         "b200idx_version": (C.c_char_p, []),
     }
     for name, (res, args) in sigs.items():
@@ -110,12 +112,13 @@ EXPORTED_SYMBOLS = [
     "b200idx_create_flat", "b200idx_create_int8flat", "b200idx_create_ivfpq", "b200idx_destroy", "b200idx_add",
     "b200idx_add_f16", "b200idx_add_device", "b200idx_search", "b200idx_search_f16", "b200idx_search_device",
     "b200idx_search_device_noalloc",
-    "b200idx_search_multi", "b200idx_merge_topk_device", "b200idx_reset", "b200idx_remove_ids", "b200idx_ntotal",
+    "b200idx_search_multi", "b200idx_merge_topk_device", "b200idx_merge_topk_device_strided", "b200idx_reset", "b200idx_remove_ids", "b200idx_ntotal",
     "b200idx_dim", "b200idx_device", "b200idx_get_base", "b200idx_get_ids", "b200idx_ivfpq_set_centroids",
     "b200idx_ivfpq_set_codebooks", "b200idx_ivfpq_get_centroids", "b200idx_ivfpq_get_codebooks",
     "b200idx_search_with_masks", "b200idx_save", "b200idx_load", "b200idx_kmeans", "b200idx_ivfpq_train", "b200idx_ivfpq_add_codes", "b200idx_ivfpq_set_nprobe", "b200idx_ivfpq_coarse_device",
     "b200idx_ivfpq_search_preassigned_device", "b200idx_ivfpq_get_nprobe", "b200idx_ivfpq_list_length",
     "b200idx_ivfpq_get_list", "b200idx_stats", "b200idx_set_timing", "b200idx_stream", "b200idx_last_error",
+    "b200idx_status_of_message",
     "b200idx_version",
 ]
 
@@ -425,8 +428,17 @@ def search_multi(indexes, x, k: int, merged: bool = True):
 
 
 def merge_topk_device(nsrc: int, n: int, k: int, descending: bool, Din_ptr: int, Iin_ptr: int, D_ptr: int,
-                      I_ptr: int, stream_ptr: int = 0):
-    rc = load().b200idx_merge_topk_device(nsrc, n, k, int(descending), C.c_void_p(Din_ptr), C.c_void_p(Iin_ptr),
-                                          C.c_void_p(D_ptr), C.c_void_p(I_ptr), C.c_void_p(stream_ptr))
+                      I_ptr: int, stream_ptr: int = 0, src_stride_bytes: int = 0):
+    """Merge of nsrc sorted per-source results on the device.  src_stride_bytes = 0: dense
+    [nsrc][n][k] arrays; otherwise the byte distance between the blocks of consecutive sources
+    (packed per-rank blocks after one all-gather)."""
+    lib = load()
+    if src_stride_bytes:
+        rc = lib.b200idx_merge_topk_device_strided(nsrc, n, k, int(descending), C.c_void_p(Din_ptr),
+                                                   C.c_void_p(Iin_ptr), src_stride_bytes, C.c_void_p(D_ptr),
+                                                   C.c_void_p(I_ptr), C.c_void_p(stream_ptr))
+    else:
+        rc = lib.b200idx_merge_topk_device(nsrc, n, k, int(descending), C.c_void_p(Din_ptr), C.c_void_p(Iin_ptr),
+                                           C.c_void_p(D_ptr), C.c_void_p(I_ptr), C.c_void_p(stream_ptr))
     if rc:
         raise B200IdxError(rc, "merge_topk_device failed")

@@ -356,6 +356,15 @@ int b200idx_merge_topk_device(int nsrc, int64_t n, int k, int descending, const 
     return e == cudaSuccess ? B200IDX_OK : B200IDX_ERR_INNER;
 }
 
+int b200idx_merge_topk_device_strided(int nsrc, int64_t n, int k, int descending, const float* Din, const int64_t* Iin,
+                                      int64_t src_stride_bytes, float* D, int64_t* I, void* stream) {
+    if (nsrc <= 0 || n <= 0 || k <= 0 || !Din || !Iin || !D || !I) return B200IDX_ERR_INVALID_PARAM;
+    if (src_stride_bytes <= 0 || src_stride_bytes % 8 != 0) return B200IDX_ERR_INVALID_PARAM;
+    cudaError_t e = launch_merge_topk(nsrc, n, k, descending, Din, Iin, D, I, static_cast<cudaStream_t>(stream),
+                                      src_stride_bytes / 4, src_stride_bytes / 8);
+    return e == cudaSuccess ? B200IDX_OK : B200IDX_ERR_INNER;
+}
+
 int b200idx_reset(b200idx_t* h) {
     if (!h) return B200IDX_ERR_INVALID_PARAM;
     return guarded(h, [&] {
@@ -711,6 +720,11 @@ const char* b200idx_last_error(const b200idx_t* h) {
     if (h) return h->last_error.c_str();
     std::lock_guard<std::mutex> l(g_create_mutex);
     return g_create_error.c_str();
+}
+
+int b200idx_status_of_message(const char* message) {
+    if (!message) return B200IDX_ERR_INVALID_PARAM;
+    return status_of_error(message);
 }
 
 const char* b200idx_version(void) { return "b200idx 0.1 (sm_100a)"; }

@@ -410,8 +410,8 @@ __global__ void emit_kernel(const EmitArgs e) {
 
 // One warp per query; heads[] in shared memory.
 __global__ void __launch_bounds__(32)
-merge_topk_kernel(int nsrc, int64_t nq, int k, int descending, const float* Din, const int64_t* Iin, float* D,
-                  int64_t* I) {
+merge_topk_kernel(int nsrc, int64_t nq, int k, int descending, const float* Din, const int64_t* Iin,
+                  int64_t src_stride_d, int64_t src_stride_i, float* D, int64_t* I) {
     extern __shared__ int heads[];
     const int64_t q = blockIdx.x;
     const int lane = threadIdx.x;
@@ -424,13 +424,14 @@ merge_topk_kernel(int nsrc, int64_t nq, int k, int descending, const float* Din,
         for (int s = lane; s < nsrc; s += 32) {
             const int h = heads[s];
             if (h >= k) continue;
-            const int64_t off = (static_cast<int64_t>(s) * nq + q) * k + h;
-            const int64_t l = Iin[off];
+            const int64_t off = q * k + h;
+            const int64_t l = Iin[s * src_stride_i + off];
             if (l < 0) {
                 heads[s] = k;
                 continue;
             }
-            const float key = descending ? -Din[off] : Din[off];
+            const float dv = Din[s * src_stride_d + off];
+            const float key = descending ? -dv : dv;
             if (bs < 0 || key < bk || (key == bk && l < bl)) {
                 bk = key;
                 bl = l;
@@ -718,10 +719,12 @@ cudaError_t launch_emit(const EmitArgs& e, cudaStream_t stream) {
 }
 
 cudaError_t launch_merge_topk(int nsrc, int64_t nq, int k, int descending, const float* Din, const int64_t* Iin,
-                              float* D, int64_t* I, cudaStream_t stream) {
+                              float* D, int64_t* I, cudaStream_t stream, int64_t src_stride_d, int64_t src_stride_i) {
     if (nq <= 0 || k <= 0) return cudaSuccess;
+    if (src_stride_d <= 0) src_stride_d = nq * k;
+    if (src_stride_i <= 0) src_stride_i = nq * k;
     merge_topk_kernel<<<static_cast<unsigned>(nq), 32, static_cast<size_t>(nsrc) * sizeof(int), stream>>>(
-        nsrc, nq, k, descending, Din, Iin, D, I);
+        nsrc, nq, k, descending, Din, Iin, src_stride_d, src_stride_i, D, I);
     return cudaGetLastError();
 }
 

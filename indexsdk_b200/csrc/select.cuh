@@ -51,9 +51,12 @@ struct EmitArgs {
 cudaError_t launch_emit(const EmitArgs& e, cudaStream_t stream);
 
 // Merge nsrc sorted lists per query.  Din/Iin: [nsrc][nq][k]; order by (distance ascending or
-// score descending, label ascending); label < 0 marks padding.
+// score descending, label ascending); label < 0 marks padding.  src_stride_d / src_stride_i: elements
+// between the blocks of consecutive sources (0: nq * k, i.e. dense arrays) -- lets the per-rank
+// results of one packed all-gather (distances and labels of a rank side by side) be merged in place.
 cudaError_t launch_merge_topk(int nsrc, int64_t nq, int k, int descending, const float* Din, const int64_t* Iin,
-                              float* D, int64_t* I, cudaStream_t stream);
+                              float* D, int64_t* I, cudaStream_t stream, int64_t src_stride_d = 0,
+                              int64_t src_stride_i = 0);
 
 // Query preparation.  fp32 queries -> bf16 operand copy, squared norms and the filter slack
 // eps[q] (see flat_index.cu); fp16 / int8 queries -> norms only.

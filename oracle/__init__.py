@@ -182,6 +182,21 @@ def num_threads() -> int:
     return int(lib().orc_num_threads())
 
 
+def set_num_threads(n: int) -> int:
+    """OpenMP threads used by the following calls; returns the count in effect."""
+    return int(lib().orc_set_num_threads(C.c_int(int(n))))
+
+
+def use_all_host_threads() -> int:
+    """All hardware threads this process may run on, whatever OMP_NUM_THREADS said at start-up
+    (torchrun exports OMP_NUM_THREADS=1 to its workers)."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    return set_num_threads(n)
+
+
 # ---------------------------------------------------------------------------
 # Independent numpy mirror (float64, argsort) used to cross-check oracle.c.
 # ---------------------------------------------------------------------------

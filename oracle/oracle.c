@@ -167,6 +167,34 @@ static inline void ip_canon_qblock(const float* qT, const float* y, int d, float
         for (int b = 0; b < ORC_B; ++b) acc[b] = fmaf(qT[i * ORC_B + b], yi, acc[b]);
     }
 }
+/* the same for four base rows at a time: four times as many independent fmaf chains in flight (a
+ * single chain over the dimension is bound by the latency of fmaf, not by its throughput) */
+#define ORC_R 4
+static inline void l2_canon_qblock_rows(const float* qT, const float* y, int d, float acc[ORC_R][ORC_B]) {
+    for (int r = 0; r < ORC_R; ++r)
+        for (int b = 0; b < ORC_B; ++b) acc[r][b] = 0.f;
+    for (int i = 0; i < d; ++i) {
+        for (int r = 0; r < ORC_R; ++r) {
+            const float yi = y[(size_t)r * d + i];
+#pragma omp simd
+            for (int b = 0; b < ORC_B; ++b) {
+                float t = qT[i * ORC_B + b] - yi;
+                acc[r][b] = fmaf(t, t, acc[r][b]);
+            }
+        }
+    }
+}
+static inline void ip_canon_qblock_rows(const float* qT, const float* y, int d, float acc[ORC_R][ORC_B]) {
+    for (int r = 0; r < ORC_R; ++r)
+        for (int b = 0; b < ORC_B; ++b) acc[r][b] = 0.f;
+    for (int i = 0; i < d; ++i) {
+        for (int r = 0; r < ORC_R; ++r) {
+            const float yi = y[(size_t)r * d + i];
+#pragma omp simd
+            for (int b = 0; b < ORC_B; ++b) acc[r][b] = fmaf(qT[i * ORC_B + b], yi, acc[r][b]);
+        }
+    }
+}
 /* one query against a block of ORC_B rows stored transposed yT[i][ORC_B] */
 static inline void l2_canon_yblock(const float* q, const float* yT, int d, float* acc) {
     for (int b = 0; b < ORC_B; ++b) acc[b] = 0.f;
@@ -205,35 +233,56 @@ int orc_flat_search(int metric, int d, int64_t nb, const float* xb, const int64_
     if (d <= 0 || nb < 0 || nq < 0 || k <= 0) return -1;
     int fail = 0;
     if (!precise && nq > 0) {
-        /* blocks of ORC_B queries share every pass over the base */
+        /* Cache-blocked: the base is walked once per call in blocks of about 1 MB; every block of
+         * ORC_B queries (transposed, one SIMD lane per query) meets a base block while it is in
+         * cache.  Every (query, row) pair is still the canonical sequential sum, and every query
+         * still sees the rows in increasing order, so the results are those of the plain loop. */
         float* qT = transpose_blocks(xq, nq, d);
         if (!qT) return -2;
         const int64_t nblk = (nq + ORC_B - 1) / ORC_B;
+        orc_item* heaps = (orc_item*)malloc(sizeof(orc_item) * (size_t)k * (size_t)nblk * ORC_B);
+        int* cnt = (int*)calloc((size_t)nblk * ORC_B, sizeof(int));
+        if (!heaps || !cnt) { free(qT); free(heaps); free(cnt); return -2; }
+        int64_t jb = ((int64_t)1 << 20) / ((int64_t)d * 4);
+        if (jb < 64) jb = 64;
+        jb = jb / ORC_R * ORC_R;
+        const int l2 = metric == ORC_METRIC_L2;
+        for (int64_t j0 = 0; j0 < nb; j0 += jb) {
+            const int64_t j1 = j0 + jb < nb ? j0 + jb : nb;
 #pragma omp parallel for schedule(dynamic, 1)
-        for (int64_t blk = 0; blk < nblk; ++blk) {
-            orc_item* h = (orc_item*)malloc(sizeof(orc_item) * (size_t)k * ORC_B);
-            if (!h) { fail = 1; continue; }
-            int n[ORC_B] = {0};
-            const float* qb = qT + blk * d * ORC_B;
-            const int live = (int)((nq - blk * ORC_B) < ORC_B ? (nq - blk * ORC_B) : ORC_B);
-            float acc[ORC_B];
-            for (int64_t j = 0; j < nb; ++j) {
-                if (metric == ORC_METRIC_L2) l2_canon_qblock(qb, xb + j * d, d, acc);
-                else ip_canon_qblock(qb, xb + j * d, d, acc);
-                for (int b = 0; b < live; ++b)
-                    heap_offer(h + (size_t)b * k, &n[b], k, metric == ORC_METRIC_L2 ? (double)acc[b] : -(double)acc[b], j);
+            for (int64_t blk = 0; blk < nblk; ++blk) {
+                orc_item* h = heaps + (size_t)blk * ORC_B * k;
+                int* n = cnt + blk * ORC_B;
+                const float* qb = qT + blk * d * ORC_B;
+                const int live = (int)((nq - blk * ORC_B) < ORC_B ? (nq - blk * ORC_B) : ORC_B);
+                float acc4[ORC_R][ORC_B];
+                int64_t j = j0;
+                for (; j + ORC_R <= j1; j += ORC_R) {
+                    if (l2) l2_canon_qblock_rows(qb, xb + j * d, d, acc4);
+                    else ip_canon_qblock_rows(qb, xb + j * d, d, acc4);
+                    for (int r = 0; r < ORC_R; ++r)
+                        for (int b = 0; b < live; ++b)
+                            heap_offer(h + (size_t)b * k, &n[b], k, l2 ? (double)acc4[r][b] : -(double)acc4[r][b], j + r);
+                }
+                for (; j < j1; ++j) {
+                    if (l2) l2_canon_qblock(qb, xb + j * d, d, acc4[0]);
+                    else ip_canon_qblock(qb, xb + j * d, d, acc4[0]);
+                    for (int b = 0; b < live; ++b)
+                        heap_offer(h + (size_t)b * k, &n[b], k, l2 ? (double)acc4[0][b] : -(double)acc4[0][b], j);
+                }
             }
-            for (int b = 0; b < live; ++b) {
-                const int64_t q = blk * ORC_B + b;
-                heap_emit(h + (size_t)b * k, n[b], k, metric != ORC_METRIC_L2, D + q * k, I + q * k);
-                if (labels)
-                    for (int j = 0; j < k; ++j)
-                        if (I[q * k + j] >= 0) I[q * k + j] = labels[I[q * k + j]];
-            }
-            free(h);
         }
+#pragma omp parallel for schedule(static)
+        for (int64_t q = 0; q < nq; ++q) {
+            heap_emit(heaps + (size_t)q * k, cnt[q], k, !l2, D + q * k, I + q * k);
+            if (labels)
+                for (int j = 0; j < k; ++j)
+                    if (I[q * k + j] >= 0) I[q * k + j] = labels[I[q * k + j]];
+        }
+        free(heaps);
+        free(cnt);
         free(qT);
-        return fail ? -2 : 0;
+        return 0;
     }
 #pragma omp parallel for schedule(dynamic, 1)
     for (int64_t q = 0; q < nq; ++q) {
@@ -286,34 +335,47 @@ void orc_round_bf16(int64_t n, const float* x, float* out) {
 int orc_int8_search(int metric, int d, int64_t nb, const int8_t* xb, const int64_t* labels,
                     int64_t nq, const int8_t* xq, int k, float* D, int64_t* I) {
     if (d <= 0 || nb < 0 || nq < 0 || k <= 0) return -1;
-    int fail = 0;
+    if (nq == 0) return 0;
+    /* cache-blocked like orc_flat_search: base blocks of about 1 MB, all queries against a block
+     * while it is in cache; integer arithmetic, so the order of the sums is immaterial */
+    orc_item* heaps = (orc_item*)malloc(sizeof(orc_item) * (size_t)k * (size_t)nq);
+    int* cnt = (int*)calloc((size_t)nq, sizeof(int));
+    if (!heaps || !cnt) { free(heaps); free(cnt); return -2; }
+    int64_t jb = ((int64_t)1 << 20) / (int64_t)d;
+    if (jb < 64) jb = 64;
+    for (int64_t j0 = 0; j0 < nb; j0 += jb) {
+        const int64_t j1 = j0 + jb < nb ? j0 + jb : nb;
 #pragma omp parallel for schedule(dynamic, 1)
-    for (int64_t q = 0; q < nq; ++q) {
-        orc_item* h = (orc_item*)malloc(sizeof(orc_item) * (size_t)k);
-        if (!h) { fail = 1; continue; }
-        int n = 0;
-        const int8_t* qv = xq + q * d;
-        for (int64_t j = 0; j < nb; ++j) {
-            const int8_t* yv = xb + j * d;
-            int32_t acc = 0;
-            if (metric == ORC_METRIC_L2) {
-                for (int i = 0; i < d; ++i) {
-                    int32_t t = (int32_t)qv[i] - (int32_t)yv[i];
-                    acc += t * t;
+        for (int64_t q = 0; q < nq; ++q) {
+            orc_item* h = heaps + (size_t)q * k;
+            int* n = cnt + q;
+            const int8_t* qv = xq + q * d;
+            for (int64_t j = j0; j < j1; ++j) {
+                const int8_t* yv = xb + j * d;
+                int32_t acc = 0;
+                if (metric == ORC_METRIC_L2) {
+                    for (int i = 0; i < d; ++i) {
+                        int32_t t = (int32_t)qv[i] - (int32_t)yv[i];
+                        acc += t * t;
+                    }
+                    heap_offer(h, n, k, (double)acc, j);
+                } else {
+                    for (int i = 0; i < d; ++i) acc += (int32_t)qv[i] * (int32_t)yv[i];
+                    heap_offer(h, n, k, -(double)acc, j);
                 }
-                heap_offer(h, &n, k, (double)acc, j);
-            } else {
-                for (int i = 0; i < d; ++i) acc += (int32_t)qv[i] * (int32_t)yv[i];
-                heap_offer(h, &n, k, -(double)acc, j);
             }
         }
-        heap_emit(h, n, k, metric != ORC_METRIC_L2, D + q * k, I + q * k);
+    }
+#pragma omp parallel for schedule(static)
+    for (int64_t q = 0; q < nq; ++q) {
+        heap_emit(heaps + (size_t)q * k, cnt[q], k, metric != ORC_METRIC_L2, D + q * k, I + q * k);
         if (labels)
             for (int j = 0; j < k; ++j)
                 if (I[q * k + j] >= 0) I[q * k + j] = labels[I[q * k + j]];
-        free(h);
     }
-    return fail ? -2 : 0;
+    free(heaps);
+    free(cnt);
+    return 0;
 }
 
 /* ---- IVFPQ ---- */
@@ -457,6 +519,18 @@ int orc_merge_topk(int nsrc, int64_t nq, int k, int descending, const float* Din
         free(h);
     }
     return 0;
+}
+
+/* Sets the OpenMP thread count of the following calls (a launcher may have exported
+ * OMP_NUM_THREADS=1 for its worker processes); returns the count now in effect. */
+int orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
 }
 
 int orc_num_threads(void) {

@@ -53,3 +53,17 @@ def test_no_cpu_fallback_without_gpu(b200):
     assert b"no CUDA device" in lib.b200idx_last_error(None)
     with pytest.raises(b200.B200IdxError):
         b200.IndexFlat(128)
+
+
+def test_timeout_status_translation(b200):
+    """A kernel whose bounded wait runs out sets a device error word; the host turns that into an
+    exception whose text names the bounded wait, and the C ABI maps such a failure to the
+    reference's APP_ERR_TIMEOUT (2011) -- any other internal failure is APP_ERR_INNER_ERROR (2010).
+    The mapping is host code, so it is checked here with the messages the index classes produce
+    and without making a device wait run out."""
+    lib = b200.load()
+    for msg in (b"device pipeline reported error word 1 (bounded wait ran out)",
+                b"IVFPQ tensor-core scan reported error word 1 (bounded wait ran out)"):
+        assert lib.b200idx_status_of_message(msg) == 2011
+    assert lib.b200idx_status_of_message(b"cudaMalloc failed: out of memory") == 2010
+    assert lib.b200idx_status_of_message(None) == 2001

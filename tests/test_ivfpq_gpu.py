@@ -177,6 +177,42 @@ def test_untrained_index_is_rejected(b200):
     assert e.value.code == 2001 and "not trained" in e.value.msg
 
 
+@pytest.mark.parametrize("bad", [np.nan, np.inf])
+def test_vectors_without_a_nearest_centroid_are_refused(b200, bad):
+    """A NaN or infinite component leaves a vector without a nearest centroid; its assignment would be -1 and must never index a list.  The
+    batch is refused with INVALID_PARAM and the index is left as it was -- from host and from
+    device memory, for add and for training."""
+    import torch
+    d, nlist, M = 32, 16, 4
+    xb, _ = datasets.mixture(3000, d, nlist, seed=4)
+    cent, cb = datasets.train_ivfpq(xb[:2000], nlist, M, False, niter=3)
+    ix = _build(b200, xb[:1000], np.arange(1000, dtype=np.int64), cent, cb, False)
+    before = [ix.get_list(l) for l in range(nlist)]
+    poisoned = xb[1000:1500].copy()
+    poisoned[123, 7] = bad
+    with pytest.raises(b200.B200IdxError) as e:
+        ix.add_with_ids(poisoned, np.arange(1000, 1500, dtype=np.int64))
+    assert e.value.code == 2001
+    xd = torch.from_numpy(poisoned).cuda()
+    with pytest.raises(b200.B200IdxError) as e:
+        ix.add_device(xd.data_ptr(), xd.shape[0], np.arange(1000, 1500, dtype=np.int64))
+    assert e.value.code == 2001
+    assert ix.ntotal == 1000
+    for l in range(nlist):
+        c, i = ix.get_list(l)
+        assert np.array_equal(c, before[l][0]) and np.array_equal(i, before[l][1])
+    # the index still works
+    ix.add_with_ids(xb[1000:1500], np.arange(1000, 1500, dtype=np.int64))
+    assert ix.ntotal == 1500
+    fresh = b200.IndexIVFPQ(d, nlist, M, 8)
+    with pytest.raises(b200.B200IdxError) as e:
+        fresh.train(np.concatenate([xb[:2000], poisoned]), niter=2, seed=1)
+    assert e.value.code == 2001
+    with pytest.raises(b200.B200IdxError) as e:
+        b200.kmeans(poisoned, 8, niter=2)
+    assert e.value.code == 2001
+
+
 @pytest.mark.parametrize("resid", [False, True])
 def test_coarse_plus_preassigned_equals_search(b200, resid):
     """The two halves of a search run apart -- probes selected for slices of the queries, as the
