@@ -290,14 +290,25 @@ class IvfpqWorkload(Workload):
 
         t0 = time.time()
         base_seed = 1000 * cfg["seed"]
-        sample = gen(base_seed, min(chunk, self.N))[:500_000]
-        cent = torch_kmeans(sample, self.nlist, 25, seed=41, plusplus=True)
-        train = sample
-        if self.by_residual:
-            train = sample - cent[assign_torch(sample, cent)]
         dsub = self.d // self.M
-        cb = torch.stack([torch_kmeans(train[:, m * dsub:(m + 1) * dsub].contiguous(), 256, 25, seed=50 + m)
-                          for m in range(self.M)])
+        if rank == 0 or world == 1:
+            sample = gen(base_seed, min(chunk, self.N))[:500_000]
+            cent = torch_kmeans(sample, self.nlist, 25, seed=41, plusplus=True)
+            train = sample
+            if self.by_residual:
+                train = sample - cent[assign_torch(sample, cent)]
+            cb = torch.stack([torch_kmeans(train[:, m * dsub:(m + 1) * dsub].contiguous(), 256, 25, seed=50 + m)
+                              for m in range(self.M)])
+            del sample, train
+        else:
+            cent = torch.empty((self.nlist, self.d), device=dev)
+            cb = torch.empty((self.M, 256, dsub), device=dev)
+        if world > 1:
+            # ONE trained quantizer for all ranks: the k-means above sums with atomics, so two ranks
+            # training on their own would end up with centroids that differ in the last bits
+            import torch.distributed as dist
+            dist.broadcast(cent, 0)
+            dist.broadcast(cb, 0)
         self.train_s = time.time() - t0
         self.centroids = cent.cpu().numpy()
         self.codebooks = cb.cpu().numpy()

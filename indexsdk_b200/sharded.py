@@ -58,6 +58,13 @@ class _CudaOps:
     def synchronize(self):
         self.stream.synchronize()
 
+    def caller_waits(self):
+        """Work queued on the caller's stream from here on starts after the index's stream is done."""
+        torch.cuda.current_stream(self.device).wait_stream(self.stream)
+
+    def synchronize_caller(self):
+        torch.cuda.current_stream(self.device).synchronize()
+
     def merge(self, nsrc, n, k, descending, packed, stride_bytes, d_off, i_off, outD, outI):
         base = packed.data_ptr()
         self._merge(nsrc, n, k, descending, base + d_off, base + i_off, outD.data_ptr(), outI.data_ptr(),
@@ -109,29 +116,52 @@ class ShardedSearcher:
 
     def _search_async(self, xq: torch.Tensor, k: int):
         n = xq.shape[0]
+        # Buffers are allocated here, on the caller's stream, and only USED on the index's stream:
+        # memory that the caching allocator ties to a stream must not outlive that stream, and the
+        # index (which owns it) may be destroyed before these tensors are.
+        if self.world == 1:
+            b = self._get(("one", n, k), lambda: dict(
+                D=self.ops.empty(n * k * 4).view(torch.float32).view(n, k),
+                I=self.ops.empty(n * k * 8).view(torch.int64).view(n, k)))
+        elif self.mode == "replica":
+            b = self._replica_buffers(n, k)
+        else:
+            b = self._shard_buffers(n, k)
         self.ops.wait_for_caller()
         with self.ops.on_stream():
             if self.world == 1:
-                b = self._get(("one", n, k), lambda: dict(
-                    D=self.ops.empty(n * k * 4).view(torch.float32).view(n, k),
-                    I=self.ops.empty(n * k * 8).view(torch.int64).view(n, k)))
                 self.index.search_device(xq.data_ptr(), n, k, b["D"].data_ptr(), b["I"].data_ptr())
                 return b["D"], b["I"]
             if self.mode == "replica":
-                return self._search_replica(xq, n, k)
-            return self._search_shard(xq, n, k)
+                return self._search_replica(xq, n, k, b)
+            return self._search_shard(xq, n, k, b)
 
     # ---- mode "shard" ---------------------------------------------------------------------------
-    def _search_shard(self, xq, n, k):
+    def _use_probe_exchange(self, n):
+        return hasattr(self.index, "coarse_device") and n >= 4 * self.world
+
+    def _shard_buffers(self, n, k):
         blk, i_off = self._block_bytes(n, k)
         b = self._get(("shard", n, k), lambda: dict(
-            all=self.ops.empty(self.world * blk),
+            blk=blk, i_off=i_off, all=self.ops.empty(self.world * blk),
             outD=self.ops.empty(n * k * 4).view(torch.float32).view(n, k),
             outI=self.ops.empty(n * k * 8).view(torch.int64).view(n, k)))
+        if self._use_probe_exchange(n):
+            nprobe = min(self.index.nprobe, self.index.nlist)      # may change between calls
+            per = (n + self.world - 1) // self.world
+            pblk, pi_off = self._block_bytes(per, nprobe)
+            b["probe"] = self._get(("probe", n, nprobe), lambda: dict(
+                nprobe=nprobe, per=per, blk=pblk, i_off=pi_off, all=self.ops.empty(self.world * pblk),
+                cD=self.ops.empty(self.world * per * nprobe * 4).view(torch.float32).view(self.world * per, nprobe),
+                cI=self.ops.empty(self.world * per * nprobe * 8).view(torch.int64).view(self.world * per, nprobe)))
+        return b
+
+    def _search_shard(self, xq, n, k, b):
+        blk, i_off = b["blk"], b["i_off"]
         mine = b["all"][self.rank * blk:(self.rank + 1) * blk]      # this rank's block, filled in place
         locD, locI = self._views(mine, n, k, i_off)
-        if hasattr(self.index, "coarse_device") and n >= 4 * self.world:
-            cD, cI = self._exchange_probes(xq, n)
+        if self._use_probe_exchange(n):
+            cD, cI = self._exchange_probes(xq, n, b["probe"])
             self.index.search_preassigned_device(xq.data_ptr(), n, k, cD.data_ptr(), cI.data_ptr(),
                                                  locD.data_ptr(), locI.data_ptr())
         else:
@@ -140,18 +170,12 @@ class ShardedSearcher:
         self.ops.merge(self.world, n, k, self.descending, b["all"], blk, 0, i_off, b["outD"], b["outI"])
         return b["outD"], b["outI"]
 
-    def _exchange_probes(self, xq, n):
+    def _exchange_probes(self, xq, n, p):
         """Each rank selects the probes of an even slice of the queries (every shard holds the full
         coarse quantizer, so the selection would otherwise be repeated on every rank); one
         all-gather of packed (distance, list) blocks makes them known everywhere.  Returns
         [n][nprobe] tensors, identical on every rank and identical to a local probe selection."""
-        nprobe = min(self.index.nprobe, self.index.nlist)
-        per = (n + self.world - 1) // self.world
-        blk, i_off = self._block_bytes(per, nprobe)
-        p = self._get(("probe", n, nprobe), lambda: dict(
-            all=self.ops.empty(self.world * blk),
-            cD=self.ops.empty(self.world * per * nprobe * 4).view(torch.float32).view(self.world * per, nprobe),
-            cI=self.ops.empty(self.world * per * nprobe * 8).view(torch.int64).view(self.world * per, nprobe)))
+        nprobe, per, blk, i_off = p["nprobe"], p["per"], p["blk"], p["i_off"]
         mine = p["all"][self.rank * blk:(self.rank + 1) * blk]
         myD, myI = self._views(mine, per, nprobe, i_off)
         lo = min(self.rank * per, n)
@@ -168,13 +192,16 @@ class ShardedSearcher:
         return p["cD"], p["cI"]
 
     # ---- mode "replica" -------------------------------------------------------------------------
-    def _search_replica(self, xq, n, k):
+    def _replica_buffers(self, n, k):
         per = (n + self.world - 1) // self.world
         blk, i_off = self._block_bytes(per, k)
-        b = self._get(("replica", n, k), lambda: dict(
-            all=self.ops.empty(self.world * blk),
+        return self._get(("replica", n, k), lambda: dict(
+            per=per, blk=blk, i_off=i_off, all=self.ops.empty(self.world * blk),
             outD=self.ops.empty(self.world * per * k * 4).view(torch.float32).view(self.world * per, k),
             outI=self.ops.empty(self.world * per * k * 8).view(torch.int64).view(self.world * per, k)))
+
+    def _search_replica(self, xq, n, k, b):
+        per, blk, i_off = b["per"], b["blk"], b["i_off"]
         mine = b["all"][self.rank * blk:(self.rank + 1) * blk]
         myD, myI = self._views(mine, per, k, i_off)
         lo = min(self.rank * per, n)
@@ -195,19 +222,24 @@ class ShardedSearcher:
                out_I: torch.Tensor | None = None):
         """xq_host is a (preferably pinned) CPU tensor; results are copied back on rank 0 (other
         ranks return None)."""
-        with self.ops.on_stream():
-            xq = xq_host.to(self.device, non_blocking=True)
+        shape, dt = tuple(xq_host.shape), xq_host.dtype
+        xq = self._get(("xq", shape, dt), lambda: self.ops.empty(xq_host.numel() * xq_host.element_size())
+                       .view(dt).view(shape))
+        # Copies from and to the caller's host tensors run on the CALLER's stream: the allocator of
+        # pinned memory remembers the streams a block was used on until the block is freed, which
+        # may be after the index -- and with it the index's stream -- is gone.
+        xq.copy_(xq_host, non_blocking=True)
         D, I = self._search_async(xq, k)
+        self.ops.caller_waits()
         if self.rank != 0:
-            self.ops.synchronize()
+            self.ops.synchronize_caller()
             return None
         if out_D is None:
             out_D = torch.empty(D.shape, dtype=D.dtype, pin_memory=D.is_cuda)
             out_I = torch.empty(I.shape, dtype=I.dtype, pin_memory=I.is_cuda)
-        with self.ops.on_stream():
-            out_D.copy_(D, non_blocking=True)
-            out_I.copy_(I, non_blocking=True)
-        self.ops.synchronize()
+        out_D.copy_(D, non_blocking=True)
+        out_I.copy_(I, non_blocking=True)
+        self.ops.synchronize_caller()
         return out_D, out_I
 
 

@@ -52,6 +52,12 @@ class CpuOps:
     def synchronize(self):
         pass
 
+    def caller_waits(self):
+        pass
+
+    def synchronize_caller(self):
+        pass
+
     def merge(self, nsrc, n, k, descending, packed, stride_bytes, d_off, i_off, outD, outI):
         blocks = packed.view(nsrc, stride_bytes)
         Ds = [blocks[s, d_off:d_off + n * k * 4].view(torch.float32).view(n, k).numpy() for s in range(nsrc)]
