@@ -53,6 +53,23 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
     return ok;
 }
 
+// The same with a suspend-time hint (nanoseconds): the thread may be parked by the hardware until
+// the phase completes or the time is up, instead of returning at once -- a waiting role then
+// leaves the issue slots of its scheduler to the warps that have work.
+__device__ __forceinline__ uint32_t mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred P;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n"
+        "selp.b32 %0, 1, 0, P;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok;
+}
+
 // Bounded wait: gives up after `limit_cycles` SM clocks or as soon as *abort_flag is set by
 // another role of the same CTA.  Returns true when the phase completed.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
@@ -61,7 +78,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     const long long t0 = clock64();
     uint32_t spins = 0;
     for (;;) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait_parked(bar, parity, 2000u)) return true;
         if ((++spins & 255u) == 0u) {
             if (*abort_flag) return false;
             if (clock64() - t0 > limit_cycles) {
