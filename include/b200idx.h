@@ -96,6 +96,14 @@ int b200idx_search_device_noalloc(b200idx_t* h, int64_t n, const void* x_dev, in
 int b200idx_search_multi(b200idx_t* const* hs, int nh, int64_t n, const void* x, int k, float* distances,
                          int64_t* labels, int merged);
 
+/* Counters of the segmented path of b200idx_search_multi on one device: small Flat / Int8Flat
+ * indexes of a device are searched in one pass over their concatenated bases, the counterpart of
+ * the reference's single top-k operator over the blocks of all indexes
+ * (FR/ops/cpukernel/impl/topk_multisearch_cpu_kernel.cpp:316-430).  group_launches: kernels
+ * launched by that path so far (per call it does not depend on the number of indexes);
+ * group_rebuilds: times the concatenated copy was (re)built -- it is kept until a member changes. */
+int b200idx_search_multi_stats(int device, uint64_t* group_launches, uint64_t* group_rebuilds);
+
 /* Merge of nsrc sorted per-shard results resident on one device: Din/Iin [nsrc][n][k] ->
  * D/I [n][k]; descending = 1 for inner-product scores.  Stands in for the host merge
  * FR/ascend/impl/AscendIndexImpl.cpp:587-642 after a gather of per-rank results.

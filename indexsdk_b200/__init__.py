@@ -68,6 +68,7 @@ def load() -> C.CDLL:
         "b200idx_search_device": (i32, [vp, i64, vp, i32, vp, vp]),
         "b200idx_search_device_noalloc": (i32, [vp, i64, vp, i32, vp, vp]),
         "b200idx_search_multi": (i32, [pp, i32, i64, vp, i32, vp, vp, i32]),
+        "b200idx_search_multi_stats": (i32, [i32, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
         "b200idx_merge_topk_device": (i32, [i32, i64, i32, i32, vp, vp, vp, vp, vp]),
         "b200idx_merge_topk_device_strided": (i32, [i32, i64, i32, i32, vp, vp, i64, vp, vp, vp]),
         "b200idx_reset": (i32, [vp]),
@@ -112,7 +113,7 @@ EXPORTED_SYMBOLS = [
     "b200idx_create_flat", "b200idx_create_int8flat", "b200idx_create_ivfpq", "b200idx_destroy", "b200idx_add",
     "b200idx_add_f16", "b200idx_add_device", "b200idx_search", "b200idx_search_f16", "b200idx_search_device",
     "b200idx_search_device_noalloc",
-    "b200idx_search_multi", "b200idx_merge_topk_device", "b200idx_merge_topk_device_strided", "b200idx_reset", "b200idx_remove_ids", "b200idx_ntotal",
+    "b200idx_search_multi", "b200idx_search_multi_stats", "b200idx_merge_topk_device", "b200idx_merge_topk_device_strided", "b200idx_reset", "b200idx_remove_ids", "b200idx_ntotal",
     "b200idx_dim", "b200idx_device", "b200idx_get_base", "b200idx_get_ids", "b200idx_ivfpq_set_centroids",
     "b200idx_ivfpq_set_codebooks", "b200idx_ivfpq_get_centroids", "b200idx_ivfpq_get_codebooks",
     "b200idx_search_with_masks", "b200idx_save", "b200idx_load", "b200idx_kmeans", "b200idx_ivfpq_train", "b200idx_ivfpq_add_codes", "b200idx_ivfpq_set_nprobe", "b200idx_ivfpq_coarse_device",
@@ -425,6 +426,13 @@ def search_multi(indexes, x, k: int, merged: bool = True):
     rc = lib.b200idx_search_multi(arr, nh, n, _ptr(x), k, _ptr(D), _ptr(I), int(merged))
     _check(rc, indexes[0].handle)
     return D, I
+
+
+def search_multi_stats(device: int = 0) -> dict:
+    """Counters of the segmented (one pass over all small indexes) path of search_multi."""
+    a, b_ = C.c_uint64(0), C.c_uint64(0)
+    load().b200idx_search_multi_stats(device, C.byref(a), C.byref(b_))
+    return dict(group_launches=int(a.value), group_rebuilds=int(b_.value))
 
 
 def merge_topk_device(nsrc: int, n: int, k: int, descending: bool, Din_ptr: int, Iin_ptr: int, D_ptr: int,

@@ -16,7 +16,7 @@ BUILD_DIR = os.path.join(_HERE, "_build")
 LIB_PATH = os.path.join(BUILD_DIR, "libb200idx.so")
 SHIM_LIB_PATH = os.path.join(BUILD_DIR, "libb200idx_ascend.so")
 
-SOURCES = ["dist_gemm.cu", "select.cu", "flat_index.cu", "ivfpq_index.cu", "ivfpq_tc_scan.cu", "kmeans.cu", "c_api.cu", "noalloc.cu"]
+SOURCES = ["dist_gemm.cu", "select.cu", "flat_index.cu", "multi_flat.cu", "ivfpq_index.cu", "ivfpq_tc_scan.cu", "kmeans.cu", "c_api.cu", "noalloc.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-O3", "--expt-relaxed-constexpr",

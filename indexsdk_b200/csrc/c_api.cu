@@ -16,6 +16,7 @@
 #include "flat_index.h"
 #include "ivfpq_index.h"
 #include "kmeans.h"
+#include "multi_flat.h"
 #include "select.cuh"
 
 using namespace b200;
@@ -109,7 +110,8 @@ void check_search_args(const b200idx_index* h, int64_t n, const void* x, int k, 
 // Device buffers of b200idx_search_multi, one set per device, grown on demand and kept.
 struct MultiScratch {
     std::mutex mu;           // held for a whole multi-index search that uses this device
-    DeviceBuffer q, D, I, allD, allI, mD, mI;
+    DeviceBuffer q, D, I, allD, allI, mD, mI, gD, gI;
+    std::unique_ptr<FlatGroup> group;   // concatenated copy of the small Flat indexes searched together last
 };
 MultiScratch& multi_scratch(int device) {
     static std::mutex table_mu;
@@ -308,6 +310,41 @@ int b200idx_search_multi(b200idx_t* const* hs, int nh, int64_t n, const void* x,
                     cudaStream_t st = static_cast<cudaStream_t>(b200idx_stream(hs[members[0]]));
                     B200_CUDA_CHECK(cudaMemcpyAsync(dq, x, static_cast<size_t>(n) * row, cudaMemcpyHostToDevice, st));
                     B200_CUDA_CHECK(cudaStreamSynchronize(st));
+                    // Small exact indexes of one device are searched in ONE pass over their
+                    // concatenated bases (segmented search): launches do not grow with their number.
+                    std::vector<FlatIndex*> fm;
+                    bool groupable = members.size() >= 2 && hs[members[0]]->kind != 2;
+                    for (size_t j = 0; groupable && j < members.size(); ++j) {
+                        FlatIndex* f = hs[members[j]]->flat.get();
+                        groupable = f->dtype() == hs[members[0]]->flat->dtype() && f->metric() == hs[members[0]]->flat->metric();
+                        fm.push_back(f);
+                    }
+                    if (groupable && FlatGroup::eligible(fm, n, k)) {
+                        if (!sc.group) sc.group.reset(new FlatGroup(dev));
+                        const size_t m = members.size();
+                        bool contiguous = true;
+                        for (size_t j = 1; j < m; ++j) contiguous = contiguous && members[j] == members[0] + static_cast<int>(j);
+                        const bool direct = merged && dev == dev0 && contiguous;
+                        float* gD = direct ? allD + per * members[0] : static_cast<float*>(sc.gD.ensure(per * m * 4));
+                        int64_t* gI = direct ? allI + per * members[0] : static_cast<int64_t*>(sc.gI.ensure(per * m * 8));
+                        sc.group->search_device(fm, n, dq, k, gD, gI, st);
+                        if (!direct) {
+                            const cudaMemcpyKind kind = merged ? cudaMemcpyDefault : cudaMemcpyDeviceToHost;
+                            float* dstD = merged ? allD : D;
+                            int64_t* dstI = merged ? allI : I;
+                            if (contiguous) {
+                                B200_CUDA_CHECK(cudaMemcpyAsync(dstD + per * members[0], gD, per * m * 4, kind, st));
+                                B200_CUDA_CHECK(cudaMemcpyAsync(dstI + per * members[0], gI, per * m * 8, kind, st));
+                            } else {
+                                for (size_t j = 0; j < m; ++j) {
+                                    B200_CUDA_CHECK(cudaMemcpyAsync(dstD + per * members[j], gD + per * j, per * 4, kind, st));
+                                    B200_CUDA_CHECK(cudaMemcpyAsync(dstI + per * members[j], gI + per * j, per * 8, kind, st));
+                                }
+                            }
+                            B200_CUDA_CHECK(cudaStreamSynchronize(st));
+                        }
+                        return;
+                    }
                     for (int i : members) {
                         b200idx_index* h = hs[i];
                         // with merged results on this device the member writes its slice directly
@@ -347,6 +384,14 @@ int b200idx_search_multi(b200idx_t* const* hs, int nh, int64_t n, const void* x,
             B200_CUDA_CHECK(cudaStreamSynchronize(st));
         }
     }, /*lock=*/false);
+}
+
+int b200idx_search_multi_stats(int device, uint64_t* group_launches, uint64_t* group_rebuilds) {
+    MultiScratch& sc = multi_scratch(device);
+    std::lock_guard<std::mutex> l(sc.mu);
+    if (group_launches) *group_launches = sc.group ? sc.group->launches() : 0;
+    if (group_rebuilds) *group_rebuilds = sc.group ? sc.group->rebuilds() : 0;
+    return B200IDX_OK;
 }
 
 int b200idx_merge_topk_device(int nsrc, int64_t n, int k, int descending, const float* Din, const int64_t* Iin,

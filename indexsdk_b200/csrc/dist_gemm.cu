@@ -206,7 +206,7 @@ struct RowEpilogue {
 
     // Folded operands: r holds D for 32 columns.
     // ci: index of the chunk inside this thread's part of the tile (a constant after unrolling)
-    __device__ __forceinline__ void chunk_fold(const uint32_t (&r)[32], int64_t col0, int nvalid, int ci) {
+    __device__ __forceinline__ void chunk_fold(const uint32_t (&r)[32], int64_t col0, int nvalid, int ci, int64_t cbase) {
         if (!row_ok && (MODE == kModeBurstMin || a.direct)) return;
         if (MODE == kModeBurstMin) {
             constexpr int NB = 32 / BURST;
@@ -237,7 +237,7 @@ struct RowEpilogue {
                 res[ci * NB + b] = float_to_ord(key);
             }
         } else if (a.direct) {
-            uint64_t* crow = a.cand + static_cast<int64_t>(q) * a.cap + col0;
+            uint64_t* crow = a.cand + static_cast<int64_t>(q) * a.cap + (col0 - cbase);
             uint32_t keep = nvalid >= 32 ? 0xFFFFFFFFu : ((1u << nvalid) - 1u);
             if (a.qmask) keep &= mask_word(col0);
 #pragma unroll
@@ -300,10 +300,11 @@ struct RowEpilogue {
     // ci: see chunk_fold.  The hot path is straight-line code: the threshold test of the 32
     // columns is folded into a bit mask, and only a non-zero mask (rare) enters the compact
     // candidate loop.
+    // cbase: position of the first base row of the segment the tile belongs to (0 without segments)
     __device__ __forceinline__ void chunk(const uint32_t (&r)[32], const uint32_t* nb, int64_t col0, int nvalid,
-                                          int bslot, int ci) {
+                                          int bslot, int ci, int64_t cbase) {
         if (FOLD) {
-            chunk_fold(r, col0, nvalid, ci);
+            chunk_fold(r, col0, nvalid, ci, cbase);
             return;
         }
         if (!row_ok) return;
@@ -349,7 +350,7 @@ struct RowEpilogue {
                 dst[b] = K::ord(ma < mb ? ma : mb);
             }
         } else if (a.direct) {
-            uint64_t* crow = a.cand + static_cast<int64_t>(q) * a.cap + col0;
+            uint64_t* crow = a.cand + static_cast<int64_t>(q) * a.cap + (col0 - cbase);
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
                 const AccT key = K::key(K::from_bits(r[c]), K::from_bits(bnb[c]), l2);
@@ -680,13 +681,21 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             const int tile = tile_of(a, sel);
             const uint32_t ab = t & 1u;
             const uint32_t aph = (t >> 1) & 1u;
-            const int q = qb * kTileQ + row_in_tile;
+            const int q_in = qb * kTileQ + row_in_tile;
             const int64_t tile_col0 = static_cast<int64_t>(tile) * kTileB;
+            // segmented base: the tile's index decides the candidate row and the valid extent
+            int q = q_in;
+            int64_t cbase = 0, n_end = a.N;
+            if (a.seg_index) {
+                q += (__ldg(a.seg_index + tile) - a.seg_first) * a.nq;
+                cbase = __ldg(a.seg_col0 + tile);
+                n_end = __ldg(a.seg_end + tile);
+            }
             const long long e0 = profiler ? clock64() : 0;
             // The tile's norms travel global -> registers while the MMA is still running.
             uint32_t n0 = 0;
             if (l2 && et < kTileB) n0 = __ldg(gnorm + tile_col0 + et);
-            epi.begin_tile(q, q < a.nq);
+            epi.begin_tile(q, q_in < a.nq);
             if (!ptx::mbar_wait_bounded(&bar_acc_full[ab], aph, &abort_flag)) {
                 // leave without stranding a sibling warp at the named barrier below
                 if (!FOLD) asm volatile("bar.arrive 1, %0;" ::"n"(32 * epi_warps(KIND)) : "memory");
@@ -717,9 +726,9 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 {
                     const long long c0 = profiler ? clock64() : 0;
                     const int64_t col0 = half_col0 + c * 32;
-                    const int64_t rem = a.N - col0;
+                    const int64_t rem = n_end - col0;
                     epi.chunk(ra, hnorm + c * 32, col0, rem >= 32 ? 32 : (rem > 0 ? static_cast<int>(rem) : 0),
-                              hslot + c * (32 / BURST), c);
+                              hslot + c * (32 / BURST), c, cbase);
                     if (profiler) ecc += clock64() - c0;
                 }
                 const long long w1 = profiler ? clock64() : 0;
@@ -728,9 +737,9 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 if (c + 2 < kCols / 32) ptx::tmem_ld_32x32(tacc + (c + 2) * 32, ra);
                 {
                     const int64_t col0 = half_col0 + (c + 1) * 32;
-                    const int64_t rem = a.N - col0;
+                    const int64_t rem = n_end - col0;
                     epi.chunk(rb, hnorm + (c + 1) * 32, col0, rem >= 32 ? 32 : (rem > 0 ? static_cast<int>(rem) : 0),
-                              hslot + (c + 1) * (32 / BURST), c + 1);
+                              hslot + (c + 1) * (32 / BURST), c + 1, cbase);
                 }
             };
             if (FOLD) {   // small body: unrolled, so the chunk index is a constant
@@ -808,10 +817,17 @@ dist_gemm_simt_kernel(const GemmArgs a) {
         const int qb = cur.qb;
         const int sel = cur.sel;
         const int tile = tile_of(a, sel);
-        const int q = qb * kTileQ + threadIdx.x;
-        const bool row_ok = q < a.nq;
-        const int qc = row_ok ? q : a.nq - 1;
+        const int q_in = qb * kTileQ + threadIdx.x;
+        const bool row_ok = q_in < a.nq;
+        const int qc = row_ok ? q_in : a.nq - 1;
         const int64_t tile_col0 = static_cast<int64_t>(tile) * kTileB;
+        int q = q_in;
+        int64_t cbase = 0, n_end = a.N;
+        if (a.seg_index) {
+            q += (a.seg_index[tile] - a.seg_first) * a.nq;
+            cbase = a.seg_col0[tile];
+            n_end = a.seg_end[tile];
+        }
         __syncthreads();
         epi_sh.norm[0][threadIdx.x] = l2 ? __ldg(gnorm + tile_col0 + threadIdx.x) : 0u;
         epi_sh.norm[0][kTileQ + threadIdx.x] = l2 ? __ldg(gnorm + tile_col0 + kTileQ + threadIdx.x) : 0u;
@@ -819,7 +835,7 @@ dist_gemm_simt_kernel(const GemmArgs a) {
         epi.begin_tile(q, row_ok);
         for (int c = 0; c < kTileB / 32; ++c) {
             const int64_t col0 = tile_col0 + c * 32;
-            int64_t rem = a.N - col0;
+            int64_t rem = n_end - col0;
             const int nvalid = rem >= 32 ? 32 : (rem > 0 ? static_cast<int>(rem) : 0);
             uint32_t r[32];
             for (int j = 0; j < 32; ++j) {
@@ -832,7 +848,7 @@ dist_gemm_simt_kernel(const GemmArgs a) {
                 else r[j] = __float_as_uint(acc);
             }
             const int bslot = sel * (kTileB / BURST) + c * (32 / BURST);
-            epi.chunk(r, &epi_sh.norm[0][c * 32], col0, nvalid, bslot, c);
+            epi.chunk(r, &epi_sh.norm[0][c * 32], col0, nvalid, bslot, c, cbase);
         }
         epi.end_tile(sel * (kTileB / BURST));
     }

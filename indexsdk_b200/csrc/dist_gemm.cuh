@@ -55,6 +55,18 @@ struct GemmArgs {
     // lets the row take part (nullptr: every row does)
     const uint32_t* qmask;
     int64_t qmask_stride;
+    // optional segmented base: the concatenated bases of several indexes that are searched with the
+    // same queries in ONE pass (multi-index search).  A tile belongs to exactly one index (segments
+    // start on tile boundaries); per tile:
+    //   seg_index: which index; the candidates of (index i, query q) go to row
+    //              (i - seg_first) * nq + q of cand / tau (direct mode only)
+    //   seg_col0 : position of the index's first base row in the concatenated base (the slot of a
+    //              candidate is its position minus this)
+    //   seg_end  : position one past the index's last real base row
+    const int32_t* seg_index;
+    int seg_first;        // index of the first member this pass covers
+    const int64_t* seg_col0;
+    const int64_t* seg_end;
     int* err;             // device error word
     // optional phase profile (nullptr = off): 8 counters of SM cycles summed over CTAs
     //   0 producer wait-empty   1 mma wait-acc-empty   2 mma wait-full   3 epilogue wait-acc-full

@@ -132,6 +132,7 @@ void FlatIndex::add(int64_t n, const void* x, bool x_is_f16, const int64_t* ids,
     }
     B200_CUDA_CHECK(cudaStreamSynchronize(stream_));
     n_ += n;
+    ++generation_;
     map_b_valid_ = false;
 }
 
@@ -139,6 +140,7 @@ void FlatIndex::reset() {
     DeviceGuard g(device_);
     cudaStreamSynchronize(stream_);
     n_ = 0;
+    ++generation_;
     max_norm_ = 0.f;
     cudaMemset(maxnorm_.get(), 0, sizeof(float));
     map_b_valid_ = false;
@@ -173,6 +175,7 @@ int64_t FlatIndex::remove_ids(int64_t n, const int64_t* ids) {
     }
     B200_CUDA_CHECK(cudaStreamSynchronize(stream_));
     n_ -= static_cast<int64_t>(pos.size());
+    ++generation_;
     map_b_valid_ = false;
     return static_cast<int64_t>(pos.size());
 }

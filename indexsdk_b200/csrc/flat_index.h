@@ -100,6 +100,8 @@ public:
     int dtype() const { return dtype_; }
     int device() const { return device_; }
     int64_t ntotal() const { return n_; }
+    // changes whenever the stored rows change (add / reset / remove_ids): lets a cached copy notice
+    uint64_t generation() const { return generation_; }
     cudaStream_t stream() const { return stream_; }
     SearchStats& stats() { return stats_; }
     StageTimer& timer() { return timer_; }
@@ -167,6 +169,7 @@ private:
     int num_sms_ = 0;
     bool use_simt_ = false;
     int64_t n_ = 0, cap_rows_ = 0;
+    uint64_t generation_ = 0;
     int64_t next_auto_id_ = 0;
     cudaStream_t stream_ = nullptr;
 

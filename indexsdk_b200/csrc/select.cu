@@ -299,17 +299,20 @@ constexpr int kRefChunk = 32;     // small, so that many warps fit an SM: the ke
 constexpr int kRefPitch = kRefChunk + 4;
 __global__ void __launch_bounds__(128)
 refine_f32_kernel(uint64_t* cand, const uint32_t* counts, uint32_t n_fixed, uint32_t cap, int d, int metric,
-                  const float* xq, const float* xb) {
+                  const float* xq, const float* xb, int q_first, int q_mod) {
     extern __shared__ __align__(16) float ref_sm[];
     float* qs = ref_sm;                                              // [d]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* rows = ref_sm + d + warp * (32 * kRefPitch);              // [32][kRefPitch] per warp
     const int q = blockIdx.y;
+    // candidate row q_first + q holds the candidates of query (q_first + q) % q_mod (several indexes
+    // searched with the same queries) or of query q_first + q (q_mod = 0)
+    const int qrow = q_mod > 0 ? (q_first + q) % q_mod : q_first + q;
     uint32_t n = counts ? counts[q] : n_fixed;
     if (n > cap) n = cap;
     if (blockIdx.x * 128u >= n) return;
     for (int i = threadIdx.x; i < d / 4; i += 128)
-        reinterpret_cast<float4*>(qs)[i] = __ldg(reinterpret_cast<const float4*>(xq + static_cast<int64_t>(q) * d) + i);
+        reinterpret_cast<float4*>(qs)[i] = __ldg(reinterpret_cast<const float4*>(xq + static_cast<int64_t>(qrow) * d) + i);
     __syncthreads();
     uint64_t* row = cand + static_cast<int64_t>(q) * cap;
     for (uint32_t i0 = (blockIdx.x * 4 + warp) * 32; i0 < n; i0 += gridDim.x * 128) {
@@ -378,6 +381,7 @@ __global__ void emit_kernel(const EmitArgs e) {
     if (idx >= static_cast<int64_t>(e.nq) * e.k) return;
     const int q = static_cast<int>(idx / e.k), j = static_cast<int>(idx % e.k);
     const int orow = e.qmap ? e.qmap[q] : q;
+    const int qn = e.q_mod > 0 ? q % e.q_mod : q;   // row of the query norms
     const uint64_t c = e.sel[idx];
     float dist;
     int64_t label;
@@ -389,13 +393,13 @@ __global__ void emit_kernel(const EmitArgs e) {
         label = e.labels ? e.labels[pos] : static_cast<int64_t>(pos);
         if (e.mode == 2) {
             int32_t kv = ord_to_int(ok);
-            if (e.metric == kMetricL2) dist = static_cast<float>(kv + static_cast<const int32_t*>(e.qnorm)[q]);
+            if (e.metric == kMetricL2) dist = static_cast<float>(kv + static_cast<const int32_t*>(e.qnorm)[qn]);
             else dist = static_cast<float>(-kv);
         } else {
             float kv = ord_to_float(ok);
             if (e.metric == kMetricL2) {
                 if (e.mode == 0) {
-                    kv += static_cast<const float*>(e.qnorm)[q];
+                    kv += static_cast<const float*>(e.qnorm)[qn];
                     kv = kv < 0.f ? 0.f : kv;
                 }
                 dist = kv;
@@ -686,7 +690,7 @@ cudaError_t launch_prune_candidates(uint64_t* cand, uint32_t* counts, uint32_t c
 }
 
 cudaError_t launch_refine_f32(uint64_t* cand, const uint32_t* counts, uint32_t n_fixed, uint32_t cap, int nq, int d,
-                              int metric, const float* xq, const float* xb, cudaStream_t stream) {
+                              int metric, const float* xq, const float* xb, cudaStream_t stream, int q_mod) {
     if (nq <= 0) return cudaSuccess;
     uint32_t per_row = counts ? cap : (n_fixed < cap ? n_fixed : cap);
     // Blocks stride over a row's candidates, so a few thousand blocks in total keep the machine
@@ -706,7 +710,7 @@ cudaError_t launch_refine_f32(uint64_t* cand, const uint32_t* counts, uint32_t n
         const int nqq = nq - q0 < 65535 ? nq - q0 : 65535;
         refine_f32_kernel<<<dim3(gx, nqq), 128, smem, stream>>>(cand + static_cast<int64_t>(q0) * cap,
                                                             counts ? counts + q0 : nullptr, n_fixed, cap, d, metric,
-                                                            xq + static_cast<int64_t>(q0) * d, xb);
+                                                            xq, xb, q0, q_mod);
     }
     return cudaGetLastError();
 }

@@ -33,8 +33,9 @@ cudaError_t launch_tighten_tau(const uint64_t* cand, const uint32_t* counts, uin
 // is compacted and counts[row] updated
 cudaError_t launch_prune_candidates(uint64_t* cand, uint32_t* counts, uint32_t cap, int nq, int k,
                                     const float* eps, cudaStream_t stream);
+// q_mod > 0: candidate row r belongs to query r % q_mod (rows = [index][query] of a multi-index search)
 cudaError_t launch_refine_f32(uint64_t* cand, const uint32_t* counts, uint32_t n_fixed, uint32_t cap, int nq, int d,
-                              int metric, const float* xq, const float* xb, cudaStream_t stream);
+                              int metric, const float* xq, const float* xb, cudaStream_t stream, int q_mod = 0);
 
 struct EmitArgs {
     const uint64_t* sel;     // [nq][k] sorted candidates
@@ -47,6 +48,7 @@ struct EmitArgs {
     int64_t* I;
     int ldk;
     const int32_t* qmap;     // optional: output row = qmap[q] (fallback re-runs scatter into place)
+    int q_mod;               // > 0: row q uses the query norm of row q % q_mod (multi-index search)
 };
 cudaError_t launch_emit(const EmitArgs& e, cudaStream_t stream);
 

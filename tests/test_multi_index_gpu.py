@@ -82,3 +82,87 @@ def test_merge_kernel_with_torch_buffers(b200):
                            torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
     assert_exact(oD.cpu().numpy(), oI.cpu().numpy(), Dr, Ir)
+
+
+@pytest.mark.parametrize("kind", ["f32_l2", "f32_ip", "i8_ip", "i8_l2", "f16_ip"])
+def test_many_small_indexes_one_pass(b200, kind):
+    """64 small indexes of one device: the segmented path searches them in one pass over their
+    concatenated bases.  Results per index and merged are those of the oracle; the number of
+    kernels launched per call does not depend on the number of indexes; the second call allocates
+    nothing; a change of one member is noticed."""
+    import torch
+    from helpers import assert_close_gap_aware
+    d, k, nq, nidx = 64, 10, 33, 64
+    rng = np.random.default_rng(5)
+    sizes = [int(v) for v in rng.integers(40, 3000, size=nidx)]
+    sizes[3], sizes[17] = 256, 257                          # exactly one tile / one row more
+    is_int = kind.startswith("i8")
+    metric = IP if kind.endswith("ip") else L2
+    xq = datasets.uniform_int8(nq, d, seed=3) if is_int else datasets.gaussian(nq, d, seed=1)
+    if kind.startswith("f16"):
+        xq = oracle.round_fp16(xq)
+    indexes, Ds, Is, bases = [], [], [], []
+    base_id = 0
+    for s_, n in enumerate(sizes):
+        ids = np.arange(base_id, base_id + n, dtype=np.int64) * 2 + 1
+        base_id += n
+        if is_int:
+            xb = datasets.uniform_int8(n, d, seed=100 + s_)
+            ix = b200.IndexInt8Flat(d, metric)
+            Dr, Ir = oracle.int8_search(metric, xb, xq, k, labels=ids)
+        else:
+            xb = datasets.gaussian(n, d, seed=100 + s_)
+            if kind.startswith("f16"):
+                xb = oracle.round_fp16(xb)
+            ix = b200.IndexFlat(d, metric, dtype=b200.F16 if kind.startswith("f16") else b200.F32)
+            Dr, Ir = oracle.flat_search(metric, xb, xq, k, labels=ids)
+        ix.add_with_ids(xb, ids)
+        indexes.append(ix)
+        bases.append((xb, ids))
+        Ds.append(Dr)
+        Is.append(Ir)
+    exact = not kind.startswith("f16")
+
+    def check(D, I, Dref, Iref, what):
+        if exact:
+            assert_exact(D, I, Dref, Iref)
+        else:
+            assert_close_gap_aware(D.reshape(-1, k), I.reshape(-1, k), Dref.reshape(-1, k), Iref.reshape(-1, k), 1e-3, what)
+
+    s0 = b200.search_multi_stats()
+    D, I = b200.search_multi(indexes, xq, k, merged=False)
+    s1 = b200.search_multi_stats()
+    check(D, I, np.stack(Ds), np.stack(Is), "per index")
+    assert s1["group_rebuilds"] == s0["group_rebuilds"] + 1
+    per_call_64 = s1["group_launches"] - s0["group_launches"]
+    assert 0 < per_call_64 <= 8
+    # second call: same copy, same number of launches, no device allocation
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info()[0]
+    Dm, Im = b200.search_multi(indexes, xq, k, merged=True)
+    free1 = torch.cuda.mem_get_info()[0]
+    s2 = b200.search_multi_stats()
+    Dr, Ir = oracle.merge_topk(np.stack(Ds), np.stack(Is), descending=(metric == IP))
+    check(Dm, Im, Dr, Ir, "merged")
+    assert s2["group_rebuilds"] == s1["group_rebuilds"] and s2["group_launches"] - s1["group_launches"] == per_call_64
+    D2, I2 = b200.search_multi(indexes, xq, k, merged=False)
+    free2 = torch.cuda.mem_get_info()[0]
+    assert free2 == free1, "a steady-state multi-index search allocated device memory"
+    # eight of them: the same number of launches
+    s3 = b200.search_multi_stats()
+    D8, I8 = b200.search_multi(indexes[:8], xq, k, merged=False)
+    s4 = b200.search_multi_stats()
+    check(D8, I8, np.stack(Ds[:8]), np.stack(Is[:8]), "eight indexes")
+    assert s4["group_launches"] - s3["group_launches"] == per_call_64
+    # a member changes: the copy is rebuilt and the new row is found
+    xb5, ids5 = bases[5]
+    extra = xq[:1].copy()
+    indexes[5].add_with_ids(extra, np.array([10**9], dtype=np.int64))
+    Dn, In = b200.search_multi(indexes, xq, k, merged=False)
+    assert b200.search_multi_stats()["group_rebuilds"] == s4["group_rebuilds"] + 1   # the copy follows its members
+    assert In[5, 0, 0] == 10**9 or metric == IP
+    if is_int:
+        Dr5, Ir5 = oracle.int8_search(metric, np.concatenate([xb5, extra]), xq, k, labels=np.concatenate([ids5, [10**9]]))
+    else:
+        Dr5, Ir5 = oracle.flat_search(metric, np.concatenate([xb5, extra]), xq, k, labels=np.concatenate([ids5, [10**9]]))
+    check(Dn[5], In[5], Dr5, Ir5, "changed member")
