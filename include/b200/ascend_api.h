@@ -282,6 +282,32 @@ void Search(std::vector<AscendIndex*> indexes, idx_t n, const float* x, idx_t k,
 void Search(std::vector<AscendIndexInt8*> indexes, idx_t n, const int8_t* x, idx_t k, float* distances, idx_t* labels,
             bool merged);
 
+// ---- cloner: CPU index <-> index on the devices (ascend/AscendCloner.h, AscendClonerOptions.h of
+//      the reference).  Covered: IndexFlat / IndexIDMap(IndexFlat) <-> AscendIndexFlat,
+//      IndexIVFPQ <-> AscendIndexIVFPQ, IndexScalarQuantizer / IndexIDMap(IndexScalarQuantizer)
+//      <-> AscendIndexInt8Flat; other index types raise "not supported". ----
+struct AscendClonerOptions {
+    AscendClonerOptions() : reserveVecs(0), verbose(false), resourceSize(-1), indexMode(0), blockSize(0) {}
+    long reserveVecs;
+    bool verbose;
+    int64_t resourceSize;
+    bool slim = false;         // (scalar-quantizer indexes of the reference; not used here)
+    bool filterable = false;
+    uint32_t indexMode;
+    uint32_t blockSize;
+};
+faiss::Index* index_ascend_to_cpu(const faiss::Index* ascend_index);
+faiss::Index* index_cpu_to_ascend(std::initializer_list<int> devices, const faiss::Index* index,
+                                  const AscendClonerOptions* options = nullptr);
+faiss::Index* index_cpu_to_ascend(std::vector<int> devices, const faiss::Index* index,
+                                  const AscendClonerOptions* options = nullptr);
+// the int8 index does not derive from faiss::Index
+faiss::Index* index_int8_ascend_to_cpu(const AscendIndexInt8* index);
+AscendIndexInt8* index_int8_cpu_to_ascend(std::initializer_list<int> devices, const faiss::Index* index,
+                                          const AscendClonerOptions* options = nullptr);
+AscendIndexInt8* index_int8_cpu_to_ascend(std::vector<int> devices, const faiss::Index* index,
+                                          const AscendClonerOptions* options = nullptr);
+
 // Relaxed mode (env B200IDX_RELAXED=1 or this switch): lifts the reference's whitelists (dims,
 // nlist, msubs, k <= 320 for IVFPQ, same-device rule and n, k <= 1024 of multi-index search) to
 // the limits of the C ABI.  Off by default: the reference's checks and messages apply.

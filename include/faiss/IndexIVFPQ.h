@@ -38,6 +38,7 @@ struct IndexIVF : Index {
 struct IndexIVFPQ : IndexIVF {
     bool by_residual = true;
     ProductQuantizer pq;
+    IndexIVFPQ() : IndexIVF(nullptr, 0, 0, METRIC_L2) { is_trained = false; }
     IndexIVFPQ(Index* q, size_t d_, size_t nlist_, size_t M, size_t nbits, MetricType m = METRIC_L2)
         : IndexIVF(q, d_, nlist_, m), pq(d_, M, nbits) {
         invlists = new ArrayInvertedLists(nlist_, pq.code_size);
@@ -49,6 +50,7 @@ struct IndexIVFPQ : IndexIVF {
         FAISS_THROW_MSG("not supported by this stand-in");
     }
     void reset() override {
+        if (!invlists) return;
         for (auto& c : invlists->codes) c.clear();
         for (auto& i : invlists->ids) i.clear();
         ntotal = 0;

@@ -17,6 +17,7 @@
 #include <mutex>
 #include <random>
 #include <shared_mutex>
+#include <thread>
 #include <string>
 
 #include "../../../include/b200idx.h"
@@ -93,7 +94,12 @@ public:
     void rc(int code, b200idx_t* h, const char* what) const {
         if (code != B200IDX_OK) FAISS_THROW_FMT("%s failed (%d): %s", what, code, b200idx_last_error(h));
     }
+    // Query-parallel layout (AscendIndexIVFPQConfig::enableQueryParallelSearch, FR/ascend/impl/
+    // AscendIndexIVFPQImpl.cpp:323-333 replication, :1305-1328 search): every device holds the WHOLE
+    // index and a search splits the QUERIES over the devices instead of the base.
+    bool replicated = false;
     idx_t total() const {
+        if (replicated) return handles.empty() ? 0 : b200idx_ntotal(handles[0]);
         idx_t t = 0;
         for (b200idx_t* h : handles) t += b200idx_ntotal(h);
         return t;
@@ -110,6 +116,11 @@ public:
         return cnt;
     }
     void add_rows(idx_t n, const void* x, size_t row_bytes, const idx_t* ids, bool f16) {
+        if (replicated) {
+            for (b200idx_t* h : handles)
+                rc(f16 ? b200idx_add_f16(h, n, static_cast<const uint16_t*>(x), ids) : b200idx_add(h, n, x, ids), h, "add");
+            return;
+        }
         const std::vector<idx_t> cnt = split(n);
         idx_t off = 0;
         for (size_t i = 0; i < handles.size(); ++i) {
@@ -128,10 +139,42 @@ public:
             rc(code, handles[0], "search");
             return;
         }
-        FAISS_THROW_IF_NOT_MSG(!f16, "fp16 queries on a multi-device index are not implemented");
+        // fp16 queries: widened on the host (exact); an fp16-storage index rounds them back to the same bits
+        std::vector<float> wide;
+        if (f16) {
+            const uint16_t* xh = static_cast<const uint16_t*>(x);
+            wide.resize(static_cast<size_t>(n) * dims);
+            for (size_t i = 0; i < wide.size(); ++i) {
+                _Float16 v;
+                std::memcpy(&v, xh + i, 2);
+                wide[i] = static_cast<float>(v);
+            }
+            x = wide.data();
+        }
+        if (replicated) {
+            // near-even slices of the queries, one worker per device
+            const size_t nd = std::min<size_t>(handles.size(), static_cast<size_t>(n));
+            const size_t row = static_cast<size_t>(dims) * row_elem_bytes;
+            std::vector<std::string> errs(nd);
+            std::vector<std::thread> workers;
+            for (size_t i = 0; i < nd; ++i) {
+                const idx_t lo = n * static_cast<idx_t>(i) / static_cast<idx_t>(nd);
+                const idx_t hi = n * static_cast<idx_t>(i + 1) / static_cast<idx_t>(nd);
+                workers.emplace_back([=, &errs] {
+                    const int code = b200idx_search(handles[i], hi - lo, static_cast<const uint8_t*>(x) + static_cast<size_t>(lo) * row,
+                                                    static_cast<int>(k), D + lo * k, I + lo * k);
+                    if (code != B200IDX_OK) errs[i] = b200idx_last_error(handles[i]);
+                });
+            }
+            for (auto& w : workers) w.join();
+            for (auto& e : errs)
+                if (!e.empty()) FAISS_THROW_FMT("search failed: %s", e.c_str());
+            return;
+        }
         rc(b200idx_search_multi(handles.data(), static_cast<int>(handles.size()), n, x, static_cast<int>(k), D, I, 1),
            handles[0], "search");
     }
+    size_t row_elem_bytes = sizeof(float);   // bytes per query component (1 for the int8 index)
     void reset_all() {
         for (b200idx_t* h : handles) rc(b200idx_reset(h), h, "reset");
     }
@@ -262,7 +305,7 @@ size_t AscendIndex::remove_ids(const faiss::IDSelector& sel) {
         if (hit.empty()) continue;
         int64_t r = 0;
         impl_->rc(b200idx_remove_ids(h, static_cast<int64_t>(hit.size()), hit.data(), &r), h, "remove_ids");
-        removed += static_cast<size_t>(r);
+        if (!impl_->replicated || h == impl_->handles[0]) removed += static_cast<size_t>(r);   // replicas hold the same rows
     }
     ntotal = impl_->total();
     return removed;
@@ -471,6 +514,7 @@ AscendIndexInt8::AscendIndexInt8(int dims, faiss::MetricType metric, AscendIndex
     impl_->devices = config.deviceList;
     impl_->dims = dims;
     impl_->metric = metric;
+    impl_->row_elem_bytes = 1;
 }
 AscendIndexInt8::~AscendIndexInt8() {}
 void AscendIndexInt8::train(idx_t, const int8_t*) {}                       // a flat index needs no training
@@ -709,7 +753,10 @@ size_t AscendIndexIVF::reclaimMemory() { return 0; }
 uint32_t AscendIndexIVF::getListLength(int listId) const {
     FAISS_THROW_IF_NOT_FMT(listId >= 0 && listId < impl_->core->nlist, "listId must be in range [0, %d)", impl_->core->nlist);
     uint32_t len = 0;
-    for (b200idx_t* h : impl_->core->handles) len += static_cast<uint32_t>(b200idx_ivfpq_list_length(h, listId));
+    for (b200idx_t* h : impl_->core->handles) {
+        len += static_cast<uint32_t>(b200idx_ivfpq_list_length(h, listId));
+        if (impl_->core->replicated) break;   // every device holds the whole list
+    }
     return len;
 }
 void AscendIndexIVF::getListCodesAndIds(int listId, std::vector<uint8_t>& codes, std::vector<ascend_idx_t>& ids) const {
@@ -725,6 +772,7 @@ void AscendIndexIVF::getListCodesAndIds(int listId, std::vector<uint8_t>& codes,
         ids.resize(o + static_cast<size_t>(len));
         impl_->core->rc(b200idx_ivfpq_get_list(h, listId, codes.data() + o * M, reinterpret_cast<int64_t*>(ids.data() + o)),
                         h, "get_list");
+        if (impl_->core->replicated) break;   // every device holds the whole list
     }
 }
 
@@ -748,8 +796,8 @@ AscendIndexIVFPQ::AscendIndexIVFPQ(int dims, faiss::MetricType metric, int nlist
     im.nbits = nbits;
     im.by_residual = env_is("B200IDX_IVFPQ_BY_RESIDUAL", "1");   // the reference encodes raw vectors
     im.nprobe = std::min(64, nlist);
+    im.replicated = config.enableQueryParallelSearch && im.devices.size() > 1;
     create_ivfpq_handles(im);
-    (void)config;
 }
 AscendIndexIVFPQ::~AscendIndexIVFPQ() {}
 
@@ -808,10 +856,12 @@ void AscendIndexIVFPQ::copyFrom(const faiss::IndexIVFPQ* index) {
         const auto& li = index->invlists->ids[l];
         FAISS_THROW_IF_NOT_MSG(lc.size() == li.size() * M, "list codes and ids disagree in size");
         for (size_t v = 0; v < li.size(); ++v, ++turn) {
-            const size_t dv = turn % nd;
-            ln[dv].push_back(static_cast<int32_t>(l));
-            cd[dv].insert(cd[dv].end(), lc.begin() + v * M, lc.begin() + (v + 1) * M);
-            id[dv].push_back(li[v]);
+            for (size_t dv = im.replicated ? 0 : turn % nd; dv < nd; ++dv) {
+                ln[dv].push_back(static_cast<int32_t>(l));
+                cd[dv].insert(cd[dv].end(), lc.begin() + v * M, lc.begin() + (v + 1) * M);
+                id[dv].push_back(li[v]);
+                if (!im.replicated) break;
+            }
         }
     }
     for (size_t dv = 0; dv < nd; ++dv)
@@ -963,6 +1013,98 @@ void Search(std::vector<AscendIndexInt8*> indexes, idx_t n, const int8_t* x, idx
         impls.push_back(&ix->GetIndexImplBase());
     }
     multi_search(impls, n, x, k, distances, labels, merged);
+}
+
+// ------------------------------------------------------------------ cloner
+// FR/ascend/AscendCloner.cpp:64-99 (to CPU), :159-196 (to the devices), :232-281 (entry points).
+faiss::Index* index_ascend_to_cpu(const faiss::Index* ascend_index) {
+    FAISS_THROW_IF_NOT_MSG(ascend_index != nullptr, "Invalid index nullptr.");
+    faiss::Index* res = nullptr;
+    try {
+        if (auto flat = dynamic_cast<const AscendIndexFlat*>(ascend_index)) {
+            faiss::IndexFlat* cpu = new faiss::IndexFlat(flat->d, flat->metric_type);
+            faiss::IndexIDMap* map = new faiss::IndexIDMap(cpu);
+            res = map;
+            map->own_fields = true;
+            flat->copyTo(map);
+            return res;
+        }
+        if (auto pq = dynamic_cast<const AscendIndexIVFPQ*>(ascend_index)) {
+            faiss::IndexIVFPQ* cpu = new faiss::IndexIVFPQ();
+            res = cpu;
+            pq->copyTo(cpu);
+            return res;
+        }
+    } catch (const std::exception& e) {
+        delete res;
+        FAISS_THROW_FMT("clone from ascend to cpu failed, %s", e.what());
+    }
+    FAISS_THROW_MSG("clone from ascend to cpu not supported for this type of Index");
+}
+
+faiss::Index* index_cpu_to_ascend(std::vector<int> devices, const faiss::Index* index, const AscendClonerOptions* options) {
+    FAISS_THROW_IF_NOT_MSG(index != nullptr, "Invalid index nullptr.");
+    const int64_t res = options ? options->resourceSize : -1;
+    if (auto flat = dynamic_cast<const faiss::IndexFlat*>(index)) {
+        AscendIndexFlatConfig config(devices);
+        if (res >= 0) config.resourceSize = res;
+        return new AscendIndexFlat(flat, config);
+    }
+    if (auto pq = dynamic_cast<const faiss::IndexIVFPQ*>(index)) {
+        AscendIndexIVFPQConfig config(devices);
+        if (res >= 0) config.resourceSize = res;
+        std::unique_ptr<AscendIndexIVFPQ> out(new AscendIndexIVFPQ(pq->d, pq->metric_type, static_cast<int>(pq->nlist),
+                                                                   static_cast<int>(pq->pq.M), static_cast<int>(pq->pq.nbits),
+                                                                   config));
+        out->copyFrom(pq);
+        return out.release();
+    }
+    if (auto map = dynamic_cast<const faiss::IndexIDMap*>(index)) {
+        FAISS_THROW_IF_NOT_MSG(dynamic_cast<const faiss::IndexFlat*>(map->index) != nullptr,
+                               "clone from cpu to ascend not supported for this type of Index");
+        AscendIndexFlatConfig config(devices);
+        if (res >= 0) config.resourceSize = res;
+        return new AscendIndexFlat(map, config);
+    }
+    FAISS_THROW_MSG("clone from cpu to ascend not supported for this type of Index");
+}
+faiss::Index* index_cpu_to_ascend(std::initializer_list<int> devices, const faiss::Index* index,
+                                  const AscendClonerOptions* options) {
+    return index_cpu_to_ascend(std::vector<int>(devices), index, options);
+}
+
+faiss::Index* index_int8_ascend_to_cpu(const AscendIndexInt8* index) {
+    FAISS_THROW_IF_NOT_MSG(index != nullptr, "Invalid index nullptr.");
+    if (auto flat = dynamic_cast<const AscendIndexInt8Flat*>(index)) {
+        faiss::IndexScalarQuantizer* sq = new faiss::IndexScalarQuantizer();
+        faiss::IndexIDMap* map = new faiss::IndexIDMap(sq);
+        map->own_fields = true;
+        try {
+            flat->copyTo(map);
+        } catch (const std::exception& e) {
+            delete map;
+            FAISS_THROW_FMT("clone from ascend to cpu failed, %s", e.what());
+        }
+        return map;
+    }
+    FAISS_THROW_MSG("clone from ascend to cpu not supported for this type of Index");
+}
+AscendIndexInt8* index_int8_cpu_to_ascend(std::vector<int> devices, const faiss::Index* index,
+                                          const AscendClonerOptions* options) {
+    FAISS_THROW_IF_NOT_MSG(index != nullptr, "Invalid index nullptr.");
+    AscendIndexInt8FlatConfig config(devices);
+    if (options && options->resourceSize >= 0) config.resourceSize = options->resourceSize;
+    if (auto sq = dynamic_cast<const faiss::IndexScalarQuantizer*>(index)) return new AscendIndexInt8Flat(sq, config);
+    if (auto map = dynamic_cast<const faiss::IndexIDMap*>(index)) {
+        FAISS_THROW_IF_NOT_MSG(dynamic_cast<const faiss::IndexScalarQuantizer*>(map->index) != nullptr,
+                               "clone from cpu to ascend not supported for this type of Index");
+        return new AscendIndexInt8Flat(map, config);
+    }
+    FAISS_THROW_MSG("clone from cpu to ascend not supported for this type of Index");
+}
+AscendIndexInt8* index_int8_cpu_to_ascend(std::initializer_list<int> devices, const faiss::Index* index,
+                                          const AscendClonerOptions* options) {
+    return index_int8_cpu_to_ascend(std::vector<int>(devices), index, options);
 }
 
 }  // namespace ascend

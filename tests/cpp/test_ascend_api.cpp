@@ -8,11 +8,13 @@
 #include <faiss/ascend/AscendIndexFlat.h>
 #include <faiss/ascend/AscendIndexIVFPQ.h>
 #include <faiss/ascend/AscendIndexInt8Flat.h>
+#include <faiss/ascend/AscendCloner.h>
 #include <faiss/ascend/AscendMultiIndexSearch.h>
 
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <functional>
 #include <memory>
@@ -374,6 +376,119 @@ static void test_multi_search_gpu() {
     SetRelaxedLimits(false);
 }
 
+// index_cpu_to_ascend / index_ascend_to_cpu (FR/ascend/AscendCloner.cpp:64-99,159-196,232-281): a CPU
+// index goes to the device and back with its vectors, ids and (IVFPQ) lists intact, and the device
+// copy answers like an index built directly.
+static void test_cloner_gpu() {
+    const int d = 64;
+    const size_t nb = 3000, nq = 7;
+    auto xb = gauss(nb, d, 41);
+    auto xq = gauss(nq, d, 42);
+    // Flat behind an id map
+    IndexFlat* cpu_flat = new IndexFlat(d, METRIC_L2);
+    IndexIDMap cpu_map(cpu_flat);
+    cpu_map.own_fields = true;
+    std::vector<idx_t> ids(nb);
+    for (size_t i = 0; i < nb; ++i) ids[i] = 1000 + 3 * static_cast<idx_t>(i);
+    cpu_map.add_with_ids(static_cast<idx_t>(nb), xb.data(), ids.data());
+    std::unique_ptr<faiss::Index> dev(index_cpu_to_ascend({0}, &cpu_map));
+    CHECK(dynamic_cast<AscendIndexFlat*>(dev.get()) != nullptr && dev->ntotal == static_cast<idx_t>(nb));
+    std::vector<float> D(nq * 5), D2(nq * 5);
+    std::vector<idx_t> I(nq * 5), I2(nq * 5);
+    dev->search(static_cast<idx_t>(nq), xq.data(), 5, D.data(), I.data());
+    AscendIndexFlat direct(d, METRIC_L2);
+    direct.add_with_ids(static_cast<idx_t>(nb), xb.data(), ids.data());
+    direct.search(static_cast<idx_t>(nq), xq.data(), 5, D2.data(), I2.data());
+    CHECK(D == D2 && I == I2);
+    std::unique_ptr<faiss::Index> back(index_ascend_to_cpu(dev.get()));
+    IndexIDMap* back_map = dynamic_cast<IndexIDMap*>(back.get());
+    CHECK(back_map != nullptr && back_map->ntotal == static_cast<idx_t>(nb) && back_map->id_map == ids);
+    CHECK(throws_with([&] { index_ascend_to_cpu(&cpu_map); }, "not supported for this type of Index"));
+    CHECK(throws_with([&] { index_cpu_to_ascend({0}, &direct); }, "not supported for this type of Index"));
+    // IVFPQ: device index -> CPU struct -> device index, identical lists and answers
+    const int nlist = 1024, M = 16, d2 = 128;
+    auto xv = mixture(20000, d2, 128, 4, 77);
+    AscendIndexIVFPQ ix(d2, METRIC_L2, nlist, M, 8);
+    ix.train(20000, xv.data());
+    ix.add(20000, xv.data());
+    ix.setNumProbes(16);
+    std::unique_ptr<faiss::Index> cpu_pq(index_ascend_to_cpu(&ix));
+    IndexIVFPQ* pq = dynamic_cast<IndexIVFPQ*>(cpu_pq.get());
+    CHECK(pq != nullptr && pq->ntotal == 20000 && pq->nlist == static_cast<size_t>(nlist) && pq->pq.M == static_cast<size_t>(M));
+    std::unique_ptr<faiss::Index> dev_pq(index_cpu_to_ascend(std::vector<int>{0}, pq));
+    AscendIndexIVFPQ* ix2 = dynamic_cast<AscendIndexIVFPQ*>(dev_pq.get());
+    CHECK(ix2 != nullptr && ix2->ntotal == 20000 && ix2->getNumProbes() == 16);
+    std::vector<float> Da(nq * 10), Db(nq * 10);
+    std::vector<idx_t> Ia(nq * 10), Ib(nq * 10);
+    ix.search(static_cast<idx_t>(nq), xv.data(), 10, Da.data(), Ia.data());
+    if (ix2) ix2->search(static_cast<idx_t>(nq), xv.data(), 10, Db.data(), Ib.data());
+    CHECK(Da == Db && Ia == Ib);
+    // int8: the index that is not a faiss::Index
+    std::vector<int8_t> xi(2000 * 64);
+    std::mt19937 rng(5);
+    for (auto& v : xi) v = static_cast<int8_t>(static_cast<int>(rng() % 256) - 128);
+    AscendIndexInt8Flat i8(64, METRIC_L2);
+    i8.add(2000, xi.data());
+    std::unique_ptr<faiss::Index> cpu8(index_int8_ascend_to_cpu(&i8));
+    CHECK(cpu8 != nullptr && cpu8->ntotal == 2000);
+    std::unique_ptr<AscendIndexInt8> dev8(index_int8_cpu_to_ascend({0}, cpu8.get()));
+    CHECK(dev8 != nullptr && dev8->getNTotal() == 2000);
+    std::vector<float> D8a(3 * 4), D8b(3 * 4);
+    std::vector<idx_t> I8a(3 * 4), I8b(3 * 4);
+    i8.search(3, xi.data(), 4, D8a.data(), I8a.data());
+    if (dev8) dev8->search(3, xi.data(), 4, D8b.data(), I8b.data());
+    CHECK(D8a == D8b && I8a == I8b);
+}
+
+// Two devices (skipped on a box with one): an index spread over both answers fp16 queries, and the
+// query-parallel IVFPQ layout (enableQueryParallelSearch: the index replicated, the queries split)
+// answers exactly like the index on one device.
+static void test_two_devices_gpu(int ndev) {
+    if (ndev < 2) {
+        std::printf("two-device checks skipped (%d device)\n", ndev);
+        return;
+    }
+    const int d = 64;
+    const size_t nb = 5000, nq = 11;
+    auto xb = gauss(nb, d, 51);
+    auto xq = gauss(nq, d, 52);
+    AscendIndexFlatConfig two({0, 1});
+    AscendIndexFlat spread(d, METRIC_L2, two), one(d, METRIC_L2);
+    spread.add(static_cast<idx_t>(nb), xb.data());
+    one.add(static_cast<idx_t>(nb), xb.data());
+    std::vector<uint16_t> xh(nq * d);
+    for (size_t i = 0; i < xh.size(); ++i) {
+        const _Float16 h = static_cast<_Float16>(xq[i]);
+        std::memcpy(&xh[i], &h, 2);
+    }
+    std::vector<float> D(nq * 5), D1(nq * 5);
+    std::vector<idx_t> I(nq * 5), I1(nq * 5);
+    spread.search(static_cast<idx_t>(nq), xh.data(), 5, D.data(), I.data());
+    one.search(static_cast<idx_t>(nq), xh.data(), 5, D1.data(), I1.data());
+    CHECK(D == D1 && I == I1);
+    const int nlist = 1024, M = 16, d2 = 128;
+    auto xv = mixture(20000, d2, 128, 4, 78);
+    AscendIndexIVFPQConfig rc({0, 1});
+    rc.enableQueryParallelSearch = true;
+    AscendIndexIVFPQ rep(d2, METRIC_L2, nlist, M, 8, rc), single(d2, METRIC_L2, nlist, M, 8);
+    rep.train(20000, xv.data());
+    single.train(20000, xv.data());
+    rep.add(20000, xv.data());
+    single.add(20000, xv.data());
+    CHECK(rep.ntotal == 20000);
+    uint32_t total = 0;
+    for (int l = 0; l < nlist; ++l) total += rep.getListLength(l);
+    CHECK(total == 20000);
+    rep.setNumProbes(16);
+    single.setNumProbes(16);
+    const size_t nq2 = 37;
+    std::vector<float> Da(nq2 * 10), Db(nq2 * 10);
+    std::vector<idx_t> Ia(nq2 * 10), Ib(nq2 * 10);
+    rep.search(static_cast<idx_t>(nq2), xv.data(), 10, Da.data(), Ia.data());
+    single.search(static_cast<idx_t>(nq2), xv.data(), 10, Db.data(), Ib.data());
+    CHECK(Da == Db && Ia == Ib);
+}
+
 int main(int argc, char** argv) {
     const std::string mode = argc > 1 ? argv[1] : "cpu";
     test_parameter_errors();
@@ -384,6 +499,8 @@ int main(int argc, char** argv) {
         test_int8_gpu();
         test_ivfpq_gpu();
         test_multi_search_gpu();
+        test_cloner_gpu();
+        test_two_devices_gpu(argc > 2 ? std::atoi(argv[2]) : 1);
     }
     std::printf("%d checks, %d failed\n", g_checks, g_fail);
     return g_fail ? 1 : 0;

@@ -19,8 +19,8 @@ def _build(b200):
     return EXE
 
 
-def _run(mode):
-    r = subprocess.run([EXE, mode], capture_output=True, text=True, timeout=1200)
+def _run(mode, *extra):
+    r = subprocess.run([EXE, mode, *extra], capture_output=True, text=True, timeout=1200)
     print(r.stdout[-4000:], r.stderr[-2000:])
     assert r.returncode == 0, r.stdout[-4000:] + r.stderr[-2000:]
     assert "0 failed" in r.stdout
@@ -37,5 +37,6 @@ def test_cpp_api_parameter_contract(b200):
 
 @pytest.mark.gpu
 def test_cpp_api_on_gpu(b200):
+    import torch
     _build(b200)
-    _run("gpu")
+    _run("gpu", str(torch.cuda.device_count()))
