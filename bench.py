@@ -811,7 +811,8 @@ def measure(wl, args, b, dev, rank, world, dist, sampler, peaks, mode):
                 gpu_launches=int(launches),
                 roofline=roof,
                 stage_ms_per_step={n: v / args.steps for n, v in stats["stage_ms"].items() if v > 0},
-                fallback_queries_per_step=(s1["fallback_queries"] - s0["fallback_queries"]) / args.steps)
+                fallback_queries_per_step=(s1["fallback_queries"] - s0["fallback_queries"]) / args.steps,
+                second_pass_queries_per_step=(s1["second_pass_queries"] - s0["second_pass_queries"]) / args.steps)
     return line, (outD_np, outI_np)
 
 

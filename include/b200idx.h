@@ -199,10 +199,12 @@ typedef struct {
     uint64_t stage_launches[B200IDX_NUM_STAGES];
     uint64_t searches;
     uint64_t queries;
-    uint64_t fallback_queries; /* queries re-run without a threshold after a candidate overflow */
+    uint64_t fallback_queries; /* queries re-run without a threshold after a candidate overflow (IVFPQ: exact re-scan) */
     uint64_t gemm_launches;
     uint64_t kernel_launches;  /* kernels of this library launched by searches */
     uint64_t scan_codes;       /* IVFPQ: PQ codes visited so far */
+    uint64_t second_pass_queries; /* IVFPQ: queries whose first filter pass could not be verified (ties at its
+                                     boundary) and that took the second, fixed-threshold filter pass */
 } b200idx_stats_t;
 int b200idx_stats(b200idx_t* h, b200idx_stats_t* out, int reset);
 /* Per-stage CUDA-event timing on the index's stream (off by default; the reference only has

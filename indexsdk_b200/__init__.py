@@ -36,7 +36,8 @@ STAGES = ("sample", "full_gemm", "refine", "select", "coarse", "lut", "scan", "m
 class Stats(C.Structure):
     _fields_ = [("stage_ms", C.c_double * 8), ("stage_launches", C.c_uint64 * 8)] + [
         (n, C.c_uint64) for n in
-        ("searches", "queries", "fallback_queries", "gemm_launches", "kernel_launches", "scan_codes")]
+        ("searches", "queries", "fallback_queries", "gemm_launches", "kernel_launches", "scan_codes",
+         "second_pass_queries")]
 
 
 def lib_path() -> str:

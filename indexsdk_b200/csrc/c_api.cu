@@ -745,6 +745,7 @@ int b200idx_stats(b200idx_t* h, b200idx_stats_t* out, int reset) {
     out->gemm_launches = s.gemm_launches;
     out->kernel_launches = s.kernel_launches;
     out->scan_codes = s.scan_codes;
+    out->second_pass_queries = s.second_pass_queries;
     if (reset) s = SearchStats();
     return B200IDX_OK;
 }

@@ -45,7 +45,9 @@ FlatIndex::FlatIndex(int d, int metric, int dtype, int device)
     B200_CUDA_CHECK(cudaDeviceGetAttribute(&num_sms_, cudaDevAttrMultiProcessorCount, device_));
     B200_CUDA_CHECK(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
     use_simt_ = env_flag("B200IDX_GEMM", "simt");
-    prof_ = env_flag("B200IDX_PROF", "1");   // development aid: per-role cycle counters of the GEMM kernel
+#ifdef B200IDX_DEV_PROF
+    prof_ = env_flag("B200IDX_PROF", "1");   // development builds: per-role cycle counters of the GEMM kernel
+#endif
     if (prof_) {
         w_prof_.ensure(32 * 8);
         B200_CUDA_CHECK(cudaMemset(w_prof_.get(), 0, 32 * 8));

@@ -35,7 +35,8 @@ struct SearchStats {
     uint64_t stage_launches[kNumStages] = {0, 0, 0, 0, 0, 0, 0, 0};
     uint64_t searches = 0;
     uint64_t queries = 0;
-    uint64_t fallback_queries = 0;   // queries re-run without a threshold after a candidate overflow
+    uint64_t fallback_queries = 0;   // queries re-run without a threshold after a candidate overflow (IVFPQ: exact re-scan)
+    uint64_t second_pass_queries = 0;   // IVFPQ: queries that took the second (fixed-threshold) filter pass
     uint64_t gemm_launches = 0;
     uint64_t kernel_launches = 0;    // every kernel of this library launched by searches
     uint64_t scan_codes = 0;         // IVFPQ: codes visited

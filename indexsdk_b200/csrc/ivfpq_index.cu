@@ -1320,6 +1320,149 @@ ivfpq_exact_scan_kernel(const ScanArgs a) {
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// 3b'. second filter pass for queries the verification turned down.
+//      The first pass keeps the k' best approximate distances; when more than k' vectors are (nearly)
+//      tied at the boundary -- identical codes: raw encoding of clustered data gives hundreds -- the
+//      exact k-th distance cannot be told from the worst kept one and the query is flagged.  The
+//      refined result still gives an UPPER bound U of the true k-th distance (k of the kept vectors
+//      are at or below it), and every true top-k member has an approximate distance <= U + eps.
+//      This pass collects ALL vectors under that fixed threshold (no kept lists, one shared counter),
+//      and ivfpq_collect_refine_kernel orders them exactly by (distance, label): ties are then
+//      decided by the labels of all tied vectors, as in the exact scan, at the cost of one more
+//      filter scan instead of a canonical one.  More than `cap` vectors under the threshold leave
+//      the flag set (exact scan).
+// ---------------------------------------------------------------------------------------
+constexpr int kCollectCap = 1024;
+
+template <int MT>
+__global__ void __launch_bounds__(kScanThreads)
+ivfpq_collect_kernel(const ScanArgs a, uint32_t* cpos, uint32_t* ccount) {
+    extern __shared__ __align__(16) uint8_t col_smem[];
+    float* lut = reinterpret_cast<float*>(col_smem);   // [MT][256][32]
+    __shared__ unsigned int s_count;
+    __shared__ float s_thr;
+    const int slot = blockIdx.x;
+    const int64_t q = a.qlist[slot];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) s_count = 0;
+    switch (a.dsub) {
+        case 4: build_scan_table<4>(a, q, MT, lut, 32, warp, kScanThreads / 32); break;
+        case 8: build_scan_table<8>(a, q, MT, lut, 32, warp, kScanThreads / 32); break;
+        default: build_scan_table<0>(a, q, MT, lut, 32, warp, kScanThreads / 32); break;
+    }
+    if (warp == 0) {
+        float qn2 = 0.f;
+        if (a.by_residual)
+            for (int t = lane; t < a.d; t += 32) qn2 = fmaf(a.xq[q * a.d + t], a.xq[q * a.d + t], qn2);
+        for (int o = 16; o > 0; o >>= 1) qn2 += __shfl_xor_sync(0xffffffffu, qn2, o);
+        if (lane == 0) {
+            // U: the k-th refined distance of the first pass (+inf when fewer than k were kept)
+            const bool have = a.outI[q * a.k + a.k - 1] >= 0;
+            const float u = have ? a.outD[q * a.k + a.k - 1] : __int_as_float(0x7f800000);
+            float eps = a.err_rel * fabsf(u);
+            if (a.by_residual) {
+                const float coarse_max = a.cD[q * a.nprobe + a.nprobe - 1];
+                eps = a.err_rel * (fabsf(coarse_max) + a.t2_bound + 2.f * sqrtf(qn2) * a.cb_bound + fabsf(u));
+            }
+            s_thr = u + 2.f * eps;
+        }
+    }
+    __syncthreads();
+    const float thr = s_thr;
+    RowSum128<MT> sum;
+    const uint32_t lut_base = static_cast<uint32_t>(__cvta_generic_to_shared(lut));
+#pragma unroll
+    for (int s = 0; s < 16; ++s) sum.offb[s] = lut_base + 4u * (((s + lane) & 15) + (lane & 16));
+    const uint4* codes4 = reinterpret_cast<const uint4*>(a.codes);
+    const unsigned lt = (1u << lane) - 1u;
+    for (int p = warp; p < a.nprobe; p += kScanThreads / 32) {
+        const int64_t list = a.cI[q * a.nprobe + p];
+        if (list < 0 || list >= a.nlist) continue;
+        const uint32_t begin = static_cast<uint32_t>(a.offsets[list]);
+        const uint32_t end = begin + static_cast<uint32_t>(a.lens[list]);
+        const float base = a.by_residual ? a.cD[q * a.nprobe + p] : 0.f;
+        for (uint32_t v0 = begin; v0 < end; v0 += 32) {
+            const uint32_t v = v0 + lane;          // padded slots carry NaN in t2; raw encoding: bounds test
+            uint4 c[MT];
+#pragma unroll
+            for (int g = 0; g < MT; ++g) c[g] = __ldg(codes4 + static_cast<size_t>(v) * MT + g);
+            float acc = a.by_residual ? base + __ldg(a.t2 + v) : (v < end ? 0.f : __int_as_float(0x7fc00000));
+            sum(c, acc);
+            const bool pass = acc <= thr;
+            const unsigned bal = __ballot_sync(0xffffffffu, pass);
+            if (bal) {
+                unsigned int i0 = 0;
+                if (lane == 0) i0 = atomicAdd(&s_count, static_cast<unsigned int>(__popc(bal)));
+                i0 = __shfl_sync(0xffffffffu, i0, 0);
+                const unsigned int i = i0 + __popc(bal & lt);
+                if (pass && i < static_cast<unsigned int>(kCollectCap)) cpos[static_cast<size_t>(slot) * kCollectCap + i] = v;
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) ccount[slot] = s_count;
+}
+
+// The collected vectors of a flagged query: canonical distances, order by (distance, label), top k.
+__global__ void __launch_bounds__(kScanThreads)
+ivfpq_collect_refine_kernel(const ScanArgs a, const uint32_t* cpos, const uint32_t* ccount) {
+    extern __shared__ __align__(16) uint8_t cr_smem[];
+    const int slot = blockIdx.x;
+    const int64_t q = a.qlist[slot];
+    const unsigned int n = ccount[slot];
+    if (n > static_cast<unsigned int>(kCollectCap)) return;   // too many under the threshold: the flag stays set
+    int P = 32;
+    while (P < static_cast<int>(n)) P <<= 1;
+    int64_t* sl = reinterpret_cast<int64_t*>(cr_smem);
+    float* sd = reinterpret_cast<float*>(cr_smem + static_cast<size_t>(P) * 8);
+    __shared__ uint32_t s_lb[kRefMaxProbe], s_le[kRefMaxProbe];
+    __shared__ int32_t s_ll[kRefMaxProbe];
+    const bool staged = a.by_residual && a.nprobe <= kRefMaxProbe;
+    if (staged) {
+        for (int p = threadIdx.x; p < a.nprobe; p += kScanThreads) {
+            const int64_t list = a.cI[q * a.nprobe + p];
+            const bool ok = list >= 0 && list < a.nlist;
+            s_ll[p] = ok ? static_cast<int32_t>(list) : 0;
+            s_lb[p] = ok ? static_cast<uint32_t>(a.offsets[list]) : 0u;
+            s_le[p] = ok ? s_lb[p] + static_cast<uint32_t>(a.lens[list]) : 0u;
+        }
+        __syncthreads();
+    }
+    for (int i = threadIdx.x; i < P; i += kScanThreads) {
+        float dist = __int_as_float(0x7f800000);
+        int64_t label = kNoLabel;
+        if (i < static_cast<int>(n)) {
+            const uint32_t pos = cpos[static_cast<size_t>(slot) * kCollectCap + i];
+            int64_t list = 0;
+            if (staged) {
+                for (int p = 0; p < a.nprobe; ++p)
+                    if (pos >= s_lb[p] && pos < s_le[p]) list = s_ll[p];
+            } else if (a.by_residual) {
+                int lo = 0, hi = a.nlist;
+                while (hi - lo > 1) {
+                    const int mid = (lo + hi) >> 1;
+                    if (a.offsets[mid] <= static_cast<int64_t>(pos)) lo = mid;
+                    else hi = mid;
+                }
+                list = lo;
+            }
+            dist = exact_distance(a, q, pos, list);
+            label = a.ids[pos];
+        }
+        sd[i] = dist;
+        sl[i] = label;
+    }
+    __syncthreads();
+    block_sort_pairs<int64_t>(sd, sl, P);
+    for (int i = threadIdx.x; i < a.k; i += kScanThreads) {
+        const bool real = i < P && sl[i] != kNoLabel;
+        a.outD[q * a.k + i] = real ? sd[i] : kInf;
+        a.outI[q * a.k + i] = real ? sl[i] : -1;
+    }
+    if (threadIdx.x == 0) a.flag[q] = 0;
+}
+
 template <typename Kern>
 cudaError_t set_smem(Kern kern, size_t smem) {
     if (smem > 48 * 1024)
@@ -1410,6 +1553,32 @@ cudaError_t launch_exact(const ScanArgs& a, int nq_launch, cudaStream_t st) {
 #undef B200_EXACT_CASE
 }
 
+cudaError_t launch_collect(const ScanArgs& a, int nslots, uint32_t* cpos, uint32_t* ccount, cudaStream_t st) {
+    const int mt = a.M / 16;
+    const size_t smem = static_cast<size_t>(mt) * kKsub * 32 * 4;
+    cudaError_t e = cudaSuccess;
+#define B200_COLLECT_CASE(MTV)                                                \
+    case MTV: {                                                               \
+        auto kern = ivfpq_collect_kernel<MTV>;                                \
+        e = set_smem(kern, smem);                                             \
+        if (e != cudaSuccess) return e;                                       \
+        kern<<<nslots, kScanThreads, smem, st>>>(a, cpos, ccount);            \
+        break;                                                                \
+    }
+    switch (mt) {
+        B200_COLLECT_CASE(1)
+        B200_COLLECT_CASE(2)
+        B200_COLLECT_CASE(3)
+        B200_COLLECT_CASE(4)
+        default: return cudaErrorInvalidValue;
+    }
+#undef B200_COLLECT_CASE
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    ivfpq_collect_refine_kernel<<<nslots, kScanThreads, static_cast<size_t>(kCollectCap) * 12, st>>>(a, cpos, ccount);
+    return cudaGetLastError();
+}
+
 inline unsigned blocks_for(int64_t n, int threads) { return static_cast<unsigned>((n + threads - 1) / threads); }
 inline int pow2_ceil_int(int v) {
     int p = 1;
@@ -1437,8 +1606,10 @@ IvfpqIndex::IvfpqIndex(int d, int nlist, int M, int nbits, bool by_residual, int
     B200_CUDA_CHECK(cudaMemset(w_tmp_.get(), 0, sizeof(unsigned long long)));
     const char* e = std::getenv("B200IDX_IVFPQ_EXACT");
     force_exact_ = e && std::strcmp(e, "1") == 0;
-    const char* np = std::getenv("B200IDX_IVFPQ_NO_PERSIST");   // development aid: always the per-query CTAs
+#ifdef B200IDX_DEV_PROF
+    const char* np = std::getenv("B200IDX_IVFPQ_NO_PERSIST");   // development builds: always the per-query CTAs
     no_persist_ = np && std::strcmp(np, "1") == 0;
+#endif
     const char* tc = std::getenv("B200IDX_IVFPQ_TC");
     tc_scan_ = tc && std::strcmp(tc, "1") == 0;
     w_work_.ensure(sizeof(unsigned int));
@@ -1821,6 +1992,9 @@ void IvfpqIndex::search_stages(int64_t nq, const float* xq, int k, float* D, int
     const bool fast = rotated_ && !force_exact_ && kpt <= 32;
     const int kprime = 32 * kpt;
     const int64_t page = 16384;
+    unsigned long long scanned = stats_.scan_codes;
+    const unsigned long long* scanned_src = &scanned;
+    bool idle = true;    // the stream has been synchronised and nothing was queued since
     for (int64_t q0 = 0; q0 < nq; q0 += page) {
         const int64_t m = std::min(page, nq - q0);
         const float* xp = xq + q0 * d_;
@@ -1870,6 +2044,7 @@ void IvfpqIndex::search_stages(int64_t nq, const float* xq, int k, float* D, int
             B200_CUDA_CHECK(launch_exact(a, static_cast<int>(m), st));
             timer_.end(st);
             stats_.kernel_launches += 2;
+            idle = false;
             continue;
         }
         // probe splits: enough CTAs to fill the machine, bounded so that the refine kernel's
@@ -1964,8 +2139,12 @@ void IvfpqIndex::search_stages(int64_t nq, const float* xq, int k, float* D, int
                 B200_CUDA_CHECK(cudaMemsetAsync(w_tc_err_.get(), 0, 4, st));
             }
             t.err = tc_err = w_tc_err_.as<unsigned int>();
+#ifdef B200IDX_DEV_PROF
             const char* pe = std::getenv("B200IDX_PROF");
             const bool tc_prof = pe && std::strcmp(pe, "1") == 0;
+#else
+            const bool tc_prof = false;
+#endif
             if (tc_prof) {
                 w_tc_prof_.ensure(64 + static_cast<size_t>(m) * 4);
                 B200_CUDA_CHECK(cudaMemsetAsync(w_tc_prof_.get(), 0, 64, st));
@@ -2026,11 +2205,19 @@ void IvfpqIndex::search_stages(int64_t nq, const float* xq, int k, float* D, int
         B200_CUDA_CHECK(cudaGetLastError());
         timer_.end(st);
         stats_.kernel_launches += 3;
-        uint8_t* hf = static_cast<uint8_t*>(h_flag_.ensure(static_cast<size_t>(m)));
+        // flags of the page and, behind them, the counter of visited codes: one copy-back and one
+        // synchronisation per page
+        const size_t cnt_off = (static_cast<size_t>(m) + 7) & ~size_t(7);
+        uint8_t* hf = static_cast<uint8_t*>(h_flag_.ensure(cnt_off + 8));
         B200_CUDA_CHECK(cudaMemcpyAsync(hf, a.flag, static_cast<size_t>(m), cudaMemcpyDeviceToHost, st));
+        B200_CUDA_CHECK(cudaMemcpyAsync(hf + cnt_off, w_tmp_.get(), 8, cudaMemcpyDeviceToHost, st));
+        scanned_src = reinterpret_cast<const unsigned long long*>(hf + cnt_off);
+        idle = false;
         unsigned int tc_err_host = 0;
         if (tc_err) B200_CUDA_CHECK(cudaMemcpyAsync(&tc_err_host, tc_err, 4, cudaMemcpyDeviceToHost, st));
         B200_CUDA_CHECK(cudaStreamSynchronize(st));
+        idle = true;
+        scanned = *scanned_src;
         if (tc_err_host) cudaMemsetAsync(tc_err, 0, 4, st);
         if (tc_err_host & 2u)                       // a staging area overflowed: candidates were lost,
             std::memset(hf, 1, static_cast<size_t>(m));   // every query of the page takes the exact path
@@ -2041,6 +2228,25 @@ void IvfpqIndex::search_stages(int64_t nq, const float* xq, int k, float* D, int
         std::vector<int32_t> bad;
         for (int64_t i = 0; i < m; ++i)
             if (hf[i]) bad.push_back(static_cast<int32_t>(i));
+        if (!bad.empty() && k <= kCollectCap && !(tc_err_host & 2u)) {
+            // second filter pass with a fixed threshold for the flagged queries (ties at the k' boundary)
+            stats_.second_pass_queries += bad.size();
+            int32_t* ql = static_cast<int32_t*>(w_qlist_.ensure(bad.size() * 4));
+            B200_CUDA_CHECK(cudaMemcpyAsync(ql, bad.data(), bad.size() * 4, cudaMemcpyHostToDevice, st));
+            a.qlist = ql;
+            uint32_t* cpos = static_cast<uint32_t*>(w_cpos_.ensure(bad.size() * kCollectCap * 4));
+            uint32_t* ccount = static_cast<uint32_t*>(w_ccount_.ensure(bad.size() * 4));
+            timer_.begin(kStageScan, st);
+            B200_CUDA_CHECK(launch_collect(a, static_cast<int>(bad.size()), cpos, ccount, st));
+            timer_.end(st);
+            B200_CUDA_CHECK(cudaMemcpyAsync(hf, a.flag, static_cast<size_t>(m), cudaMemcpyDeviceToHost, st));
+            B200_CUDA_CHECK(cudaStreamSynchronize(st));
+            stats_.kernel_launches += 2;
+            std::vector<int32_t> still;
+            for (int32_t i : bad)
+                if (hf[i]) still.push_back(i);
+            bad.swap(still);
+        }
         if (!bad.empty()) {
             stats_.fallback_queries += bad.size();
             int32_t* ql = static_cast<int32_t*>(w_qlist_.ensure(bad.size() * 4));
@@ -2051,9 +2257,10 @@ void IvfpqIndex::search_stages(int64_t nq, const float* xq, int k, float* D, int
             stats_.kernel_launches += 1;
         }
     }
-    unsigned long long scanned = 0;
-    B200_CUDA_CHECK(cudaMemcpyAsync(&scanned, w_tmp_.get(), 8, cudaMemcpyDeviceToHost, st));
-    B200_CUDA_CHECK(cudaStreamSynchronize(st));
+    if (!idle) {   // (the exact-only path queues its kernels without reading anything back)
+        B200_CUDA_CHECK(cudaMemcpyAsync(&scanned, w_tmp_.get(), 8, cudaMemcpyDeviceToHost, st));
+        B200_CUDA_CHECK(cudaStreamSynchronize(st));
+    }
     timer_.collect(stats_);
     stats_.scan_codes = scanned;
     stats_.kernel_launches += coarse_->stats().kernel_launches;

@@ -98,7 +98,7 @@ private:
     DeviceBuffer codes_, ids_, t2_;
     // scratch
     DeviceBuffer w_work_, w_cD_, w_cI_, w_fd_, w_fp_, w_fth_, w_flag_, w_qlist_, w_q_, w_D_, w_I_, w_assign_D_,
-        w_assign_I_, w_list_, w_codes_, w_t2_, w_ids_, w_x_, w_tmp_, w_vflag_;
+        w_assign_I_, w_list_, w_codes_, w_t2_, w_ids_, w_x_, w_tmp_, w_vflag_, w_cpos_, w_ccount_;
     DeviceBuffer w_tc_keys_, w_tc_vals_, w_tc_keys2_, w_tc_vals2_, w_tc_first_, w_tc_last_, w_tc_cI0_, w_tc_cD0_,
         w_tc_fd0_, w_tc_fp0_, w_tc_fth0_, w_tc_tau_, w_tc_cd_, w_tc_cp_, w_tc_cn_, w_tc_sort_, w_tc_err_, w_tc_prof_, w_tc_stage_, w_tc_stage_n_, w_tc_okeys_, w_tc_osort_;
     PinnedBuffer h_flag_;

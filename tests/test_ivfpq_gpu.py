@@ -100,12 +100,16 @@ def test_empty_lists_duplicates_and_short_results(b200):
 
 
 @pytest.mark.parametrize("resid", [False, True])
-def test_more_duplicates_than_the_filter_keeps(b200, resid):
-    """200 copies of each vector: the filter keeps k' = 32 candidates per query, the top ties are
-    wider than that, verification must fail and the exact re-scan must return the lowest labels."""
+@pytest.mark.parametrize("copies,second_pass", [(200, True), (1500, False)])
+def test_more_duplicates_than_the_filter_keeps(b200, resid, copies, second_pass):
+    """Many copies of each vector: the filter keeps k' = 32 candidates per query, the top ties are
+    wider than that and the verification must fail.  With 200 copies the second filter pass (fixed
+    threshold, every tied vector collected, exact order by label) settles the query; with 1500
+    copies more vectors lie under its threshold than it can hold and the exact re-scan takes over.
+    Either way the lowest labels among the tied vectors must come back."""
     d, nlist, M = 64, 8, 16
     base, _ = datasets.mixture(40, d, 4, seed=3)
-    xb = np.repeat(base, 200, axis=0)
+    xb = np.repeat(base, copies, axis=0)
     ids = np.random.default_rng(0).permutation(xb.shape[0]).astype(np.int64)
     cent, cb = datasets.train_ivfpq(base, nlist, M, resid, niter=3)
     ix = _build(b200, xb, ids, cent, cb, resid, chunks=2)
@@ -115,7 +119,9 @@ def test_more_duplicates_than_the_filter_keeps(b200, resid):
     D, I = ix.search(xq, 10)
     Dr, Ir = oracle.ivfpq_search(cent, cb, resid, off, cs, idl, xq, nlist, 10)
     assert_exact(D, I, Dr, Ir)
-    assert ix.stats()["fallback_queries"] == 12
+    st = ix.stats()
+    assert st["second_pass_queries"] == 12
+    assert st["fallback_queries"] == (0 if second_pass else 12)
 
 
 def test_exact_scan_kernels_alone(b200, monkeypatch):
