@@ -249,48 +249,31 @@ struct RowEpilogue {
             }
         } else {
             if (!row_ok) return;
-            // A column passes when its D is not negative.  The AND of the sign bits is kept per group
-            // of four columns: one test rules the whole chunk out (the common case), eight tests find
-            // the groups that hold a candidate, and inside such a group the four columns are tested
-            // where they are -- no bit mask to assemble and no run-time indexed register to fetch.
-            uint32_t n4[8];
+            uint32_t t[16];
 #pragma unroll
-            for (int g = 0; g < 8; ++g) n4[g] = (r[4 * g] & r[4 * g + 1]) & (r[4 * g + 2] & r[4 * g + 3]);
-            const uint32_t all = ((n4[0] & n4[1]) & (n4[2] & n4[3])) & ((n4[4] & n4[5]) & (n4[6] & n4[7]));
-            if (static_cast<int32_t>(all) < 0) return;   // every D negative: no key <= tau here
-            uint32_t keep = nvalid >= 32 ? 0xFFFFFFFFu : ((1u << nvalid) - 1u);   // bit c: column c takes part
-            if (a.qmask) keep &= mask_word(col0);
-            // bit (7 - g) of gm: every D of group g is negative.  The groups with a candidate are
-            // walked in a loop whose body exists once (a switch copies the group's four registers):
-            // the code stays small enough to live in the instruction cache.
-            uint32_t gm = 0;
+            for (int i = 0; i < 16; ++i) t[i] = r[2 * i] & r[2 * i + 1];
 #pragma unroll
-            for (int g = 0; g < 8; ++g) gm = __funnelshift_l(n4[g], gm, 1);
-            uint32_t hit = ~gm & 0xFFu;
-            while (hit) {
-                const int g = 7 - (31 - __clz(hit));
-                hit &= ~(0x80u >> g);
-                uint32_t v[4];
-                switch (g) {
-                    case 0: v[0] = r[0]; v[1] = r[1]; v[2] = r[2]; v[3] = r[3]; break;
-                    case 1: v[0] = r[4]; v[1] = r[5]; v[2] = r[6]; v[3] = r[7]; break;
-                    case 2: v[0] = r[8]; v[1] = r[9]; v[2] = r[10]; v[3] = r[11]; break;
-                    case 3: v[0] = r[12]; v[1] = r[13]; v[2] = r[14]; v[3] = r[15]; break;
-                    case 4: v[0] = r[16]; v[1] = r[17]; v[2] = r[18]; v[3] = r[19]; break;
-                    case 5: v[0] = r[20]; v[1] = r[21]; v[2] = r[22]; v[3] = r[23]; break;
-                    case 6: v[0] = r[24]; v[1] = r[25]; v[2] = r[26]; v[3] = r[27]; break;
-                    default: v[0] = r[28]; v[1] = r[29]; v[2] = r[30]; v[3] = r[31]; break;
-                }
-                const uint32_t k4 = keep >> (4 * g);
+            for (int w = 8; w > 0; w >>= 1)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float dv = __uint_as_float(v[j]);
-                    if (dv >= 0.f && ((k4 >> j) & 1u)) {   // false for NaN
-                        // approximate key (the fp32 refinement recomputes it): D = (tau' - key) / 2 or tau' - key
-                        const float key = l2 ? fmaf(-2.f, dv, tq) : tq - dv;
-                        append(pack_cand(float_to_ord(key), static_cast<uint32_t>(col0 + 4 * g + j)));
-                    }
-                }
+                for (int i = 0; i < w; ++i) t[i] &= t[i + w];
+            if (static_cast<int32_t>(t[0]) < 0) return;   // every D negative: no key <= tau here
+            uint32_t m0 = 0, m1 = 0;                      // bit (31 - c): D of column c has its sign set
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                m0 = __funnelshift_l(r[c], m0, 1);
+                m1 = __funnelshift_l(r[16 + c], m1, 1);
+            }
+            uint32_t mask = ~((m0 << 16) | (m1 & 0xFFFFu));
+            mask &= nvalid >= 32 ? 0xFFFFFFFFu : ~(0xFFFFFFFFu >> nvalid);
+            if (a.qmask) mask &= __brev(mask_word(col0));   // column c is bit (31 - c) here, bit c in the filter
+            while (mask) {
+                const uint32_t c = __clz(mask);
+                mask &= ~(0x80000000u >> c);
+                const float dv = __uint_as_float(pick(r, c));
+                if (!(dv >= 0.f)) continue;   // NaN
+                // approximate key (the fp32 refinement recomputes it): D = (tau' - key) / 2 or tau' - key
+                const float key = l2 ? fmaf(-2.f, dv, tq) : tq - dv;
+                append(pack_cand(float_to_ord(key), static_cast<uint32_t>(col0 + c)));
             }
         }
     }
