@@ -314,6 +314,13 @@ AscendIndexInt8* index_int8_cpu_to_ascend(std::vector<int> devices, const faiss:
 void SetRelaxedLimits(bool on);
 bool RelaxedLimits();
 
+// What METRIC_INNER_PRODUCT means on an AscendIndexInt8Flat created from now on.  Off (default):
+// the exact int32 dot product, returned as float.  On (this switch or env B200IDX_INT8_IP_COSINE=1):
+// the fp16 cosine the reference computes for that metric (its "Cos" index,
+// FR/ascend/impl/AscendIndexInt8FlatImpl.cpp:790-793) -- B200IDX_METRIC_INT8_COSINE of the C ABI.
+void SetInt8InnerProductAsCosine(bool on);
+bool Int8InnerProductAsCosine();
+
 #define VALUE_UNUSED(x) (void)(x)
 }  // namespace ascend
 }  // namespace faiss

@@ -30,7 +30,18 @@ enum {
 };
 
 /* Metric values mirror the device layer of the reference: FR/ascenddaemon/impl/Index.h:60-64. */
-enum { B200IDX_METRIC_INNER_PRODUCT = 0, B200IDX_METRIC_L2 = 1 };
+enum {
+    B200IDX_METRIC_INNER_PRODUCT = 0,
+    B200IDX_METRIC_L2 = 1,
+    /* Int8Flat only: the fp16 cosine the reference's Int8Flat index returns for
+     * METRIC_INNER_PRODUCT (FR/ascend/impl/AscendIndexInt8FlatImpl.cpp:790-793 instantiates the
+     * "Cos" index; arithmetic of FR/ops/tbe/impl/int8_l2_norm.py:140-183 and
+     * FR/ops/tbe/impl/distance_int8_cos_maxs.py:256-284):
+     *   fp16( fp16(q.x * 0.01) * fp16( rnorm(x) * rnorm(q) ) ),  rnorm(v) = fp16(1 / sqrt(fp16(|v|^2 * 0.01)));
+     * larger is better, ties by lower position, a NaN score ranks last and is reported as -inf.
+     * B200IDX_METRIC_INNER_PRODUCT on an Int8Flat index stays the exact int32 dot product. */
+    B200IDX_METRIC_INT8_COSINE = 2
+};
 
 /* Storage / arithmetic type of a Flat index.
  *   F32: fp32 rows; a bf16 tensor-core pass filters candidates, results are re-computed in fp32.

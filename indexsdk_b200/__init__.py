@@ -17,6 +17,7 @@ from . import build as _build
 
 METRIC_INNER_PRODUCT = 0
 METRIC_L2 = 1
+METRIC_INT8_COSINE = 2     # Int8Flat only: the reference's fp16 cosine (see include/b200idx.h)
 F32 = 0
 F16 = 1
 

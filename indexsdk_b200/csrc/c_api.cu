@@ -84,11 +84,12 @@ int guarded_create(F&& f) {
     }
 }
 
-void check_common_create(int d, int metric, int device, b200idx_t** out) {
+void check_common_create(int d, int metric, int device, b200idx_t** out, bool allow_cosine = false) {
     if (!out) throw std::invalid_argument("out must not be NULL");
     if (d <= 0 || d % 16 != 0 || d > 4096)
         throw std::invalid_argument("Unsupported dims: d must be a multiple of 16 in (0, 4096]");
-    if (metric != B200IDX_METRIC_INNER_PRODUCT && metric != B200IDX_METRIC_L2)
+    if (metric != B200IDX_METRIC_INNER_PRODUCT && metric != B200IDX_METRIC_L2 &&
+        !(allow_cosine && metric == B200IDX_METRIC_INT8_COSINE))
         throw std::invalid_argument("Unsupported metric type");
     int count = 0;
     if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) {
@@ -128,7 +129,7 @@ size_t query_row_bytes(const b200idx_index* h) {
     return static_cast<size_t>(dim_of(h)) * (h->kind == 1 ? 1 : 4);
 }
 bool descending_of(const b200idx_index* h) {
-    return h->kind != 2 && h->flat->metric() == kMetricIP;
+    return h->kind != 2 && h->flat->metric() != kMetricL2;
 }
 
 }  // namespace
@@ -153,7 +154,7 @@ int b200idx_create_flat(int d, int metric, int dtype, int device, b200idx_t** ou
 
 int b200idx_create_int8flat(int d, int metric, int device, b200idx_t** out) {
     return guarded_create([&] {
-        check_common_create(d, metric, device, out);
+        check_common_create(d, metric, device, out, true);
         std::unique_ptr<b200idx_index> h(new b200idx_index);
         h->kind = 1;
         h->flat.reset(new FlatIndex(d, metric, kI8, device));

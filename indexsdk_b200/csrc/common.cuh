@@ -20,7 +20,9 @@ enum Status : int {
     kTimeout = 2011,
 };
 
-enum Metric : int { kMetricIP = 0, kMetricL2 = 1 };
+// kMetricCos: int8 only -- the fp16 cosine the reference's Int8Flat index computes for
+// METRIC_INNER_PRODUCT (see cos16_* below); larger is better, like kMetricIP.
+enum Metric : int { kMetricIP = 0, kMetricL2 = 1, kMetricCos = 2 };
 enum DType : int { kF32 = 0, kF16 = 1, kBF16 = 2, kI8 = 3 };
 
 // Device error word bits (one int per index, polled by the host after each search).

@@ -17,6 +17,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include "cos16.cuh"
 
 #include <type_traits>
 
@@ -37,11 +38,10 @@ constexpr int kResidentMaxChunks = 4;                            // query tile k
 // of the columns each for the folded bf16 kind, whose short ALU-only epilogue is latency-bound
 // and scales with the number of warps.
 __host__ __device__ constexpr int epi_warps(int kind) { return kind == kKindBF16 ? 16 : 8; }
-// + the producer warp, the MMA warp and, behind the epilogue warps, a second MMA warp and a second
-// producer warp (even and odd items have their own issuing threads and their own stage sub-ring)
-__host__ __device__ constexpr int gemm_threads(int kind) { return 64 + 32 * epi_warps(kind) + 64; }
+// + the producer warp, the MMA warp and, behind the epilogue warps, a second MMA warp (even and odd
+// items, i.e. the two accumulators, have their own issuing threads)
+__host__ __device__ constexpr int gemm_threads(int kind) { return 64 + 32 * epi_warps(kind) + 32; }
 __host__ __device__ constexpr int mma2_warp(int kind) { return 2 + epi_warps(kind); }
-__host__ __device__ constexpr int prod2_warp(int kind) { return 3 + epi_warps(kind); }
 constexpr uint32_t kTmemCols = 512;
 // Per-role cycle counters (GemmArgs::prof) exist in development builds only (-DB200IDX_DEV_PROF):
 // the epilogue is bound by instruction issue, and even predicated-off clock reads cost slots.
@@ -90,6 +90,7 @@ struct KeyOps<int32_t> {
     static __device__ __forceinline__ int32_t neg(int32_t v) { return -v; }
 };
 
+constexpr uint32_t kNoTmem = 0xFFFFFFFFu;   // chunk(): the accumulator columns cannot be re-read from TMEM
 constexpr uint32_t kCandBlock = 8;   // candidate slots a thread reserves with one atomic
 
 // Shared-memory side of the epilogue: the tile's base norms, double-buffered with the TMEM
@@ -118,6 +119,8 @@ struct RowEpilogue {
     int q;        // query row, valid when row_ok
     bool row_ok;
     bool l2;
+    bool cosm;                // int8 cosine: the accumulators are turned into ordered fp16 scores first
+    __half2 rq2;              // cosine: the row's query term
     AccT tau, tau_up;
     float tq;                 // FOLD append: the row's threshold, for the approximate key
     int blk_q;                // row of the open candidate block (-1: none)
@@ -127,7 +130,8 @@ struct RowEpilogue {
     uint32_t res[NCH * (32 / BURST)];   // burst-min results of this thread's part of the tile
 
     __device__ __forceinline__ explicit RowEpilogue(const GemmArgs& a_)
-        : a(a_), q(-1), row_ok(false), l2(a_.metric == kMetricL2), tau(AccT(0)), tau_up(AccT(0)), tq(0.f),
+        : a(a_), q(-1), row_ok(false), l2(a_.metric == kMetricL2),
+          cosm(std::is_same<AccT, int32_t>::value && a_.metric == kMetricCos), tau(AccT(0)), tau_up(AccT(0)), tq(0.f),
           blk_q(-1), blk_next(0), blk_left(0), pre_base(0), pre_ok(false) {}
 
     // 32 filter bits of this row for base positions col0 .. col0 + 31 (col0 is a multiple of 32).
@@ -155,6 +159,10 @@ struct RowEpilogue {
         if (MODE == kModeAppend && !a.direct && (q_ != blk_q || !ok)) close_block();
         q = q_;
         row_ok = ok;
+        if (std::is_same<AccT, int32_t>::value && cosm && ok && new_row) {
+            const int qn = a.seg_index ? q % a.nq : q;   // segmented base: candidate row -> query
+            rq2 = cos16_query_term(__ldg(a.qnorm_i32 + qn));
+        }
         if (MODE == kModeAppend && ok && new_row) {
             // once per run of tiles of the same row: the threshold, and (threshold mode) the first
             // candidate block -- reserved now, while the accumulator is still being computed, so
@@ -206,7 +214,8 @@ struct RowEpilogue {
 
     // Folded operands: r holds D for 32 columns.
     // ci: index of the chunk inside this thread's part of the tile (a constant after unrolling)
-    __device__ __forceinline__ void chunk_fold(const uint32_t (&r)[32], int64_t col0, int nvalid, int ci, int64_t cbase) {
+    __device__ __forceinline__ void chunk_fold(const uint32_t (&r)[32], int64_t col0, int nvalid, int ci, int64_t cbase,
+                                               uint32_t tchunk) {
         if (!row_ok && (MODE == kModeBurstMin || a.direct)) return;
         if (MODE == kModeBurstMin) {
             constexpr int NB = 32 / BURST;
@@ -248,7 +257,13 @@ struct RowEpilogue {
                 if (((keep >> c) & 1u) && key <= tau) crow[c] = pack_cand(float_to_ord(key), static_cast<uint32_t>(col0 + c));
             }
         } else {
-            if (!row_ok) return;
+            // tchunk: TMEM address of r[0] for this warp (kNoTmem: the accumulator is not in TMEM).
+            // With it the candidates are taken out by the whole warp: a loop over the union of the
+            // lanes' hit columns, each fetched again from TMEM with a one-column load, so that a
+            // lane never indexes its 32 registers at run time and the warp never walks the loop
+            // with one lane active per trip.
+            const bool coop = tchunk != kNoTmem;
+            if (!coop && !row_ok) return;
             uint32_t t[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) t[i] = r[2 * i] & r[2 * i + 1];
@@ -256,7 +271,12 @@ struct RowEpilogue {
             for (int w = 8; w > 0; w >>= 1)
 #pragma unroll
                 for (int i = 0; i < w; ++i) t[i] &= t[i + w];
-            if (static_cast<int32_t>(t[0]) < 0) return;   // every D negative: no key <= tau here
+            const bool hit = row_ok && static_cast<int32_t>(t[0]) >= 0;   // not every D negative
+            if (coop) {
+                if (!__any_sync(0xFFFFFFFFu, hit)) return;
+            } else if (!hit) {
+                return;
+            }
             uint32_t m0 = 0, m1 = 0;                      // bit (31 - c): D of column c has its sign set
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
@@ -265,15 +285,30 @@ struct RowEpilogue {
             }
             uint32_t mask = ~((m0 << 16) | (m1 & 0xFFFFu));
             mask &= nvalid >= 32 ? 0xFFFFFFFFu : ~(0xFFFFFFFFu >> nvalid);
-            if (a.qmask) mask &= __brev(mask_word(col0));   // column c is bit (31 - c) here, bit c in the filter
-            while (mask) {
-                const uint32_t c = __clz(mask);
-                mask &= ~(0x80000000u >> c);
-                const float dv = __uint_as_float(pick(r, c));
-                if (!(dv >= 0.f)) continue;   // NaN
-                // approximate key (the fp32 refinement recomputes it): D = (tau' - key) / 2 or tau' - key
-                const float key = l2 ? fmaf(-2.f, dv, tq) : tq - dv;
-                append(pack_cand(float_to_ord(key), static_cast<uint32_t>(col0 + c)));
+            if (a.qmask && row_ok) mask &= __brev(mask_word(col0));   // column c is bit (31 - c) here, bit c in the filter
+            if (!hit) mask = 0u;
+            if (coop) {
+                uint32_t um = __reduce_or_sync(0xFFFFFFFFu, mask);
+                while (um) {
+                    const uint32_t c = __clz(um);
+                    const uint32_t bit = 0x80000000u >> c;
+                    um &= ~bit;
+                    const float dv = __uint_as_float(ptx::tmem_ld_col(tchunk + c));
+                    if ((mask & bit) && dv >= 0.f) {   // dv >= 0 is false for NaN
+                        const float key = l2 ? fmaf(-2.f, dv, tq) : tq - dv;
+                        append(pack_cand(float_to_ord(key), static_cast<uint32_t>(col0 + c)));
+                    }
+                }
+            } else {
+                while (mask) {
+                    const uint32_t c = __clz(mask);
+                    mask &= ~(0x80000000u >> c);
+                    const float dv = __uint_as_float(pick(r, c));
+                    if (!(dv >= 0.f)) continue;   // NaN
+                    // approximate key (the fp32 refinement recomputes it): D = (tau' - key) / 2 or tau' - key
+                    const float key = l2 ? fmaf(-2.f, dv, tq) : tq - dv;
+                    append(pack_cand(float_to_ord(key), static_cast<uint32_t>(col0 + c)));
+                }
             }
         }
     }
@@ -285,12 +320,30 @@ struct RowEpilogue {
     // candidate loop.
     // cbase: position of the first base row of the segment the tile belongs to (0 without segments)
     __device__ __forceinline__ void chunk(const uint32_t (&r)[32], const uint32_t* nb, int64_t col0, int nvalid,
-                                          int bslot, int ci, int64_t cbase) {
+                                          int bslot, int ci, int64_t cbase, uint32_t tchunk = kNoTmem) {
         if (FOLD) {
-            chunk_fold(r, col0, nvalid, ci, cbase);
+            chunk_fold(r, col0, nvalid, ci, cbase, tchunk);
             return;
         }
         if (!row_ok) return;
+        if (std::is_same<AccT, int32_t>::value && cosm) {
+            // nb holds the base rows' fp16 reciprocal norms; from here on the scores are inner products
+            uint32_t s[32];
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+                int32_t s0, s1;
+                cos16_pair(static_cast<int32_t>(r[c]), static_cast<int32_t>(r[c + 1]), nb[c], nb[c + 1], rq2, s0, s1);
+                s[c] = static_cast<uint32_t>(s0);
+                s[c + 1] = static_cast<uint32_t>(s1);
+            }
+            chunk_keys(s, nb, col0, nvalid, bslot, ci, cbase);
+            return;
+        }
+        chunk_keys(r, nb, col0, nvalid, bslot, ci, cbase);
+    }
+
+    __device__ __forceinline__ void chunk_keys(const uint32_t (&r)[32], const uint32_t* nb, int64_t col0, int nvalid,
+                                               int bslot, int ci, int64_t cbase) {
         uint32_t bnb[32];
         if (l2) {
             const uint4* p = reinterpret_cast<const uint4*>(nb);
@@ -483,16 +536,15 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int nkc = (a.d + kChunkElems - 1) / kChunkElems;
     const bool resident = a.a_resident != 0;
-    const int nst = a.n_stages / 2;          // stages per sub-ring (even / odd items)
+    const int nst = a.n_stages;              // stages of the ring
     const uint32_t stage_bytes = resident ? kStageBBytes : kStageBytes;
     uint8_t* ring = smem + (resident ? nkc * kStageABytes : 0);
 
     if (threadIdx.x == 0) {
-        for (int r = 0; r < 2; ++r)
-            for (int s = 0; s < nst; ++s) {
-                ptx::mbar_init(&bar_full[r * (kMaxStages / 2) + s], 1);
-                ptx::mbar_init(&bar_empty[r * (kMaxStages / 2) + s], 1);
-            }
+        for (int s = 0; s < nst; ++s) {
+            ptx::mbar_init(&bar_full[s], 1);
+            ptx::mbar_init(&bar_empty[s], 1);
+        }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(&bar_acc_full[b], 1);
             ptx::mbar_init(&bar_acc_empty[b], epi_warps(KIND));
@@ -516,13 +568,13 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     const int n_qb = (a.nq + kTileQ - 1) / kTileQ;
     const ItemRange range(a, n_qb);
 
-    if (warp == 0 || warp == prod2_warp(KIND)) {
+    if (warp == 0) {
         if (lane == 0) {
-            const uint32_t pidx = warp == 0 ? 0u : 1u;   // this producer serves the items of this parity
-            // Two sub-rings of nst / 2 stages: even items travel through the first, odd items through
-            // the second, so that each ring's barriers have exactly one consuming thread (a consumer a
-            // whole revolution ahead of the other would otherwise read a parity that has not happened).
-            // The resident query tile is loaded by producer 0.
+            // One ring for all items, filled in item order, so that the chunks of the next item (and
+            // the first ones of the one after) are on their way while the current item is multiplied:
+            // an item of K = 144 takes three stages of the five that fit, and a ring split per
+            // consumer would leave no room to load ahead.
+            const uint32_t pidx = 0u;
             int rs = 0;
             uint32_t rph = 0;
             int cur_qb = -1;
@@ -531,7 +583,6 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             long long pw = 0;
             const bool prof_on = kDevProf && a.prof && pidx == 0;
             const long long k0 = prof_on ? clock64() : 0;
-            const uint32_t r = pidx;
             ItemCursor cur(range);
             for (int64_t i = 0; i < range.count && ok; ++i, ++t, cur.next()) {
                 const int qb = cur.qb;
@@ -544,16 +595,15 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                     ++a_loads;
                     cur_qb = qb;
                 }
-                if ((t & 1u) != pidx) continue;
                 const int tile = tile_of(a, cur.sel);
                 for (int kc = 0; kc < nkc; ++kc) {
                     const int s = rs;
-                    uint64_t* full = &bar_full[r * (kMaxStages / 2) + s];
+                    uint64_t* full = &bar_full[s];
                     const long long w0 = prof_on ? clock64() : 0;
-                    if (!ptx::mbar_wait_bounded(&bar_empty[r * (kMaxStages / 2) + s], rph ^ 1u, &abort_flag)) { ok = false; break; }
+                    if (!ptx::mbar_wait_bounded(&bar_empty[s], rph ^ 1u, &abort_flag)) { ok = false; break; }
                     if (prof_on) pw += clock64() - w0;
                     ptx::mbar_expect_tx(full, stage_bytes);
-                    uint8_t* st = ring + static_cast<size_t>(r * nst + s) * stage_bytes;
+                    uint8_t* st = ring + static_cast<size_t>(s) * stage_bytes;
                     if (!resident) {
                         ptx::tma_load_2d(st, &mapA, full, kc * kChunkElems, qb * kTileQ);
                         st += kStageABytes;
@@ -561,6 +611,7 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                     ptx::tma_load_2d(st, &mapB, full, kc * kChunkElems, tile * kTileB);
                     if (++rs == nst) { rs = 0; rph ^= 1u; }
                 }
+                if (kDevProf && a.trace && blockIdx.x == 0 && t < 64) a.trace[0 * 64 + t] = clock64();
             }
             if (prof_on) {
                 atomicAdd(a.prof + 0, static_cast<unsigned long long>(pw));
@@ -571,8 +622,9 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         // Two threads issue the UMMAs, one for the even items (accumulator 0) and one for the odd
         // items (accumulator 1), on different schedulers: a single issuing thread, sharing its
         // scheduler with busy epilogue warps, could not keep the tensor pipe fed.  Both walk the
-        // whole item list so that their view of the query-block runs agrees; each consumes its own
-        // sub-ring of stages.
+        // whole item list AND wait for every fill of the ring in order -- also the fills the other
+        // thread consumes -- so that a thread can never look at a stage's barrier a whole revolution
+        // early and take a phase that has not happened for one that has.
         if (lane == 0) {
             const uint32_t parity = warp == 1 ? 0u : 1u;
             const bool prof_on = kDevProf && a.prof && parity == 0;
@@ -600,7 +652,12 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 }
                 const bool run_ends = resident && (i + 1 == range.count || cur.last_of_qb());
                 if ((t & 1u) != parity) {
-                    // the other thread's item (it travels through the other sub-ring)
+                    // the other thread's item: only follow its fills
+                    for (int kc = 0; kc < nkc; ++kc) {
+                        if (!ptx::mbar_wait_bounded(&bar_full[s], ph, &abort_flag)) { ok = false; break; }
+                        if (++s == nst) { s = 0; ph ^= 1u; }
+                    }
+                    if (!ok) break;
                     if (run_ends) ptx::umma_commit(&bar_a_free);   // nothing of this run left on this thread
                     continue;
                 }
@@ -609,14 +666,16 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 long long w0 = prof_on ? clock64() : 0;
                 if (!ptx::mbar_wait_bounded(&bar_acc_empty[ab], aph ^ 1u, &abort_flag)) { ok = false; break; }
                 if (prof_on) mw0 += clock64() - w0;
+                if (kDevProf && a.trace && blockIdx.x == 0 && t < 64) a.trace[1 * 64 + t] = clock64();
                 ptx::tc_fence_after();
                 const uint32_t tacc = tmem_base + ab * kTileB;
                 for (int kc = 0; kc < nkc; ++kc) {
                     w0 = prof_on ? clock64() : 0;
-                    if (!ptx::mbar_wait_bounded(&bar_full[parity * (kMaxStages / 2) + s], ph, &abort_flag)) { ok = false; break; }
+                    if (!ptx::mbar_wait_bounded(&bar_full[s], ph, &abort_flag)) { ok = false; break; }
                     if (prof_on) mw1 += clock64() - w0;
+                    if (kDevProf && a.trace && blockIdx.x == 0 && t < 64 && kc + 1 == nkc) a.trace[2 * 64 + t] = clock64();
                     ptx::tc_fence_after();
-                    const uint32_t st_lo = ring_lo + (parity * static_cast<uint32_t>(nst) + static_cast<uint32_t>(s)) * stage_lo;
+                    const uint32_t st_lo = ring_lo + static_cast<uint32_t>(s) * stage_lo;
                     const uint32_t sa_lo = resident ? a_res_lo + static_cast<uint32_t>(kc) * (kStageABytes >> 4) : st_lo;
                     const uint32_t sb_lo = resident ? st_lo : st_lo + (kStageABytes >> 4);
                     // the last chunk may hold fewer than four 32-byte K steps (the rest is zero fill)
@@ -627,14 +686,16 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                         const uint64_t da = desc_hi | static_cast<uint64_t>(sa_lo + ks * 2);
                         const uint64_t db = desc_hi | static_cast<uint64_t>(sb_lo + ks * 2);
                         const uint32_t accum = (kc > 0 || ks > 0) ? 1u : 0u;
+                        if (kDevProf && (a.dbg & 4)) continue;
                         if (KIND == kKindI8) ptx::umma_i8(tacc, da, db, kIdesc, accum);
                         else ptx::umma_f16(tacc, da, db, kIdesc, accum);
                     }
-                    ptx::umma_commit(&bar_empty[parity * (kMaxStages / 2) + s]);
+                    ptx::umma_commit(&bar_empty[s]);
                     if (++s == nst) { s = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
                 ptx::umma_commit(&bar_acc_full[ab]);
+                if (kDevProf && a.trace && blockIdx.x == 0 && t < 64) a.trace[3 * 64 + t] = clock64();
                 // last item of this CTA for the query block: the resident tile may be replaced once
                 // everything both threads issued so far has completed
                 if (run_ends) ptx::umma_commit(&bar_a_free);
@@ -652,6 +713,7 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         constexpr int kCols = kTileB / (epi_warps(KIND) / 4);   // columns per epilogue thread
         RowEpilogue<AccT, MODE, BURST, FOLD, kCols / 32> epi(a);
         const bool l2 = a.metric == kMetricL2 && !FOLD;   // FOLD: no norms to fetch
+        const bool cosm = KIND == kKindI8 && a.metric == kMetricCos;
         const uint32_t* gnorm = static_cast<const uint32_t*>(a.bnorm);
         uint32_t t = 0;
         bool ok = true;
@@ -677,7 +739,10 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             const long long e0 = profiler ? clock64() : 0;
             // The tile's norms travel global -> registers while the MMA is still running.
             uint32_t n0 = 0;
-            if (l2 && et < kTileB) n0 = __ldg(gnorm + tile_col0 + et);
+            if ((l2 || cosm) && et < kTileB) {
+                n0 = __ldg(gnorm + tile_col0 + et);
+                if (cosm) n0 = cos16_rnorm_bits(static_cast<int32_t>(n0));
+            }
             epi.begin_tile(q, q_in < a.nq);
             if (!ptx::mbar_wait_bounded(&bar_acc_full[ab], aph, &abort_flag)) {
                 // leave without stranding a sibling warp at the named barrier below
@@ -686,6 +751,8 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 break;
             }
             const long long e1 = profiler ? clock64() : 0;
+            if (kDevProf && a.trace && blockIdx.x == 0 && t < 64 && lane == 0 && (warp == 2 || warp == 2 + epi_warps(KIND) - 1))
+                a.trace[(warp == 2 ? 4 : 6) * 64 + t] = clock64();
             ptx::tc_fence_after();
             const long long b0 = profiler ? clock64() : 0;
             if (!FOLD) {
@@ -699,9 +766,11 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             const uint32_t* hnorm = &epi_sh.norm[ab][half * kCols];
             const int hslot = sel * (kTileB / BURST) + half * (kCols / BURST);
             uint32_t ra[32], rb[32];
-            ptx::tmem_ld_32x32(tacc, ra);
+            const bool dbg_no_ld = kDevProf && (a.dbg & 2), dbg_no_chunk = kDevProf && (a.dbg & 3);
+            if (!dbg_no_ld) ptx::tmem_ld_32x32(tacc, ra);
             // two chunks per step, the TMEM load of the next chunk in flight behind the current one
             auto step = [&](int c) {
+                if (dbg_no_ld) return;
                 const long long w0 = profiler ? clock64() : 0;
                 ptx::tmem_ld_wait(ra);
                 if (profiler) elw += clock64() - w0;
@@ -710,8 +779,8 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                     const long long c0 = profiler ? clock64() : 0;
                     const int64_t col0 = half_col0 + c * 32;
                     const int64_t rem = n_end - col0;
-                    epi.chunk(ra, hnorm + c * 32, col0, rem >= 32 ? 32 : (rem > 0 ? static_cast<int>(rem) : 0),
-                              hslot + c * (32 / BURST), c, cbase);
+                    if (!dbg_no_chunk) epi.chunk(ra, hnorm + c * 32, col0, rem >= 32 ? 32 : (rem > 0 ? static_cast<int>(rem) : 0),
+                              hslot + c * (32 / BURST), c, cbase, tacc + c * 32);
                     if (profiler) ecc += clock64() - c0;
                 }
                 const long long w1 = profiler ? clock64() : 0;
@@ -721,8 +790,8 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 {
                     const int64_t col0 = half_col0 + (c + 1) * 32;
                     const int64_t rem = n_end - col0;
-                    epi.chunk(rb, hnorm + (c + 1) * 32, col0, rem >= 32 ? 32 : (rem > 0 ? static_cast<int>(rem) : 0),
-                              hslot + (c + 1) * (32 / BURST), c + 1, cbase);
+                    if (!dbg_no_chunk) epi.chunk(rb, hnorm + (c + 1) * 32, col0, rem >= 32 ? 32 : (rem > 0 ? static_cast<int>(rem) : 0),
+                              hslot + (c + 1) * (32 / BURST), c + 1, cbase, tacc + (c + 1) * 32);
                 }
             };
             if (FOLD) {   // small body: unrolled, so the chunk index is a constant
@@ -736,6 +805,8 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&bar_acc_empty[ab]);
+            if (kDevProf && a.trace && blockIdx.x == 0 && t < 64 && lane == 0 && (warp == 2 || warp == 2 + epi_warps(KIND) - 1))
+                a.trace[(warp == 2 ? 5 : 7) * 64 + t] = clock64();
             const long long e2 = profiler ? clock64() : 0;
             epi.end_tile(hslot);
             if (profiler) {
@@ -793,6 +864,7 @@ dist_gemm_simt_kernel(const GemmArgs a) {
     const int n_qb = (a.nq + kTileQ - 1) / kTileQ;
     const ItemRange range(a, n_qb);
     const bool l2 = a.metric == kMetricL2;
+    const bool cosm = KIND == kKindI8 && a.metric == kMetricCos;
     const uint32_t* gnorm = static_cast<const uint32_t*>(a.bnorm);
     RowEpilogue<AccT, MODE, BURST, KIND == kKindBF16, kTileB / 32> epi(a);
     ItemCursor cur(range);
@@ -812,8 +884,11 @@ dist_gemm_simt_kernel(const GemmArgs a) {
             n_end = a.seg_end[tile];
         }
         __syncthreads();
-        epi_sh.norm[0][threadIdx.x] = l2 ? __ldg(gnorm + tile_col0 + threadIdx.x) : 0u;
-        epi_sh.norm[0][kTileQ + threadIdx.x] = l2 ? __ldg(gnorm + tile_col0 + kTileQ + threadIdx.x) : 0u;
+        for (int h = 0; h < kTileB; h += kTileQ) {
+            uint32_t nv = (l2 || cosm) ? __ldg(gnorm + tile_col0 + h + threadIdx.x) : 0u;
+            if (cosm) nv = cos16_rnorm_bits(static_cast<int32_t>(nv));
+            epi_sh.norm[0][h + threadIdx.x] = nv;
+        }
         __syncthreads();
         epi.begin_tile(q, row_ok);
         for (int c = 0; c < kTileB / 32; ++c) {
@@ -857,7 +932,6 @@ cudaError_t launch_one(const GemmLaunch& L, GemmArgs a, const CUtensorMap* mapA,
     const int stage_bytes = a.a_resident ? kStageBBytes : kStageBytes;
     int nst = (kGemmSmemBudget - 1024 - a_bytes) / stage_bytes;
     if (nst > kMaxStages) nst = kMaxStages;
-    nst &= ~1;                       // two sub-rings of equal depth
     if (nst < 2) return cudaErrorInvalidConfiguration;
     a.n_stages = nst;
     const int smem = a_bytes + nst * stage_bytes + 1024;

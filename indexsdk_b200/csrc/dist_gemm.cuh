@@ -40,8 +40,9 @@ struct GemmArgs {
     int n_tiles_sel;      // tiles visited by this pass
     int tile_first;       // >= 0: tiles tile_first .. tile_first + n_tiles_sel - 1;
                           // -1: n_tiles_sel tiles spread evenly, tile(i) = i * n_tiles_total / n_tiles_sel
-    int metric;           // kMetricIP / kMetricL2
-    const void* bnorm;    // float* (f16/bf16 kinds) or int32_t* (i8): squared norm per base row, L2 only
+    int metric;           // kMetricIP / kMetricL2 / kMetricCos (i8 only)
+    const void* bnorm;    // float* (f16/bf16 kinds) or int32_t* (i8): squared norm per base row, L2 and cosine
+    const int32_t* qnorm_i32;   // kMetricCos: squared norm per query
     // kModeBurstMin
     uint32_t* mins;       // [nq][mins_stride] ordered keys
     int mins_stride;      // n_tiles_sel * (kTileB / burst)
@@ -72,6 +73,8 @@ struct GemmArgs {
     //   0 producer wait-empty   1 mma wait-acc-empty   2 mma wait-full   3 epilogue wait-acc-full
     //   4 epilogue chunks       5 epilogue flush       6 items           7 total kernel cycles (per CTA, summed)
     unsigned long long* prof;
+    unsigned long long* trace;   // development builds only: [6][64] clock64 stamps of CTA 0's first 64 items
+    int dbg;              // development builds only: 1 skip the epilogue's chunk work, 2 also its TMEM loads, 4 skip the UMMAs
     // filled in by launch_dist_gemm (tcgen05 variant): shared-memory plan
     int a_resident;       // 1: the query tile stays in shared memory for a whole query block
     int n_stages;         // ring stages (base chunks, or query + base chunks when not resident)

@@ -41,6 +41,8 @@ bool pointer_on_device(const void* p) {
 
 FlatIndex::FlatIndex(int d, int metric, int dtype, int device)
     : d_(d), metric_(metric), dtype_(dtype), device_(device) {
+    if (metric != kMetricIP && metric != kMetricL2 && !(metric == kMetricCos && dtype == kI8))
+        throw std::invalid_argument("Unsupported metric type");
     DeviceGuard g(device_);
     B200_CUDA_CHECK(cudaDeviceGetAttribute(&num_sms_, cudaDevAttrMultiProcessorCount, device_));
     B200_CUDA_CHECK(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
@@ -49,8 +51,8 @@ FlatIndex::FlatIndex(int d, int metric, int dtype, int device)
     prof_ = env_flag("B200IDX_PROF", "1");   // development builds: per-role cycle counters of the GEMM kernel
 #endif
     if (prof_) {
-        w_prof_.ensure(32 * 8);
-        B200_CUDA_CHECK(cudaMemset(w_prof_.get(), 0, 32 * 8));
+        w_prof_.ensure((32 + 8 * 64) * 8);
+        B200_CUDA_CHECK(cudaMemset(w_prof_.get(), 0, (32 + 8 * 64) * 8));
     }
     w_err_.ensure(sizeof(int));
     B200_CUDA_CHECK(cudaMemset(w_err_.get(), 0, sizeof(int)));
@@ -314,10 +316,14 @@ void FlatIndex::run_page(int nq, const void* xq_raw, const void* xq_op_in, int k
     a.n_tiles_total = static_cast<int>((n_ + kTileB - 1) / kTileB);
     a.metric = metric_;
     a.bnorm = norms_.get();
+    a.qnorm_i32 = is_int ? static_cast<const int32_t*>(qnorm) : nullptr;
     a.err = w_err_.as<int>();
     a.qmask = mask_cur_;
     a.qmask_stride = mask_stride_;
     a.prof = nullptr;
+#ifdef B200IDX_DEV_PROF
+    if (const char* dv = getenv("B200IDX_GEMM_DBG")) a.dbg = atoi(dv);
+#endif
     GemmLaunch L{};
     L.kind = kind;
     L.simt = use_simt_ ? 1 : 0;
@@ -396,7 +402,11 @@ void FlatIndex::run_page(int nq, const void* xq_raw, const void* xq_op_in, int k
         a.tile_first = first_stretch;
         a.n_tiles_sel = n_tiles - first_stretch;
         a.prof = nullptr;
+#ifdef B200IDX_DEV_PROF
+        if (prof_ && getenv("B200IDX_GEMM_TRACE")) a.trace = w_prof_.as<unsigned long long>() + 32;
+#endif
         B200_CUDA_CHECK(launch_dist_gemm(L, a, &map_a, &map_b_, stream_));
+        a.trace = nullptr;
         stats_.gemm_launches += 1;
         stats_.kernel_launches += 3;
         report_counts("after the second stretch");
@@ -488,6 +498,19 @@ void FlatIndex::search_device(int64_t nq, const void* xq, bool q_is_f16, int k, 
             unsigned long long pc[32];
             cudaMemcpy(pc, w_prof_.get(), sizeof(pc), cudaMemcpyDeviceToHost);
             cudaMemset(w_prof_.get(), 0, sizeof(pc));
+            if (getenv("B200IDX_GEMM_TRACE")) {
+                static unsigned long long tr[8 * 64];
+                cudaMemcpy(tr, w_prof_.as<unsigned long long>() + 32, sizeof(tr), cudaMemcpyDeviceToHost);
+                unsigned long long t0 = ~0ull;
+                for (int i = 0; i < 8 * 64; ++i)
+                    if (tr[i] && tr[i] < t0) t0 = tr[i];
+                fprintf(stderr, "[b200idx trace] item: loads_issued mma_start mma_last_chunk_in mma_committed | epiA acc_full, released | epiZ acc_full, released\n");
+                for (int t = 0; t < 40; ++t)
+                    fprintf(stderr, "[b200idx trace] %2d: %7lld %7lld %7lld %7lld | %7lld %7lld | %7lld %7lld\n", t,
+                            (long long)(tr[t] - t0), (long long)(tr[64 + t] - t0), (long long)(tr[128 + t] - t0),
+                            (long long)(tr[192 + t] - t0), (long long)(tr[256 + t] - t0), (long long)(tr[320 + t] - t0),
+                            (long long)(tr[384 + t] - t0), (long long)(tr[448 + t] - t0));
+            }
             for (int p = 0; p < 2; ++p) {
                 const unsigned long long* c = pc + 16 * p;
                 const double items = c[6] ? static_cast<double>(c[6]) : 1.0;

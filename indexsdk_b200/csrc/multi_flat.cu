@@ -159,6 +159,7 @@ void FlatGroup::search_device(const std::vector<FlatIndex*>& members, int64_t nq
         a.n_tiles_sel = static_cast<int>((seg_start_[m1] - seg_start_[m0]) / kTileB);
         a.metric = metric_;
         a.bnorm = norms_.get();
+        a.qnorm_i32 = dtype_ == kI8 ? static_cast<const int32_t*>(qnorm) : nullptr;
         a.tau = tau;
         a.cand = cand;
         a.counts = nullptr;

@@ -146,6 +146,7 @@ extern "C" int b200idx_search_device_noalloc(b200idx_t* h, int64_t n, const void
         a.tile_first = 0;
         a.metric = ix->metric();
         a.bnorm = v.norms;
+        a.qnorm_i32 = ix->dtype() == kI8 ? static_cast<const int32_t*>(qnorm) : nullptr;
         a.tau = tau;
         a.cand = cand;
         a.counts = nullptr;

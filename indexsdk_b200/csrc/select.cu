@@ -2,6 +2,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include "cos16.cuh"
 
 #include "common.cuh"
 #include "dist_gemm.cuh"
@@ -394,6 +395,7 @@ __global__ void emit_kernel(const EmitArgs e) {
         if (e.mode == 2) {
             int32_t kv = ord_to_int(ok);
             if (e.metric == kMetricL2) dist = static_cast<float>(kv + static_cast<const int32_t*>(e.qnorm)[qn]);
+            else if (e.metric == kMetricCos) dist = cos16_value(-kv);
             else dist = static_cast<float>(-kv);
         } else {
             float kv = ord_to_float(ok);

@@ -77,6 +77,11 @@ struct RwGuard {   // no-op unless MX_INDEX_MULTITHREAD=1
 }  // namespace
 
 void SetRelaxedLimits(bool on) { g_relaxed = on; }
+namespace {
+bool g_int8_ip_cosine = false;
+}
+void SetInt8InnerProductAsCosine(bool on) { g_int8_ip_cosine = on; }
+bool Int8InnerProductAsCosine() { return g_int8_ip_cosine || env_is("B200IDX_INT8_IP_COSINE", "1"); }
 bool RelaxedLimits() { return g_relaxed || env_is("B200IDX_RELAXED", "1"); }
 
 // One object per index: the handles of its device list.
@@ -587,7 +592,9 @@ void check_int8_params(int dims, MetricType metric, const AscendIndexInt8FlatCon
 void create_int8_handles(AscendIndexInt8Impl& im) {
     for (int dev : im.devices) {
         b200idx_t* h = nullptr;
-        const int code = b200idx_create_int8flat(im.dims, to_abi_metric(im.metric), dev, &h);
+        const int metric = (im.metric == METRIC_INNER_PRODUCT && Int8InnerProductAsCosine()) ? B200IDX_METRIC_INT8_COSINE
+                                                                                              : to_abi_metric(im.metric);
+        const int code = b200idx_create_int8flat(im.dims, metric, dev, &h);
         if (code != B200IDX_OK) FAISS_THROW_FMT("create index failed (%d): %s", code, b200idx_last_error(nullptr));
         im.handles.push_back(h);
     }

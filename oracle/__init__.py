@@ -21,6 +21,7 @@ _lib = None
 
 METRIC_IP = 0
 METRIC_L2 = 1
+METRIC_INT8_COS = 2      # int8 only: the reference's fp16 cosine (oracle.c, cos16_*)
 
 
 def build(force: bool = False) -> str:
@@ -91,6 +92,25 @@ def int8_search(metric, xb, xq, k, labels=None):
     if rc:
         raise RuntimeError(f"orc_int8_search rc={rc}")
     return D, I
+
+
+def cos16(dot, sq_x, sq_q):
+    """One fp16 cosine score from the exact dot product and squared norms (oracle.c: cos16_score)."""
+    f = lib().orc_cos16
+    f.restype = C.c_float
+    return float(f(C.c_int32(int(dot)), C.c_int32(int(sq_x)), C.c_int32(int(sq_q))))
+
+
+def f2h(x):
+    f = lib().orc_f2h
+    f.restype = C.c_uint16
+    return int(f(C.c_float(x)))
+
+
+def h2f(h):
+    f = lib().orc_h2f
+    f.restype = C.c_float
+    return float(f(C.c_uint16(h)))
 
 
 def ivf_assign(centroids, x):
@@ -216,8 +236,32 @@ def np_flat_search(metric, xb, xq, k):
     return _pad(D.astype(np.float32), order.astype(np.int64), k)
 
 
+def np_int8_cos_scores(xb, xq):
+    """The fp16 cosine with numpy's own float16 (an implementation independent of oracle.c's bit
+    routines): [nq, nb] float16, NaN where the reference's arithmetic gives NaN."""
+    b, q = np.asarray(xb, np.int64), np.asarray(xq, np.int64)
+
+    def rnorm(v):
+        sq = (v * v).sum(1).astype(np.float32)
+        s = (sq * np.float32(0.01)).astype(np.float16).astype(np.float32)
+        with np.errstate(divide="ignore"):
+            return (np.float32(1.0) / np.sqrt(s)).astype(np.float16)
+    with np.errstate(over="ignore", invalid="ignore"):
+        ip = ((q @ b.T).astype(np.float32) * np.float32(0.01)).astype(np.float16)
+        w = (rnorm(q)[:, None].astype(np.float32) * rnorm(b)[None, :].astype(np.float32)).astype(np.float16)
+        return (ip.astype(np.float32) * w.astype(np.float32)).astype(np.float16)
+
+
 def np_int8_search(metric, xb, xq, k):
     b, q = np.asarray(xb, np.int64), np.asarray(xq, np.int64)
+    if metric == METRIC_INT8_COS:
+        sc = np_int8_cos_scores(xb, xq).astype(np.float32)
+        sc = np.where(np.isnan(sc), -np.inf, sc)
+        key = -sc
+        # -0.0 ranks directly below +0.0 in the restatement
+        key = np.where((sc == 0) & np.signbit(sc), np.float32(1e-30), key)
+        order = np.lexsort((np.broadcast_to(np.arange(b.shape[0]), key.shape), key), axis=1)[:, :k]
+        return _pad(np.take_along_axis(sc, order, 1).astype(np.float32), order.astype(np.int64), k)
     if metric == METRIC_L2:
         key = ((q[:, None, :] - b[None, :, :]) ** 2).sum(-1)
     else:

@@ -46,6 +46,7 @@
 
 #define ORC_METRIC_IP 0
 #define ORC_METRIC_L2 1
+#define ORC_METRIC_INT8_COS 2
 
 typedef struct {
     double key;
@@ -327,10 +328,84 @@ void orc_round_bf16(int64_t n, const float* x, float* out) {
     }
 }
 
+
+/* ---- fp16 arithmetic for the int8 cosine ---- */
+
+/* float -> fp16 bits, round to nearest even, subnormals and overflow to inf as IEEE 754 */
+static uint16_t f2h(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    const uint32_t sign = (u >> 16) & 0x8000u;
+    const uint32_t a = u & 0x7FFFFFFFu;
+    if (a > 0x7F800000u) return (uint16_t)(sign | 0x7FFFu);            /* NaN */
+    if (a >= 0x477FF000u) return (uint16_t)(sign | 0x7C00u);           /* >= 65520 rounds to inf */
+    if (a < 0x33000001u) return (uint16_t)sign;                        /* <= 2^-25 rounds to zero */
+    int e = (int)(a >> 23) - 127;
+    uint32_t m = (a & 0x7FFFFFu) | 0x800000u;                          /* 24-bit significand */
+    int shift = e >= -14 ? 13 : 13 + (-14 - e);                        /* bits dropped */
+    uint32_t keep = m >> shift;
+    const uint32_t rem = m & ((1u << shift) - 1u), half = 1u << (shift - 1);
+    if (rem > half || (rem == half && (keep & 1u))) ++keep;
+    /* normal: keep has the hidden bit at 0x400, adding the biased exponent minus one absorbs it
+     * (and a carry out of the significand bumps the exponent); subnormal: exponent field 0 */
+    const uint32_t h = e >= -14 ? ((uint32_t)(e + 14) << 10) + keep : keep;
+    return (uint16_t)(sign | h);
+}
+
+static float h2f(uint16_t h) {
+    const uint32_t sign = ((uint32_t)h & 0x8000u) << 16;
+    const uint32_t e = (h >> 10) & 0x1Fu, m = h & 0x3FFu;
+    uint32_t u;
+    if (e == 0x1F) u = sign | 0x7F800000u | (m << 13);
+    else if (e) u = sign | ((e + 112u) << 23) | (m << 13);
+    else if (!m) u = sign;
+    else {
+        int sh = 0;
+        uint32_t mm = m;
+        while (!(mm & 0x400u)) { mm <<= 1; ++sh; }
+        u = sign | ((uint32_t)(113 - sh) << 23) | ((mm & 0x3FFu) << 13);
+    }
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+/* fp16 product of two fp16 values: the float product of two 11-bit significands is exact */
+static uint16_t hmul(uint16_t a, uint16_t b) { return f2h(h2f(a) * h2f(b)); }
+
+/* rnorm(v) = fp16(1 / sqrt(fp16(|v|^2 * 0.01)))
+ * (feature_retrieval/src/ascendfaiss/ops/tbe/impl/int8_l2_norm.py:140-183: the squared norms leave
+ * the cube unit through a 0.01 dequantisation to fp16, then vec_rsqrt_high_preci) */
+static uint16_t cos16_rnorm(int32_t sq) {
+    volatile float scaled = (float)sq * 0.01f;
+    const float s = h2f(f2h(scaled));
+    volatile float root = sqrtf(s);
+    volatile float r = 1.0f / root;
+    return f2h(r);
+}
+
+/* the fp16 score as an integer with the order of the values; NaN below everything
+ * (feature_retrieval/src/ascendfaiss/ops/tbe/impl/distance_int8_cos_maxs.py:256-284:
+ *  res = (rnorm_x * rnorm_q) in fp16; ip = int32 * 0.01 -> fp16; res = ip * res in fp16) */
+static int32_t cos16_score(int32_t dot, uint16_t rx, uint16_t rq) {
+    volatile float scaled = (float)dot * 0.01f;
+    const uint16_t ip = f2h(scaled);
+    const uint16_t r = hmul(ip, hmul(rx, rq));
+    if ((r & 0x7FFFu) > 0x7C00u) return -32768;
+    const int32_t x = (int16_t)r;
+    return x ^ ((x >> 31) & 0x7FFF);
+}
+
+static float cos16_value(int32_t s) {
+    if (s <= -32768) return -INFINITY;
+    return h2f((uint16_t)(s >= 0 ? (uint32_t)s : (0x8000u | (uint32_t)(-1 - s))));
+}
+
 /*
  * Exact int8 Flat search, int32 accumulation, no scaling.  IP: score = sum q*x, larger
  * is better; L2: sum (q-x)^2, smaller is better.  Ties -> lower position.  Distances are
  * returned as float (|value| <= 1024*2^14 < 2^24, exactly representable).
+ * ORC_METRIC_INT8_COS: the fp16 cosine above, larger is better, NaN last and returned as -inf.
  */
 int orc_int8_search(int metric, int d, int64_t nb, const int8_t* xb, const int64_t* labels,
                     int64_t nq, const int8_t* xq, int k, float* D, int64_t* I) {
@@ -340,7 +415,21 @@ int orc_int8_search(int metric, int d, int64_t nb, const int8_t* xb, const int64
      * while it is in cache; integer arithmetic, so the order of the sums is immaterial */
     orc_item* heaps = (orc_item*)malloc(sizeof(orc_item) * (size_t)k * (size_t)nq);
     int* cnt = (int*)calloc((size_t)nq, sizeof(int));
-    if (!heaps || !cnt) { free(heaps); free(cnt); return -2; }
+    uint16_t *rx = NULL, *rq = NULL;
+    if (metric == ORC_METRIC_INT8_COS) {
+        rx = (uint16_t*)malloc(sizeof(uint16_t) * (size_t)(nb > 0 ? nb : 1));
+        rq = (uint16_t*)malloc(sizeof(uint16_t) * (size_t)nq);
+        if (!rx || !rq) { free(heaps); free(cnt); free(rx); free(rq); return -2; }
+#pragma omp parallel for schedule(static)
+        for (int64_t j = 0; j < nb + nq; ++j) {
+            const int8_t* v = j < nb ? xb + j * d : xq + (j - nb) * d;
+            int32_t sq = 0;
+            for (int i = 0; i < d; ++i) sq += (int32_t)v[i] * (int32_t)v[i];
+            if (j < nb) rx[j] = cos16_rnorm(sq);
+            else rq[j - nb] = cos16_rnorm(sq);
+        }
+    }
+    if (!heaps || !cnt) { free(heaps); free(cnt); free(rx); free(rq); return -2; }
     int64_t jb = ((int64_t)1 << 20) / (int64_t)d;
     if (jb < 64) jb = 64;
     for (int64_t j0 = 0; j0 < nb; j0 += jb) {
@@ -353,7 +442,10 @@ int orc_int8_search(int metric, int d, int64_t nb, const int8_t* xb, const int64
             for (int64_t j = j0; j < j1; ++j) {
                 const int8_t* yv = xb + j * d;
                 int32_t acc = 0;
-                if (metric == ORC_METRIC_L2) {
+                if (metric == ORC_METRIC_INT8_COS) {
+                    for (int i = 0; i < d; ++i) acc += (int32_t)qv[i] * (int32_t)yv[i];
+                    heap_offer(h, n, k, -(double)cos16_score(acc, rx[j], rq[q]), j);
+                } else if (metric == ORC_METRIC_L2) {
                     for (int i = 0; i < d; ++i) {
                         int32_t t = (int32_t)qv[i] - (int32_t)yv[i];
                         acc += t * t;
@@ -369,13 +461,26 @@ int orc_int8_search(int metric, int d, int64_t nb, const int8_t* xb, const int64
 #pragma omp parallel for schedule(static)
     for (int64_t q = 0; q < nq; ++q) {
         heap_emit(heaps + (size_t)q * k, cnt[q], k, metric != ORC_METRIC_L2, D + q * k, I + q * k);
+        if (metric == ORC_METRIC_INT8_COS)
+            for (int j = 0; j < k; ++j)
+                if (I[q * k + j] >= 0) D[q * k + j] = cos16_value((int32_t)D[q * k + j]);
         if (labels)
             for (int j = 0; j < k; ++j)
                 if (I[q * k + j] >= 0) I[q * k + j] = labels[I[q * k + j]];
     }
     free(heaps);
     free(cnt);
+    free(rx);
+    free(rq);
     return 0;
+}
+
+/* fp16 helpers exported for the tests of the restatement itself */
+uint16_t orc_f2h(float f) { return f2h(f); }
+float orc_h2f(uint16_t h) { return h2f(h); }
+uint16_t orc_cos16_rnorm(int32_t sq) { return cos16_rnorm(sq); }
+float orc_cos16(int32_t dot, int32_t sq_x, int32_t sq_q) {
+    return cos16_value(cos16_score(dot, cos16_rnorm(sq_x), cos16_rnorm(sq_q)));
 }
 
 /* ---- IVFPQ ---- */

@@ -255,6 +255,28 @@ static void test_int8_gpu() {
     CHECK(I == I2 && D == D2);
     ix.reset();
     CHECK(ix.getNTotal() == 0);
+
+    // the reference's own meaning of METRIC_INNER_PRODUCT on this index (fp16 cosine), behind the switch
+    SetInt8InnerProductAsCosine(true);
+    {
+        AscendIndexInt8Flat cs(d, METRIC_INNER_PRODUCT);
+        cs.add(static_cast<idx_t>(nb), xb.data());
+        std::vector<int8_t> q2(xb.begin() + 17 * d, xb.begin() + 19 * d);   // two base rows as queries
+        std::vector<float> Dc(2 * k);
+        std::vector<idx_t> Ic(2 * k);
+        cs.search(2, q2.data(), k, Dc.data(), Ic.data());
+        for (int q = 0; q < 2; ++q) {
+            bool found = false;
+            for (int j = 0; j < k; ++j) {
+                CHECK(Dc[q * k + j] <= 1.01f && Dc[q * k + j] >= -1.01f);
+                if (j) CHECK(Dc[q * k + j] <= Dc[q * k + j - 1]);
+                found = found || Ic[q * k + j] == 17 + q;
+            }
+            CHECK(found && Dc[q * k] > 0.99f);
+        }
+    }
+    SetInt8InnerProductAsCosine(false);
+    CHECK(!Int8InnerProductAsCosine());
 }
 
 static std::vector<float> mixture(size_t n, int d, int ncenters, unsigned seed, unsigned cseed) {

@@ -29,7 +29,7 @@ def test_multi_index_flat(b200, metric):
     D, I = b200.search_multi(indexes, xq, k, merged=False)       # layout [index][query][k]
     assert_exact(D, I, np.stack(Ds), np.stack(Is))
     Dm, Im = b200.search_multi(indexes, xq, k, merged=True)
-    Dr, Ir = oracle.merge_topk(np.stack(Ds), np.stack(Is), descending=(metric == IP))
+    Dr, Ir = oracle.merge_topk(np.stack(Ds), np.stack(Is), descending=(metric != L2))
     assert_exact(Dm, Im, Dr, Ir)
 
 
@@ -84,7 +84,7 @@ def test_merge_kernel_with_torch_buffers(b200):
     assert_exact(oD.cpu().numpy(), oI.cpu().numpy(), Dr, Ir)
 
 
-@pytest.mark.parametrize("kind", ["f32_l2", "f32_ip", "i8_ip", "i8_l2", "f16_ip"])
+@pytest.mark.parametrize("kind", ["f32_l2", "f32_ip", "i8_ip", "i8_l2", "f16_ip", "i8_cos"])
 def test_many_small_indexes_one_pass(b200, kind):
     """64 small indexes of one device: the segmented path searches them in one pass over their
     concatenated bases.  Results per index and merged are those of the oracle; the number of
@@ -97,7 +97,7 @@ def test_many_small_indexes_one_pass(b200, kind):
     sizes = [int(v) for v in rng.integers(40, 3000, size=nidx)]
     sizes[3], sizes[17] = 256, 257                          # exactly one tile / one row more
     is_int = kind.startswith("i8")
-    metric = IP if kind.endswith("ip") else L2
+    metric = 2 if kind.endswith("cos") else (IP if kind.endswith("ip") else L2)
     xq = datasets.uniform_int8(nq, d, seed=3) if is_int else datasets.gaussian(nq, d, seed=1)
     if kind.startswith("f16"):
         xq = oracle.round_fp16(xq)
@@ -142,7 +142,7 @@ def test_many_small_indexes_one_pass(b200, kind):
     Dm, Im = b200.search_multi(indexes, xq, k, merged=True)
     free1 = torch.cuda.mem_get_info()[0]
     s2 = b200.search_multi_stats()
-    Dr, Ir = oracle.merge_topk(np.stack(Ds), np.stack(Is), descending=(metric == IP))
+    Dr, Ir = oracle.merge_topk(np.stack(Ds), np.stack(Is), descending=(metric != L2))
     check(Dm, Im, Dr, Ir, "merged")
     assert s2["group_rebuilds"] == s1["group_rebuilds"] and s2["group_launches"] - s1["group_launches"] == per_call_64
     D2, I2 = b200.search_multi(indexes, xq, k, merged=False)
@@ -160,7 +160,7 @@ def test_many_small_indexes_one_pass(b200, kind):
     indexes[5].add_with_ids(extra, np.array([10**9], dtype=np.int64))
     Dn, In = b200.search_multi(indexes, xq, k, merged=False)
     assert b200.search_multi_stats()["group_rebuilds"] == s4["group_rebuilds"] + 1   # the copy follows its members
-    assert In[5, 0, 0] == 10**9 or metric == IP
+    assert In[5, 0, 0] == 10**9 or metric != L2
     if is_int:
         Dr5, Ir5 = oracle.int8_search(metric, np.concatenate([xb5, extra]), xq, k, labels=np.concatenate([ids5, [10**9]]))
     else:

@@ -73,6 +73,58 @@ def test_int8_matches_numpy_mirror(metric):
     np.testing.assert_array_equal(D, Dn)
 
 
+def _int8_rows_with_varied_norms(n, d, seed):
+    rng = np.random.default_rng(seed)
+    x = rng.integers(-128, 128, (n, d)).astype(np.float32) * rng.uniform(0.02, 1.0, (n, 1)).astype(np.float32)
+    return np.rint(x).astype(np.int8)
+
+
+def test_fp16_conversions_match_numpy():
+    rng = np.random.default_rng(0)
+    xs = np.concatenate([rng.standard_normal(3000).astype(np.float32) * s for s in (1e-8, 1e-6, 1e-4, 1, 100, 7e4)]
+                        + [np.array([0, -0.0, 65504, 65519.99, 65520, 6e-8, 2.9802322e-8, 2.9802326e-8, np.inf,
+                                     -np.inf, 6.1e-5, 6.097e-5], np.float32)])
+    with np.errstate(over="ignore"):
+        ref = xs.astype(np.float16).view(np.uint16)
+    got = np.array([oracle.f2h(float(v)) for v in xs], np.uint16)
+    np.testing.assert_array_equal(got, ref)
+    hs = np.arange(0, 65536, 7, dtype=np.uint16)
+    ref = hs.view(np.float16).astype(np.float32)
+    got = np.array([oracle.h2f(int(h)) for h in hs], np.float32)
+    assert np.all((ref == got) | (np.isnan(ref) & np.isnan(got)))
+
+
+def test_int8_cosine_known_answers():
+    """The reference's fp16 chain by hand: |x|^2 = |q|^2 = 64 * 100^2 = 640000 -> fp16(6400) = 6400,
+    rnorm = fp16(1 / 80) = 0.0125 (fp16: 0.012496948); x = q gives fp16(6400 * fp16(rnorm^2))."""
+    rn = np.float16(1.0 / 80.0)
+    w = np.float16(np.float32(rn) * np.float32(rn))
+    expect = float(np.float16(np.float32(6400.0) * np.float32(w)))
+    assert oracle.cos16(640000, 640000, 640000) == expect
+    assert abs(expect - 1.0) < 2e-3
+    assert oracle.cos16(-640000, 640000, 640000) == -expect
+    assert oracle.cos16(0, 640000, 640000) == 0.0
+    assert oracle.cos16(0, 0, 640000) == -np.inf            # zero vector: 0 x inf = NaN, ranked last
+    # |x|^2 * 0.01 beyond the fp16 range: rnorm = 0, and a saturated product times 0 is NaN as well
+    assert oracle.cos16(100, 8258048, 640000) == 0.0
+    assert oracle.cos16(8258048, 8258048, 8258048) == -np.inf
+
+
+@pytest.mark.parametrize("d", [32, 512])
+def test_int8_cosine_matches_numpy_float16(d):
+    xb = _int8_rows_with_varied_norms(3000, d, seed=31)
+    xq = _int8_rows_with_varied_norms(11, d, seed=32)
+    xb[5] = 0
+    xb[7] = 127
+    xq[3] = 127
+    xb[9] = xq[4]
+    D, I = oracle.int8_search(oracle.METRIC_INT8_COS, xb, xq, 40)
+    Dn, In = oracle.np_int8_search(oracle.METRIC_INT8_COS, xb, xq, 40)
+    np.testing.assert_array_equal(I, In)
+    np.testing.assert_array_equal(D, Dn)
+    assert I[4, 0] == 9 or D[4, 0] == D[4, list(I[4]).index(9)]
+
+
 def test_fixtures_reproduce():
     g = np.load(os.path.join(GOLD, "flat_small.npz"))
     for name, metric in (("l2", oracle.METRIC_L2), ("ip", oracle.METRIC_IP)):

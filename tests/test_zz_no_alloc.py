@@ -26,12 +26,13 @@ def _run(ix, fn, xq_t, k):
     return D.cpu().numpy(), I.cpu().numpy()
 
 
-@pytest.mark.parametrize("kind", ["f32_l2", "f32_ip", "f16_l2", "i8_ip", "i8_l2"])
+@pytest.mark.parametrize("kind", ["f32_l2", "f32_ip", "f16_l2", "i8_ip", "i8_l2", "i8_cos"])
 def test_noalloc_matches_regular_entry_point_twice(b200, kind):
     import torch
     d, n_base, k = 64, 5000, 10
     if kind.startswith("i8"):
-        metric = b200.METRIC_INNER_PRODUCT if kind.endswith("ip") else b200.METRIC_L2
+        metric = (b200.METRIC_INT8_COSINE if kind.endswith("cos") else
+                  b200.METRIC_INNER_PRODUCT if kind.endswith("ip") else b200.METRIC_L2)
         ix = b200.IndexInt8Flat(d, metric)
         ix.add(datasets.uniform_int8(n_base, d, seed=2))
         queries = [torch.from_numpy(datasets.uniform_int8(nq, d, seed=s)).cuda() for nq, s in ((9, 3), (16, 4))]
