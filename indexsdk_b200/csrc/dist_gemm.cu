@@ -28,6 +28,10 @@ namespace b200 {
 namespace {
 
 constexpr int kMaxStages = 8;
+// int8 with the fp16 cosine epilogue: a kernel instantiation of its own (chosen by launch_dist_gemm from
+// GemmArgs::metric), so that the inner-product / L2 kernels carry none of its code
+constexpr int kKindI8Cos = 3;
+__host__ __device__ constexpr bool is_i8(int kind) { return kind == kKindI8 || kind == kKindI8Cos; }
 constexpr int kStageABytes = kTileQ * kChunkBytes;               // 16 KB
 constexpr int kStageBBytes = kTileB * kChunkBytes;               // 32 KB
 constexpr int kStageBytes = kStageABytes + kStageBBytes;         // 48 KB
@@ -38,10 +42,11 @@ constexpr int kResidentMaxChunks = 4;                            // query tile k
 // of the columns each for the folded bf16 kind, whose short ALU-only epilogue is latency-bound
 // and scales with the number of warps.
 __host__ __device__ constexpr int epi_warps(int kind) { return kind == kKindBF16 ? 16 : 8; }
-// + the producer warp, the MMA warp and, behind the epilogue warps, a second MMA warp (even and odd
-// items, i.e. the two accumulators, have their own issuing threads)
-__host__ __device__ constexpr int gemm_threads(int kind) { return 64 + 32 * epi_warps(kind) + 32; }
+// + the producer warp, the MMA warp and, behind the epilogue warps, a second MMA warp and a second
+// producer warp (even and odd items have their own issuing threads and their own stage sub-ring)
+__host__ __device__ constexpr int gemm_threads(int kind) { return 64 + 32 * epi_warps(kind) + 64; }
 __host__ __device__ constexpr int mma2_warp(int kind) { return 2 + epi_warps(kind); }
+__host__ __device__ constexpr int prod2_warp(int kind) { return 3 + epi_warps(kind); }
 constexpr uint32_t kTmemCols = 512;
 // Per-role cycle counters (GemmArgs::prof) exist in development builds only (-DB200IDX_DEV_PROF):
 // the epilogue is bound by instruction issue, and even predicated-off clock reads cost slots.
@@ -112,14 +117,14 @@ struct EpiShared {
 //                 norms are read and "key <= tau" is the sign of D: 32 columns are tested with a
 //                 16-instruction AND tree, and the burst minimum of the key is a maximum of D.
 // NCH: 32-column chunks a thread handles per tile.
-template <typename AccT, int MODE, int BURST, bool FOLD, int NCH>
+template <typename AccT, int MODE, int BURST, bool FOLD, int NCH, bool COS = false>
 struct RowEpilogue {
     using K = KeyOps<AccT>;
     const GemmArgs& a;
     int q;        // query row, valid when row_ok
     bool row_ok;
     bool l2;
-    bool cosm;                // int8 cosine: the accumulators are turned into ordered fp16 scores first
+    static constexpr bool cosm = COS;   // int8 cosine: the accumulators are turned into ordered fp16 scores first
     __half2 rq2;              // cosine: the row's query term
     AccT tau, tau_up;
     float tq;                 // FOLD append: the row's threshold, for the approximate key
@@ -131,7 +136,7 @@ struct RowEpilogue {
 
     __device__ __forceinline__ explicit RowEpilogue(const GemmArgs& a_)
         : a(a_), q(-1), row_ok(false), l2(a_.metric == kMetricL2),
-          cosm(std::is_same<AccT, int32_t>::value && a_.metric == kMetricCos), tau(AccT(0)), tau_up(AccT(0)), tq(0.f),
+          tau(AccT(0)), tau_up(AccT(0)), tq(0.f),
           blk_q(-1), blk_next(0), blk_left(0), pre_base(0), pre_ok(false) {}
 
     // 32 filter bits of this row for base positions col0 .. col0 + 31 (col0 is a multiple of 32).
@@ -159,7 +164,7 @@ struct RowEpilogue {
         if (MODE == kModeAppend && !a.direct && (q_ != blk_q || !ok)) close_block();
         q = q_;
         row_ok = ok;
-        if (std::is_same<AccT, int32_t>::value && cosm && ok && new_row) {
+        if (cosm && ok && new_row) {
             const int qn = a.seg_index ? q % a.nq : q;   // segmented base: candidate row -> query
             rq2 = cos16_query_term(__ldg(a.qnorm_i32 + qn));
         }
@@ -319,25 +324,23 @@ struct RowEpilogue {
     // columns is folded into a bit mask, and only a non-zero mask (rare) enters the compact
     // candidate loop.
     // cbase: position of the first base row of the segment the tile belongs to (0 without segments)
-    __device__ __forceinline__ void chunk(const uint32_t (&r)[32], const uint32_t* nb, int64_t col0, int nvalid,
+    __device__ __forceinline__ void chunk(uint32_t (&r)[32], const uint32_t* nb, int64_t col0, int nvalid,
                                           int bslot, int ci, int64_t cbase, uint32_t tchunk = kNoTmem) {
         if (FOLD) {
             chunk_fold(r, col0, nvalid, ci, cbase, tchunk);
             return;
         }
         if (!row_ok) return;
-        if (std::is_same<AccT, int32_t>::value && cosm) {
-            // nb holds the base rows' fp16 reciprocal norms; from here on the scores are inner products
-            uint32_t s[32];
+        if (cosm) {
+            // nb holds the base rows' fp16 reciprocal norms; the accumulators become ordered scores in
+            // place, and from here on they are treated as inner products
 #pragma unroll
             for (int c = 0; c < 32; c += 2) {
                 int32_t s0, s1;
                 cos16_pair(static_cast<int32_t>(r[c]), static_cast<int32_t>(r[c + 1]), nb[c], nb[c + 1], rq2, s0, s1);
-                s[c] = static_cast<uint32_t>(s0);
-                s[c + 1] = static_cast<uint32_t>(s1);
+                r[c] = static_cast<uint32_t>(s0);
+                r[c + 1] = static_cast<uint32_t>(s1);
             }
-            chunk_keys(s, nb, col0, nvalid, bslot, ci, cbase);
-            return;
         }
         chunk_keys(r, nb, col0, nvalid, bslot, ci, cbase);
     }
@@ -513,11 +516,11 @@ template <int KIND, int MODE, int BURST>
 __global__ void __launch_bounds__(gemm_threads(KIND), 1)
 dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                     const GemmArgs a) {
-    using AccT = typename std::conditional<KIND == kKindI8, int32_t, float>::type;
-    constexpr int kElemBytes = KIND == kKindI8 ? 1 : 2;
+    using AccT = typename std::conditional<is_i8(KIND), int32_t, float>::type;
+    constexpr int kElemBytes = is_i8(KIND) ? 1 : 2;
     constexpr int kChunkElems = kChunkBytes / kElemBytes;
     constexpr bool FOLD = KIND == kKindBF16;
-    constexpr uint32_t kIdesc = KIND == kKindI8 ? ptx::umma_idesc(2, 1, kTileQ, kTileB)
+    constexpr uint32_t kIdesc = is_i8(KIND) ? ptx::umma_idesc(2, 1, kTileQ, kTileB)
                                                 : ptx::umma_idesc(1, KIND == kKindBF16 ? 1 : 0, kTileQ, kTileB);
 
     extern __shared__ uint8_t smem_raw[];
@@ -536,15 +539,16 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int nkc = (a.d + kChunkElems - 1) / kChunkElems;
     const bool resident = a.a_resident != 0;
-    const int nst = a.n_stages;              // stages of the ring
+    const int nst = a.n_stages / 2;          // stages per sub-ring (even / odd items)
     const uint32_t stage_bytes = resident ? kStageBBytes : kStageBytes;
     uint8_t* ring = smem + (resident ? nkc * kStageABytes : 0);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < nst; ++s) {
-            ptx::mbar_init(&bar_full[s], 1);
-            ptx::mbar_init(&bar_empty[s], 1);
-        }
+        for (int r = 0; r < 2; ++r)
+            for (int s = 0; s < nst; ++s) {
+                ptx::mbar_init(&bar_full[r * (kMaxStages / 2) + s], 1);
+                ptx::mbar_init(&bar_empty[r * (kMaxStages / 2) + s], 1);
+            }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(&bar_acc_full[b], 1);
             ptx::mbar_init(&bar_acc_empty[b], epi_warps(KIND));
@@ -568,13 +572,13 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     const int n_qb = (a.nq + kTileQ - 1) / kTileQ;
     const ItemRange range(a, n_qb);
 
-    if (warp == 0) {
+    if (warp == 0 || warp == prod2_warp(KIND)) {
         if (lane == 0) {
-            // One ring for all items, filled in item order, so that the chunks of the next item (and
-            // the first ones of the one after) are on their way while the current item is multiplied:
-            // an item of K = 144 takes three stages of the five that fit, and a ring split per
-            // consumer would leave no room to load ahead.
-            const uint32_t pidx = 0u;
+            const uint32_t pidx = warp == 0 ? 0u : 1u;   // this producer serves the items of this parity
+            // Two sub-rings of nst / 2 stages: even items travel through the first, odd items through
+            // the second, so that each ring's barriers have exactly one consuming thread (a consumer a
+            // whole revolution ahead of the other would otherwise read a parity that has not happened).
+            // The resident query tile is loaded by producer 0.
             int rs = 0;
             uint32_t rph = 0;
             int cur_qb = -1;
@@ -583,6 +587,7 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             long long pw = 0;
             const bool prof_on = kDevProf && a.prof && pidx == 0;
             const long long k0 = prof_on ? clock64() : 0;
+            const uint32_t r = pidx;
             ItemCursor cur(range);
             for (int64_t i = 0; i < range.count && ok; ++i, ++t, cur.next()) {
                 const int qb = cur.qb;
@@ -595,15 +600,16 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                     ++a_loads;
                     cur_qb = qb;
                 }
+                if ((t & 1u) != pidx) continue;
                 const int tile = tile_of(a, cur.sel);
                 for (int kc = 0; kc < nkc; ++kc) {
                     const int s = rs;
-                    uint64_t* full = &bar_full[s];
+                    uint64_t* full = &bar_full[r * (kMaxStages / 2) + s];
                     const long long w0 = prof_on ? clock64() : 0;
-                    if (!ptx::mbar_wait_bounded(&bar_empty[s], rph ^ 1u, &abort_flag)) { ok = false; break; }
+                    if (!ptx::mbar_wait_bounded(&bar_empty[r * (kMaxStages / 2) + s], rph ^ 1u, &abort_flag)) { ok = false; break; }
                     if (prof_on) pw += clock64() - w0;
                     ptx::mbar_expect_tx(full, stage_bytes);
-                    uint8_t* st = ring + static_cast<size_t>(s) * stage_bytes;
+                    uint8_t* st = ring + static_cast<size_t>(r * nst + s) * stage_bytes;
                     if (!resident) {
                         ptx::tma_load_2d(st, &mapA, full, kc * kChunkElems, qb * kTileQ);
                         st += kStageABytes;
@@ -622,9 +628,8 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         // Two threads issue the UMMAs, one for the even items (accumulator 0) and one for the odd
         // items (accumulator 1), on different schedulers: a single issuing thread, sharing its
         // scheduler with busy epilogue warps, could not keep the tensor pipe fed.  Both walk the
-        // whole item list AND wait for every fill of the ring in order -- also the fills the other
-        // thread consumes -- so that a thread can never look at a stage's barrier a whole revolution
-        // early and take a phase that has not happened for one that has.
+        // whole item list so that their view of the query-block runs agrees; each consumes its own
+        // sub-ring of stages.
         if (lane == 0) {
             const uint32_t parity = warp == 1 ? 0u : 1u;
             const bool prof_on = kDevProf && a.prof && parity == 0;
@@ -652,12 +657,7 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 }
                 const bool run_ends = resident && (i + 1 == range.count || cur.last_of_qb());
                 if ((t & 1u) != parity) {
-                    // the other thread's item: only follow its fills
-                    for (int kc = 0; kc < nkc; ++kc) {
-                        if (!ptx::mbar_wait_bounded(&bar_full[s], ph, &abort_flag)) { ok = false; break; }
-                        if (++s == nst) { s = 0; ph ^= 1u; }
-                    }
-                    if (!ok) break;
+                    // the other thread's item (it travels through the other sub-ring)
                     if (run_ends) ptx::umma_commit(&bar_a_free);   // nothing of this run left on this thread
                     continue;
                 }
@@ -671,11 +671,11 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 const uint32_t tacc = tmem_base + ab * kTileB;
                 for (int kc = 0; kc < nkc; ++kc) {
                     w0 = prof_on ? clock64() : 0;
-                    if (!ptx::mbar_wait_bounded(&bar_full[s], ph, &abort_flag)) { ok = false; break; }
+                    if (!ptx::mbar_wait_bounded(&bar_full[parity * (kMaxStages / 2) + s], ph, &abort_flag)) { ok = false; break; }
                     if (prof_on) mw1 += clock64() - w0;
                     if (kDevProf && a.trace && blockIdx.x == 0 && t < 64 && kc + 1 == nkc) a.trace[2 * 64 + t] = clock64();
                     ptx::tc_fence_after();
-                    const uint32_t st_lo = ring_lo + static_cast<uint32_t>(s) * stage_lo;
+                    const uint32_t st_lo = ring_lo + (parity * static_cast<uint32_t>(nst) + static_cast<uint32_t>(s)) * stage_lo;
                     const uint32_t sa_lo = resident ? a_res_lo + static_cast<uint32_t>(kc) * (kStageABytes >> 4) : st_lo;
                     const uint32_t sb_lo = resident ? st_lo : st_lo + (kStageABytes >> 4);
                     // the last chunk may hold fewer than four 32-byte K steps (the rest is zero fill)
@@ -687,10 +687,10 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                         const uint64_t db = desc_hi | static_cast<uint64_t>(sb_lo + ks * 2);
                         const uint32_t accum = (kc > 0 || ks > 0) ? 1u : 0u;
                         if (kDevProf && (a.dbg & 4)) continue;
-                        if (KIND == kKindI8) ptx::umma_i8(tacc, da, db, kIdesc, accum);
+                        if (is_i8(KIND)) ptx::umma_i8(tacc, da, db, kIdesc, accum);
                         else ptx::umma_f16(tacc, da, db, kIdesc, accum);
                     }
-                    ptx::umma_commit(&bar_empty[s]);
+                    ptx::umma_commit(&bar_empty[parity * (kMaxStages / 2) + s]);
                     if (++s == nst) { s = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
@@ -711,9 +711,9 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         const int row_in_tile = quarter * 32 + lane;
         const int et = threadIdx.x - 64;       // epilogue thread index
         constexpr int kCols = kTileB / (epi_warps(KIND) / 4);   // columns per epilogue thread
-        RowEpilogue<AccT, MODE, BURST, FOLD, kCols / 32> epi(a);
+        RowEpilogue<AccT, MODE, BURST, FOLD, kCols / 32, KIND == kKindI8Cos> epi(a);
         const bool l2 = a.metric == kMetricL2 && !FOLD;   // FOLD: no norms to fetch
-        const bool cosm = KIND == kKindI8 && a.metric == kMetricCos;
+        constexpr bool cosm = KIND == kKindI8Cos;
         const uint32_t* gnorm = static_cast<const uint32_t*>(a.bnorm);
         uint32_t t = 0;
         bool ok = true;
@@ -849,9 +849,9 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
 // scalar FMAs.  Used to cross-check the tcgen05 variant on device.
 // ---------------------------------------------------------------------------------------
 template <int KIND>
-__device__ __forceinline__ typename std::conditional<KIND == kKindI8, int32_t, float>::type
+__device__ __forceinline__ typename std::conditional<is_i8(KIND), int32_t, float>::type
 load_elem(const void* p, int64_t idx) {
-    if (KIND == kKindI8) return static_cast<int32_t>(static_cast<const int8_t*>(p)[idx]);
+    if (is_i8(KIND)) return static_cast<int32_t>(static_cast<const int8_t*>(p)[idx]);
     else if (KIND == kKindBF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[idx]);
     else return __half2float(static_cast<const __half*>(p)[idx]);
 }
@@ -859,14 +859,14 @@ load_elem(const void* p, int64_t idx) {
 template <int KIND, int MODE, int BURST>
 __global__ void __launch_bounds__(kTileQ)
 dist_gemm_simt_kernel(const GemmArgs a) {
-    using AccT = typename std::conditional<KIND == kKindI8, int32_t, float>::type;
+    using AccT = typename std::conditional<is_i8(KIND), int32_t, float>::type;
     __shared__ __align__(16) EpiShared epi_sh;
     const int n_qb = (a.nq + kTileQ - 1) / kTileQ;
     const ItemRange range(a, n_qb);
     const bool l2 = a.metric == kMetricL2;
-    const bool cosm = KIND == kKindI8 && a.metric == kMetricCos;
+    constexpr bool cosm = KIND == kKindI8Cos;
     const uint32_t* gnorm = static_cast<const uint32_t*>(a.bnorm);
-    RowEpilogue<AccT, MODE, BURST, KIND == kKindBF16, kTileB / 32> epi(a);
+    RowEpilogue<AccT, MODE, BURST, KIND == kKindBF16, kTileB / 32, KIND == kKindI8Cos> epi(a);
     ItemCursor cur(range);
     for (int64_t i = 0; i < range.count; ++i, cur.next()) {
         const int qb = cur.qb;
@@ -902,7 +902,7 @@ dist_gemm_simt_kernel(const GemmArgs a) {
                 for (int k = 0; k < a.d; ++k)
                     acc += load_elem<KIND>(a.A, static_cast<int64_t>(qc) * a.d + k) *
                            load_elem<KIND>(a.B, col * a.d + k);
-                if (KIND == kKindI8) r[j] = static_cast<uint32_t>(acc);
+                if (is_i8(KIND)) r[j] = static_cast<uint32_t>(acc);
                 else r[j] = __float_as_uint(acc);
             }
             const int bslot = sel * (kTileB / BURST) + c * (32 / BURST);
@@ -925,13 +925,14 @@ cudaError_t launch_one(const GemmLaunch& L, GemmArgs a, const CUtensorMap* mapA,
         return cudaGetLastError();
     }
     // shared-memory plan: resident query tile (if it is small) + as many ring stages as fit
-    const int elem = KIND == kKindI8 ? 1 : 2;
+    const int elem = is_i8(KIND) ? 1 : 2;
     const int nkc = (a.d * elem + kChunkBytes - 1) / kChunkBytes;
     a.a_resident = nkc <= kResidentMaxChunks ? 1 : 0;
     const int a_bytes = a.a_resident ? nkc * kStageABytes : 0;
     const int stage_bytes = a.a_resident ? kStageBBytes : kStageBytes;
     int nst = (kGemmSmemBudget - 1024 - a_bytes) / stage_bytes;
     if (nst > kMaxStages) nst = kMaxStages;
+    nst &= ~1;                       // two sub-rings of equal depth
     if (nst < 2) return cudaErrorInvalidConfiguration;
     a.n_stages = nst;
     const int smem = a_bytes + nst * stage_bytes + 1024;
@@ -967,7 +968,9 @@ cudaError_t launch_dist_gemm(const GemmLaunch& L, const GemmArgs& a, const CUten
     switch (L.kind) {
         case kKindF16: return launch_kind<kKindF16>(L, a, mapA, mapB, stream);
         case kKindBF16: return launch_kind<kKindBF16>(L, a, mapA, mapB, stream);
-        case kKindI8: return launch_kind<kKindI8>(L, a, mapA, mapB, stream);
+        case kKindI8:
+            return a.metric == kMetricCos ? launch_kind<kKindI8Cos>(L, a, mapA, mapB, stream)
+                                          : launch_kind<kKindI8>(L, a, mapA, mapB, stream);
         default: return cudaErrorInvalidValue;
     }
 }
