@@ -19,6 +19,7 @@
 #include <cuda_fp16.h>
 #include "cos16.cuh"
 
+#include <cstring>
 #include <type_traits>
 
 #include "common.cuh"
@@ -537,11 +538,15 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const int nkc = (a.d + kChunkElems - 1) / kChunkElems;
+    // Packed operands (bf16 kind only): the query tile and a base tile are one contiguous image each;
+    // an item is ONE stage of its parity's sub-ring (nst = 1) and ONE hand-off per role.
+    const bool packed = KIND == kKindBF16 && a.packed != 0;
+    const uint32_t a_img_bytes = static_cast<uint32_t>(kTileQ) * a.d * 2u;
+    const int nkc = packed ? 1 : (a.d + kChunkElems - 1) / kChunkElems;
     const bool resident = a.a_resident != 0;
     const int nst = a.n_stages / 2;          // stages per sub-ring (even / odd items)
-    const uint32_t stage_bytes = resident ? kStageBBytes : kStageBytes;
-    uint8_t* ring = smem + (resident ? nkc * kStageABytes : 0);
+    const uint32_t stage_bytes = packed ? static_cast<uint32_t>(kTileB) * a.d * 2u : (resident ? kStageBBytes : kStageBytes);
+    uint8_t* ring = smem + (packed ? ((a_img_bytes + 1023u) & ~1023u) : (resident ? nkc * kStageABytes : 0));
 
     if (threadIdx.x == 0) {
         for (int r = 0; r < 2; ++r)
@@ -557,8 +562,10 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         ptx::mbar_init(&bar_a_free, 2);   // both MMA-issuing threads
         abort_flag = 0;
         ptx::mbar_fence_init();
-        ptx::prefetch_tensormap(&mapA);
-        ptx::prefetch_tensormap(&mapB);
+        if (!packed) {
+            ptx::prefetch_tensormap(&mapA);
+            ptx::prefetch_tensormap(&mapB);
+        }
     }
     if (warp == 1) {
         ptx::tmem_alloc(&tmem_base_slot, kTmemCols);
@@ -594,9 +601,15 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 if (resident && pidx == 0 && qb != cur_qb) {
                     // the previous query block's UMMAs must be done with the tile before it is overwritten
                     if (a_loads && !ptx::mbar_wait_bounded(&bar_a_free, (a_loads - 1u) & 1u, &abort_flag)) { ok = false; break; }
-                    ptx::mbar_expect_tx(&bar_a_full, static_cast<uint32_t>(nkc) * kStageABytes);
-                    for (int kc = 0; kc < nkc; ++kc)
-                        ptx::tma_load_2d(smem + kc * kStageABytes, &mapA, &bar_a_full, kc * kChunkElems, qb * kTileQ);
+                    if (packed) {
+                        ptx::mbar_expect_tx(&bar_a_full, a_img_bytes);
+                        ptx::bulk_load_1d(smem, static_cast<const uint8_t*>(a.A) + static_cast<size_t>(qb) * a_img_bytes,
+                                          a_img_bytes, &bar_a_full);
+                    } else {
+                        ptx::mbar_expect_tx(&bar_a_full, static_cast<uint32_t>(nkc) * kStageABytes);
+                        for (int kc = 0; kc < nkc; ++kc)
+                            ptx::tma_load_2d(smem + kc * kStageABytes, &mapA, &bar_a_full, kc * kChunkElems, qb * kTileQ);
+                    }
                     ++a_loads;
                     cur_qb = qb;
                 }
@@ -610,6 +623,12 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                     if (prof_on) pw += clock64() - w0;
                     ptx::mbar_expect_tx(full, stage_bytes);
                     uint8_t* st = ring + static_cast<size_t>(r * nst + s) * stage_bytes;
+                    if (packed) {
+                        ptx::bulk_load_1d(st, static_cast<const uint8_t*>(a.B) + static_cast<size_t>(tile) * stage_bytes,
+                                          stage_bytes, full);
+                        if (++rs == nst) { rs = 0; rph ^= 1u; }
+                        continue;
+                    }
                     if (!resident) {
                         ptx::tma_load_2d(st, &mapA, full, kc * kChunkElems, qb * kTileQ);
                         st += kStageABytes;
@@ -642,6 +661,8 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             // Descriptors differ only in their 14-bit address field: build the constant part once
             // and add byte offsets / 16 (the single issuing thread is on the critical path).
             const uint64_t desc_hi = ptx::umma_desc_k_sw128(0);
+            // packed operands: core matrices adjacent along K are 128 bytes apart, 8-row groups a.d / 8 of them
+            const uint64_t desc_hi_p = ptx::umma_desc_k_plain(0, 128u, static_cast<uint32_t>(a.d) * 16u);
             const uint32_t a_res_lo = (ptx::smem_u32(smem) & 0x3FFFFu) >> 4;
             const uint32_t ring_lo = (ptx::smem_u32(ring) & 0x3FFFFu) >> 4;
             const uint32_t stage_lo = stage_bytes >> 4;
@@ -676,6 +697,18 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                     if (kDevProf && a.trace && blockIdx.x == 0 && t < 64 && kc + 1 == nkc) a.trace[2 * 64 + t] = clock64();
                     ptx::tc_fence_after();
                     const uint32_t st_lo = ring_lo + (parity * static_cast<uint32_t>(nst) + static_cast<uint32_t>(s)) * stage_lo;
+                    if (packed) {
+                        // K / 16 steps of one 128 x 256 x 16 UMMA; a step advances both images by two core matrices
+                        const int nks_p = a.d >> 4;
+                        for (int ks = 0; ks < nks_p; ++ks) {
+                            const uint64_t da = desc_hi_p | static_cast<uint64_t>(a_res_lo + ks * 16);
+                            const uint64_t db = desc_hi_p | static_cast<uint64_t>(st_lo + ks * 16);
+                            ptx::umma_f16(tacc, da, db, kIdesc, ks > 0 ? 1u : 0u);
+                        }
+                        ptx::umma_commit(&bar_empty[parity * (kMaxStages / 2) + s]);
+                        if (++s == nst) { s = 0; ph ^= 1u; }
+                        continue;
+                    }
                     const uint32_t sa_lo = resident ? a_res_lo + static_cast<uint32_t>(kc) * (kStageABytes >> 4) : st_lo;
                     const uint32_t sb_lo = resident ? st_lo : st_lo + (kStageABytes >> 4);
                     // the last chunk may hold fewer than four 32-byte K steps (the rest is zero fill)
@@ -899,9 +932,10 @@ dist_gemm_simt_kernel(const GemmArgs a) {
             for (int j = 0; j < 32; ++j) {
                 const int64_t col = (col0 + j < a.N) ? col0 + j : a.N - 1;
                 AccT acc = AccT(0);
+                const bool packed = packed_operands(KIND, a.d);
                 for (int k = 0; k < a.d; ++k)
-                    acc += load_elem<KIND>(a.A, static_cast<int64_t>(qc) * a.d + k) *
-                           load_elem<KIND>(a.B, col * a.d + k);
+                    acc += load_elem<KIND>(a.A, operand_elem(packed, qc, k, a.d, kTileQ)) *
+                           load_elem<KIND>(a.B, operand_elem(packed, col, k, a.d, kTileB));
                 if (is_i8(KIND)) r[j] = static_cast<uint32_t>(acc);
                 else r[j] = __float_as_uint(acc);
             }
@@ -927,15 +961,17 @@ cudaError_t launch_one(const GemmLaunch& L, GemmArgs a, const CUtensorMap* mapA,
     // shared-memory plan: resident query tile (if it is small) + as many ring stages as fit
     const int elem = is_i8(KIND) ? 1 : 2;
     const int nkc = (a.d * elem + kChunkBytes - 1) / kChunkBytes;
-    a.a_resident = nkc <= kResidentMaxChunks ? 1 : 0;
-    const int a_bytes = a.a_resident ? nkc * kStageABytes : 0;
-    const int stage_bytes = a.a_resident ? kStageBBytes : kStageBytes;
-    int nst = (kGemmSmemBudget - 1024 - a_bytes) / stage_bytes;
+    a.packed = packed_operands(KIND, a.d) ? 1 : 0;
+    a.a_resident = (a.packed || nkc <= kResidentMaxChunks) ? 1 : 0;
+    const int a_bytes = a.packed ? ((kTileQ * a.d * 2 + 1023) & ~1023) : (a.a_resident ? nkc * kStageABytes : 0);
+    const int stage_bytes = a.packed ? kTileB * a.d * 2 : (a.a_resident ? kStageBBytes : kStageBytes);
+    int nst = a.packed ? 2 : (kGemmSmemBudget - 1024 - a_bytes) / stage_bytes;   // packed: one whole tile per parity
     if (nst > kMaxStages) nst = kMaxStages;
     nst &= ~1;                       // two sub-rings of equal depth
     if (nst < 2) return cudaErrorInvalidConfiguration;
     a.n_stages = nst;
     const int smem = a_bytes + nst * stage_bytes + 1024;
+    if (smem > kGemmSmemBudget) return cudaErrorInvalidConfiguration;
     auto kern = dist_gemm_tc_kernel<KIND, MODE, BURST>;
     // per-device attribute; cheap enough to set on every launch
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBudget);
@@ -976,6 +1012,10 @@ cudaError_t launch_dist_gemm(const GemmLaunch& L, const GemmArgs& a, const CUten
 }
 
 int encode_operand_map(CUtensorMap* out, int kind, const void* base, int64_t rows, int d, int box_rows) {
+    if (packed_operands(kind, d)) {   // read with contiguous copies: no tensor map
+        std::memset(out, 0, sizeof(*out));
+        return 0;
+    }
     typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);

@@ -30,9 +30,34 @@ enum GemmKind : int { kKindF16 = 0, kKindBF16 = 1, kKindI8 = 2 };
 constexpr int kFoldCols = 16;
 enum GemmMode : int { kModeBurstMin = 0, kModeAppend = 1 };
 
+// Packed operands.  Folded bf16 operands of at most kPackedMaxCols columns (fp32 indexes up to
+// d = 144, the IVFPQ coarse quantizers) are not kept as rows but as the shared-memory image the
+// tensor core reads: per tile of R rows (R = kTileQ for queries, kTileB for base rows) a block of
+// R * cols bf16 in the UMMA's K-major no-swizzle layout -- "core matrices" of 8 rows x 8 columns
+// (128 contiguous bytes, a row's 8 values = 16 bytes), the core matrices of an 8-row group side by
+// side along K, the groups one after the other:
+//   element (r, k) of the tile sits at bf16 index ((r / 8) * (cols / 8) + k / 8) * 64 + (r % 8) * 8 + k % 8.
+// A tile is then ONE contiguous copy into shared memory (cp.async.bulk), K = 144 needs 72 KB per
+// base tile instead of three 32 KB swizzle-128 boxes (the third three quarters zero fill), and an
+// item of the kernel's work list is one hand-off between its roles instead of three.
+constexpr int kPackedMaxCols = 160;
+__host__ __device__ constexpr bool packed_operands(int kind, int cols) {
+    return kind == kKindBF16 && cols <= kPackedMaxCols && cols % 16 == 0;
+}
+__host__ __device__ __forceinline__ int64_t packed_elem(int64_t r, int k, int cols, int rows_per_tile) {
+    const int64_t tile = r / rows_per_tile;
+    const int rr = static_cast<int>(r - tile * rows_per_tile);
+    return tile * rows_per_tile * cols + static_cast<int64_t>((rr >> 3) * (cols >> 3) + (k >> 3)) * 64 + (rr & 7) * 8 +
+           (k & 7);
+}
+// bf16 index of (r, k) in an operand buffer, packed or row-major
+__host__ __device__ __forceinline__ int64_t operand_elem(bool packed, int64_t r, int k, int cols, int rows_per_tile) {
+    return packed ? packed_elem(r, k, cols, rows_per_tile) : r * cols + k;
+}
+
 struct GemmArgs {
-    const void* A;        // queries [nq, d] in the operand dtype (SIMT variant only)
-    const void* B;        // base    [N, d]  in the operand dtype (SIMT variant only)
+    const void* A;        // queries [nq, d] in the operand dtype (SIMT variant, packed operands)
+    const void* B;        // base    [N, d]  in the operand dtype (SIMT variant, packed operands)
     int d;                // elements per operand row = K extent (bf16 kind: includes the 16 folded columns)
     int nq;
     int64_t N;
@@ -76,6 +101,7 @@ struct GemmArgs {
     unsigned long long* trace;   // development builds only: [6][64] clock64 stamps of CTA 0's first 64 items
     int dbg;              // development builds only: 1 skip the epilogue's chunk work, 2 also its TMEM loads, 4 skip the UMMAs
     // filled in by launch_dist_gemm (tcgen05 variant): shared-memory plan
+    int packed;           // 1: packed operands (see packed_operands), read through A / B with contiguous copies
     int a_resident;       // 1: the query tile stays in shared memory for a whole query block
     int n_stages;         // ring stages (base chunks, or query + base chunks when not resident)
     int aligned_ranges;   // 1: CTA = (query block, even share of the tiles); 0: equal cuts of the item list

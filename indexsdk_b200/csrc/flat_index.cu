@@ -79,7 +79,8 @@ void FlatIndex::reserve(int64_t n) {
     const size_t row_op = static_cast<size_t>(op_cols()) * op_elem_bytes();
     if (dtype_ == kF32)
         x32_.grow_keep(static_cast<size_t>(want) * d_ * 4, static_cast<size_t>(n_) * d_ * 4, stream_);
-    xop_.grow_keep(static_cast<size_t>(want) * row_op, static_cast<size_t>(n_) * row_op, stream_);
+    // whole tiles are kept: a packed operand copy interleaves the rows of a tile
+    xop_.grow_keep(static_cast<size_t>(want) * row_op, static_cast<size_t>(std::min(cap_rows_, round_up(n_, kTileB))) * row_op, stream_);
     norms_.grow_keep(static_cast<size_t>(want) * 4, static_cast<size_t>(n_) * 4, stream_);
     labels_.grow_keep(static_cast<size_t>(want) * 8, static_cast<size_t>(n_) * 8, stream_);
     cap_rows_ = want;
@@ -100,8 +101,8 @@ void FlatIndex::add(int64_t n, const void* x, bool x_is_f16, const int64_t* ids,
             float* dst = x32_.as<float>() + row0 * d_;
             B200_CUDA_CHECK(cudaMemcpyAsync(dst, static_cast<const float*>(x) + off * d_,
                                             static_cast<size_t>(m) * d_ * 4, kind, stream_));
-            B200_CUDA_CHECK(launch_base_prep_f32(dst, m, d_, metric_, xop_.as<uint16_t>() + row0 * op_cols(),
-                                                 norms_.as<float>() + row0, maxnorm_.as<float>(), stream_));
+            B200_CUDA_CHECK(launch_base_prep_f32(dst, m, d_, metric_, xop_.get(), row0, norms_.as<float>() + row0,
+                                                 maxnorm_.as<float>(), stream_));
         } else if (dtype_ == kF16) {
             uint16_t* dst = xop_.as<uint16_t>() + row0 * d_;
             if (x_is_f16) {
@@ -170,8 +171,12 @@ int64_t FlatIndex::remove_ids(int64_t n, const int64_t* ids) {
         if (dtype_ == kF32)
             B200_CUDA_CHECK(cudaMemcpyAsync(x32_.as<float>() + p * d_, x32_.as<float>() + last * d_,
                                             static_cast<size_t>(d_) * 4, cudaMemcpyDeviceToDevice, stream_));
-        B200_CUDA_CHECK(cudaMemcpyAsync(xop_.as<uint8_t>() + p * row_op, xop_.as<uint8_t>() + last * row_op, row_op,
-                                        cudaMemcpyDeviceToDevice, stream_));
+        if (dtype_ == kF32)   // the operand copy may be packed: rewrite the row from its fp32 values
+            B200_CUDA_CHECK(launch_base_prep_f32(x32_.as<float>() + p * d_, 1, d_, metric_, xop_.get(), p,
+                                                 norms_.as<float>() + p, maxnorm_.as<float>(), stream_));
+        else
+            B200_CUDA_CHECK(cudaMemcpyAsync(xop_.as<uint8_t>() + p * row_op, xop_.as<uint8_t>() + last * row_op, row_op,
+                                            cudaMemcpyDeviceToDevice, stream_));
         B200_CUDA_CHECK(cudaMemcpyAsync(norms_.as<uint8_t>() + p * norm_b, norms_.as<uint8_t>() + last * norm_b,
                                         norm_b, cudaMemcpyDeviceToDevice, stream_));
         B200_CUDA_CHECK(cudaMemcpyAsync(labels_.as<int64_t>() + p, labels_.as<int64_t>() + last, 8,
@@ -275,8 +280,8 @@ void FlatIndex::run_page(int nq, const void* xq_raw, const void* xq_op_in, int k
     float* eps = nullptr;
     void* qnorm = w_qnorm_.ensure(static_cast<size_t>(nq) * 4);
     if (dtype_ == kF32) {
-        void* qop = force_full ? w_fb_qop_.ensure(static_cast<size_t>(nq) * op_cols() * 2)
-                               : w_qop_.ensure(static_cast<size_t>(nq) * op_cols() * 2);
+        const size_t qop_bytes = static_cast<size_t>(round_up(nq, kTileQ)) * op_cols() * 2;   // whole tiles (packed copy)
+        void* qop = force_full ? w_fb_qop_.ensure(qop_bytes) : w_qop_.ensure(qop_bytes);
         eps = static_cast<float*>(w_eps_.ensure(static_cast<size_t>(nq) * 4));
         B200_CUDA_CHECK(launch_prep_queries_f32(static_cast<const float*>(xq_raw), nq, d_, metric_, max_norm_, qop,
                                                 static_cast<float*>(qnorm), eps, stream_));

@@ -72,7 +72,10 @@ void FlatGroup::refresh(const std::vector<FlatIndex*>& members, cudaStream_t st)
         const FlatIndex::RawView v = members[i]->raw_view();
         const int64_t s0 = seg_start_[i];
         const size_t n = static_cast<size_t>(v.n);
-        B200_CUDA_CHECK(cudaMemcpyAsync(static_cast<uint8_t*>(xop) + static_cast<size_t>(s0) * row_op, v.operand, n * row_op,
+        // packed operands (fp32 members of few dimensions) are whole-tile images: a member starts on a
+        // tile boundary here as in its own buffer, so its tiles are copied as they are
+        const size_t n_op = packed_operands(kind_, op_cols_) ? static_cast<size_t>((v.n + kTileB - 1) / kTileB * kTileB) : n;
+        B200_CUDA_CHECK(cudaMemcpyAsync(static_cast<uint8_t*>(xop) + static_cast<size_t>(s0) * row_op, v.operand, n_op * row_op,
                                         cudaMemcpyDeviceToDevice, st));
         B200_CUDA_CHECK(cudaMemcpyAsync(static_cast<uint8_t*>(nrm) + static_cast<size_t>(s0) * 4, v.norms, n * 4,
                                         cudaMemcpyDeviceToDevice, st));
@@ -115,7 +118,7 @@ void FlatGroup::search_device(const std::vector<FlatIndex*>& members, int64_t nq
     void* qnorm = w_qnorm_.ensure(static_cast<size_t>(nq) * 4);
     const void* xq_op = xq;
     if (dtype_ == kF32) {
-        void* qop = w_qop_.ensure(static_cast<size_t>(nq) * op_cols_ * 2);
+        void* qop = w_qop_.ensure(static_cast<size_t>((nq + kTileQ - 1) / kTileQ * kTileQ) * op_cols_ * 2);   // whole tiles
         float* eps = static_cast<float*>(w_eps_.ensure(static_cast<size_t>(nq) * 4));
         B200_CUDA_CHECK(launch_prep_queries_f32(static_cast<const float*>(xq), nq, d_, metric_, max_norm_, qop,
                                                 static_cast<float*>(qnorm), eps, st));

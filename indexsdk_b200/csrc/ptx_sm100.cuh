@@ -104,6 +104,15 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         : "memory");
 }
 
+// Contiguous copy global -> shared (this CTA), completion on an mbarrier.  Both addresses 16-byte
+// aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gptr, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(__cvta_generic_to_global(gptr)), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
 // Asks the L2 cache to fetch `bytes` (a multiple of 16) starting at the 16-byte aligned global
 // address `gptr`; one thread, no completion to wait for.
 __device__ __forceinline__ void bulk_prefetch_l2(const void* gptr, uint32_t bytes) {
@@ -142,6 +151,18 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
     desc |= static_cast<uint64_t>(1024 >> 4) << 32;
     desc |= static_cast<uint64_t>(1) << 46;
     desc |= static_cast<uint64_t>(2) << 61;
+    return desc;
+}
+
+// K-major operand without swizzle: core matrices of 8 rows x 16 bytes (128 contiguous bytes);
+// lbo_bytes = distance between core matrices adjacent along K, sbo_bytes = distance between
+// 8-row groups.  Layout type 0.
+__device__ __forceinline__ uint64_t umma_desc_k_plain(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t desc = 0;
+    desc |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    desc |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    desc |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    desc |= static_cast<uint64_t>(1) << 46;
     return desc;
 }
 

@@ -499,13 +499,14 @@ __global__ void prep_queries_f32_kernel(const float* xq, int nq, int d, int metr
     const int lane = threadIdx.x & 31;
     if (q >= nq) return;
     const int dp = d + kFoldCols;
+    const bool packed = packed_operands(kKindBF16, dp);
     float s = 0.f;
     for (int i = lane; i < d; i += 32) {
         const float v = xq[static_cast<int64_t>(q) * d + i];
         s = fmaf(v, v, s);
-        qb[static_cast<int64_t>(q) * dp + i] = __float2bfloat16_rn(v);
+        qb[operand_elem(packed, q, i, dp, kTileQ)] = __float2bfloat16_rn(v);
     }
-    if (lane < kFoldCols) qb[static_cast<int64_t>(q) * dp + d + lane] = __float2bfloat16_rn(lane < 3 ? 1.f : 0.f);
+    if (lane < kFoldCols) qb[operand_elem(packed, q, d + lane, dp, kTileQ)] = __float2bfloat16_rn(lane < 3 ? 1.f : 0.f);
     s = warp_sum(s);
     if (lane == 0) {
         qnorm[q] = s;
@@ -536,7 +537,10 @@ __global__ void fold_tau_kernel(const uint32_t* tau, const float* qnorm, float y
     const float m = sqrtf(qnorm[q]) * ymax + 0.5f * ymax * ymax + fabsf(t);
     float c = t + 0.000244140625f * m;
     if (metric == kMetricL2) c *= 0.5f;
-    split3_bf16(c, qb + static_cast<int64_t>(q) * (d + kFoldCols) + d + 3);
+    const int dp = d + kFoldCols;
+    // columns d + 3 .. d + 5 lie in one 8-column group (d is a multiple of 16), so they are
+    // consecutive in the packed layout as well
+    split3_bf16(c, qb + operand_elem(packed_operands(kKindBF16, dp), q, d + 3, dp, kTileQ));
 }
 
 __global__ void prep_queries_f16_kernel(const __half* xq, int nq, int d, float* qnorm) {
@@ -567,22 +571,25 @@ __global__ void prep_queries_i8_kernel(const int8_t* xq, int nq, int d, int32_t*
 
 // Base operand rows of d + kFoldCols bf16: the vector, -|y|^2 / 2 in three terms (zeros for inner
 // product), three ones (they pick up the query's threshold terms) and zero padding.
-__global__ void base_prep_f32_kernel(const float* x, int64_t n, int d, int metric, __nv_bfloat16* xb, float* norms,
-                                     float* max_norm_sq) {
+// x, norms: the n rows being added; xb: the whole operand buffer, whose row row0 + r belongs to x's row r.
+__global__ void base_prep_f32_kernel(const float* x, int64_t n, int d, int metric, __nv_bfloat16* xb, int64_t row0,
+                                     float* norms, float* max_norm_sq) {
     const int64_t r = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (r >= n) return;
     const int dp = d + kFoldCols;
+    const bool packed = packed_operands(kKindBF16, dp);
+    const int64_t ro = row0 + r;
     float s = 0.f;
     for (int i = lane; i < d; i += 32) {
         const float v = x[r * d + i];
         s = fmaf(v, v, s);
-        xb[r * dp + i] = __float2bfloat16_rn(v);
+        xb[operand_elem(packed, ro, i, dp, kTileB)] = __float2bfloat16_rn(v);
     }
     s = warp_sum(s);
-    if (lane >= 3 && lane < kFoldCols) xb[r * dp + d + lane] = __float2bfloat16_rn(lane < 6 ? 1.f : 0.f);
+    if (lane >= 3 && lane < kFoldCols) xb[operand_elem(packed, ro, d + lane, dp, kTileB)] = __float2bfloat16_rn(lane < 6 ? 1.f : 0.f);
     if (lane == 0) {
-        split3_bf16(metric == kMetricL2 ? -0.5f * s : 0.f, xb + r * dp + d);
+        split3_bf16(metric == kMetricL2 ? -0.5f * s : 0.f, xb + operand_elem(packed, ro, d, dp, kTileB));
         norms[r] = s;
         atomicMax(reinterpret_cast<unsigned int*>(max_norm_sq), __float_as_uint(s));
     }
@@ -751,11 +758,11 @@ cudaError_t launch_prep_queries_i8(const int8_t* xq, int nq, int d, int32_t* qno
     prep_queries_i8_kernel<<<(nq + 7) / 8, 256, 0, stream>>>(xq, nq, d, qnorm);
     return cudaGetLastError();
 }
-cudaError_t launch_base_prep_f32(const float* x, int64_t n, int d, int metric, void* x_bf16, float* norms,
-                                 float* max_norm_sq, cudaStream_t stream) {
+cudaError_t launch_base_prep_f32(const float* x, int64_t n, int d, int metric, void* x_bf16, int64_t row0,
+                                 float* norms, float* max_norm_sq, cudaStream_t stream) {
     if (n <= 0) return cudaSuccess;
     base_prep_f32_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(
-        x, n, d, metric, static_cast<__nv_bfloat16*>(x_bf16), norms, max_norm_sq);
+        x, n, d, metric, static_cast<__nv_bfloat16*>(x_bf16), row0, norms, max_norm_sq);
     return cudaGetLastError();
 }
 cudaError_t launch_fold_tau(const uint32_t* tau, const float* qnorm, float base_max_norm, int nq, int d, int metric,

@@ -60,7 +60,8 @@ cudaError_t launch_merge_topk(int nsrc, int64_t nq, int k, int descending, const
                               float* D, int64_t* I, cudaStream_t stream, int64_t src_stride_d = 0,
                               int64_t src_stride_i = 0);
 
-// Query preparation.  fp32 queries -> bf16 operand copy, squared norms and the filter slack
+// Query preparation.  fp32 queries -> bf16 operand copy (row-major or packed, see dist_gemm.cuh: a
+// packed copy needs room for nq rounded up to kTileQ rows), squared norms and the filter slack
 // eps[q] (see flat_index.cu); fp16 / int8 queries -> norms only.
 cudaError_t launch_prep_queries_f32(const float* xq, int nq, int d, int metric, float base_max_norm, void* q_bf16,
                                     float* qnorm, float* eps, cudaStream_t stream);
@@ -68,9 +69,11 @@ cudaError_t launch_prep_queries_f16(const void* xq_f16, int nq, int d, float* qn
 cudaError_t launch_prep_queries_i8(const int8_t* xq, int nq, int d, int32_t* qnorm, cudaStream_t stream);
 
 // Base preparation at add time.
-// fp32 index: operand rows are d + kFoldCols bf16 wide (see dist_gemm.cuh)
-cudaError_t launch_base_prep_f32(const float* x, int64_t n, int d, int metric, void* x_bf16, float* norms,
-                                 float* max_norm_sq, cudaStream_t stream);
+// fp32 index: operand rows are d + kFoldCols bf16 wide, row-major or packed (see dist_gemm.cuh;
+// the layout follows from d).  x_bf16 is the whole operand buffer, row0 the position of x's first row
+// in it; norms points at the norms of the rows being added.
+cudaError_t launch_base_prep_f32(const float* x, int64_t n, int d, int metric, void* x_bf16, int64_t row0,
+                                 float* norms, float* max_norm_sq, cudaStream_t stream);
 // threshold terms of the folded query rows, from the ordered-key thresholds tau[nq]
 cudaError_t launch_fold_tau(const uint32_t* tau, const float* qnorm, float base_max_norm, int nq, int d, int metric,
                             void* q_bf16, cudaStream_t stream);
