@@ -319,6 +319,42 @@ struct RowEpilogue {
         }
     }
 
+    // Folded operands, append mode, split in two so that the accumulator can be handed back between
+    // them.  fold_mask: bit (31 - c) of the result = column c of this lane's row passes (D >= 0, a
+    // real base row, not filtered out); warp-collective, 0 for everybody when no lane has a hit.
+    __device__ __forceinline__ uint32_t fold_mask(const uint32_t (&r)[32], int64_t col0, int nvalid) {
+        uint32_t t[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) t[i] = r[2 * i] & r[2 * i + 1];
+#pragma unroll
+        for (int w = 8; w > 0; w >>= 1)
+#pragma unroll
+            for (int i = 0; i < w; ++i) t[i] &= t[i + w];
+        const bool hit = row_ok && static_cast<int32_t>(t[0]) >= 0;   // not every D negative
+        if (!__any_sync(0xFFFFFFFFu, hit)) return 0u;
+        uint32_t m0 = 0, m1 = 0;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+            m0 = __funnelshift_l(r[c], m0, 1);
+            m1 = __funnelshift_l(r[16 + c], m1, 1);
+        }
+        uint32_t mask = ~((m0 << 16) | (m1 & 0xFFFFu));
+        mask &= nvalid >= 32 ? 0xFFFFFFFFu : ~(0xFFFFFFFFu >> nvalid);
+        if (a.qmask && row_ok) mask &= __brev(mask_word(col0));
+        return hit ? mask : 0u;
+    }
+    // fold_extract: appends the columns of `mask` from the registers (select tree; no TMEM access).
+    __device__ __forceinline__ void fold_extract(const uint32_t (&r)[32], uint32_t mask, int64_t col0) {
+        while (mask) {
+            const uint32_t c = __clz(mask);
+            mask &= ~(0x80000000u >> c);
+            const float dv = __uint_as_float(pick(r, c));
+            if (!(dv >= 0.f)) continue;   // NaN
+            const float key = l2 ? fmaf(-2.f, dv, tq) : tq - dv;
+            append(pack_cand(float_to_ord(key), static_cast<uint32_t>(col0 + c)));
+        }
+    }
+
     // r: 32 accumulator columns; nb: the matching 32 norms in shared memory; col0: base position
     // of r[0]; nvalid: real base rows among the 32; bslot: first burst slot (burst-min mode);
     // ci: see chunk_fold.  The hot path is straight-line code: the threshold test of the 32
@@ -799,6 +835,26 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             const uint32_t* hnorm = &epi_sh.norm[ab][half * kCols];
             const int hslot = sel * (kTileB / BURST) + half * (kCols / BURST);
             uint32_t ra[32], rb[32];
+            if (FOLD && MODE == kModeAppend && kCols == 64 && !a.direct && !(kDevProf && a.dbg)) {
+                // Both chunks into registers, the pass masks, and the accumulator goes back to the MMA
+                // side at once: taking the candidates out (the slow, uneven part -- a warp with three
+                // hits would otherwise hold the buffer for all sixteen) happens afterwards, from the
+                // registers, while the tensor core already refills the buffer.
+                ptx::tmem_ld_32x32(tacc, ra);
+                ptx::tmem_ld_32x32(tacc + 32, rb);
+                ptx::tmem_ld_wait(ra);
+                ptx::tmem_ld_wait(rb);
+                const int64_t rem_a = n_end - half_col0, rem_b = rem_a - 32;
+                const uint32_t ma = epi.fold_mask(ra, half_col0, rem_a >= 32 ? 32 : (rem_a > 0 ? static_cast<int>(rem_a) : 0));
+                const uint32_t mb = epi.fold_mask(rb, half_col0 + 32, rem_b >= 32 ? 32 : (rem_b > 0 ? static_cast<int>(rem_b) : 0));
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&bar_acc_empty[ab]);
+                epi.fold_extract(ra, ma, half_col0);
+                epi.fold_extract(rb, mb, half_col0 + 32);
+                epi.end_tile(hslot);
+                continue;
+            }
             const bool dbg_no_ld = kDevProf && (a.dbg & 2), dbg_no_chunk = kDevProf && (a.dbg & 3);
             if (!dbg_no_ld) ptx::tmem_ld_32x32(tacc, ra);
             // two chunks per step, the TMEM load of the next chunk in flight behind the current one
