@@ -298,6 +298,7 @@ select_topk_kernel(const uint64_t* cand, const uint32_t* counts, uint32_t n_fixe
 // reading one float4 each fall into 8 different 16-byte bank groups.
 constexpr int kRefChunk = 32;     // small, so that many warps fit an SM: the kernel lives on memory-level parallelism
 constexpr int kRefPitch = kRefChunk + 4;
+constexpr uint32_t kRefWindow = 512;   // candidate slots compacted at a time
 __global__ void __launch_bounds__(128)
 refine_f32_kernel(uint64_t* cand, const uint32_t* counts, uint32_t n_fixed, uint32_t cap, int d, int metric,
                   const float* xq, const float* xb, int q_first, int q_mod) {
@@ -311,18 +312,36 @@ refine_f32_kernel(uint64_t* cand, const uint32_t* counts, uint32_t n_fixed, uint
     const int qrow = q_mod > 0 ? (q_first + q) % q_mod : q_first + q;
     uint32_t n = counts ? counts[q] : n_fixed;
     if (n > cap) n = cap;
-    if (blockIdx.x * 128u >= n) return;
+    if (blockIdx.x * kRefWindow >= n) return;
     for (int i = threadIdx.x; i < d / 4; i += 128)
         reinterpret_cast<float4*>(qs)[i] = __ldg(reinterpret_cast<const float4*>(xq + static_cast<int64_t>(qrow) * d) + i);
     __syncthreads();
     uint64_t* row = cand + static_cast<int64_t>(q) * cap;
-    for (uint32_t i0 = (blockIdx.x * 4 + warp) * 32; i0 < n; i0 += gridDim.x * 128) {
-        const uint32_t i = i0 + lane;
-        const uint64_t c = i < n ? row[i] : kCandInvalid;
-        const bool live = c != kCandInvalid;
-        const uint32_t pos = live ? static_cast<uint32_t>(c) : 0u;
+    // The list is sparse (reserved but unused slots, see the GEMM's block reservation): a window of
+    // slots is compacted into shared memory first, so that every warp pass works on 32 live
+    // candidates.  The result goes back to the candidate's own slot: the order of compaction is free.
+    __shared__ uint32_t s_slot[kRefWindow];
+    __shared__ uint32_t s_pos[kRefWindow];
+    __shared__ uint32_t s_cnt;
+    for (uint32_t win0 = blockIdx.x * kRefWindow; win0 < n; win0 += gridDim.x * kRefWindow) {
+    if (threadIdx.x == 0) s_cnt = 0u;
+    __syncthreads();
+    const uint32_t win1 = win0 + kRefWindow < n ? win0 + kRefWindow : n;
+    for (uint32_t i = win0 + threadIdx.x; i < win1; i += 128) {
+        const uint64_t c = row[i];
+        if (c != kCandInvalid) {
+            const uint32_t j = atomicAdd(&s_cnt, 1u);
+            s_slot[j] = i;
+            s_pos[j] = static_cast<uint32_t>(c);
+        }
+    }
+    __syncthreads();
+    const uint32_t cnt = s_cnt;
+    for (uint32_t i0 = warp * 32; i0 < cnt; i0 += 128) {
+        const bool live = i0 + lane < cnt;
+        const uint32_t i = live ? s_slot[i0 + lane] : 0u;
+        const uint32_t pos = live ? s_pos[i0 + lane] : 0u;
         const uint32_t live_mask = __ballot_sync(0xffffffffu, live);
-        if (live_mask == 0) continue;
         float acc = 0.f;
         for (int ch0 = 0; ch0 < d; ch0 += kRefChunk) {
             const int w = d - ch0 < kRefChunk ? d - ch0 : kRefChunk;
@@ -374,6 +393,8 @@ refine_f32_kernel(uint64_t* cand, const uint32_t* counts, uint32_t n_fixed, uint
         }
         if (metric != kMetricL2) acc = -acc;
         if (live) row[i] = pack_cand(float_to_ord(acc), pos);
+    }
+    __syncthreads();   // the window's lists are reused
     }
 }
 
@@ -704,7 +725,7 @@ cudaError_t launch_refine_f32(uint64_t* cand, const uint32_t* counts, uint32_t n
     uint32_t per_row = counts ? cap : (n_fixed < cap ? n_fixed : cap);
     // Blocks stride over a row's candidates, so a few thousand blocks in total keep the machine
     // busy; one block per 128 candidate SLOTS would mostly launch blocks that find nothing to do.
-    int gx = static_cast<int>((per_row + 127) / 128);
+    int gx = static_cast<int>((per_row + kRefWindow - 1) / kRefWindow);
     const int want = (2048 + nq - 1) / nq;
     if (gx > want) gx = want;
     if (gx > 64) gx = 64;
