@@ -815,7 +815,7 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             epi.begin_tile(q, q_in < a.nq);
             if (!ptx::mbar_wait_bounded(&bar_acc_full[ab], aph, &abort_flag)) {
                 // leave without stranding a sibling warp at the named barrier below
-                if (!FOLD) asm volatile("bar.arrive 1, %0;" ::"n"(32 * epi_warps(KIND)) : "memory");
+                if (!FOLD && (l2 || cosm)) asm volatile("bar.arrive 1, %0;" ::"n"(32 * epi_warps(KIND)) : "memory");
                 ok = false;
                 break;
             }
@@ -824,7 +824,7 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 a.trace[(warp == 2 ? 4 : 6) * 64 + t] = clock64();
             ptx::tc_fence_after();
             const long long b0 = profiler ? clock64() : 0;
-            if (!FOLD) {
+            if (!FOLD && (l2 || cosm)) {   // inner product: no norms, and no reason to keep the warps in step
                 if (et < kTileB) epi_sh.norm[ab][et] = n0;
                 asm volatile("bar.sync 1, %0;" ::"n"(32 * epi_warps(KIND)) : "memory");   // the epilogue warps
             }
