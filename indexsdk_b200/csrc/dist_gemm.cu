@@ -32,7 +32,11 @@ constexpr int kMaxStages = 8;
 // int8 with the fp16 cosine epilogue: a kernel instantiation of its own (chosen by launch_dist_gemm from
 // GemmArgs::metric), so that the inner-product / L2 kernels carry none of its code
 constexpr int kKindI8Cos = 3;
-__host__ __device__ constexpr bool is_i8(int kind) { return kind == kKindI8 || kind == kKindI8Cos; }
+// int8 inner product: reads no norms, so its epilogue is light enough for sixteen warps of two
+// chunks (96 registers) instead of eight of four -- the eight, two per scheduler, cannot hide their
+// own instruction latency
+constexpr int kKindI8IP = 4;
+__host__ __device__ constexpr bool is_i8(int kind) { return kind == kKindI8 || kind == kKindI8Cos || kind == kKindI8IP; }
 constexpr int kStageABytes = kTileQ * kChunkBytes;               // 16 KB
 constexpr int kStageBBytes = kTileB * kChunkBytes;               // 32 KB
 constexpr int kStageBytes = kStageABytes + kStageBBytes;         // 48 KB
@@ -42,7 +46,7 @@ constexpr int kResidentMaxChunks = 4;                            // query tile k
 // epilogue is bound by shared-memory norm loads (fp16, int8); four per scheduler and a quarter
 // of the columns each for the folded bf16 kind, whose short ALU-only epilogue is latency-bound
 // and scales with the number of warps.
-__host__ __device__ constexpr int epi_warps(int kind) { return kind == kKindBF16 ? 16 : 8; }
+__host__ __device__ constexpr int epi_warps(int kind) { return (kind == kKindBF16 || kind == kKindI8IP) ? 16 : 8; }
 // + the producer warp, the MMA warp and, behind the epilogue warps, a second MMA warp and a second
 // producer warp (even and odd items have their own issuing threads and their own stage sub-ring)
 __host__ __device__ constexpr int gemm_threads(int kind) { return 64 + 32 * epi_warps(kind) + 64; }
@@ -118,7 +122,7 @@ struct EpiShared {
 //                 norms are read and "key <= tau" is the sign of D: 32 columns are tested with a
 //                 16-instruction AND tree, and the burst minimum of the key is a maximum of D.
 // NCH: 32-column chunks a thread handles per tile.
-template <typename AccT, int MODE, int BURST, bool FOLD, int NCH, bool COS = false>
+template <typename AccT, int MODE, int BURST, bool FOLD, int NCH, bool COS = false, bool IPONLY = false>
 struct RowEpilogue {
     using K = KeyOps<AccT>;
     const GemmArgs& a;
@@ -136,7 +140,7 @@ struct RowEpilogue {
     uint32_t res[NCH * (32 / BURST)];   // burst-min results of this thread's part of the tile
 
     __device__ __forceinline__ explicit RowEpilogue(const GemmArgs& a_)
-        : a(a_), q(-1), row_ok(false), l2(a_.metric == kMetricL2),
+        : a(a_), q(-1), row_ok(false), l2(!IPONLY && a_.metric == kMetricL2),
           tau(AccT(0)), tau_up(AccT(0)), tq(0.f),
           blk_q(-1), blk_next(0), blk_left(0), pre_base(0), pre_ok(false) {}
 
@@ -352,6 +356,31 @@ struct RowEpilogue {
             if (!(dv >= 0.f)) continue;   // NaN
             const float key = l2 ? fmaf(-2.f, dv, tq) : tq - dv;
             append(pack_cand(float_to_ord(key), static_cast<uint32_t>(col0 + c)));
+        }
+    }
+
+    // The same split for an inner product without folded operands and without norms (int8): bit
+    // (31 - c) = column c has key = -acc <= tau.
+    __device__ __forceinline__ uint32_t ip_mask(const uint32_t (&r)[32], int64_t col0, int nvalid) {
+        const AccT ntup = K::neg(tau_up);
+        uint32_t m0 = 0, m1 = 0;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+            m0 = __funnelshift_l(K::sign_ip(K::from_bits(r[c]), ntup), m0, 1);
+            m1 = __funnelshift_l(K::sign_ip(K::from_bits(r[16 + c]), ntup), m1, 1);
+        }
+        uint32_t mask = (m0 << 16) | (m1 & 0xFFFFu);
+        uint32_t valid = nvalid >= 32 ? 0xFFFFFFFFu : ((1u << nvalid) - 1u);
+        if (a.qmask && row_ok) valid &= mask_word(col0);
+        return row_ok ? (mask & __brev(valid)) : 0u;
+    }
+    __device__ __forceinline__ void ip_extract(const uint32_t (&r)[32], uint32_t mask, int64_t col0) {
+        while (mask) {
+            const uint32_t c = __clz(mask);
+            mask &= ~(0x80000000u >> c);
+            const AccT key = K::neg(K::from_bits(pick(r, c)));
+            if (!(key <= tau)) continue;
+            append(pack_cand(K::ord(key), static_cast<uint32_t>(col0 + c)));
         }
     }
 
@@ -780,8 +809,8 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         const int row_in_tile = quarter * 32 + lane;
         const int et = threadIdx.x - 64;       // epilogue thread index
         constexpr int kCols = kTileB / (epi_warps(KIND) / 4);   // columns per epilogue thread
-        RowEpilogue<AccT, MODE, BURST, FOLD, kCols / 32, KIND == kKindI8Cos> epi(a);
-        const bool l2 = a.metric == kMetricL2 && !FOLD;   // FOLD: no norms to fetch
+        RowEpilogue<AccT, MODE, BURST, FOLD, kCols / 32, KIND == kKindI8Cos, KIND == kKindI8IP> epi(a);
+        const bool l2 = a.metric == kMetricL2 && !FOLD && KIND != kKindI8IP;   // FOLD, int8 inner product: no norms to fetch
         constexpr bool cosm = KIND == kKindI8Cos;
         const uint32_t* gnorm = static_cast<const uint32_t*>(a.bnorm);
         uint32_t t = 0;
@@ -835,6 +864,23 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             const uint32_t* hnorm = &epi_sh.norm[ab][half * kCols];
             const int hslot = sel * (kTileB / BURST) + half * (kCols / BURST);
             uint32_t ra[32], rb[32];
+            if (KIND == kKindI8IP && MODE == kModeAppend && kCols == 64 && !a.direct) {
+                // as below: both chunks, both masks, the accumulator back, then the candidates
+                ptx::tmem_ld_32x32(tacc, ra);
+                ptx::tmem_ld_32x32(tacc + 32, rb);
+                ptx::tmem_ld_wait(ra);
+                ptx::tmem_ld_wait(rb);
+                const int64_t rem_a = n_end - half_col0, rem_b = rem_a - 32;
+                const uint32_t ma = epi.ip_mask(ra, half_col0, rem_a >= 32 ? 32 : (rem_a > 0 ? static_cast<int>(rem_a) : 0));
+                const uint32_t mb = epi.ip_mask(rb, half_col0 + 32, rem_b >= 32 ? 32 : (rem_b > 0 ? static_cast<int>(rem_b) : 0));
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&bar_acc_empty[ab]);
+                epi.ip_extract(ra, ma, half_col0);
+                epi.ip_extract(rb, mb, half_col0 + 32);
+                epi.end_tile(hslot);
+                continue;
+            }
             if (FOLD && MODE == kModeAppend && kCols == 64 && !a.direct && !(kDevProf && a.dbg)) {
                 // Both chunks into registers, the pass masks, and the accumulator goes back to the MMA
                 // side at once: taking the candidates out (the slow, uneven part -- a warp with three
@@ -955,7 +1001,7 @@ dist_gemm_simt_kernel(const GemmArgs a) {
     const bool l2 = a.metric == kMetricL2;
     constexpr bool cosm = KIND == kKindI8Cos;
     const uint32_t* gnorm = static_cast<const uint32_t*>(a.bnorm);
-    RowEpilogue<AccT, MODE, BURST, KIND == kKindBF16, kTileB / 32, KIND == kKindI8Cos> epi(a);
+    RowEpilogue<AccT, MODE, BURST, KIND == kKindBF16, kTileB / 32, KIND == kKindI8Cos, KIND == kKindI8IP> epi(a);
     ItemCursor cur(range);
     for (int64_t i = 0; i < range.count; ++i, cur.next()) {
         const int qb = cur.qb;
@@ -1061,8 +1107,9 @@ cudaError_t launch_dist_gemm(const GemmLaunch& L, const GemmArgs& a, const CUten
         case kKindF16: return launch_kind<kKindF16>(L, a, mapA, mapB, stream);
         case kKindBF16: return launch_kind<kKindBF16>(L, a, mapA, mapB, stream);
         case kKindI8:
-            return a.metric == kMetricCos ? launch_kind<kKindI8Cos>(L, a, mapA, mapB, stream)
-                                          : launch_kind<kKindI8>(L, a, mapA, mapB, stream);
+            return a.metric == kMetricCos  ? launch_kind<kKindI8Cos>(L, a, mapA, mapB, stream)
+                   : a.metric == kMetricIP ? launch_kind<kKindI8IP>(L, a, mapA, mapB, stream)
+                                           : launch_kind<kKindI8>(L, a, mapA, mapB, stream);
         default: return cudaErrorInvalidValue;
     }
 }
