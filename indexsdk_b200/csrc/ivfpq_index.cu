@@ -604,7 +604,7 @@ __device__ __forceinline__ void scan_warp_probes(const ScanArgs& a, Feed& feed, 
     const uint4* codes4 = reinterpret_cast<const uint4*>(a.codes);
     uint32_t begin = 0, end = 0, v0 = 0;
     float base = 0.f;
-    constexpr int U = 2;                 // 32-vector groups per chunk
+    constexpr int U = MT >= 4 ? 1 : 2;   // 32-vector groups per chunk (wide codes: one, the chunk must stay in registers)
     // One chunk in flight: codes, the per-vector term and where it came from.  A padding slot
     // carries NaN in its term (residual encoding: stored in t2; raw encoding: from the list's end),
     // which fails every comparison, so the lookups need no per-lane bounds logic; a group that does
@@ -728,7 +728,8 @@ struct RowSum128 {
 // NT threads per CTA: 128, or 256 when the table (MT x 32 KB) leaves room for only one or two CTAs
 // per SM and the warps of a CTA are what hides the load latency.
 template <int MT, int KPT, int NT>
-__global__ void __launch_bounds__(NT, (MT == 1 && KPT <= 2) ? 6 : 1)
+// (M = 48: a 96 KB table, two CTAs per SM if each keeps to 128 registers)
+__global__ void __launch_bounds__(NT, (MT == 1 && KPT <= 2) ? 6 : ((MT == 3 && KPT <= 8) ? 2 : 1))
 ivfpq_fast_scan_kernel(const ScanArgs a) {
     extern __shared__ __align__(16) uint8_t scan_smem[];
     float* lut = reinterpret_cast<float*>(scan_smem);   // [MT][256][32]
