@@ -350,10 +350,12 @@ class IvfpqWorkload(Workload):
                              list_len_size_biased_mean=float((lens * lens).sum() / max(lens.sum(), 1)))
 
     def roofline(self, stats, steps, peaks):
-        ms = stats["stage_ms"]["scan"] / max(1, stats["stage_launches"]["scan"])
+        # the scan stage of ONE search: the filter scan and, where queries were left unverified (raw
+        # encoding), the second filter pass -- all of it is charged to the algorithmic bytes of one scan
+        ms = stats["stage_ms"]["scan"] / max(1, steps)
         alg = self.units_bytes_per_query * self.nq / max(1, self.world_size)
         ach = alg / (ms * 1e-3) / 1e9 if ms > 0 else None
-        visited = stats["scan_codes_delta"] * self.M / max(1, stats["stage_launches"]["scan"])
+        visited = stats["scan_codes_delta"] * self.M / max(1, steps)
         kern = "ivfpq_scan_persist_kernel" if self.M == 16 else "ivfpq_fast_scan_kernel"
         return dict(bound="hbm", kernel=kern, achieved=ach, peak=peaks["hbm"], unit="GB/s",
                     frac=(ach / peaks["hbm"]) if ach else None, peak_source=peaks["source"],
