@@ -343,6 +343,62 @@ refine_f32_kernel(uint64_t* cand, const uint32_t* counts, uint32_t n_fixed, uint
         const uint32_t pos = live ? s_pos[i0 + lane] : 0u;
         const uint32_t live_mask = __ballot_sync(0xffffffffu, live);
         float acc = 0.f;
+        if (d % kRefChunk == 0) {
+            // Whole chunks only: a lane stages the same 8 rows in every chunk, so their addresses are
+            // formed once per pass, and the loads of the next chunk are in flight while the current
+            // one is accumulated from shared memory.
+            const int j = lane & 7;
+            const float4* src[8];
+            uint32_t okm = 0;
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+                const int r = it * 4 + (lane >> 3);
+                const uint32_t pr = __shfl_sync(0xffffffffu, pos, r);
+                src[it] = reinterpret_cast<const float4*>(xb + static_cast<int64_t>(pr) * d) + j;
+                okm |= ((live_mask >> r) & 1u) << it;   // rows of unused slots are neither fetched nor read
+            }
+            float4* dst = reinterpret_cast<float4*>(rows + (lane >> 3) * kRefPitch + 4 * j);
+            const float4* mine = reinterpret_cast<const float4*>(rows + lane * kRefPitch);
+            float4 v[8];
+#pragma unroll
+            for (int it = 0; it < 8; ++it)
+                if ((okm >> it) & 1u) v[it] = __ldg(src[it]);
+            for (int ch0 = 0; ch0 < d; ch0 += kRefChunk) {
+#pragma unroll
+                for (int it = 0; it < 8; ++it)
+                    if ((okm >> it) & 1u) dst[it * kRefPitch] = v[it];   // 4 rows further per step
+                __syncwarp();
+                if (ch0 + kRefChunk < d) {
+#pragma unroll
+                    for (int it = 0; it < 8; ++it)
+                        if ((okm >> it) & 1u) v[it] = __ldg(src[it] + (ch0 + kRefChunk) / 4);
+                }
+                const float4* qv = reinterpret_cast<const float4*>(qs + ch0);
+                if (live) {
+                    if (metric == kMetricL2) {
+#pragma unroll
+                        for (int jj = 0; jj < kRefChunk / 4; ++jj) {
+                            const float4 a = qv[jj], b = mine[jj];
+                            float t;
+                            t = a.x - b.x; acc = fmaf(t, t, acc);
+                            t = a.y - b.y; acc = fmaf(t, t, acc);
+                            t = a.z - b.z; acc = fmaf(t, t, acc);
+                            t = a.w - b.w; acc = fmaf(t, t, acc);
+                        }
+                    } else {
+#pragma unroll
+                        for (int jj = 0; jj < kRefChunk / 4; ++jj) {
+                            const float4 a = qv[jj], b = mine[jj];
+                            acc = fmaf(a.x, b.x, acc);
+                            acc = fmaf(a.y, b.y, acc);
+                            acc = fmaf(a.z, b.z, acc);
+                            acc = fmaf(a.w, b.w, acc);
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+        } else
         for (int ch0 = 0; ch0 < d; ch0 += kRefChunk) {
             const int w = d - ch0 < kRefChunk ? d - ch0 : kRefChunk;
             const int lpr = w >> 2;                                  // float4 pieces per row
