@@ -110,6 +110,33 @@ def test_fp16_mode_vs_oracle(b200, metric, n, nq, k, d):
     np.testing.assert_array_equal(ix.get_base(0, 3), xb[:3].astype(np.float16).view(np.uint16))
 
 
+@pytest.mark.parametrize("d", [144, 160])
+def test_fp32_operand_layouts_grow_and_remove(b200, d):
+    """d = 144 is the widest index whose operand copy is kept in the packed (tile image) layout,
+    d = 160 the first that keeps rows: both must survive growth of the buffers over several adds
+    that end inside a tile, and the removal of rows (which moves the last row into the gap)."""
+    n_parts = [300, 70000, 5, 1111]
+    n = sum(n_parts)
+    xb = datasets.gaussian(n, d, seed=31)
+    xq = datasets.gaussian(21, d, seed=32)
+    ids = (np.arange(n) * 3 + 1).astype(np.int64)
+    ix = b200.IndexFlat(d, L2)
+    o = 0
+    for m in n_parts:
+        ix.add_with_ids(xb[o:o + m], ids[o:o + m])
+        o += m
+        D, I = ix.search(xq, 10)
+        Dr, Ir = oracle.flat_search(L2, xb[:o], xq, 10, labels=ids[:o])
+        assert_exact(D, I, Dr, Ir)
+    gone = ids[[0, 255, 256, 300, 70299, n - 1]]
+    assert ix.remove_ids(gone) == 6
+    base_now, ids_now = ix.get_base(), ix.get_ids()
+    D, I = ix.search(xq, 50)
+    Dr, Ir = oracle.flat_search(L2, base_now, xq, 50, labels=ids_now)
+    assert_exact(D, I, Dr, Ir)
+    assert not set(gone.tolist()) & set(I.ravel().tolist())
+
+
 def test_self_hit_rank_one(b200):
     """The property the reference's device test asserts (TestAscendIndexFlat.cpp:117-123)."""
     xb = datasets.gaussian(20000, 128, seed=9)
