@@ -36,7 +36,9 @@ constexpr int kKindI8Cos = 3;
 // chunks (96 registers) instead of eight of four -- the eight, two per scheduler, cannot hide their
 // own instruction latency
 constexpr int kKindI8IP = 4;
+constexpr int kKindF16IP = 5;   // the same for fp16 operands
 __host__ __device__ constexpr bool is_i8(int kind) { return kind == kKindI8 || kind == kKindI8Cos || kind == kKindI8IP; }
+__host__ __device__ constexpr bool ip_only(int kind) { return kind == kKindI8IP || kind == kKindF16IP; }
 constexpr int kStageABytes = kTileQ * kChunkBytes;               // 16 KB
 constexpr int kStageBBytes = kTileB * kChunkBytes;               // 32 KB
 constexpr int kStageBytes = kStageABytes + kStageBBytes;         // 48 KB
@@ -46,7 +48,7 @@ constexpr int kResidentMaxChunks = 4;                            // query tile k
 // epilogue is bound by shared-memory norm loads (fp16, int8); four per scheduler and a quarter
 // of the columns each for the folded bf16 kind, whose short ALU-only epilogue is latency-bound
 // and scales with the number of warps.
-__host__ __device__ constexpr int epi_warps(int kind) { return (kind == kKindBF16 || kind == kKindI8IP) ? 16 : 8; }
+__host__ __device__ constexpr int epi_warps(int kind) { return (kind == kKindBF16 || ip_only(kind)) ? 16 : 8; }
 // + the producer warp, the MMA warp and, behind the epilogue warps, a second MMA warp and a second
 // producer warp (even and odd items have their own issuing threads and their own stage sub-ring)
 __host__ __device__ constexpr int gemm_threads(int kind) { return 64 + 32 * epi_warps(kind) + 64; }
@@ -809,8 +811,8 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         const int row_in_tile = quarter * 32 + lane;
         const int et = threadIdx.x - 64;       // epilogue thread index
         constexpr int kCols = kTileB / (epi_warps(KIND) / 4);   // columns per epilogue thread
-        RowEpilogue<AccT, MODE, BURST, FOLD, kCols / 32, KIND == kKindI8Cos, KIND == kKindI8IP> epi(a);
-        const bool l2 = a.metric == kMetricL2 && !FOLD && KIND != kKindI8IP;   // FOLD, int8 inner product: no norms to fetch
+        RowEpilogue<AccT, MODE, BURST, FOLD, kCols / 32, KIND == kKindI8Cos, ip_only(KIND)> epi(a);
+        const bool l2 = a.metric == kMetricL2 && !FOLD && !ip_only(KIND);   // FOLD, plain inner products: no norms to fetch
         constexpr bool cosm = KIND == kKindI8Cos;
         const uint32_t* gnorm = static_cast<const uint32_t*>(a.bnorm);
         uint32_t t = 0;
@@ -864,7 +866,7 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             const uint32_t* hnorm = &epi_sh.norm[ab][half * kCols];
             const int hslot = sel * (kTileB / BURST) + half * (kCols / BURST);
             uint32_t ra[32], rb[32];
-            if (KIND == kKindI8IP && MODE == kModeAppend && kCols == 64 && !a.direct) {
+            if (ip_only(KIND) && MODE == kModeAppend && kCols == 64 && !a.direct) {
                 // as below: both chunks, both masks, the accumulator back, then the candidates
                 ptx::tmem_ld_32x32(tacc, ra);
                 ptx::tmem_ld_32x32(tacc + 32, rb);
@@ -1001,7 +1003,7 @@ dist_gemm_simt_kernel(const GemmArgs a) {
     const bool l2 = a.metric == kMetricL2;
     constexpr bool cosm = KIND == kKindI8Cos;
     const uint32_t* gnorm = static_cast<const uint32_t*>(a.bnorm);
-    RowEpilogue<AccT, MODE, BURST, KIND == kKindBF16, kTileB / 32, KIND == kKindI8Cos, KIND == kKindI8IP> epi(a);
+    RowEpilogue<AccT, MODE, BURST, KIND == kKindBF16, kTileB / 32, KIND == kKindI8Cos, ip_only(KIND)> epi(a);
     ItemCursor cur(range);
     for (int64_t i = 0; i < range.count; ++i, cur.next()) {
         const int qb = cur.qb;
@@ -1104,7 +1106,9 @@ cudaError_t launch_kind(const GemmLaunch& L, const GemmArgs& a, const CUtensorMa
 cudaError_t launch_dist_gemm(const GemmLaunch& L, const GemmArgs& a, const CUtensorMap* mapA, const CUtensorMap* mapB,
                              cudaStream_t stream) {
     switch (L.kind) {
-        case kKindF16: return launch_kind<kKindF16>(L, a, mapA, mapB, stream);
+        case kKindF16:
+            return a.metric == kMetricIP ? launch_kind<kKindF16IP>(L, a, mapA, mapB, stream)
+                                         : launch_kind<kKindF16>(L, a, mapA, mapB, stream);
         case kKindBF16: return launch_kind<kKindBF16>(L, a, mapA, mapB, stream);
         case kKindI8:
             return a.metric == kMetricCos  ? launch_kind<kKindI8Cos>(L, a, mapA, mapB, stream)
