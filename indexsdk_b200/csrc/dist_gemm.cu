@@ -37,8 +37,17 @@ constexpr int kKindI8Cos = 3;
 // own instruction latency
 constexpr int kKindI8IP = 4;
 constexpr int kKindF16IP = 5;   // the same for fp16 operands
-__host__ __device__ constexpr bool is_i8(int kind) { return kind == kKindI8 || kind == kKindI8Cos || kind == kKindI8IP; }
+constexpr int kKindI8L2 = 6;    // sixteen-warp L2 kinds, see l2_global
+constexpr int kKindF16L2 = 7;
+__host__ __device__ constexpr bool is_i8(int kind) {
+    return kind == kKindI8 || kind == kKindI8Cos || kind == kKindI8IP || kind == kKindI8L2;
+}
 __host__ __device__ constexpr bool ip_only(int kind) { return kind == kKindI8IP || kind == kKindF16IP; }
+// L2 with sixteen epilogue warps as well: the norms are not staged in shared memory (which costs a
+// barrier per item and 32 registers per chunk) but read from global memory where they are used --
+// the 32 lanes of a warp want the same 32 norms, so a load is one broadcast that hits L1 after the
+// first warp of the CTA has asked for it.
+__host__ __device__ constexpr bool l2_global(int kind) { return kind == kKindI8L2 || kind == kKindF16L2; }
 constexpr int kStageABytes = kTileQ * kChunkBytes;               // 16 KB
 constexpr int kStageBBytes = kTileB * kChunkBytes;               // 32 KB
 constexpr int kStageBytes = kStageABytes + kStageBBytes;         // 48 KB
@@ -48,7 +57,7 @@ constexpr int kResidentMaxChunks = 4;                            // query tile k
 // epilogue is bound by shared-memory norm loads (fp16, int8); four per scheduler and a quarter
 // of the columns each for the folded bf16 kind, whose short ALU-only epilogue is latency-bound
 // and scales with the number of warps.
-__host__ __device__ constexpr int epi_warps(int kind) { return (kind == kKindBF16 || ip_only(kind)) ? 16 : 8; }
+__host__ __device__ constexpr int epi_warps(int kind) { return (kind == kKindBF16 || ip_only(kind) || l2_global(kind)) ? 16 : 8; }
 // + the producer warp, the MMA warp and, behind the epilogue warps, a second MMA warp and a second
 // producer warp (even and odd items have their own issuing threads and their own stage sub-ring)
 __host__ __device__ constexpr int gemm_threads(int kind) { return 64 + 32 * epi_warps(kind) + 64; }
@@ -386,6 +395,37 @@ struct RowEpilogue {
         }
     }
 
+    // ... and for L2 with the norms taken from global memory (gn: the norms of the chunk's 32 columns)
+    __device__ __forceinline__ uint32_t l2_mask(const uint32_t (&r)[32], const uint32_t* gn, int64_t col0, int nvalid) {
+        uint32_t m0 = 0, m1 = 0;
+        const uint4* g4 = reinterpret_cast<const uint4*>(gn);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const uint4 na = __ldg(g4 + g), nb4 = __ldg(g4 + 4 + g);
+            m0 = __funnelshift_l(K::sign_l2(K::from_bits(r[4 * g + 0]), K::from_bits(na.x), tau_up), m0, 1);
+            m0 = __funnelshift_l(K::sign_l2(K::from_bits(r[4 * g + 1]), K::from_bits(na.y), tau_up), m0, 1);
+            m0 = __funnelshift_l(K::sign_l2(K::from_bits(r[4 * g + 2]), K::from_bits(na.z), tau_up), m0, 1);
+            m0 = __funnelshift_l(K::sign_l2(K::from_bits(r[4 * g + 3]), K::from_bits(na.w), tau_up), m0, 1);
+            m1 = __funnelshift_l(K::sign_l2(K::from_bits(r[16 + 4 * g + 0]), K::from_bits(nb4.x), tau_up), m1, 1);
+            m1 = __funnelshift_l(K::sign_l2(K::from_bits(r[16 + 4 * g + 1]), K::from_bits(nb4.y), tau_up), m1, 1);
+            m1 = __funnelshift_l(K::sign_l2(K::from_bits(r[16 + 4 * g + 2]), K::from_bits(nb4.z), tau_up), m1, 1);
+            m1 = __funnelshift_l(K::sign_l2(K::from_bits(r[16 + 4 * g + 3]), K::from_bits(nb4.w), tau_up), m1, 1);
+        }
+        uint32_t mask = (m0 << 16) | (m1 & 0xFFFFu);
+        uint32_t valid = nvalid >= 32 ? 0xFFFFFFFFu : ((1u << nvalid) - 1u);
+        if (a.qmask && row_ok) valid &= mask_word(col0);
+        return row_ok ? (mask & __brev(valid)) : 0u;
+    }
+    __device__ __forceinline__ void l2_extract(const uint32_t (&r)[32], uint32_t mask, int64_t col0, const uint32_t* gn) {
+        while (mask) {
+            const uint32_t c = __clz(mask);
+            mask &= ~(0x80000000u >> c);
+            const AccT key = K::key(K::from_bits(pick(r, c)), K::from_bits(__ldg(gn + c)), true);
+            if (!(key <= tau)) continue;   // NaN
+            append(pack_cand(K::ord(key), static_cast<uint32_t>(col0 + c)));
+        }
+    }
+
     // r: 32 accumulator columns; nb: the matching 32 norms in shared memory; col0: base position
     // of r[0]; nvalid: real base rows among the 32; bslot: first burst slot (burst-min mode);
     // ci: see chunk_fold.  The hot path is straight-line code: the threshold test of the 32
@@ -415,54 +455,56 @@ struct RowEpilogue {
 
     __device__ __forceinline__ void chunk_keys(const uint32_t (&r)[32], const uint32_t* nb, int64_t col0, int nvalid,
                                                int bslot, int ci, int64_t cbase) {
-        uint32_t bnb[32];
-        if (l2) {
-            const uint4* p = reinterpret_cast<const uint4*>(nb);
+        // The norms (L2) are taken eight at a time, next to their use: nb may point into shared or
+        // into global memory, and 32 of them held in registers beside the 32 accumulator words are
+        // what a 96-register kernel cannot afford.
+        const uint4* np4 = reinterpret_cast<const uint4*>(nb);
+        auto norms8 = [&](int s8, uint32_t (&n8)[8]) {
+            if (l2) {
+                const uint4 x = np4[2 * s8], y = np4[2 * s8 + 1];
+                n8[0] = x.x; n8[1] = x.y; n8[2] = x.z; n8[3] = x.w;
+                n8[4] = y.x; n8[5] = y.y; n8[6] = y.z; n8[7] = y.w;
+            } else {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const uint4 v = p[j];
-                bnb[4 * j + 0] = v.x;
-                bnb[4 * j + 1] = v.y;
-                bnb[4 * j + 2] = v.z;
-                bnb[4 * j + 3] = v.w;
+                for (int j = 0; j < 8; ++j) n8[j] = 0u;   // +0.0f / 0
             }
-        } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) bnb[j] = 0u;   // +0.0f / 0
-        }
+        };
         uint32_t valid = nvalid >= 32 ? 0xFFFFFFFFu : ((1u << nvalid) - 1u);
         if (a.qmask) valid &= mask_word(col0);
         if (MODE == kModeBurstMin) {
-            constexpr int NB = 32 / BURST;
             uint32_t* dst = a.mins + static_cast<int64_t>(q) * a.mins_stride + bslot;
+            const bool full = valid == 0xFFFFFFFFu;
+            AccT m[4] = {K::worst(), K::worst(), K::worst(), K::worst()};   // independent chains
 #pragma unroll
-            for (int b = 0; b < NB; ++b) {
-                AccT m[4] = {K::worst(), K::worst(), K::worst(), K::worst()};   // independent chains
-                if (valid == 0xFFFFFFFFu) {
+            for (int s8 = 0; s8 < 4; ++s8) {
+                uint32_t n8[8];
+                norms8(s8, n8);
 #pragma unroll
-                    for (int j = 0; j < BURST; ++j) {
-                        const int c = b * BURST + j;
-                        const AccT key = K::key(K::from_bits(r[c]), K::from_bits(bnb[c]), l2);
-                        m[j & 3] = key < m[j & 3] ? key : m[j & 3];
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < BURST; ++j) {
-                        const int c = b * BURST + j;
-                        const AccT key = K::key(K::from_bits(r[c]), K::from_bits(bnb[c]), l2);
-                        if ((valid >> c) & 1u) m[j & 3] = key < m[j & 3] ? key : m[j & 3];
-                    }
+                for (int j = 0; j < 8; ++j) {
+                    const int c = s8 * 8 + j;
+                    const AccT key = K::key(K::from_bits(r[c]), K::from_bits(n8[j]), l2);
+                    if (full || ((valid >> c) & 1u)) m[j & 3] = key < m[j & 3] ? key : m[j & 3];
                 }
-                const AccT ma = m[0] < m[1] ? m[0] : m[1], mb = m[2] < m[3] ? m[2] : m[3];
-                dst[b] = K::ord(ma < mb ? ma : mb);
+                if (BURST == 8 || s8 == 3) {   // a burst of 8 ends with every group, a burst of 32 with the last
+                    const AccT ma = m[0] < m[1] ? m[0] : m[1], mb = m[2] < m[3] ? m[2] : m[3];
+                    dst[BURST == 8 ? s8 : 0] = K::ord(ma < mb ? ma : mb);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) m[i] = K::worst();
+                }
             }
         } else if (a.direct) {
             uint64_t* crow = a.cand + static_cast<int64_t>(q) * a.cap + (col0 - cbase);
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                const AccT key = K::key(K::from_bits(r[c]), K::from_bits(bnb[c]), l2);
-                // NaN keys are left at the buffer's "invalid" fill
-                if (((valid >> c) & 1u) && key <= tau) crow[c] = pack_cand(K::ord(key), static_cast<uint32_t>(col0 + c));
+            for (int s8 = 0; s8 < 4; ++s8) {
+                uint32_t n8[8];
+                norms8(s8, n8);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int c = s8 * 8 + j;
+                    const AccT key = K::key(K::from_bits(r[c]), K::from_bits(n8[j]), l2);
+                    // NaN keys are left at the buffer's "invalid" fill
+                    if (((valid >> c) & 1u) && key <= tau) crow[c] = pack_cand(K::ord(key), static_cast<uint32_t>(col0 + c));
+                }
             }
         } else {
             // bit (31 - c) of mask = "column c passes": the sign of key - above(tau), shifted in
@@ -470,9 +512,15 @@ struct RowEpilogue {
             uint32_t m0 = 0, m1 = 0;
             if (l2) {
 #pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                    m0 = __funnelshift_l(K::sign_l2(K::from_bits(r[c]), K::from_bits(bnb[c]), tau_up), m0, 1);
-                    m1 = __funnelshift_l(K::sign_l2(K::from_bits(r[16 + c]), K::from_bits(bnb[16 + c]), tau_up), m1, 1);
+                for (int s8 = 0; s8 < 2; ++s8) {
+                    uint32_t na[8], nc[8];
+                    norms8(s8, na);
+                    norms8(s8 + 2, nc);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        m0 = __funnelshift_l(K::sign_l2(K::from_bits(r[s8 * 8 + j]), K::from_bits(na[j]), tau_up), m0, 1);
+                        m1 = __funnelshift_l(K::sign_l2(K::from_bits(r[16 + s8 * 8 + j]), K::from_bits(nc[j]), tau_up), m1, 1);
+                    }
                 }
             } else {
                 const AccT ntup = K::neg(tau_up);
@@ -812,7 +860,8 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         const int et = threadIdx.x - 64;       // epilogue thread index
         constexpr int kCols = kTileB / (epi_warps(KIND) / 4);   // columns per epilogue thread
         RowEpilogue<AccT, MODE, BURST, FOLD, kCols / 32, KIND == kKindI8Cos, ip_only(KIND)> epi(a);
-        const bool l2 = a.metric == kMetricL2 && !FOLD && !ip_only(KIND);   // FOLD, plain inner products: no norms to fetch
+        // FOLD, plain inner products: no norms; sixteen-warp L2: norms read where they are used
+        const bool l2 = a.metric == kMetricL2 && !FOLD && !ip_only(KIND) && !l2_global(KIND);
         constexpr bool cosm = KIND == kKindI8Cos;
         const uint32_t* gnorm = static_cast<const uint32_t*>(a.bnorm);
         uint32_t t = 0;
@@ -863,7 +912,8 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             const uint32_t tacc =
                 tmem_base + ab * kTileB + half * kCols + (static_cast<uint32_t>(quarter * 32) << 16);
             const int64_t half_col0 = tile_col0 + half * kCols;
-            const uint32_t* hnorm = &epi_sh.norm[ab][half * kCols];
+            // sixteen-warp L2: the generic chunk code (sample pass, direct mode) reads the norms from global memory too
+            const uint32_t* hnorm = l2_global(KIND) ? gnorm + tile_col0 + half * kCols : &epi_sh.norm[ab][half * kCols];
             const int hslot = sel * (kTileB / BURST) + half * (kCols / BURST);
             uint32_t ra[32], rb[32];
             if (ip_only(KIND) && MODE == kModeAppend && kCols == 64 && !a.direct) {
@@ -880,6 +930,23 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 if (lane == 0) ptx::mbar_arrive(&bar_acc_empty[ab]);
                 epi.ip_extract(ra, ma, half_col0);
                 epi.ip_extract(rb, mb, half_col0 + 32);
+                epi.end_tile(hslot);
+                continue;
+            }
+            if (l2_global(KIND) && MODE == kModeAppend && kCols == 64 && !a.direct) {
+                ptx::tmem_ld_32x32(tacc, ra);
+                ptx::tmem_ld_32x32(tacc + 32, rb);
+                ptx::tmem_ld_wait(ra);
+                ptx::tmem_ld_wait(rb);
+                const uint32_t* gna = gnorm + half_col0;
+                const int64_t rem_a = n_end - half_col0, rem_b = rem_a - 32;
+                const uint32_t ma = epi.l2_mask(ra, gna, half_col0, rem_a >= 32 ? 32 : (rem_a > 0 ? static_cast<int>(rem_a) : 0));
+                const uint32_t mb = epi.l2_mask(rb, gna + 32, half_col0 + 32, rem_b >= 32 ? 32 : (rem_b > 0 ? static_cast<int>(rem_b) : 0));
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&bar_acc_empty[ab]);
+                epi.l2_extract(ra, ma, half_col0, gna);
+                epi.l2_extract(rb, mb, half_col0 + 32, gna + 32);
                 epi.end_tile(hslot);
                 continue;
             }
@@ -1108,12 +1175,12 @@ cudaError_t launch_dist_gemm(const GemmLaunch& L, const GemmArgs& a, const CUten
     switch (L.kind) {
         case kKindF16:
             return a.metric == kMetricIP ? launch_kind<kKindF16IP>(L, a, mapA, mapB, stream)
-                                         : launch_kind<kKindF16>(L, a, mapA, mapB, stream);
+                                         : launch_kind<kKindF16L2>(L, a, mapA, mapB, stream);
         case kKindBF16: return launch_kind<kKindBF16>(L, a, mapA, mapB, stream);
         case kKindI8:
             return a.metric == kMetricCos  ? launch_kind<kKindI8Cos>(L, a, mapA, mapB, stream)
                    : a.metric == kMetricIP ? launch_kind<kKindI8IP>(L, a, mapA, mapB, stream)
-                                           : launch_kind<kKindI8>(L, a, mapA, mapB, stream);
+                                           : launch_kind<kKindI8L2>(L, a, mapA, mapB, stream);
         default: return cudaErrorInvalidValue;
     }
 }
