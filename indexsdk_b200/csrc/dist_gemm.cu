@@ -57,7 +57,9 @@ constexpr int kResidentMaxChunks = 4;                            // query tile k
 // epilogue is bound by shared-memory norm loads (fp16, int8); four per scheduler and a quarter
 // of the columns each for the folded bf16 kind, whose short ALU-only epilogue is latency-bound
 // and scales with the number of warps.
-__host__ __device__ constexpr int epi_warps(int kind) { return (kind == kKindBF16 || ip_only(kind) || l2_global(kind)) ? 16 : 8; }
+__host__ __device__ constexpr int epi_warps(int kind) {
+    return (kind == kKindBF16 || ip_only(kind) || l2_global(kind) || kind == kKindI8Cos) ? 16 : 8;
+}
 // + the producer warp, the MMA warp and, behind the epilogue warps, a second MMA warp and a second
 // producer warp (even and odd items have their own issuing threads and their own stage sub-ring)
 __host__ __device__ constexpr int gemm_threads(int kind) { return 64 + 32 * epi_warps(kind) + 64; }
@@ -439,18 +441,20 @@ struct RowEpilogue {
             return;
         }
         if (!row_ok) return;
-        if (cosm) {
-            // nb holds the base rows' fp16 reciprocal norms; the accumulators become ordered scores in
-            // place, and from here on they are treated as inner products
-#pragma unroll
-            for (int c = 0; c < 32; c += 2) {
-                int32_t s0, s1;
-                cos16_pair(static_cast<int32_t>(r[c]), static_cast<int32_t>(r[c + 1]), nb[c], nb[c + 1], rq2, s0, s1);
-                r[c] = static_cast<uint32_t>(s0);
-                r[c + 1] = static_cast<uint32_t>(s1);
-            }
-        }
+        if (cosm) cos_scores(r, nb);
         chunk_keys(r, nb, col0, nvalid, bslot, ci, cbase);
+    }
+
+    // nb holds the base rows' fp16 reciprocal norms; the accumulators become ordered scores in place,
+    // and from here on they are treated as inner products
+    __device__ __forceinline__ void cos_scores(uint32_t (&r)[32], const uint32_t* nb) const {
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+            int32_t s0, s1;
+            cos16_pair(static_cast<int32_t>(r[c]), static_cast<int32_t>(r[c + 1]), nb[c], nb[c + 1], rq2, s0, s1);
+            r[c] = static_cast<uint32_t>(s0);
+            r[c + 1] = static_cast<uint32_t>(s1);
+        }
     }
 
     __device__ __forceinline__ void chunk_keys(const uint32_t (&r)[32], const uint32_t* nb, int64_t col0, int nvalid,
@@ -916,6 +920,27 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             const uint32_t* hnorm = l2_global(KIND) ? gnorm + tile_col0 + half * kCols : &epi_sh.norm[ab][half * kCols];
             const int hslot = sel * (kTileB / BURST) + half * (kCols / BURST);
             uint32_t ra[32], rb[32];
+            if (KIND == kKindI8Cos && MODE == kModeAppend && kCols == 64 && !a.direct) {
+                // cosine: the accumulators of both chunks become ordered fp16 scores in place (the
+                // reciprocal norms staged above are read here, before the buffer goes back), and from
+                // there on they are inner products
+                ptx::tmem_ld_32x32(tacc, ra);
+                ptx::tmem_ld_32x32(tacc + 32, rb);
+                ptx::tmem_ld_wait(ra);
+                ptx::tmem_ld_wait(rb);
+                epi.cos_scores(ra, hnorm);
+                epi.cos_scores(rb, hnorm + 32);
+                const int64_t rem_a = n_end - half_col0, rem_b = rem_a - 32;
+                const uint32_t ma = epi.ip_mask(ra, half_col0, rem_a >= 32 ? 32 : (rem_a > 0 ? static_cast<int>(rem_a) : 0));
+                const uint32_t mb = epi.ip_mask(rb, half_col0 + 32, rem_b >= 32 ? 32 : (rem_b > 0 ? static_cast<int>(rem_b) : 0));
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&bar_acc_empty[ab]);
+                epi.ip_extract(ra, ma, half_col0);
+                epi.ip_extract(rb, mb, half_col0 + 32);
+                epi.end_tile(hslot);
+                continue;
+            }
             if (ip_only(KIND) && MODE == kModeAppend && kCols == 64 && !a.direct) {
                 // as below: both chunks, both masks, the accumulator back, then the candidates
                 ptx::tmem_ld_32x32(tacc, ra);
