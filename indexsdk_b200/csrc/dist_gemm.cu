@@ -113,7 +113,6 @@ struct KeyOps<int32_t> {
     static __device__ __forceinline__ int32_t neg(int32_t v) { return -v; }
 };
 
-constexpr uint32_t kNoTmem = 0xFFFFFFFFu;   // chunk(): the accumulator columns cannot be re-read from TMEM
 constexpr uint32_t kCandBlock = 8;   // candidate slots a thread reserves with one atomic
 
 // Shared-memory side of the epilogue: the tile's base norms, double-buffered with the TMEM
@@ -237,8 +236,7 @@ struct RowEpilogue {
 
     // Folded operands: r holds D for 32 columns.
     // ci: index of the chunk inside this thread's part of the tile (a constant after unrolling)
-    __device__ __forceinline__ void chunk_fold(const uint32_t (&r)[32], int64_t col0, int nvalid, int ci, int64_t cbase,
-                                               uint32_t tchunk) {
+    __device__ __forceinline__ void chunk_fold(const uint32_t (&r)[32], int64_t col0, int nvalid, int ci, int64_t cbase) {
         if (!row_ok && (MODE == kModeBurstMin || a.direct)) return;
         if (MODE == kModeBurstMin) {
             constexpr int NB = 32 / BURST;
@@ -280,59 +278,10 @@ struct RowEpilogue {
                 if (((keep >> c) & 1u) && key <= tau) crow[c] = pack_cand(float_to_ord(key), static_cast<uint32_t>(col0 + c));
             }
         } else {
-            // tchunk: TMEM address of r[0] for this warp (kNoTmem: the accumulator is not in TMEM).
-            // With it the candidates are taken out by the whole warp: a loop over the union of the
-            // lanes' hit columns, each fetched again from TMEM with a one-column load, so that a
-            // lane never indexes its 32 registers at run time and the warp never walks the loop
-            // with one lane active per trip.
-            const bool coop = tchunk != kNoTmem;
-            if (!coop && !row_ok) return;
-            uint32_t t[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) t[i] = r[2 * i] & r[2 * i + 1];
-#pragma unroll
-            for (int w = 8; w > 0; w >>= 1)
-#pragma unroll
-                for (int i = 0; i < w; ++i) t[i] &= t[i + w];
-            const bool hit = row_ok && static_cast<int32_t>(t[0]) >= 0;   // not every D negative
-            if (coop) {
-                if (!__any_sync(0xFFFFFFFFu, hit)) return;
-            } else if (!hit) {
-                return;
-            }
-            uint32_t m0 = 0, m1 = 0;                      // bit (31 - c): D of column c has its sign set
-#pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                m0 = __funnelshift_l(r[c], m0, 1);
-                m1 = __funnelshift_l(r[16 + c], m1, 1);
-            }
-            uint32_t mask = ~((m0 << 16) | (m1 & 0xFFFFu));
-            mask &= nvalid >= 32 ? 0xFFFFFFFFu : ~(0xFFFFFFFFu >> nvalid);
-            if (a.qmask && row_ok) mask &= __brev(mask_word(col0));   // column c is bit (31 - c) here, bit c in the filter
-            if (!hit) mask = 0u;
-            if (coop) {
-                uint32_t um = __reduce_or_sync(0xFFFFFFFFu, mask);
-                while (um) {
-                    const uint32_t c = __clz(um);
-                    const uint32_t bit = 0x80000000u >> c;
-                    um &= ~bit;
-                    const float dv = __uint_as_float(ptx::tmem_ld_col(tchunk + c));
-                    if ((mask & bit) && dv >= 0.f) {   // dv >= 0 is false for NaN
-                        const float key = l2 ? fmaf(-2.f, dv, tq) : tq - dv;
-                        append(pack_cand(float_to_ord(key), static_cast<uint32_t>(col0 + c)));
-                    }
-                }
-            } else {
-                while (mask) {
-                    const uint32_t c = __clz(mask);
-                    mask &= ~(0x80000000u >> c);
-                    const float dv = __uint_as_float(pick(r, c));
-                    if (!(dv >= 0.f)) continue;   // NaN
-                    // approximate key (the fp32 refinement recomputes it): D = (tau' - key) / 2 or tau' - key
-                    const float key = l2 ? fmaf(-2.f, dv, tq) : tq - dv;
-                    append(pack_cand(float_to_ord(key), static_cast<uint32_t>(col0 + c)));
-                }
-            }
+            // (the tcgen05 kernel calls fold_mask / fold_extract itself, with the accumulator handed
+            // back in between; this is the path of the CUDA-core variant)
+            const uint32_t m = fold_mask(r, col0, nvalid);
+            fold_extract(r, m, col0);
         }
     }
 
@@ -435,9 +384,9 @@ struct RowEpilogue {
     // candidate loop.
     // cbase: position of the first base row of the segment the tile belongs to (0 without segments)
     __device__ __forceinline__ void chunk(uint32_t (&r)[32], const uint32_t* nb, int64_t col0, int nvalid,
-                                          int bslot, int ci, int64_t cbase, uint32_t tchunk = kNoTmem) {
+                                          int bslot, int ci, int64_t cbase) {
         if (FOLD) {
-            chunk_fold(r, col0, nvalid, ci, cbase, tchunk);
+            chunk_fold(r, col0, nvalid, ci, cbase);
             return;
         }
         if (!row_ok) return;
@@ -1009,7 +958,7 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                     const int64_t col0 = half_col0 + c * 32;
                     const int64_t rem = n_end - col0;
                     if (!dbg_no_chunk) epi.chunk(ra, hnorm + c * 32, col0, rem >= 32 ? 32 : (rem > 0 ? static_cast<int>(rem) : 0),
-                              hslot + c * (32 / BURST), c, cbase, tacc + c * 32);
+                              hslot + c * (32 / BURST), c, cbase);
                     if (profiler) ecc += clock64() - c0;
                 }
                 const long long w1 = profiler ? clock64() : 0;
@@ -1020,7 +969,7 @@ dist_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                     const int64_t col0 = half_col0 + (c + 1) * 32;
                     const int64_t rem = n_end - col0;
                     if (!dbg_no_chunk) epi.chunk(rb, hnorm + (c + 1) * 32, col0, rem >= 32 ? 32 : (rem > 0 ? static_cast<int>(rem) : 0),
-                              hslot + (c + 1) * (32 / BURST), c + 1, cbase, tacc + (c + 1) * 32);
+                              hslot + (c + 1) * (32 / BURST), c + 1, cbase);
                 }
             };
             if (FOLD) {   // small body: unrolled, so the chunk index is a constant

@@ -1,5 +1,7 @@
 #include "flat_index.h"
 
+#include <atomic>
+
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
@@ -38,6 +40,11 @@ bool pointer_on_device(const void* p) {
 }
 
 }  // namespace
+
+uint64_t FlatIndex::next_generation() {
+    static std::atomic<uint64_t> counter{0};
+    return ++counter;
+}
 
 FlatIndex::FlatIndex(int d, int metric, int dtype, int device)
     : d_(d), metric_(metric), dtype_(dtype), device_(device) {
@@ -137,7 +144,7 @@ void FlatIndex::add(int64_t n, const void* x, bool x_is_f16, const int64_t* ids,
     }
     B200_CUDA_CHECK(cudaStreamSynchronize(stream_));
     n_ += n;
-    ++generation_;
+    generation_ = next_generation();
     map_b_valid_ = false;
 }
 
@@ -145,7 +152,7 @@ void FlatIndex::reset() {
     DeviceGuard g(device_);
     cudaStreamSynchronize(stream_);
     n_ = 0;
-    ++generation_;
+    generation_ = next_generation();
     max_norm_ = 0.f;
     cudaMemset(maxnorm_.get(), 0, sizeof(float));
     map_b_valid_ = false;
@@ -184,7 +191,7 @@ int64_t FlatIndex::remove_ids(int64_t n, const int64_t* ids) {
     }
     B200_CUDA_CHECK(cudaStreamSynchronize(stream_));
     n_ -= static_cast<int64_t>(pos.size());
-    ++generation_;
+    generation_ = next_generation();
     map_b_valid_ = false;
     return static_cast<int64_t>(pos.size());
 }

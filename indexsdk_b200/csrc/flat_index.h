@@ -170,7 +170,11 @@ private:
     int num_sms_ = 0;
     bool use_simt_ = false;
     int64_t n_ = 0, cap_rows_ = 0;
-    uint64_t generation_ = 0;
+    // Changes with every mutation; drawn from one process-wide counter, so that no two states of any
+    // two indexes share a value (a cache keyed on (address, generation) must not mistake a new index
+    // that the allocator placed where a destroyed one lived for the old one).
+    static uint64_t next_generation();
+    uint64_t generation_ = next_generation();
     int64_t next_auto_id_ = 0;
     cudaStream_t stream_ = nullptr;
 

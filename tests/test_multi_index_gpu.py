@@ -166,3 +166,29 @@ def test_many_small_indexes_one_pass(b200, kind):
     else:
         Dr5, Ir5 = oracle.flat_search(metric, np.concatenate([xb5, extra]), xq, k, labels=np.concatenate([ids5, [10**9]]))
     check(Dn[5], In[5], Dr5, Ir5, "changed member")
+
+
+def test_group_copy_does_not_outlive_its_members(b200):
+    """The concatenated copy of a group is cached against its members' identity.  New indexes that
+    the allocator places where destroyed ones lived (same addresses, same number of adds) must not
+    be mistaken for them: several rounds of create / search / destroy with different data and
+    alternating metrics, each checked against the oracle."""
+    import gc
+    d, k, nq = 64, 10, 17
+    xq = datasets.gaussian(nq, d, seed=1)
+    for rnd in range(6):
+        metric = L2 if rnd % 2 == 0 else IP
+        indexes, Ds, Is = [], [], []
+        for s_, n in enumerate((900, 300, 2000)):
+            xb = datasets.gaussian(n, d, seed=1000 + 10 * rnd + s_)
+            ids = np.arange(n, dtype=np.int64) + 5000 * s_
+            ix = b200.IndexFlat(d, metric)
+            ix.add_with_ids(xb, ids)
+            indexes.append(ix)
+            Dr, Ir = oracle.flat_search(metric, xb, xq, k, labels=ids)
+            Ds.append(Dr)
+            Is.append(Ir)
+        D, I = b200.search_multi(indexes, xq, k, merged=False)
+        assert_exact(D, I, np.stack(Ds), np.stack(Is))
+        del indexes, ix
+        gc.collect()
