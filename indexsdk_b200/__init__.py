@@ -148,7 +148,7 @@ class _Index:
         h = getattr(self, "_h", None)
         if h is not None and h.value:
             self._lib.b200idx_destroy(h)
-            self._h = C.c_void_p()
+            self._h = None      # (module globals may already be gone when the interpreter shuts down)
 
     @property
     def handle(self) -> C.c_void_p:
