@@ -43,9 +43,9 @@ FALLBACK_BF16_TFLOPS = 1590.0
 # that kernel: full-size launch for the IVFPQ scan; quarter-size captures scaled by four for the
 # exact-search GEMMs (their traffic grows with the base).  None until a capture exists.
 NCU_TRAFFIC_BYTES = {
-    "ivfpq10m": 1.616e9,
-    "flat1m": 3.21e8,
-    "int8flat4m": 1.049e9,
+    "ivfpq10m": 1.766e9,      # ivfpq_scan_persist_kernel: 1.722 GB read + 43.9 MB written
+    "flat1m": 2.98e8,         # append pass, both stretches: 4 x (73.4 MB read + 1.0 MB written)
+    "int8flat4m": 1.051e9,    # append pass, both stretches: 4 x (257.3 MB read + 5.4 MB written)
 }
 
 
